@@ -1,0 +1,262 @@
+/*
+ * qdecode.h - C ABI of libqdecode.so: the Qwen3 greedy-decode hot path as
+ * hand-written sm_100a CUDA kernels.
+ *
+ * Conventions (all entry points):
+ *   - return 0 on success, a negative q_status on error; q_last_error() gives
+ *     the message of the calling thread's last failure. Nothing throws, aborts
+ *     or traps.
+ *   - every pointer named d_* is a DEVICE pointer borrowed from the caller (the
+ *     caller owns it and keeps it alive until the stream work has finished).
+ *     Outputs are caller-allocated so that addresses are stable under CUDA
+ *     graph capture.
+ *   - `stream` is a cudaStream_t passed as void*. No entry point allocates,
+ *     synchronises or reads device values on the host (except where stated),
+ *     so all of them may be captured in a CUDA graph.
+ *   - bf16 tensors are row-major, innermost dimension contiguous.
+ *
+ * Each declaration cites the reference interface (jadenpxrk/starter, path
+ * within that project) it replaces.
+ */
+#ifndef QDECODE_H
+#define QDECODE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum q_status {
+  Q_OK = 0,
+  Q_ERR_ARG = -1,      /* bad shape / null pointer / unsupported size */
+  Q_ERR_CUDA = -2,     /* a CUDA runtime call failed */
+  Q_ERR_STATE = -3,    /* engine not fully bound */
+  Q_ERR_DEVICE = -4    /* device status word reported a bounded wait ran out */
+} q_status;
+
+#define Q_PAGE_TOKENS 64   /* tokens per KV page (one attention key tile) */
+#define Q_HEAD_DIM 128     /* the only supported head dimension */
+#define Q_MAX_ROWS 64      /* most activation rows (batch x query tokens) per GEMM */
+
+const char* q_last_error(void);
+int q_version(void);
+
+/* Programmatic dependent launch between consecutive kernels (default on).
+ * Off = plain stream-ordered launches. */
+int q_set_pdl(int enabled);
+
+/* ---- split-K weight-streaming GEMM --------------------------------------
+ * Replaces engine/kernels/skinny_gemm.py:100-109 (linear_partials) and the
+ * split planning at :86-91 (split_count).
+ *
+ * P[slot][m][n] (fp32) holds partial sums of X[M,K] . W[N,K]^T. The work is
+ * cut into units of 16 weight rows x 32 k; every warp of the grid takes one
+ * contiguous run of `units_per_worker` units, so a 16-row group is covered by
+ * `count(group)` consecutive workers, and worker w writes slot
+ * w - first_worker(group). A consumer sums slots 0..count-1 in order and
+ * rounds once to bf16. q_gemm_plan gives the numbers a consumer needs. */
+typedef struct q_gemm_plan_t {
+  int32_t M, N, K;
+  int32_t chunks_per_group;   /* K / 32 */
+  int32_t groups;             /* ceil(N / 16) */
+  int32_t units_per_worker;   /* u */
+  int32_t workers;            /* warps that get work */
+  int32_t slots;              /* max count(group); P needs slots*M*N floats */
+  int32_t grid, block;        /* launch shape used */
+} q_gemm_plan_t;
+
+int q_gemm_plan(int M, int N, int K, q_gemm_plan_t* plan);
+
+int q_gemm_splitk(const void* d_x, const void* d_w, float* d_partials,
+                  int M, int N, int K, void* stream);
+
+/* Sums the slots of a plan into one fp32 [M,N] buffer (no rounding). Used
+ * before a tensor-parallel all-reduce, which must add fp32 partials. */
+int q_reduce_partials(const float* d_partials, const q_gemm_plan_t* plan,
+                      float* d_out, void* stream);
+
+/* ---- fused element-wise consumers ----------------------------------------*/
+
+/* engine/kernels/rmsnorm.py:39-62 (rms_norm): out = bf16(x*rsqrt(mean x^2+eps))*w */
+int q_rmsnorm(const void* d_x, const void* d_gain, void* d_out,
+              int rows, int cols, float eps, void* stream);
+
+/* engine/decode_step.py:38-39: embedding gather + first RMSNorm.
+ * d_tokens int64[rows]; writes x (the residual stream) and normed. */
+int q_embed_rmsnorm(const int64_t* d_tokens, const void* d_embed, const void* d_gain,
+                    void* d_x, void* d_normed, int rows, int cols, int vocab,
+                    float eps, void* stream);
+
+/* engine/kernels/decode_fused.py:140-158 (add_rms_norm). The branch is either
+ * split-K partials described by `plan` (plan != NULL) or one fp32 [rows,cols]
+ * buffer (plan == NULL, e.g. after an all-reduce). total = bf16(x + bf16(sum)),
+ * normed = bf16(total*rsqrt(mean total^2 + eps)) * gain. d_x_in may equal
+ * d_total_out. */
+int q_add_rmsnorm(const void* d_x_in, const float* d_branch, const q_gemm_plan_t* plan,
+                  const void* d_gain, void* d_total_out, void* d_normed_out,
+                  int rows, int cols, float eps, void* stream);
+
+/* engine/kernels/skinny_gemm.py:66-72 epilogue / decode_fused.py:161-169
+ * (silu_mul) on split-K partials of the packed gate|up projection
+ * (columns [0,I) gate, [I,2I) up): out = bf16(bf16(silu(bf16 g)) * bf16 u). */
+int q_swiglu(const float* d_branch, const q_gemm_plan_t* plan, void* d_out,
+             int rows, int inter, void* stream);
+
+/* Paged KV cache of one layer: pool[page][kv_head][64 tokens][128] bf16, the
+ * 16-byte chunks of each token row XOR-swizzled by (token & 7) so that a page
+ * tile can be bulk-copied to shared memory and read conflict-free.
+ * block_table int32 [batch][pages_per_seq] maps a sequence's tile to a page. */
+typedef struct q_kv_layout_t {
+  void* d_kpool;
+  void* d_vpool;
+  const int32_t* d_block_table;
+  int32_t pages_per_seq;
+  int32_t n_kv_heads;        /* heads held in this pool (local heads under TP) */
+} q_kv_layout_t;
+
+/* engine/kernels/decode_fused.py:172-210 (qkv_norm_rope_cache), generalised to
+ * T consecutive query tokens per sequence (row m = b*T + t sits at absolute
+ * position *d_pos + t). Consumes the packed [q|k|v] projection partials, does
+ * per-head RMSNorm + RoPE, writes Q [rows][n_q][128] and the K,V rows into
+ * their page slots. cos/sin are bf16 [capacity][128] tables. */
+int q_qkv_norm_rope_cache(const float* d_branch, const q_gemm_plan_t* plan,
+                          const void* d_q_gain, const void* d_k_gain,
+                          const void* d_cos, const void* d_sin, const int32_t* d_pos,
+                          void* d_q_out, const q_kv_layout_t* kv,
+                          int batch, int T, int n_q_heads, float eps, void* stream);
+
+/* Scatters already-rotated K and V rows [batch][n_kv][len][128] (bf16) into the
+ * pages at positions start..start+len-1. Host-side helper for prefill
+ * (engine/kernels/prefill.py:19-63 writes cache[:, :, :T] the same way). */
+int q_kv_scatter(const void* d_k, const void* d_v, const q_kv_layout_t* kv,
+                 int batch, int len, int start, void* stream);
+
+/* ---- attention -------------------------------------------------------------
+ * engine/kernels/small_query_attention.py:113-158 (SmallQueryAttention.run) and
+ * engine/flash_decode.py:78-83, generalised to T in 1..(32/G) query tokens per
+ * sequence with a causal limit inside the query block: row (b,t,head) sees keys
+ * [0, *d_pos + t + 1). Split-KV partials go to caller scratch, a second kernel
+ * merges them and rounds once to bf16. out is [batch*T][n_q*128].
+ *   d_scratch_o: float[batch*n_kv][splits][T*G][128]
+ *   d_scratch_ml: float[batch*n_kv][splits][T*G][2]
+ * q_attention_splits returns the split count to size those for a capacity. */
+int q_attention_splits(int batch, int n_kv_heads, int capacity);
+
+int q_attention(const void* d_q, const q_kv_layout_t* kv, const int32_t* d_pos,
+                float* d_scratch_o, float* d_scratch_ml, void* d_out,
+                int batch, int T, int n_q_heads, int splits, float scale,
+                void* stream);
+
+/* ---- lm_head + argmax -------------------------------------------------------
+ * engine/decode_step.py:60 (F.linear on lm_head) + engine/decode.py:106-107
+ * (argmax, position += 1). Consumes the lm_head GEMM partials; writes bf16
+ * logits [rows][vocab] if d_logits != NULL; picks per row the largest bf16
+ * logit, lowest index on ties. d_val/d_idx get the per-row winner (idx +
+ * vocab_offset, for vocab-sharded tensor parallelism); if d_tokens != NULL the
+ * winner is also stored there as int64 and, if d_pos != NULL, *d_pos += pos_inc.
+ * d_block_scratch: at least q_argmax_scratch_bytes(rows, vocab) bytes, zeroed
+ * once by the caller before first use. */
+int64_t q_argmax_scratch_bytes(int rows, int vocab);
+
+int q_logits_argmax(const float* d_branch, const q_gemm_plan_t* plan,
+                    void* d_logits, float* d_val, int32_t* d_idx,
+                    int64_t* d_tokens, int32_t* d_pos, int pos_inc,
+                    void* d_block_scratch, int rows, int vocab, int vocab_offset,
+                    void* stream);
+
+/* Final pick over tensor-parallel shards: val/idx are [shards][rows]; lowest
+ * global index wins ties. Writes tokens and bumps *d_pos like above. */
+int q_argmax_merge(const float* d_val, const int32_t* d_idx, int shards, int rows,
+                   int64_t* d_tokens, int32_t* d_pos, int pos_inc, void* stream);
+
+/* ---- whole decode step ------------------------------------------------------
+ * engine/decode_step.py:33-60 (fused_decode_forward) + engine/decode.py:97-108
+ * (DecodeState.step). The engine object only stores borrowed pointers and
+ * launch plans; it owns no device memory. */
+typedef struct q_config_t {
+  int32_t hidden, inter, n_layers, n_q_heads, n_kv_heads, vocab;
+  /* sizes above are the LOCAL shard sizes under tensor parallelism, except
+   * hidden. vocab_offset = first vocabulary row of the local lm_head shard. */
+  int32_t vocab_offset;
+  int32_t full_vocab;        /* rows of the (replicated) embedding table */
+  int32_t tp_size;           /* 1 = single GPU */
+  int32_t max_rows;          /* batch * T upper bound, <= Q_MAX_ROWS */
+  float rms_eps;
+  float attn_scale;
+} q_config_t;
+
+typedef struct q_layer_weights_t {
+  const void* wqkv;     /* [(n_q+2*n_kv)*128][hidden]  q rows | k rows | v rows */
+  const void* wo;       /* [hidden][n_q*128] */
+  const void* wgu;      /* [2*inter][hidden]  gate rows | up rows */
+  const void* wdown;    /* [hidden][inter] */
+  const void* ln_in;    /* [hidden] */
+  const void* ln_post;  /* [hidden] */
+  const void* q_gain;   /* [128] */
+  const void* k_gain;   /* [128] */
+  void* kpool;
+  void* vpool;
+} q_layer_weights_t;
+
+typedef struct q_state_t {
+  const void* embed;        /* [full_vocab][hidden] */
+  const void* lm_head;      /* [vocab][hidden] (local shard; == embed when tied, tp 1) */
+  const void* ln_final;     /* [hidden] */
+  const void* cos;          /* [capacity][128] bf16 */
+  const void* sin;
+  int64_t* tokens;          /* [batch] current token per sequence */
+  int32_t* pos;             /* [1] position of the current token */
+  const int32_t* block_table;
+  int32_t pages_per_seq;
+  int32_t batch;
+  int32_t attn_splits;
+  /* scratch, all caller-allocated */
+  void* x;                  /* bf16 [rows][hidden] residual stream */
+  void* normed;             /* bf16 [rows][hidden] */
+  void* q;                  /* bf16 [rows][n_q*128] */
+  void* attended;           /* bf16 [rows][n_q*128] */
+  void* act;                /* bf16 [rows][inter] */
+  float* partials;          /* q_engine_partial_floats() floats */
+  float* reduced;           /* fp32 [rows][hidden] (tensor parallel only, else NULL) */
+  float* attn_o;            /* see q_attention */
+  float* attn_ml;
+  void* logits;             /* bf16 [rows][vocab] or NULL */
+  float* arg_val;           /* [rows] */
+  int32_t* arg_idx;         /* [rows] */
+  void* arg_scratch;        /* q_argmax_scratch_bytes() bytes, zeroed once */
+} q_state_t;
+
+typedef struct q_engine q_engine;
+
+int q_create(const q_config_t* cfg, q_engine** out);
+int q_bind_layer(q_engine* e, int layer, const q_layer_weights_t* w);
+int q_bind_state(q_engine* e, const q_state_t* s);
+int64_t q_engine_partial_floats(const q_engine* e, int rows);
+void q_destroy(q_engine* e);
+
+/* One full step for T=1 on a single GPU: embed .. argmax, tokens and pos updated. */
+int q_decode_step(q_engine* e, void* stream);
+
+/* The same step in pieces, for tensor parallelism: the caller all-reduces
+ * state.reduced (fp32 [rows][hidden]) between the pieces.
+ *   q_step_begin:      embed + first norm
+ *   q_step_attn:       QKV .. O-proj; leaves the local fp32 sum in `reduced`
+ *   q_step_post_attn:  add+norm from `reduced`, gate/up, SwiGLU, down -> `reduced`
+ *   q_step_post_mlp:   add+norm from `reduced` with the next gain
+ *   q_step_head:       lm_head shard + local argmax into arg_val/arg_idx */
+int q_step_begin(q_engine* e, void* stream);
+int q_step_attn(q_engine* e, int layer, void* stream);
+int q_step_post_attn(q_engine* e, int layer, void* stream);
+int q_step_post_mlp(q_engine* e, int layer, void* stream);
+int q_step_head(q_engine* e, void* stream);
+
+/* Reads the library's device status word of the current device (synchronises
+ * the device; not capturable). out[0] != 0 means a bounded wait inside a kernel
+ * ran out (1 = attention producer, 2 = attention consumer). */
+int q_device_status(int32_t out[4]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QDECODE_H */

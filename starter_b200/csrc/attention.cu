@@ -1,0 +1,465 @@
+// Split-KV GQA attention for 1..8 query tokens per sequence over a paged bf16 KV
+// cache (reference: engine/kernels/small_query_attention.py:41-110 is the
+// single-token version over a contiguous cache).
+//
+// One CTA = one (sequence, kv head) x one key split. Warp 4 is the producer: a
+// single lane walks the block table and brings each 64-key page tile (K 16 KB +
+// V 16 KB, already XOR-swizzled in global memory) into a shared-memory ring with
+// cp.async.bulk + mbarrier transaction counts. Warps 0..3 are consumers: every
+// consumer owns 16 of the 64 keys of each tile, computes S = Q K^T and P V with
+// mma.m16n8k16 (all T*G query rows of the kv head share the tile), and keeps its
+// own online-softmax state; the four states are merged once at the end through
+// shared memory. Cast boundaries: fp32 scores from bf16 q,k; fp32 statistics;
+// P rounded to bf16 for P V; fp32 accumulation; a single bf16 rounding after all
+// splits are merged (k_attn_merge).
+//
+// Every mbarrier wait is bounded: when it runs out the thread records a code in
+// the device status word and the CTA stops consuming, so a lost copy can never
+// hang the GPU.
+#include "common.cuh"
+
+namespace {
+
+constexpr int NS = 3;                      // ring stages
+constexpr int TILE_BYTES = 64 * 128 * 2;   // one K or V page tile
+constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+constexpr int CONSUMERS = 4;
+constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr unsigned WAIT_LIMIT = 1u << 22;
+
+__device__ int g_status[4];
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (it > 64) __nanosleep(64);
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                        uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                          uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void consumer_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
+}
+
+// RT = number of 16-row query tiles (T*G <= 16*RT).
+template <int RT>
+__global__ void __launch_bounds__(THREADS)
+k_attn_split(const bf16* __restrict__ Q, const char* __restrict__ kpool,
+             const char* __restrict__ vpool, const int32_t* __restrict__ block_table,
+             int pages_per_seq, const int32_t* __restrict__ pos_ptr, float* __restrict__ part_o,
+             float* __restrict__ part_ml, bf16* __restrict__ out, int T, int G, int nq, int nkv,
+             int S, float scale_log2) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* stages = smem;                               // NS * STAGE_BYTES
+  unsigned char* qtile = smem + NS * STAGE_BYTES;             // RT*16 rows * 256 B
+  uint64_t* bars = reinterpret_cast<uint64_t*>(qtile + RT * 16 * 256);  // full[NS], empty[NS]
+  __shared__ int s_fail;
+
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y, split = blockIdx.x;
+  const int b = bh / nkv, kh = bh % nkv;
+  const int R = T * G;
+
+  if (tid == 0) {
+    s_fail = 0;
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(smem_u32(&bars[i]), 1);
+      mbar_init(smem_u32(&bars[NS + i]), CONSUMERS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  pdl_wait();
+  const int pos = pos_ptr[0];
+  const int max_limit = pos + T;                                   // keys visible to the last row
+  const int tiles_used = (max_limit + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
+  const int per = (tiles_used + S - 1) / S;
+  const int tile0 = split * per;
+  int tile1 = tile0 + per;
+  if (tile1 > tiles_used) tile1 = tiles_used;
+  const int ntiles = tile1 > tile0 ? tile1 - tile0 : 0;
+
+  if (warp == CONSUMERS) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      for (int it = 0; it < ntiles; ++it) {
+        const int s = it % NS;
+        if (it >= NS) {
+          if (!mbar_wait(smem_u32(&bars[NS + s]), ((it / NS) - 1) & 1)) {
+            atomicExch(&g_status[0], 1);
+            atomicExch(&s_fail, 1);
+            break;
+          }
+        }
+        const int page = block_table[(size_t)b * pages_per_seq + tile0 + it];
+        const size_t off = ((size_t)page * nkv + kh) * TILE_BYTES;
+        const uint32_t bar = smem_u32(&bars[s]);
+        mbar_expect_tx(bar, STAGE_BYTES);
+        bulk_g2s(smem_u32(stages + s * STAGE_BYTES), kpool + off, TILE_BYTES, bar);
+        bulk_g2s(smem_u32(stages + s * STAGE_BYTES + TILE_BYTES), vpool + off, TILE_BYTES, bar);
+      }
+    }
+  } else {
+    // ---------------- consumers ----------------
+    // Q tile -> shared memory (swizzled rows of 256 B); rows >= R are zero.
+    for (int c = tid; c < RT * 16 * 16; c += CONSUMERS * 32) {
+      const int r = c >> 4, ch = c & 15;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < R) {
+        const int t = r / G, gq = r % G;
+        const bf16* src = Q + (((size_t)(b * T + t)) * nq + kh * G + gq) * 128 + ch * 8;
+        v = *reinterpret_cast<const uint4*>(src);
+      }
+      *reinterpret_cast<uint4*>(qtile + r * 256 + ((ch ^ (r & 7)) << 4)) = v;
+    }
+    consumer_sync();
+
+    const int g = lane >> 2, t4 = lane & 3;
+    float m_run[RT][2], l_run[RT][2];
+    float oacc[RT][16][4];
+    int limit[RT][2];
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        m_run[rt][h] = -INFINITY;
+        l_run[rt][h] = 0.f;
+        const int r = rt * 16 + g + 8 * h;
+        limit[rt][h] = r < R ? pos + r / G + 1 : max_limit;
+      }
+#pragma unroll
+      for (int n = 0; n < 16; ++n) oacc[rt][n][0] = oacc[rt][n][1] = oacc[rt][n][2] = oacc[rt][n][3] = 0.f;
+    }
+    const uint32_t q_base = smem_u32(qtile);
+    bool alive = true;
+
+    for (int it = 0; it < ntiles && alive; ++it) {
+      const int s = it % NS;
+      if (!mbar_wait(smem_u32(&bars[s]), (it / NS) & 1)) {
+        atomicExch(&g_status[0], 2);
+        alive = false;
+        break;
+      }
+      unsigned char* kt = stages + s * STAGE_BYTES;
+      unsigned char* vt = kt + TILE_BYTES;
+      const int key_base = (tile0 + it) * Q_PAGE_TOKENS;
+      const int my_key0 = key_base + warp * 16;
+      if (my_key0 + 16 > max_limit) {
+        // rows past the newest key may hold stale bits: clear the V rows so that
+        // 0 * garbage cannot produce NaN in P V.
+        for (int c = lane; c < 16 * 16; c += 32) {
+          const int kr = warp * 16 + (c >> 4);
+          if (key_base + kr >= max_limit)
+            *reinterpret_cast<uint4*>(vt + kr * 256 + ((c & 15) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
+      }
+      const uint32_t k_base = smem_u32(kt), v_base = smem_u32(vt);
+
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+        float sacc[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+          {
+            const int row = rt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+            const int ch = 2 * ks + (lane >> 4);
+            ldsm_x4(q_base + row * 256 + ((ch ^ (row & 7)) << 4), a0, a1, a2, a3);
+          }
+          {
+            const int mi = lane >> 3;
+            const int key = warp * 16 + 8 * (mi >> 1) + (lane & 7);
+            const int ch = 2 * ks + (mi & 1);
+            ldsm_x4(k_base + key * 256 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+          }
+          mma16816(sacc[0], a0, a1, a2, a3, b0, b1);
+          mma16816(sacc[1], a0, a1, a2, a3, b2, b3);
+        }
+        // online softmax for rows g (h=0) and g+8 (h=1)
+        float p[2][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float mx = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int key = my_key0 + 8 * j + 2 * t4 + e;
+              float v = sacc[j][2 * h + e] * scale_log2;
+              v = key < limit[rt][h] ? v : -INFINITY;
+              sacc[j][2 * h + e] = v;
+              mx = fmaxf(mx, v);
+            }
+          }
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+          const float m_new = fmaxf(m_run[rt][h], mx);
+          const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+          const float resc = exp2f(m_run[rt][h] - m_safe);   // exp2(-inf) = 0 on the first tile
+          float sum = 0.f;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float pv = exp2f(sacc[j][2 * h + e] - m_safe);
+              p[j][2 * h + e] = pv;
+              sum += pv;
+            }
+          }
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          l_run[rt][h] = l_run[rt][h] * resc + sum;
+          m_run[rt][h] = m_new;
+#pragma unroll
+          for (int n = 0; n < 16; ++n) {
+            oacc[rt][n][2 * h] *= resc;
+            oacc[rt][n][2 * h + 1] *= resc;
+          }
+        }
+        const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]);
+        const uint32_t pa1 = pack_bf16(p[0][2], p[0][3]);
+        const uint32_t pa2 = pack_bf16(p[1][0], p[1][1]);
+        const uint32_t pa3 = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+        for (int dp = 0; dp < 8; ++dp) {
+          uint32_t b0, b1, b2, b3;
+          const int mi = lane >> 3;
+          const int key = warp * 16 + 8 * (mi & 1) + (lane & 7);
+          const int ch = 2 * dp + (mi >> 1);
+          ldsm_x4_t(v_base + key * 256 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+          mma16816(oacc[rt][2 * dp], pa0, pa1, pa2, pa3, b0, b1);
+          mma16816(oacc[rt][2 * dp + 1], pa0, pa1, pa2, pa3, b2, b3);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars[NS + s]));
+    }
+    if (!alive) atomicExch(&s_fail, 1);
+
+    // ---- merge the four consumer states through shared memory ----
+    consumer_sync();   // every consumer is done with the ring
+    if (s_fail == 0) {
+      float* mo = reinterpret_cast<float*>(stages);                      // [4][RT*16][128]
+      float* mml = mo + CONSUMERS * RT * 16 * 128;                       // [4][RT*16][2]
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int r = rt * 16 + g + 8 * h;
+          float* dst = mo + ((size_t)warp * RT * 16 + r) * 128;
+#pragma unroll
+          for (int n = 0; n < 16; ++n) {
+            dst[8 * n + 2 * t4] = oacc[rt][n][2 * h];
+            dst[8 * n + 2 * t4 + 1] = oacc[rt][n][2 * h + 1];
+          }
+          if (t4 == 0) {
+            mml[((size_t)warp * RT * 16 + r) * 2] = m_run[rt][h];
+            mml[((size_t)warp * RT * 16 + r) * 2 + 1] = l_run[rt][h];
+          }
+        }
+      }
+      consumer_sync();
+      const int d = tid;  // 128 consumer threads = 128 dims
+      for (int r = 0; r < R; ++r) {
+        float mw[CONSUMERS], M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < CONSUMERS; ++w) {
+          mw[w] = mml[((size_t)w * RT * 16 + r) * 2];
+          M = fmaxf(M, mw[w]);
+        }
+        const float Ms = M == -INFINITY ? 0.f : M;
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < CONSUMERS; ++w) {
+          const float wt = exp2f(mw[w] - Ms);
+          L += wt * mml[((size_t)w * RT * 16 + r) * 2 + 1];
+          O += wt * mo[((size_t)w * RT * 16 + r) * 128 + d];
+        }
+        if (S == 1) {
+          const int t = r / G, gq = r % G;
+          const float res = L > 0.f ? O / L : 0.f;
+          out[(((size_t)(b * T + t)) * nq + kh * G + gq) * 128 + d] = __float2bfloat16_rn(res);
+        } else {
+          const size_t row = ((size_t)bh * S + split) * R + r;
+          part_o[row * 128 + d] = O;
+          if (d == 0) {
+            part_ml[row * 2] = M;
+            part_ml[row * 2 + 1] = L;
+          }
+        }
+      }
+    }
+  }
+}
+
+// One warp per (sequence, token, q head): lanes hold one split each for the
+// log-sum-exp weights (shuffle reductions), then every lane sums 4 dims.
+__global__ void __launch_bounds__(128)
+k_attn_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+             bf16* __restrict__ out, int batch, int T, int G, int nq, int nkv, int S) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= batch * T * nq) return;
+  const int head = item % nq, bt = item / nq;
+  const int b = bt / T, t = bt % T;
+  const int kh = head / G, gq = head % G;
+  const int R = T * G, r = t * G + gq;
+  const size_t base = ((size_t)(b * nkv + kh) * S) * R + r;   // + split * R
+  float m = -INFINITY, l = 0.f;
+  if (lane < S) {
+    m = part_ml[(base + (size_t)lane * R) * 2];
+    l = part_ml[(base + (size_t)lane * R) * 2 + 1];
+  }
+  float M = warp_max(m);
+  if (M == -INFINITY) M = 0.f;
+  const float wgt = l > 0.f ? exp2f(m - M) : 0.f;
+  const float L = warp_sum(wgt * l);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < S; ++s) {
+    const float ws = __shfl_sync(0xffffffffu, wgt, s);
+    if (ws != 0.f) {
+      const float4 o = *reinterpret_cast<const float4*>(part_o + (base + (size_t)s * R) * 128 + lane * 4);
+      acc[0] += ws * o.x; acc[1] += ws * o.y; acc[2] += ws * o.z; acc[3] += ws * o.w;
+    }
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  bf16* dst = out + ((size_t)bt * nq + head) * 128 + lane * 4;
+  uint2 packed;
+  packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+  packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+template <int RT>
+constexpr size_t attn_smem() { return NS * STAGE_BYTES + RT * 16 * 256 + 2 * NS * 8; }
+
+}  // namespace
+
+extern "C" int q_attention_splits(int batch, int n_kv_heads, int capacity) {
+  if (batch < 1 || n_kv_heads < 1 || capacity < 1) return 1;
+  int sms = q_sm_count();
+  if (sms <= 0) sms = 148;
+  const int vh = batch * n_kv_heads;
+  const int tiles = (capacity + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
+  int desired = (2 * sms + vh - 1) / vh;
+  int s = desired < tiles ? desired : tiles;
+  if (s > 32) s = 32;
+  if (s < 1) s = 1;
+  return s;
+}
+
+extern "C" int q_attention(const void* d_q, const q_kv_layout_t* kv, const int32_t* d_pos,
+                           float* d_scratch_o, float* d_scratch_ml, void* d_out, int batch, int T,
+                           int n_q_heads, int splits, float scale, void* stream) {
+  Q_CHECK_ARG(d_q && kv && d_pos && d_out, "q_attention: null pointer");
+  Q_CHECK_ARG(kv->d_kpool && kv->d_vpool && kv->d_block_table && kv->pages_per_seq >= 1 &&
+                  kv->n_kv_heads >= 1,
+              "q_attention: incomplete KV layout");
+  const int nkv = kv->n_kv_heads;
+  Q_CHECK_ARG(batch >= 1 && T >= 1 && n_q_heads >= nkv && n_q_heads % nkv == 0,
+              "q_attention: bad batch/T/heads");
+  const int G = n_q_heads / nkv;
+  Q_CHECK_ARG(T * G <= 32, "q_attention: T*G = %d exceeds 32 query rows per kv head", T * G);
+  Q_CHECK_ARG(splits >= 1 && splits <= 32, "q_attention: splits %d outside 1..32", splits);
+  Q_CHECK_ARG(splits == 1 || (d_scratch_o && d_scratch_ml), "q_attention: split scratch missing");
+  Q_CHECK_ARG((long long)batch * nkv <= 65535, "q_attention: too many (sequence, kv head) pairs");
+  Q_CHECK_ARG(((uintptr_t)kv->d_kpool & 15) == 0 && ((uintptr_t)kv->d_vpool & 15) == 0 &&
+                  ((uintptr_t)d_q & 15) == 0,
+              "q_attention: pools and q must be 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(splits, batch * nkv), block(THREADS);
+  cudaError_t e;
+  if (T * G <= 16) {
+    static bool attr1 = false;
+    if (!attr1) {
+      Q_CHECK_CUDA(cudaFuncSetAttribute(k_attn_split<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)attn_smem<1>()));
+      attr1 = true;
+    }
+    e = q_launch(k_attn_split<1>, grid, block, attn_smem<1>(), s, (const bf16*)d_q,
+                 (const char*)kv->d_kpool, (const char*)kv->d_vpool, kv->d_block_table,
+                 kv->pages_per_seq, d_pos, d_scratch_o, d_scratch_ml, (bf16*)d_out, T, G, n_q_heads,
+                 nkv, splits, scale_log2);
+  } else {
+    static bool attr2 = false;
+    if (!attr2) {
+      Q_CHECK_CUDA(cudaFuncSetAttribute(k_attn_split<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)attn_smem<2>()));
+      attr2 = true;
+    }
+    e = q_launch(k_attn_split<2>, grid, block, attn_smem<2>(), s, (const bf16*)d_q,
+                 (const char*)kv->d_kpool, (const char*)kv->d_vpool, kv->d_block_table,
+                 kv->pages_per_seq, d_pos, d_scratch_o, d_scratch_ml, (bf16*)d_out, T, G, n_q_heads,
+                 nkv, splits, scale_log2);
+  }
+  Q_CHECK_CUDA(e);
+  if (splits > 1) {
+    const int items = batch * T * n_q_heads;
+    Q_CHECK_CUDA(q_launch(k_attn_merge, dim3((items + 3) / 4), dim3(128), 0, s, d_scratch_o,
+                          d_scratch_ml, (bf16*)d_out, batch, T, G, n_q_heads, nkv, splits));
+  }
+  return Q_OK;
+}
+
+extern "C" int q_device_status(int32_t out[4]) {
+  Q_CHECK_ARG(out != nullptr, "q_device_status: null pointer");
+  Q_CHECK_CUDA(cudaDeviceSynchronize());
+  Q_CHECK_CUDA(cudaMemcpyFromSymbol(out, g_status, sizeof(int) * 4));
+  return Q_OK;
+}

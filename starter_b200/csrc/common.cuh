@@ -1,0 +1,139 @@
+// Shared device/host helpers for the qdecode kernels (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include "../../include/qdecode.h"
+
+typedef __nv_bfloat16 bf16;
+
+// ---- host side: error text + launch helper ---------------------------------
+void q_set_error(const char* fmt, ...);
+bool q_pdl_enabled();
+
+#define Q_CHECK_ARG(cond, ...)                                   \
+  do {                                                           \
+    if (!(cond)) { q_set_error(__VA_ARGS__); return Q_ERR_ARG; } \
+  } while (0)
+
+#define Q_CHECK_CUDA(expr)                                                     \
+  do {                                                                         \
+    cudaError_t _e = (expr);                                                   \
+    if (_e != cudaSuccess) {                                                   \
+      q_set_error("%s failed: %s", #expr, cudaGetErrorString(_e));             \
+      return Q_ERR_CUDA;                                                       \
+    }                                                                          \
+  } while (0)
+
+// Launches `kernel` with the programmatic-dependent-launch attribute so that its
+// prologue may overlap the previous kernel's tail. Every kernel here executes
+// pdl_wait() before it touches memory another kernel of the step writes.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t q_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                   size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = q_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+int q_sm_count();
+
+// Split-K plan passed by value to consumer kernels. u == 0 means "one plain
+// fp32 [rows][cols] buffer".
+struct PlanView {
+  int u;       // units per worker
+  int C;       // chunks per 16-row group
+  long long slot_stride;  // M*N floats
+};
+
+static inline PlanView plan_view(const q_gemm_plan_t* p) {
+  PlanView v;
+  if (p) {
+    v.u = p->units_per_worker;
+    v.C = p->chunks_per_group;
+    v.slot_stride = (long long)p->M * p->N;
+  } else {
+    v.u = 0; v.C = 0; v.slot_stride = 0;
+  }
+  return v;
+}
+
+// ---- device side ---------------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ float bf16_round(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+__device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&p);
+}
+
+// Number of split-K slots that hold a partial for column n, and their sum.
+__device__ __forceinline__ int plan_count(const PlanView& pv, int n) {
+  if (pv.u == 0) return 1;
+  long long g = n >> 4;
+  long long first = (g * pv.C) / pv.u;
+  long long last = ((g + 1) * pv.C - 1) / pv.u;
+  return (int)(last - first + 1);
+}
+
+// Sum of the partial slots of element (m, n) in slot order 0..count-1.
+__device__ __forceinline__ float plan_sum(const float* __restrict__ P, const PlanView& pv,
+                                          long long idx, int n) {
+  int cnt = plan_count(pv, n);
+  float s = P[idx];
+  for (int k = 1; k < cnt; ++k) s += P[idx + k * pv.slot_stride];
+  return s;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum; `red` is shared float[32]. All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  int nw = (blockDim.x + 31) >> 5;
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+// Byte offset of element (token r, dim d) inside one swizzled 64x128 bf16 page tile.
+__device__ __forceinline__ int kv_tile_offset_bytes(int r, int d) {
+  int chunk = (d >> 3) ^ (r & 7);
+  return r * 256 + chunk * 16 + (d & 7) * 2;
+}
+
+#endif  // __CUDACC__

@@ -1,0 +1,444 @@
+// Element-wise consumers of the split-K partials. Each one reproduces the bf16
+// rounding points of the native model exactly; fp32 reductions are free to
+// reorder.
+//   1. a Linear output rounds once fp32->bf16 after all partials are summed
+//   2. residual add: bf16(x + y) of two bf16 values
+//   3. RMSNorm: fp32 x*rsqrt(mean(x^2)+eps) -> bf16 -> times bf16 gain -> bf16
+//   4. per-head q/k norm: as 3 over 128 values; V untouched
+//   5. RoPE: bf16(bf16(n*cos) + bf16(rot*sin)), partner = (col+64) mod 128
+//   6. SwiGLU: bf16(bf16(silu(bf16 g)) * bf16 u)
+//   8. argmax over bf16 logits, lowest index on ties
+// (reference: engine/kernels/decode_fused.py:19-118, engine/kernels/rmsnorm.py:12-36)
+#include "common.cuh"
+
+namespace {
+
+// ---- RMSNorm (plain) -------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_rmsnorm(const bf16* __restrict__ X, const bf16* __restrict__ G, bf16* __restrict__ O,
+          int cols, float eps) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  const bf16* x = X + row * cols;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float v = __bfloat162float(x[c]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)cols + eps);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float v = bf16_round(__bfloat162float(x[c]) * inv);
+    O[row * cols + c] = __float2bfloat16_rn(v * __bfloat162float(G[c]));
+  }
+}
+
+// ---- embedding gather + RMSNorm --------------------------------------------
+__global__ void __launch_bounds__(256)
+k_embed_rmsnorm(const int64_t* __restrict__ tokens, const bf16* __restrict__ E,
+                const bf16* __restrict__ G, bf16* __restrict__ Xo, bf16* __restrict__ No,
+                int cols, int vocab, float eps) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  long long tok = tokens[row];
+  if (tok < 0) tok = 0;
+  if (tok >= vocab) tok = vocab - 1;
+  const bf16* x = E + (size_t)tok * cols;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    bf16 raw = x[c];
+    Xo[row * cols + c] = raw;
+    float v = __bfloat162float(raw);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)cols + eps);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float v = bf16_round(__bfloat162float(x[c]) * inv);
+    No[row * cols + c] = __float2bfloat16_rn(v * __bfloat162float(G[c]));
+  }
+}
+
+// ---- residual add + RMSNorm on partials ------------------------------------
+// One CTA per row; each thread keeps its elements of the new residual in
+// registers between the two passes (cols <= 256*MAXE).
+constexpr int ADD_MAXE = 40;  // 256 threads * 40 = 10240 columns
+
+template <int EPT>
+__global__ void __launch_bounds__(256)
+k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanView pv,
+              const bf16* __restrict__ G, bf16* __restrict__ Tout, bf16* __restrict__ Nout,
+              int cols, float eps) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  float keep[EPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) {
+    int c = threadIdx.x + e * 256;
+    if (c < cols) {
+      float y = bf16_round(plan_sum(P, pv, (long long)row * cols + c, c));
+      float tot = bf16_round(__bfloat162float(Xin[row * cols + c]) + y);
+      keep[e] = tot;
+      ss += tot * tot;
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)cols + eps);
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) {
+    int c = threadIdx.x + e * 256;
+    if (c < cols) {
+      float tot = keep[e];
+      Tout[row * cols + c] = __float2bfloat16_rn(tot);
+      float v = bf16_round(tot * inv);
+      Nout[row * cols + c] = __float2bfloat16_rn(v * __bfloat162float(G[c]));
+    }
+  }
+}
+
+// ---- SwiGLU on gate|up partials ---------------------------------------------
+__global__ void __launch_bounds__(256)
+k_swiglu(const float* __restrict__ P, PlanView pv, bf16* __restrict__ O, int rows, int inter) {
+  pdl_launch_dependents();
+  pdl_wait();
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)rows * inter) return;
+  int m = (int)(i / inter), c = (int)(i % inter);
+  long long base = (long long)m * 2 * inter;
+  float g = bf16_round(plan_sum(P, pv, base + c, c));
+  float u = bf16_round(plan_sum(P, pv, base + inter + c, inter + c));
+  float a = bf16_round(g / (1.0f + expf(-g)));
+  O[i] = __float2bfloat16_rn(a * u);
+}
+
+// ---- q/k head norm + RoPE + KV page write -------------------------------------
+// One warp per (row, head) for q and k heads; lane l owns dims l, l+32, l+64,
+// l+96, so the rotate-half partner (d +- 64) is in the same lane. The warp that
+// handles k head h also copies v head h.
+__global__ void __launch_bounds__(128)
+k_qkv_norm_rope_cache(const float* __restrict__ P, PlanView pv, const bf16* __restrict__ QG,
+                      const bf16* __restrict__ KG, const bf16* __restrict__ COS,
+                      const bf16* __restrict__ SIN, const int32_t* __restrict__ pos_ptr,
+                      bf16* __restrict__ Q, char* __restrict__ kpool, char* __restrict__ vpool,
+                      const int32_t* __restrict__ block_table, int pages_per_seq,
+                      int rows, int T, int nq, int nkv, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int heads = nq + nkv;
+  if (item >= rows * heads) return;
+  const int m = item / heads, head = item % heads;
+  const int b = m / T, tq = m % T;
+  const int pos = pos_ptr[0] + tq;
+  const int width = (nq + 2 * nkv) * 128;
+  const long long src = (long long)m * width + head * 128;  // q heads then k heads
+  float x[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    int d = lane + 32 * j;
+    x[j] = bf16_round(plan_sum(P, pv, src + d, head * 128 + d));
+    ss += x[j] * x[j];
+  }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / 128.f + eps);
+  const bf16* gain = head < nq ? QG : KG;
+  float n[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    int d = lane + 32 * j;
+    n[j] = bf16_round(bf16_round(x[j] * inv) * __bfloat162float(gain[d]));
+  }
+  float out[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    int d = lane + 32 * j;
+    float c = __bfloat162float(COS[(size_t)pos * 128 + d]);
+    float s = __bfloat162float(SIN[(size_t)pos * 128 + d]);
+    float rot = (j < 2) ? -n[j + 2] : n[j - 2];
+    float left = bf16_round(n[j] * c);
+    float right = bf16_round(rot * s);
+    out[j] = left + right;  // rounded to bf16 at the store
+  }
+  if (head < nq) {
+    bf16* q = Q + ((size_t)m * nq + head) * 128;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[lane + 32 * j] = __float2bfloat16_rn(out[j]);
+  } else {
+    const int kh = head - nq;
+    const int page = block_table[(size_t)b * pages_per_seq + pos / Q_PAGE_TOKENS];
+    const int r = pos % Q_PAGE_TOKENS;
+    const size_t tile = ((size_t)page * nkv + kh) * (Q_PAGE_TOKENS * 128 * 2);
+    const long long vsrc = (long long)m * width + (nq + nkv + kh) * 128;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int d = lane + 32 * j;
+      int off = kv_tile_offset_bytes(r, d);
+      *reinterpret_cast<bf16*>(kpool + tile + off) = __float2bfloat16_rn(out[j]);
+      float v = plan_sum(P, pv, vsrc + d, (nq + nkv + kh) * 128 + d);
+      *reinterpret_cast<bf16*>(vpool + tile + off) = __float2bfloat16_rn(v);
+    }
+  }
+}
+
+// ---- scatter rotated K/V rows into pages (prefill helper) -----------------------
+__global__ void __launch_bounds__(128)
+k_kv_scatter(const bf16* __restrict__ Kin, const bf16* __restrict__ Vin, char* __restrict__ kpool,
+             char* __restrict__ vpool, const int32_t* __restrict__ block_table,
+             int pages_per_seq, int nkv, int len, int start) {
+  // grid: (len, nkv, batch); 128 threads = one per dim
+  const int p = blockIdx.x, h = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
+  const int pos = start + p;
+  const int page = block_table[(size_t)b * pages_per_seq + pos / Q_PAGE_TOKENS];
+  const int r = pos % Q_PAGE_TOKENS;
+  const size_t tile = ((size_t)page * nkv + h) * (Q_PAGE_TOKENS * 128 * 2);
+  const size_t src = (((size_t)b * nkv + h) * len + p) * 128 + d;
+  const int off = kv_tile_offset_bytes(r, d);
+  *reinterpret_cast<bf16*>(kpool + tile + off) = Kin[src];
+  *reinterpret_cast<bf16*>(vpool + tile + off) = Vin[src];
+}
+
+// ---- logits + argmax ----------------------------------------------------------------
+// grid (blocks_per_row, rows). Each CTA rounds its slice of logits to bf16,
+// optionally stores them, and finds (max, lowest index). The last CTA of a row
+// (ticket counter) picks the row winner over the per-CTA results in index order.
+constexpr int ARG_COLS = 4096;  // columns per CTA
+
+struct ArgScratch {
+  // layout: [rows] tickets (uint32) | [rows][blocks] val (float) | [rows][blocks] idx (int)
+  unsigned int* tickets;
+  float* val;
+  int* idx;
+};
+
+__device__ __forceinline__ void arg_better(float& bv, int& bi, float v, int i) {
+  if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+}
+
+__global__ void __launch_bounds__(256)
+k_logits_argmax(const float* __restrict__ P, PlanView pv, bf16* __restrict__ logits,
+                float* __restrict__ out_val, int32_t* __restrict__ out_idx,
+                int64_t* __restrict__ tokens, int32_t* __restrict__ pos_ptr, int pos_inc,
+                unsigned int* __restrict__ tickets, float* __restrict__ bval,
+                int* __restrict__ bidx, int vocab, int vocab_offset) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  __shared__ bool is_last;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.y, nblk = gridDim.x;
+  const int c0 = blockIdx.x * ARG_COLS;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = c0 + threadIdx.x; c < c0 + ARG_COLS && c < vocab; c += 256) {
+    long long i = (long long)row * vocab + c;
+    bf16 r = __float2bfloat16_rn(plan_sum(P, pv, i, c));
+    if (logits) logits[i] = r;
+    float v = __bfloat162float(r);
+    if (v != v) v = -INFINITY;  // NaN never wins
+    arg_better(bv, bi, v, c);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    arg_better(bv, bi, ov, oi);
+  }
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int k = 1; k < 8; ++k) arg_better(bv, bi, sv[k], si[k]);
+    bval[(size_t)row * nblk + blockIdx.x] = bv;
+    bidx[(size_t)row * nblk + blockIdx.x] = bi;
+    __threadfence();
+    unsigned int ticket = atomicAdd(&tickets[row], 1u);
+    is_last = (ticket == (unsigned int)(nblk - 1));
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  bv = -INFINITY;
+  bi = 0x7fffffff;
+  for (int k = threadIdx.x; k < nblk; k += 256) {
+    float v = __ldcg(&bval[(size_t)row * nblk + k]);
+    int i = __ldcg(&bidx[(size_t)row * nblk + k]);
+    arg_better(bv, bi, v, i);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    arg_better(bv, bi, ov, oi);
+  }
+  __syncthreads();
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int k = 1; k < 8; ++k) arg_better(bv, bi, sv[k], si[k]);
+    if (bi == 0x7fffffff) bi = 0;
+    out_val[row] = bv;
+    out_idx[row] = bi + vocab_offset;
+    if (tokens) tokens[row] = (int64_t)(bi + vocab_offset);
+    if (pos_ptr && row == 0) pos_ptr[0] += pos_inc;
+    tickets[row] = 0;  // ready for the next launch (graph replay)
+  }
+}
+
+__global__ void k_argmax_merge(const float* __restrict__ val, const int32_t* __restrict__ idx,
+                               int shards, int rows, int64_t* __restrict__ tokens,
+                               int32_t* __restrict__ pos_ptr, int pos_inc) {
+  pdl_launch_dependents();
+  pdl_wait();
+  int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row < rows) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int s = 0; s < shards; ++s) arg_better(bv, bi, val[(size_t)s * rows + row], idx[(size_t)s * rows + row]);
+    if (bi == 0x7fffffff) bi = 0;
+    tokens[row] = bi;
+    if (row == 0 && pos_ptr) pos_ptr[0] += pos_inc;
+  }
+}
+
+}  // namespace
+
+#define S(x) ((cudaStream_t)(x))
+
+extern "C" int q_rmsnorm(const void* d_x, const void* d_gain, void* d_out, int rows, int cols,
+                         float eps, void* stream) {
+  Q_CHECK_ARG(d_x && d_gain && d_out && rows >= 1 && cols >= 1, "q_rmsnorm: bad argument");
+  Q_CHECK_CUDA(q_launch(k_rmsnorm, dim3(rows), dim3(256), 0, S(stream), (const bf16*)d_x,
+                        (const bf16*)d_gain, (bf16*)d_out, cols, eps));
+  return Q_OK;
+}
+
+extern "C" int q_embed_rmsnorm(const int64_t* d_tokens, const void* d_embed, const void* d_gain,
+                               void* d_x, void* d_normed, int rows, int cols, int vocab, float eps,
+                               void* stream) {
+  Q_CHECK_ARG(d_tokens && d_embed && d_gain && d_x && d_normed && rows >= 1 && cols >= 1 && vocab >= 1,
+              "q_embed_rmsnorm: bad argument");
+  Q_CHECK_CUDA(q_launch(k_embed_rmsnorm, dim3(rows), dim3(256), 0, S(stream), d_tokens,
+                        (const bf16*)d_embed, (const bf16*)d_gain, (bf16*)d_x, (bf16*)d_normed, cols,
+                        vocab, eps));
+  return Q_OK;
+}
+
+static int check_plan(const q_gemm_plan_t* plan, int rows, int cols, const char* who) {
+  if (plan) {
+    Q_CHECK_ARG(plan->M == rows && plan->N == cols, "%s: plan is for [%d,%d], tensor is [%d,%d]", who,
+                plan->M, plan->N, rows, cols);
+    Q_CHECK_ARG(plan->units_per_worker >= 1 && plan->chunks_per_group >= 1, "%s: empty plan", who);
+  }
+  return Q_OK;
+}
+
+extern "C" int q_add_rmsnorm(const void* d_x_in, const float* d_branch, const q_gemm_plan_t* plan,
+                             const void* d_gain, void* d_total_out, void* d_normed_out, int rows,
+                             int cols, float eps, void* stream) {
+  Q_CHECK_ARG(d_x_in && d_branch && d_gain && d_total_out && d_normed_out, "q_add_rmsnorm: null pointer");
+  Q_CHECK_ARG(rows >= 1 && cols >= 1 && cols <= 256 * ADD_MAXE, "q_add_rmsnorm: cols %d outside 1..%d",
+              cols, 256 * ADD_MAXE);
+  int rc = check_plan(plan, rows, cols, "q_add_rmsnorm");
+  if (rc) return rc;
+  auto kern = cols <= 256 * 4 ? k_add_rmsnorm<4> : cols <= 256 * 12 ? k_add_rmsnorm<12> : k_add_rmsnorm<ADD_MAXE>;
+  Q_CHECK_CUDA(q_launch(kern, dim3(rows), dim3(256), 0, S(stream), (const bf16*)d_x_in,
+                        d_branch, plan_view(plan), (const bf16*)d_gain, (bf16*)d_total_out,
+                        (bf16*)d_normed_out, cols, eps));
+  return Q_OK;
+}
+
+extern "C" int q_swiglu(const float* d_branch, const q_gemm_plan_t* plan, void* d_out, int rows,
+                        int inter, void* stream) {
+  Q_CHECK_ARG(d_branch && d_out && rows >= 1 && inter >= 1, "q_swiglu: bad argument");
+  int rc = check_plan(plan, rows, 2 * inter, "q_swiglu");
+  if (rc) return rc;
+  long long total = (long long)rows * inter;
+  Q_CHECK_CUDA(q_launch(k_swiglu, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, S(stream),
+                        d_branch, plan_view(plan), (bf16*)d_out, rows, inter));
+  return Q_OK;
+}
+
+extern "C" int q_qkv_norm_rope_cache(const float* d_branch, const q_gemm_plan_t* plan,
+                                     const void* d_q_gain, const void* d_k_gain, const void* d_cos,
+                                     const void* d_sin, const int32_t* d_pos, void* d_q_out,
+                                     const q_kv_layout_t* kv, int batch, int T, int n_q_heads,
+                                     float eps, void* stream) {
+  Q_CHECK_ARG(d_branch && d_q_gain && d_k_gain && d_cos && d_sin && d_pos && d_q_out && kv,
+              "q_qkv_norm_rope_cache: null pointer");
+  Q_CHECK_ARG(kv->d_kpool && kv->d_vpool && kv->d_block_table && kv->pages_per_seq >= 1 &&
+                  kv->n_kv_heads >= 1,
+              "q_qkv_norm_rope_cache: incomplete KV layout");
+  Q_CHECK_ARG(batch >= 1 && T >= 1 && n_q_heads >= 1 && batch * T <= Q_MAX_ROWS,
+              "q_qkv_norm_rope_cache: bad batch/T");
+  const int rows = batch * T, nkv = kv->n_kv_heads;
+  int rc = check_plan(plan, rows, (n_q_heads + 2 * nkv) * 128, "q_qkv_norm_rope_cache");
+  if (rc) return rc;
+  const int items = rows * (n_q_heads + nkv);
+  Q_CHECK_CUDA(q_launch(k_qkv_norm_rope_cache, dim3((items + 3) / 4), dim3(128), 0, S(stream),
+                        d_branch, plan_view(plan), (const bf16*)d_q_gain, (const bf16*)d_k_gain,
+                        (const bf16*)d_cos, (const bf16*)d_sin, d_pos, (bf16*)d_q_out,
+                        (char*)kv->d_kpool, (char*)kv->d_vpool, kv->d_block_table, kv->pages_per_seq,
+                        rows, T, n_q_heads, nkv, eps));
+  return Q_OK;
+}
+
+extern "C" int q_kv_scatter(const void* d_k, const void* d_v, const q_kv_layout_t* kv, int batch,
+                            int len, int start, void* stream) {
+  Q_CHECK_ARG(d_k && d_v && kv && kv->d_kpool && kv->d_vpool && kv->d_block_table,
+              "q_kv_scatter: null pointer");
+  Q_CHECK_ARG(batch >= 1 && len >= 1 && start >= 0 && batch <= 65535 && kv->n_kv_heads <= 65535,
+              "q_kv_scatter: bad sizes");
+  Q_CHECK_ARG((start + len + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS <= kv->pages_per_seq,
+              "q_kv_scatter: positions exceed the block table");
+  k_kv_scatter<<<dim3(len, kv->n_kv_heads, batch), 128, 0, S(stream)>>>(
+      (const bf16*)d_k, (const bf16*)d_v, (char*)kv->d_kpool, (char*)kv->d_vpool, kv->d_block_table,
+      kv->pages_per_seq, kv->n_kv_heads, len, start);
+  Q_CHECK_CUDA(cudaGetLastError());
+  return Q_OK;
+}
+
+static inline int arg_blocks(int vocab) { return (vocab + ARG_COLS - 1) / ARG_COLS; }
+
+extern "C" int64_t q_argmax_scratch_bytes(int rows, int vocab) {
+  if (rows < 1 || vocab < 1) return 0;
+  int64_t nblk = arg_blocks(vocab);
+  int64_t tick = ((int64_t)rows * 4 + 255) / 256 * 256;
+  return tick + (int64_t)rows * nblk * 8;
+}
+
+extern "C" int q_logits_argmax(const float* d_branch, const q_gemm_plan_t* plan, void* d_logits,
+                               float* d_val, int32_t* d_idx, int64_t* d_tokens, int32_t* d_pos,
+                               int pos_inc, void* d_block_scratch, int rows, int vocab,
+                               int vocab_offset, void* stream) {
+  Q_CHECK_ARG(d_branch && d_val && d_idx && d_block_scratch, "q_logits_argmax: null pointer");
+  Q_CHECK_ARG(rows >= 1 && rows <= Q_MAX_ROWS && vocab >= 1, "q_logits_argmax: bad sizes");
+  int rc = check_plan(plan, rows, vocab, "q_logits_argmax");
+  if (rc) return rc;
+  const int nblk = arg_blocks(vocab);
+  char* base = (char*)d_block_scratch;
+  int64_t tick = ((int64_t)rows * 4 + 255) / 256 * 256;
+  unsigned int* tickets = (unsigned int*)base;
+  float* bval = (float*)(base + tick);
+  int* bidx = (int*)(base + tick + (int64_t)rows * nblk * 4);
+  Q_CHECK_CUDA(q_launch(k_logits_argmax, dim3(nblk, rows), dim3(256), 0, S(stream), d_branch,
+                        plan_view(plan), (bf16*)d_logits, d_val, d_idx, d_tokens, d_pos, pos_inc,
+                        tickets, bval, bidx, vocab, vocab_offset));
+  return Q_OK;
+}
+
+extern "C" int q_argmax_merge(const float* d_val, const int32_t* d_idx, int shards, int rows,
+                              int64_t* d_tokens, int32_t* d_pos, int pos_inc, void* stream) {
+  Q_CHECK_ARG(d_val && d_idx && d_tokens && shards >= 1 && rows >= 1, "q_argmax_merge: bad argument");
+  Q_CHECK_CUDA(q_launch(k_argmax_merge, dim3((rows + 63) / 64), dim3(64), 0, S(stream), d_val, d_idx,
+                        shards, rows, d_tokens, d_pos, pos_inc));
+  return Q_OK;
+}

@@ -1,0 +1,259 @@
+"""Fixed-address decode state, prefill, CUDA-graph capture and token emission.
+
+Mirrors the reference's DecodeState (engine/decode.py:38-148): static buffers,
+a `step()` that leaves the next token and position on the device, a captured
+graph replayed once per token, and a pinned-host handoff whose copy of step k
+is enqueued before step k+1 is launched. The KV cache is paged
+(64-token pages) instead of the reference's contiguous StaticCache.
+
+Tensor parallelism: every rank holds its head / FFN-column / vocabulary shard
+and runs the same step; the fp32 partial sums after O-proj and down-proj are
+all-reduced (so the single bf16 rounding of a Linear output happens after the
+cross-rank sum), and the per-rank (max, index) pairs of the vocabulary-sharded
+lm_head are all-gathered.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from ._lib import HEAD_DIM, PAGE_TOKENS, check, lib
+from .weights import PackedWeights, rotary_tables
+
+
+def _p(t):
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _rms(x, w, eps):
+    f = x.float()
+    return (f * torch.rsqrt(f.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+class DecodeState:
+    def __init__(self, weights: PackedWeights, batch: int, prompt_length: int, max_new_tokens: int,
+                 group=None, keep_logits: bool = False):
+        if batch < 1 or prompt_length < 1 or max_new_tokens < 1:
+            raise ValueError("positive batch, prompt length and token count required")
+        if batch > _lib.MAX_ROWS:
+            raise ValueError(f"batch {batch} exceeds {_lib.MAX_ROWS} rows")
+        self.w = weights
+        cfg = weights.cfg
+        self.cfg = cfg
+        self.group = group
+        self.tp = weights.tp_size
+        self.shape = (batch, prompt_length, max_new_tokens)
+        self.batch = batch
+        self.capacity = prompt_length + max_new_tokens
+        if self.capacity > cfg.max_position:
+            raise ValueError("prompt + new tokens exceed max_position_embeddings")
+        dev = weights.embed.device
+        self.device = dev
+        nq, nkv, inter = weights.local_q_heads, weights.local_kv_heads, weights.local_inter
+        self.pages_per_seq = (self.capacity + PAGE_TOKENS - 1) // PAGE_TOKENS
+        n_pages = batch * self.pages_per_seq
+        self.block_table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(batch, -1).contiguous()
+        pool = (n_pages, nkv, PAGE_TOKENS, HEAD_DIM)
+        self.kpools = [torch.zeros(pool, dtype=torch.bfloat16, device=dev) for _ in range(cfg.n_layers)]
+        self.vpools = [torch.zeros(pool, dtype=torch.bfloat16, device=dev) for _ in range(cfg.n_layers)]
+        self.cos, self.sin = rotary_tables(cfg, self.capacity, dev)
+        self.tokens = torch.zeros(batch, dtype=torch.int64, device=dev)
+        self.position = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.host = torch.empty(batch, dtype=torch.int64).pin_memory()
+        self.ready = torch.cuda.Event()
+        self.graph = None
+
+        ccfg = _lib.Config(cfg.hidden, inter, cfg.n_layers, nq, nkv, weights.local_vocab,
+                           weights.vocab_offset, cfg.vocab, self.tp, batch, cfg.rms_eps,
+                           float(HEAD_DIM) ** -0.5)
+        handle = C.c_void_p()
+        check(lib.q_create(C.byref(ccfg), C.byref(handle)))
+        self.handle = handle
+        for i, lt in enumerate(weights.layers):
+            lw = _lib.LayerWeights(lt.wqkv.data_ptr(), lt.wo.data_ptr(), lt.wgu.data_ptr(),
+                                   lt.wdown.data_ptr(), lt.ln_in.data_ptr(), lt.ln_post.data_ptr(),
+                                   lt.q_gain.data_ptr(), lt.k_gain.data_ptr(),
+                                   self.kpools[i].data_ptr(), self.vpools[i].data_ptr())
+            check(lib.q_bind_layer(handle, i, C.byref(lw)))
+
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.x = torch.zeros((batch, cfg.hidden), **bf)
+        self.normed = torch.zeros((batch, cfg.hidden), **bf)
+        self.q = torch.zeros((batch, nq * HEAD_DIM), **bf)
+        self.attended = torch.zeros((batch, nq * HEAD_DIM), **bf)
+        self.act = torch.zeros((batch, inter), **bf)
+        n_part = lib.q_engine_partial_floats(handle, batch)
+        if n_part <= 0:
+            raise _lib.QDecodeError("could not size the split-K partial buffer")
+        self.partials = torch.empty(n_part, **f32)
+        self.reduced = torch.zeros((batch, cfg.hidden), **f32) if self.tp > 1 else None
+        self.attn_splits = lib.q_attention_splits(batch, nkv, self.capacity)
+        g = nq // nkv
+        self.attn_o = torch.empty((batch * nkv, self.attn_splits, g, HEAD_DIM), **f32)
+        self.attn_ml = torch.empty((batch * nkv, self.attn_splits, g, 2), **f32)
+        self.logits = torch.zeros((batch, weights.local_vocab), **bf) if keep_logits else None
+        self.arg_val = torch.zeros(batch, **f32)
+        self.arg_idx = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.arg_scratch = torch.zeros(lib.q_argmax_scratch_bytes(batch, weights.local_vocab),
+                                       dtype=torch.uint8, device=dev)
+        if self.tp > 1:
+            self.gather_val = torch.zeros((self.tp, batch), **f32)
+            self.gather_idx = torch.zeros((self.tp, batch), dtype=torch.int32, device=dev)
+        st = _lib.State(
+            weights.embed.data_ptr(), weights.lm_head.data_ptr(), weights.ln_final.data_ptr(),
+            self.cos.data_ptr(), self.sin.data_ptr(), self.tokens.data_ptr(),
+            self.position.data_ptr(), self.block_table.data_ptr(), self.pages_per_seq, batch,
+            self.attn_splits, self.x.data_ptr(), self.normed.data_ptr(), self.q.data_ptr(),
+            self.attended.data_ptr(), self.act.data_ptr(), self.partials.data_ptr(),
+            0 if self.reduced is None else self.reduced.data_ptr(), self.attn_o.data_ptr(),
+            self.attn_ml.data_ptr(), 0 if self.logits is None else self.logits.data_ptr(),
+            self.arg_val.data_ptr(), self.arg_idx.data_ptr(), self.arg_scratch.data_ptr())
+        check(lib.q_bind_state(handle, C.byref(st)))
+
+    def __del__(self):
+        h = getattr(self, "handle", None)
+        if h:
+            lib.q_destroy(h)
+            self.handle = None
+
+    # ---- algorithmic bytes of one decode step on this rank (weights + KV) ----
+    def step_bytes(self, visible_keys: int) -> int:
+        cfg, w = self.cfg, self.w
+        per_layer = sum(t.numel() for t in (w.layers[0].wqkv, w.layers[0].wo, w.layers[0].wgu,
+                                            w.layers[0].wdown)) * 2
+        per_layer += (2 * cfg.hidden + 2 * HEAD_DIM) * 2
+        weights = cfg.n_layers * per_layer + w.lm_head.numel() * 2 + cfg.hidden * 2
+        kv_token = cfg.n_layers * 2 * w.local_kv_heads * HEAD_DIM * 2
+        return weights + kv_token * self.batch * visible_keys + kv_token * self.batch
+
+    # ---- prefill: outside the per-step hot path (library GEMMs + SDPA) ----
+    def _allreduce(self, t):
+        if self.tp > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+        return t
+
+    def _linear_rowpar(self, x, weight):
+        """Row-parallel Linear: fp32 partial per rank, all-reduce, one bf16 rounding."""
+        if self.tp == 1:
+            return F.linear(x, weight)
+        flat = x.reshape(-1, x.shape[-1])
+        part = torch.mm(flat, weight.t(), out_dtype=torch.float32)
+        return self._allreduce(part).to(torch.bfloat16).view(*x.shape[:-1], weight.shape[0])
+
+    def prefill(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """Runs the whole prompt, fills the KV pages, leaves the first generated
+        token in `tokens` and the prompt length in `position`. Returns the last
+        position's local logits [B, V_local]."""
+        cfg, w = self.cfg, self.w
+        B, T = input_ids.shape
+        if B != self.batch or T != self.shape[1]:
+            raise ValueError("prompt shape disagrees with this decode state")
+        nq, nkv = w.local_q_heads, w.local_kv_heads
+        eps = cfg.rms_eps
+        cos, sin = self.cos[:T][None, :, None, :], self.sin[:T][None, :, None, :]
+
+        def rotate(t):
+            half = torch.cat((-t[..., HEAD_DIM // 2:], t[..., :HEAD_DIM // 2]), -1)
+            return t * cos + half * sin
+
+        x = w.embed[input_ids]                                        # [B, T, H]
+        for i, lt in enumerate(w.layers):
+            h = _rms(x, lt.ln_in, eps)
+            qkv = F.linear(h, lt.wqkv)
+            q, k, v = qkv.split((nq * HEAD_DIM, nkv * HEAD_DIM, nkv * HEAD_DIM), -1)
+            q = rotate(_rms(q.reshape(B, T, nq, HEAD_DIM), lt.q_gain, eps)).transpose(1, 2)
+            k = rotate(_rms(k.reshape(B, T, nkv, HEAD_DIM), lt.k_gain, eps)).transpose(1, 2)
+            v = v.reshape(B, T, nkv, HEAD_DIM).transpose(1, 2)
+            kc, vc = k.contiguous(), v.contiguous()
+            layout = _lib.KVLayout(self.kpools[i].data_ptr(), self.vpools[i].data_ptr(),
+                                   self.block_table.data_ptr(), self.pages_per_seq, nkv)
+            check(lib.q_kv_scatter(_p(kc), _p(vc), C.byref(layout), B, T, 0,
+                                   C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            att = F.scaled_dot_product_attention(q, kc, vc, is_causal=True, enable_gqa=True)
+            att = att.transpose(1, 2).reshape(B, T, nq * HEAD_DIM)
+            x = x + self._linear_rowpar(att, lt.wo)
+            h = _rms(x, lt.ln_post, eps)
+            gate, up = F.linear(h, lt.wgu).chunk(2, -1)
+            x = x + self._linear_rowpar(F.silu(gate) * up, lt.wdown)
+        last = _rms(x[:, -1], w.ln_final, eps)
+        logits = F.linear(last, w.lm_head)                            # [B, V_local]
+        if self.tp == 1:
+            self.tokens.copy_(logits.argmax(-1))
+        else:
+            val, idx = logits.float().max(-1)
+            # torch.max returns the first maximal index on CUDA for 1-D reductions of
+            # distinct values; resolve exact ties explicitly to the lowest index.
+            first = (logits.float() == val[:, None]).int().argmax(-1)
+            vals = [torch.empty_like(val) for _ in range(self.tp)]
+            idxs = [torch.empty_like(first) for _ in range(self.tp)]
+            torch.distributed.all_gather(vals, val, group=self.group)
+            torch.distributed.all_gather(idxs, first + w.vocab_offset, group=self.group)
+            vals, idxs = torch.stack(vals), torch.stack(idxs)
+            best = vals.max(0).values
+            cand = torch.where(vals == best[None], idxs, torch.full_like(idxs, 2 ** 62))
+            self.tokens.copy_(cand.min(0).values)
+        self.position.fill_(T)
+        return logits
+
+    # ---- one decode step (the hot path) ----
+    def step(self) -> None:
+        s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        h = self.handle
+        if self.tp == 1:
+            check(lib.q_decode_step(h, s))
+            return
+        check(lib.q_step_begin(h, s))
+        for layer in range(self.cfg.n_layers):
+            check(lib.q_step_attn(h, layer, s))
+            torch.distributed.all_reduce(self.reduced, group=self.group)
+            check(lib.q_step_post_attn(h, layer, s))
+            torch.distributed.all_reduce(self.reduced, group=self.group)
+            check(lib.q_step_post_mlp(h, layer, s))
+        check(lib.q_step_head(h, s))
+        torch.distributed.all_gather_into_tensor(self.gather_val, self.arg_val, group=self.group)
+        torch.distributed.all_gather_into_tensor(self.gather_idx, self.arg_idx, group=self.group)
+        check(lib.q_argmax_merge(_p(self.gather_val), _p(self.gather_idx), self.tp, self.batch,
+                                 _p(self.tokens), _p(self.position), 1, s))
+
+    def capture(self) -> None:
+        """Three warm-up steps on a side stream, then one captured step
+        (engine/decode.py:130-148). Warm-up writes land in KV slots at or after the
+        current position, which the real steps overwrite before reading."""
+        tokens, position = self.tokens.clone(), self.position.clone()
+        current = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(current)
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                self.tokens.copy_(tokens)
+                self.position.copy_(position)
+                self.step()
+        current.wait_stream(side)
+        self.tokens.copy_(tokens)
+        self.position.copy_(position)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=side):
+            self.step()
+        self.tokens.copy_(tokens)
+        self.position.copy_(position)
+
+    def advance(self) -> None:
+        if self.graph is None:
+            self.step()
+        else:
+            self.graph.replay()
+
+    def emit(self, max_new_tokens: int):
+        """Yields one host list per output step; exactly max_new_tokens - 1 decode
+        steps run (engine/decode.py:110-128)."""
+        for step in range(max_new_tokens):
+            self.host.copy_(self.tokens, non_blocking=True)
+            self.ready.record()
+            if step + 1 < max_new_tokens:
+                self.advance()
+            self.ready.synchronize()
+            yield self.host.tolist()

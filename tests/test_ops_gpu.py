@@ -1,0 +1,257 @@
+"""Per-operator parity: every CUDA kernel, called through the C ABI, against the
+CPU oracle on the same seeded inputs."""
+import math
+
+import pytest
+import torch
+
+from oracle import qwen3_oracle as O
+from tests.parity import bit_equal_fraction, sum_slots
+
+pytestmark = pytest.mark.gpu
+
+H, I, V = 2560, 9728, 151936
+SHAPES = {"qkv": (6144, H), "o": (H, 4096), "gate_up": (2 * I, H), "down": (H, I), "lm_head": (V, H)}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("needs CUDA")
+    from starter_b200 import ops as ops_mod
+    return ops_mod
+
+
+def randw(n, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn((n, k), generator=g) * 0.02).to(torch.bfloat16)
+
+
+def randx(m, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn((m, k), generator=g).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("name", list(SHAPES))
+@pytest.mark.parametrize("M", [1, 4, 8, 16, 32])
+def test_split_k_gemm_matches_fp32_product(ops, name, M):
+    """Slot sum vs the fp32 product: rtol=atol=2e-3; after the single bf16 rounding
+    rtol=1.6e-2, atol=1e-2 (reference tests/test_skinny_gemm.py:479-481)."""
+    N, K = SHAPES[name]
+    if name == "lm_head" and M not in (1, 32):
+        pytest.skip("lm_head checked at the two ends of the row range")
+    w, x = randw(N, K, 11), randx(M, K, 100 + M)
+    wd, xd = w.cuda(), x.cuda()
+    before = (wd.clone(), xd.clone())
+    part = ops.linear_partials(xd, wd)
+    torch.cuda.synchronize()
+    assert torch.equal(before[0], wd) and torch.equal(before[1], xd)      # inputs untouched
+    ref = O.linear_fp32(x, w)
+    got_dev = part.sum().cpu()
+    got_host = sum_slots(part)
+    assert torch.equal(got_dev, got_host)
+    torch.testing.assert_close(got_host, ref, rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(got_host.to(torch.bfloat16).float(), ref.to(torch.bfloat16).float(),
+                               rtol=1.6e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 16, 32), (3, 127, 128), (5, 40, 64), (64, 256, 512), (33, 48, 96)])
+def test_split_k_gemm_ragged_and_tiny(ops, M, N, K):
+    w, x = randw(N, K, 5), randx(M, K, 6)
+    part = ops.linear_partials(x.cuda(), w.cuda())
+    torch.testing.assert_close(sum_slots(part), O.linear_fp32(x, w), rtol=2e-3, atol=2e-3)
+
+
+def test_gemm_rejects_bad_operands(ops):
+    x, w = randx(2, 64, 1).cuda(), randw(16, 64, 2).cuda()
+    with pytest.raises(ValueError):
+        ops.linear_partials(x.float(), w)
+    with pytest.raises(ValueError):
+        ops.linear_partials(x, w[:, :32])                 # non-contiguous
+    with pytest.raises(ValueError):
+        ops.linear_partials(randx(65, 64, 1).cuda(), w)   # too many rows
+    with pytest.raises(ValueError):
+        ops.linear_partials(x[:, :48].contiguous(), w[:, :48].contiguous())   # K % 32
+
+
+@pytest.mark.parametrize("M", [1, 8, 32])
+def test_add_rms_norm_on_partials(ops, M):
+    """Residual bit-exact; normed within one bf16 ulp (reference
+    tests/test_decode_step.py:237-238: residual exact, normed rtol=8e-3)."""
+    w, x = randw(H, 4096, 21), randx(M, 4096, 22)
+    res = randx(M, H, 23)
+    gain = (1 + 0.1 * torch.randn(H, generator=torch.Generator().manual_seed(24))).to(torch.bfloat16)
+    part = ops.linear_partials(x.cuda(), w.cuda())
+    total, normed = ops.add_rms_norm(res.cuda(), part, gain.cuda(), 1e-6)
+    et, en = O.add_rms_norm(res, sum_slots(part), gain, 1e-6)
+    assert torch.equal(total.cpu().view(torch.int16), et.view(torch.int16))
+    torch.testing.assert_close(normed.cpu().float(), en.float(), rtol=8e-3, atol=1e-6)
+    assert bit_equal_fraction(normed.cpu(), en) > 0.99
+    # plain fp32 branch (the tensor-parallel path) gives the same answer
+    total2, normed2 = ops.add_rms_norm(res.cuda(), part.sum(), gain.cuda(), 1e-6)
+    assert torch.equal(total2, total) and torch.equal(normed2, normed)
+
+
+@pytest.mark.parametrize("M", [1, 16])
+def test_swiglu_on_partials(ops, M):
+    w, x = randw(2 * I, H, 31), randx(M, H, 32) * 3
+    part = ops.linear_partials(x.cuda(), w.cuda())
+    got = ops.silu_mul(part).cpu()
+    ref = O.swiglu(sum_slots(part))
+    torch.testing.assert_close(got.float(), ref.float(), rtol=8e-3, atol=1e-6)
+    assert bit_equal_fraction(got, ref) > 0.99
+    assert torch.equal(ops.linear_silu_mul(x.cuda(), w.cuda()).cpu(), got)
+
+
+def test_rms_norm_plain(ops):
+    x = randx(7, H, 41)
+    gain = (1 + 0.1 * torch.randn(H, generator=torch.Generator().manual_seed(42))).to(torch.bfloat16)
+    got = ops.rms_norm(x.cuda(), gain.cuda(), 1e-6).cpu()
+    ref = O.rms_norm(x, gain, 1e-6)
+    torch.testing.assert_close(got.float(), ref.float(), rtol=8e-3, atol=1e-6)
+    assert bit_equal_fraction(got, ref) > 0.99
+
+
+@pytest.mark.parametrize("B,T,nq,nkv", [(1, 1, 32, 8), (4, 1, 8, 2), (2, 4, 8, 2), (3, 2, 4, 2)])
+def test_qkv_norm_rope_cache(ops, B, T, nq, nkv):
+    """Q, K within one ulp of the oracle, V exact; only the slots position..position+T-1
+    of the (NaN-poisoned) cache are written (reference tests/test_decode_step.py:278-291)."""
+    width = (nq + 2 * nkv) * 128
+    capacity, pos = 200, 70
+    w, x = randw(width, 256, 51), randx(B * T, 256, 52) * 4
+    qg = (1 + 0.1 * torch.randn(128, generator=torch.Generator().manual_seed(53))).to(torch.bfloat16)
+    kg = (1 + 0.1 * torch.randn(128, generator=torch.Generator().manual_seed(54))).to(torch.bfloat16)
+    cos, sin = O.rotary_tables(1_000_000.0, capacity)
+    part = ops.linear_partials(x.cuda(), w.cuda())
+    cache = ops.PagedKV(B, nkv, capacity, "cuda", poison=float("nan"))
+    position = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    q = ops.qkv_norm_rope_cache(part, qg.cuda(), kg.cuda(), 1e-6, 1e-6, cos.cuda(), sin.cuda(),
+                                position, cache, tokens_per_seq=T).cpu()
+    rows_pos = (pos + torch.arange(T)).repeat(B)
+    eq, ek, ev = O.qkv_norm_rope(sum_slots(part), qg, kg, 1e-6, cos[rows_pos], sin[rows_pos], nq, nkv)
+    torch.testing.assert_close(q.float(), eq.float(), rtol=0.02, atol=0.02)
+    assert bit_equal_fraction(q, eq) > 0.99
+    kc, vc = (t.cpu() for t in cache.gather(capacity))
+    knew = kc[:, :, pos:pos + T].transpose(1, 2).reshape(B * T, nkv, 128)
+    vnew = vc[:, :, pos:pos + T].transpose(1, 2).reshape(B * T, nkv, 128)
+    torch.testing.assert_close(knew.float(), ek.float(), rtol=0.02, atol=0.02)
+    assert bit_equal_fraction(knew, ek) > 0.99
+    assert torch.equal(vnew.view(torch.int16), ev.contiguous().view(torch.int16))
+    untouched = torch.ones(capacity, dtype=torch.bool)
+    untouched[pos:pos + T] = False
+    assert torch.isnan(kc[:, :, untouched].float()).all() and torch.isnan(vc[:, :, untouched].float()).all()
+
+
+def test_constant_row_rope_bit_exact(ops):
+    """eps=0 with constant rows: exactly bf16(cos -+ sin) (reference
+    tests/test_decode_step.py:296-321)."""
+    nq, nkv, pos = 4, 2, 17
+    width = (nq + 2 * nkv) * 128
+    x = torch.ones((1, 32), dtype=torch.bfloat16)
+    w = torch.full((width, 32), 3.0 / 32, dtype=torch.bfloat16)
+    cos, sin = O.rotary_tables(1_000_000.0, 64)
+    one = torch.ones(128, dtype=torch.bfloat16)
+    cache = ops.PagedKV(1, nkv, 64, "cuda")
+    part = ops.linear_partials(x.cuda(), w.cuda())
+    q = ops.qkv_norm_rope_cache(part, one.cuda(), one.cuda(), 0.0, 0.0, cos.cuda(), sin.cuda(),
+                                torch.tensor([pos], dtype=torch.int32, device="cuda"), cache).cpu()
+    sign = torch.cat((-torch.ones(64), torch.ones(64))).to(torch.bfloat16)
+    expected = cos[pos] + sign * sin[pos]
+    assert torch.equal(q[0, 0], expected) and torch.equal(q[0, 3], expected)
+    kc, vc = cache.gather(64)
+    assert torch.equal(kc[0, 1, pos].cpu(), expected)
+    assert torch.equal(vc[0, 0, pos].cpu(), torch.full((128,), 3.0, dtype=torch.bfloat16))
+
+
+def _attention_case(ops, B, T, nq, nkv, base_len, capacity, seed, poison=None):
+    g = torch.Generator().manual_seed(seed)
+    L = base_len + T                              # keys visible to the last query row
+    q = torch.randn((B, T, nq, 128), generator=g).to(torch.bfloat16)
+    k = torch.randn((B, nkv, L, 128), generator=g).to(torch.bfloat16)
+    v = torch.randn((B, nkv, L, 128), generator=g).to(torch.bfloat16)
+    cache = ops.PagedKV(B, nkv, capacity, "cuda", poison=poison)
+    cache.scatter(k.cuda(), v.cuda(), 0)
+    attn = ops.SmallQueryAttention(B, nq, nkv, capacity, "cuda", tokens_per_seq=T)
+    position = torch.tensor([base_len], dtype=torch.int32, device="cuda")
+    out = attn.run(q.reshape(B * T, nq, 128).cuda(), cache, position, 128 ** -0.5)
+    limits = (base_len + torch.arange(T) + 1)[None].repeat(B, 1)
+    ref = O.attention_fp64(q, k, v, limits, 128 ** -0.5).reshape(B * T, nq * 128)
+    return out.cpu(), ref, (q, k, v, cache, attn)
+
+
+@pytest.mark.parametrize("base_len", [0, 1, 62, 63, 64, 127, 300, 1000])
+@pytest.mark.parametrize("B,nq,nkv", [(1, 32, 8), (3, 8, 2), (2, 4, 2)])
+def test_decode_attention_vs_fp64(ops, base_len, B, nq, nkv):
+    """rtol=0.02, atol=5e-3 vs the fp64 equations (reference
+    tests/test_small_query_attention.py:253,501); unused capacity is NaN."""
+    out, ref, _ = _attention_case(ops, B, 1, nq, nkv, base_len, 1100, 60 + base_len, poison=float("nan"))
+    assert not torch.isnan(out.float()).any()
+    torch.testing.assert_close(out.float(), ref.float(), rtol=0.02, atol=5e-3)
+    assert ops.device_status()[0] == 0
+
+
+@pytest.mark.parametrize("T", [2, 4, 8])
+@pytest.mark.parametrize("base_len", [0, 60, 500])
+def test_small_query_attention_causal_block(ops, T, base_len):
+    out, ref, _ = _attention_case(ops, 2, T, 8, 2, base_len, 640, 70 + T, poison=float("nan"))
+    assert not torch.isnan(out.float()).any()
+    torch.testing.assert_close(out.float(), ref.float(), rtol=0.02, atol=5e-3)
+
+
+@pytest.mark.parametrize("T", [2, 8])
+def test_small_query_equals_token_by_token_decode(ops, T):
+    """The multi-token path against the single-token path run once per token
+    on the same cache: same kernel arithmetic, so the results agree to bf16 noise."""
+    B, nq, nkv, base, cap = 2, 8, 2, 333, 400
+    out, ref, (q, k, v, cache, attn) = _attention_case(ops, B, T, nq, nkv, base, cap, 90 + T)
+    single = ops.SmallQueryAttention(B, nq, nkv, cap, "cuda", tokens_per_seq=1)
+    rows = []
+    for t in range(T):
+        position = torch.tensor([base + t], dtype=torch.int32, device="cuda")
+        rows.append(single.run(q[:, t].contiguous().cuda(), cache, position, 128 ** -0.5).cpu())
+    stepwise = torch.stack(rows, 1).reshape(B * T, nq * 128)
+    torch.testing.assert_close(out.float(), stepwise.float(), rtol=0.02, atol=5e-3)
+
+
+def test_attention_full_size_block(ops):
+    """Batch 8, 4 query tokens, 32/8 heads, 4096 cached keys."""
+    out, ref, _ = _attention_case(ops, 8, 4, 32, 8, 4096, 4096 + 8, 99)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=0.02, atol=5e-3)
+
+
+def test_attention_rejects_bad_shapes(ops):
+    with pytest.raises(ValueError):
+        ops.SmallQueryAttention(1, 32, 8, 100, "cuda", tokens_per_seq=9)      # 9*4 > 32 rows
+    attn = ops.SmallQueryAttention(1, 8, 2, 100, "cuda")
+    cache = ops.PagedKV(1, 2, 100, "cuda")
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(ValueError):
+        attn.run(torch.zeros((1, 8, 64), dtype=torch.bfloat16, device="cuda"), cache, pos, 0.1)
+    with pytest.raises(ValueError):
+        attn.run(torch.zeros((1, 8, 128), dtype=torch.bfloat16, device="cuda"), cache, pos.long(), 0.1)
+
+
+def test_lm_head_argmax_ties_and_logits(ops):
+    w, x = randw(5000, 256, 81), randx(6, 256, 82)
+    w[4321] = w[17]                       # exact duplicate rows: tie, lowest index must win
+    logits, tokens = ops.lm_head_argmax(x.cuda(), w.cuda())
+    ref = O.linear(x, w)
+    torch.testing.assert_close(logits.cpu().float(), ref.float(), rtol=1.6e-2, atol=1e-2)
+    assert tokens.cpu().tolist() == O.greedy_pick(logits.cpu()).tolist()
+    zero = torch.zeros_like(w)
+    _, tok0 = ops.lm_head_argmax(x.cuda(), zero.cuda())
+    assert tok0.cpu().tolist() == [0] * 6
+    x1 = torch.zeros((1, 256), dtype=torch.bfloat16)
+    x1[0, 0] = 1.0
+    w2 = torch.zeros((5000, 256), dtype=torch.bfloat16)
+    w2[17, 0] = w2[4321, 0] = w2[4999, 0] = 2.0
+    _, tok = ops.lm_head_argmax(x1.cuda(), w2.cuda())
+    assert tok.cpu().tolist() == [17]
+
+
+def test_lm_head_argmax_full_vocab(ops):
+    w, x = randw(V, H, 83), randx(4, H, 84)
+    logits, tokens = ops.lm_head_argmax(x.cuda(), w.cuda())
+    ref = O.linear(x, w)
+    assert float((logits.cpu().float() - ref.float()).abs().max()) <= 2e-2
+    assert tokens.cpu().tolist() == O.greedy_pick(logits.cpu()).tolist()
