@@ -1,0 +1,447 @@
+"""Decode benchmark: Qwen3-4B bf16 greedy decode steps on N B200s.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A "step" is one decode step (one new token per sequence) of the workload
+`config.workload` over synthetic data: random-init N(0, 0.02) bf16 weights of the
+Qwen3-4B architecture (norm gains 1.0, seed 0) and uniform random prompt ids.
+Rank 0 prints ONE JSON line.
+
+  value      decode tok/s of the whole job, state resident in HBM, K graph replays
+             timed with CUDA events on the launching stream (max over ranks)
+  e2e        the same metric through Engine.generate(): host prompt in, host
+             tokens out, prefill and all copies inside the timed region
+  roofline   the weight-streaming GEMM kernel (the dominant kernel): algorithmic
+             weight bytes per launch / average launch duration, timed live here
+  cpu_baseline  native Hugging Face on the host cores (bounded sample), N=1 only
+
+--impl reference times the native Hugging Face CPU path alone.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_4B = dict(
+    vocab_size=151936, hidden_size=2560, intermediate_size=9728, num_hidden_layers=36,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=128, max_position_embeddings=40960,
+    rms_norm_eps=1e-6, rope_theta=1_000_000.0, tie_word_embeddings=True,
+)
+WORKLOADS = {
+    # name: (batch, prompt length, new tokens)
+    "c2": (1, 1024, 512),
+    "c3": (32, 2048, 256),
+    "c1": (1, 64, 16),
+}
+FALLBACK_HBM_GBS = 6650.0
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+# ----------------------------------------------------------------------------
+# synthetic checkpoint
+# ----------------------------------------------------------------------------
+def checkpoint_dir(cfg: dict) -> Path:
+    base = Path(os.environ.get("QDECODE_BENCH_DIR", "/tmp/qdecode_bench"))
+    tag = f"qwen3_L{cfg['num_hidden_layers']}_H{cfg['hidden_size']}_V{cfg['vocab_size']}_seed0"
+    return base / tag
+
+
+def make_checkpoint(cfg: dict, device) -> Path:
+    """Random-init N(0, 0.02) bf16 weights, norm gains 1.0, seed 0, written as a
+    Hugging Face directory (config.json + safetensors shards)."""
+    from safetensors.torch import save_file
+
+    out = checkpoint_dir(cfg)
+    done = out / "COMPLETE"
+    if done.exists():
+        return out
+    out.mkdir(parents=True, exist_ok=True)
+    hf_cfg = dict(cfg, architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_act="silu",
+                  attention_bias=False, attention_dropout=0.0, initializer_range=0.02,
+                  sliding_window=None, use_sliding_window=False, use_cache=True, dtype="bfloat16",
+                  rope_parameters={"rope_theta": cfg["rope_theta"], "rope_type": "default"})
+    (out / "config.json").write_text(json.dumps(hf_cfg, indent=1))
+    gen = torch.Generator(device=device).manual_seed(0)
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+
+    def rnd(*shape):
+        t = torch.empty(shape, dtype=torch.float32, device=device).normal_(0.0, 0.02, generator=gen)
+        return t.to(torch.bfloat16).cpu()
+
+    def ones(n):
+        return torch.ones(n, dtype=torch.bfloat16)
+
+    save_file({"model.embed_tokens.weight": rnd(V, H), "model.norm.weight": ones(H)},
+              str(out / "model-embed.safetensors"))
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        save_file({
+            p + "self_attn.q_proj.weight": rnd(nq * D, H), p + "self_attn.k_proj.weight": rnd(nkv * D, H),
+            p + "self_attn.v_proj.weight": rnd(nkv * D, H), p + "self_attn.o_proj.weight": rnd(H, nq * D),
+            p + "self_attn.q_norm.weight": ones(D), p + "self_attn.k_norm.weight": ones(D),
+            p + "mlp.gate_proj.weight": rnd(I, H), p + "mlp.up_proj.weight": rnd(I, H),
+            p + "mlp.down_proj.weight": rnd(H, I), p + "input_layernorm.weight": ones(H),
+            p + "post_attention_layernorm.weight": ones(H),
+        }, str(out / f"model-layer{i:02d}.safetensors"))
+    done.write_text("ok")
+    return out
+
+
+def make_prompt(batch: int, length: int, vocab: int):
+    g = torch.Generator().manual_seed(0)
+    return torch.randint(0, vocab, (batch, length), generator=g)
+
+
+# ----------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU in a thread (read-only NVML)."""
+
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+        0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[index]) if visible and visible.split(",")[index].isdigit() else index
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # no NVML: report that, do not fail the bench
+            self.nv = None
+            self.err = repr(e)
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if self.nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "error": self.err}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# ----------------------------------------------------------------------------
+# reference arm / CPU baseline: native Hugging Face on the host cores
+# ----------------------------------------------------------------------------
+def cpu_reference(model_dir: Path, batch: int, prompt_len: int, steps: int, warmup: int, vocab: int):
+    """Times `steps` decode steps of the native Hugging Face greedy loop on CPU
+    after an untimed prefill of `prompt_len` tokens and `warmup` steps."""
+    from oracle import qwen3_oracle as O
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    t0 = time.perf_counter()
+    model = O.native_model(str(model_dir))
+    load_s = time.perf_counter() - t0
+    prompt = make_prompt(batch, prompt_len, vocab)
+    stamps = []
+    O.native_greedy(model, prompt, 1 + warmup + steps, return_logits=False,
+                    on_step=lambda i: stamps.append(time.perf_counter()))
+    # stamps[0] = after prefill; then one per decode step
+    timed = stamps[warmup + steps] - stamps[warmup]
+    return {"tok_s": batch * steps / timed, "ms_per_step": 1e3 * timed / steps, "cores": cores,
+            "load_s": load_s, "prefill_s": stamps[0] - t0 - load_s, "steps": steps}
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    batch, prompt_len, _ = WORKLOADS[args.workload]
+    cfg = dict(QWEN3_4B)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    model_dir = make_checkpoint(cfg, dev)
+    steps = min(args.steps, args.cpu_steps)
+    warmup = min(args.warmup, 1)
+    sample_prompt = min(prompt_len, args.cpu_prompt)
+    r = cpu_reference(model_dir, batch, sample_prompt, steps, warmup, cfg["vocab_size"])
+    sample = (f"native Hugging Face Qwen3ForCausalLM greedy loop on CPU, batch {batch}, prompt "
+              f"{sample_prompt} of {prompt_len} tokens (untimed prefill), {steps} timed decode steps")
+    line = {
+        "impl": "reference", "metric": "decode_tok_s", "value": r["tok_s"], "unit": "tok/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": r["ms_per_step"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": workload_config(args, cfg, batch, prompt_len),
+        "cpu_baseline": {"value": r["tok_s"], "unit": "tok/s", "cores": r["cores"], "kind": "reference",
+                         "sample": sample},
+        "e2e": {"value": r["tok_s"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, cfg, batch, prompt_len):
+    new = WORKLOADS[args.workload][2]
+    return {
+        "workload": f"{args.workload}: Qwen3-4B architecture ({cfg['num_hidden_layers']} layers) bf16 "
+                    f"greedy decode, batch {batch}, prompt {prompt_len}, {new} new tokens",
+        "batch": batch, "prompt_len": prompt_len, "new_tokens": new,
+        "layers": cfg["num_hidden_layers"], "parallelism": f"tp{args.gpus}",
+        "l2": "inputs larger than L2 (weights 8.04 GB streamed once per step)",
+    }
+
+
+# ----------------------------------------------------------------------------
+# our arm
+# ----------------------------------------------------------------------------
+def time_gemm_kernel(state, reps: int = 5):
+    """Average launch duration of the weight-streaming GEMM kernel, timed live with
+    CUDA events on the launching stream: every GEMM of one decode step (4 per
+    layer + lm_head) launched in step order on the real weights (8 GB, far larger
+    than L2), nothing else in between."""
+    import ctypes as C
+    from starter_b200._lib import lib, check
+
+    w, cfg = state.w, state.cfg
+    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rows = state.batch
+    nq, inter = w.local_q_heads, w.local_inter
+    P = C.c_void_p(state.partials.data_ptr())
+    launches, nbytes = 0, 0
+
+    def seq():
+        nonlocal launches, nbytes
+        launches = nbytes = 0
+        for lt in w.layers:
+            for x, wt in ((state.normed, lt.wqkv), (state.attended, lt.wo), (state.normed, lt.wgu),
+                          (state.act, lt.wdown)):
+                check(lib.q_gemm_splitk(C.c_void_p(x.data_ptr()), C.c_void_p(wt.data_ptr()), P, rows,
+                                        wt.shape[0], wt.shape[1], s))
+                launches += 1
+                nbytes += wt.numel() * 2
+        check(lib.q_gemm_splitk(C.c_void_p(state.normed.data_ptr()), C.c_void_p(w.lm_head.data_ptr()), P,
+                                rows, w.lm_head.shape[0], w.lm_head.shape[1], s))
+        launches += 1
+        nbytes += w.lm_head.numel() * 2
+
+    for _ in range(2):
+        seq()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        seq()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / reps
+    return {"launches_per_step": launches, "bytes_per_step": nbytes,
+            "avg_launch_us": 1e3 * ms / launches, "gbs": nbytes / (ms * 1e-3) / 1e9}
+
+
+def kernels_per_step(state) -> int:
+    per_layer = 9 + (1 if state.attn_splits > 1 else 0)
+    n = 1 + state.cfg.n_layers * per_layer + 2
+    if state.tp > 1:
+        n += state.cfg.n_layers * 2 + 1      # partial reductions before each all-reduce, argmax merge
+    return n
+
+
+def run_ours(args, rank: int, world: int, local_rank: int) -> None:
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device(f"cuda:{local_rank}")
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    from starter_b200 import Engine
+
+    batch, prompt_len, new_tokens = WORKLOADS[args.workload]
+    cfg = dict(QWEN3_4B)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    K, W = args.steps, max(args.warmup, 3)
+    n_new = max(new_tokens, K + W + 2)
+    if rank == 0:
+        t0 = time.perf_counter()
+        model_dir = make_checkpoint(cfg, dev)
+        log(f"[bench] checkpoint ready in {time.perf_counter() - t0:.1f}s at {model_dir}")
+    if world > 1:
+        dist.barrier()
+    model_dir = checkpoint_dir(cfg)
+    t0 = time.perf_counter()
+    engine = Engine(str(model_dir), device=str(dev), group=group)
+    log(f"[bench] rank {rank}: weights loaded in {time.perf_counter() - t0:.1f}s")
+    prompt = make_prompt(batch, prompt_len, cfg["vocab_size"])
+    prompt_list = prompt.tolist()
+
+    # ---- device-resident timing: K graph replays ----
+    from starter_b200.decode import DecodeState
+    with torch.inference_mode():
+        state = DecodeState(engine.weights, batch, prompt_len, n_new, group=group)
+        engine.decode_state = state
+        state.prefill(prompt.to(dev))
+        state.capture()
+        for _ in range(W):
+            state.advance()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start_pos = int(state.position.item())
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            a.record()
+            for _ in range(K):
+                state.advance()
+            b.record()
+            torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        end_pos = int(state.position.item())
+        assert end_pos - start_pos == K, (start_pos, end_pos, K)
+        avg_keys = (start_pos + 1 + end_pos) / 2.0
+        step_bytes_rank = state.step_bytes(int(round(avg_keys)))
+        gemm = time_gemm_kernel(state) if rank == 0 else None
+        from starter_b200.ops import device_status
+        status = device_status()
+
+        # ---- end to end through the public API ----
+        list(engine.generate(prompt_list, n_new))            # warm-up call (capture already done)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t_start = time.perf_counter()
+        stamps = []
+        for _tok in engine.generate(prompt_list, n_new):
+            stamps.append(time.perf_counter())
+        torch.cuda.synchronize()
+        t_total = time.perf_counter() - t_start
+        te = torch.tensor([t_total], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        t_total = float(te.item())
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        peak, peak_src = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    ms_step = ms / K
+    tok_s = batch * K / (ms * 1e-3)
+    step_gbs = step_bytes_rank / (ms_step * 1e-3) / 1e9
+    line = {
+        "metric": "decode_tok_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args, cfg, batch, prompt_len),
+        "roofline": {
+            "bound": "hbm", "kernel": "k_gemm_streamk", "achieved": gemm["gbs"], "peak": peak,
+            "unit": "GB/s", "frac": gemm["gbs"] / peak, "traffic": args.traffic_bytes,
+            "peak_source": peak_src, "avg_launch_us": gemm["avg_launch_us"],
+            "launches_per_step": gemm["launches_per_step"],
+            "bytes_per_launch": gemm["bytes_per_step"] / gemm["launches_per_step"],
+        },
+        "step_roofline": {"bytes_per_step_per_gpu": step_bytes_rank, "achieved": step_gbs,
+                          "unit": "GB/s", "frac": step_gbs / peak, "avg_visible_keys": avg_keys},
+        "e2e": {
+            "value": batch * n_new / t_total, "unit": "tok/s",
+            "h2d_bytes_per_step": batch * prompt_len * 8 / n_new, "d2h_bytes_per_step": batch * 8,
+            "new_tokens": n_new, "ttft_ms": 1e3 * (stamps[0] - t_start),
+            "tpot_ms": 1e3 * (stamps[-1] - stamps[0]) / max(1, n_new - 1),
+        },
+        "gpu_launches": kernels_per_step(state) * K,
+        "clocks": clocks.summary(),
+        "device_status": status,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        r = cpu_reference(model_dir, batch, min(prompt_len, args.cpu_prompt), args.cpu_steps, 1,
+                          cfg["vocab_size"])
+        line["cpu_baseline"] = {
+            "value": r["tok_s"], "unit": "tok/s", "cores": r["cores"], "kind": "reference",
+            "ms_per_step": r["ms_per_step"],
+            "sample": f"native Hugging Face Qwen3ForCausalLM greedy loop on CPU, batch {batch}, prompt "
+                      f"{min(prompt_len, args.cpu_prompt)} tokens (untimed prefill), {r['steps']} timed decode steps",
+        }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c2")
+    ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers (not a valid bench)")
+    ap.add_argument("--cpu-steps", type=int, default=8)
+    ap.add_argument("--cpu-prompt", type=int, default=1024)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--traffic-bytes", type=float, default=None,
+                    help="DRAM bytes per GEMM launch from an ncu capture (see profiles/)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world != args.gpus:
+        if args.gpus > 1 and world == 1:
+            raise SystemExit("launch multi-GPU runs with torch.distributed.run (one rank per GPU)")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()
