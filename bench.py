@@ -86,18 +86,29 @@ def make_checkpoint(cfg: dict, device) -> Path:
     def ones(n):
         return torch.ones(n, dtype=torch.bfloat16)
 
-    save_file({"model.embed_tokens.weight": rnd(V, H), "model.norm.weight": ones(H)},
-              str(out / "model-embed.safetensors"))
+    weight_map, total_size = {}, 0
+
+    def save(tensors, name):
+        nonlocal total_size
+        save_file(tensors, str(out / name), metadata={"format": "pt"})
+        for k, v in tensors.items():
+            weight_map[k] = name
+            total_size += v.numel() * 2
+
+    save({"model.embed_tokens.weight": rnd(V, H), "model.norm.weight": ones(H)},
+         "model-embed.safetensors")
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
-        save_file({
+        save({
             p + "self_attn.q_proj.weight": rnd(nq * D, H), p + "self_attn.k_proj.weight": rnd(nkv * D, H),
             p + "self_attn.v_proj.weight": rnd(nkv * D, H), p + "self_attn.o_proj.weight": rnd(H, nq * D),
             p + "self_attn.q_norm.weight": ones(D), p + "self_attn.k_norm.weight": ones(D),
             p + "mlp.gate_proj.weight": rnd(I, H), p + "mlp.up_proj.weight": rnd(I, H),
             p + "mlp.down_proj.weight": rnd(H, I), p + "input_layernorm.weight": ones(H),
             p + "post_attention_layernorm.weight": ones(H),
-        }, str(out / f"model-layer{i:02d}.safetensors"))
+        }, f"model-layer{i:02d}.safetensors")
+    (out / "model.safetensors.index.json").write_text(
+        json.dumps({"metadata": {"total_size": total_size}, "weight_map": weight_map}))
     done.write_text("ok")
     return out
 
@@ -351,20 +362,28 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         status = device_status()
 
         # ---- end to end through the public API ----
-        list(engine.generate(prompt_list, n_new))            # warm-up call (capture already done)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        t_start = time.perf_counter()
-        stamps = []
-        for _tok in engine.generate(prompt_list, n_new):
-            stamps.append(time.perf_counter())
-        torch.cuda.synchronize()
-        t_total = time.perf_counter() - t_start
-        te = torch.tensor([t_total], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        t_total = float(te.item())
+        e2e = None
+        if not args.skip_e2e:
+            list(engine.generate(prompt_list, n_new))        # warm-up call (capture already done)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            t_start = time.perf_counter()
+            stamps = []
+            for _tok in engine.generate(prompt_list, n_new):
+                stamps.append(time.perf_counter())
+            torch.cuda.synchronize()
+            t_total = time.perf_counter() - t_start
+            te = torch.tensor([t_total], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(te, op=dist.ReduceOp.MAX)
+            t_total = float(te.item())
+            e2e = {
+                "value": batch * n_new / t_total, "unit": "tok/s",
+                "h2d_bytes_per_step": batch * prompt_len * 8 / n_new, "d2h_bytes_per_step": batch * 8,
+                "new_tokens": n_new, "ttft_ms": 1e3 * (stamps[0] - t_start),
+                "tpot_ms": 1e3 * (stamps[-1] - stamps[0]) / max(1, n_new - 1),
+            }
 
     if rank != 0:
         if world > 1:
@@ -393,12 +412,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         },
         "step_roofline": {"bytes_per_step_per_gpu": step_bytes_rank, "achieved": step_gbs,
                           "unit": "GB/s", "frac": step_gbs / peak, "avg_visible_keys": avg_keys},
-        "e2e": {
-            "value": batch * n_new / t_total, "unit": "tok/s",
-            "h2d_bytes_per_step": batch * prompt_len * 8 / n_new, "d2h_bytes_per_step": batch * 8,
-            "new_tokens": n_new, "ttft_ms": 1e3 * (stamps[0] - t_start),
-            "tpot_ms": 1e3 * (stamps[-1] - stamps[0]) / max(1, n_new - 1),
-        },
+        "e2e": e2e,
         "gpu_launches": kernels_per_step(state) * K,
         "clocks": clocks.summary(),
         "device_status": status,
@@ -428,6 +442,8 @@ def main() -> None:
     ap.add_argument("--cpu-steps", type=int, default=8)
     ap.add_argument("--cpu-prompt", type=int, default=1024)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true",
+                    help="profiling runs only: skip the Engine.generate leg (e2e becomes null)")
     ap.add_argument("--traffic-bytes", type=float, default=None,
                     help="DRAM bytes per GEMM launch from an ncu capture (see profiles/)")
     args = ap.parse_args()
