@@ -275,10 +275,20 @@ def time_gemm_kernel(state, reps: int = 5):
     for _ in range(2):
         seq()
     torch.cuda.synchronize()
+    # one CUDA graph of the whole sequence: no host launch cost between kernels
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            seq()
+    graph.replay()
+    torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(reps):
-        seq()
+        graph.replay()
     b.record()
     torch.cuda.synchronize()
     ms = a.elapsed_time(b) / reps

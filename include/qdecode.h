@@ -46,29 +46,51 @@ int q_version(void);
  * Off = plain stream-ordered launches. */
 int q_set_pdl(int enabled);
 
+/* Tuning knobs (process-wide, host side only; no reference counterpart).
+ *   "gemm_prefetch_kb": L2 prefetch window per GEMM CTA in KB (0 = off).
+ * Unknown names return Q_ERR_ARG. */
+int q_set_option(const char* name, int value);
+
+/* Measurement aid: with option "gemm_debug_flags" bit 4 set, every GEMM CTA records
+ * {SM id, start, first data, loop end, exit} (ns, %globaltimer); this copies the
+ * records of the last launch to the host (5 values per CTA). */
+int q_debug_gemm_trace(unsigned long long* out, int n_ctas);
+
 /* ---- split-K weight-streaming GEMM --------------------------------------
  * Replaces engine/kernels/skinny_gemm.py:100-109 (linear_partials) and the
  * split planning at :86-91 (split_count).
  *
  * P[slot][m][n] (fp32) holds partial sums of X[M,K] . W[N,K]^T. The work is
- * cut into units of 16 weight rows x 32 k; every warp of the grid takes one
- * contiguous run of `units_per_worker` units, so a 16-row group is covered by
- * `count(group)` consecutive workers, and worker w writes slot
+ * cut into units of 16 weight rows x 32 k; every CTA of the grid (a "worker")
+ * takes one contiguous run of `units_per_worker` units, so a 16-row group is
+ * covered by `count(group)` consecutive workers, and worker w writes slot
  * w - first_worker(group). A consumer sums slots 0..count-1 in order and
- * rounds once to bf16. q_gemm_plan gives the numbers a consumer needs. */
+ * rounds once to bf16. q_gemm_plan gives the numbers a consumer needs; P always
+ * has at least two slots. */
 typedef struct q_gemm_plan_t {
   int32_t M, N, K;
   int32_t chunks_per_group;   /* K / 32 */
   int32_t groups;             /* ceil(N / 16) */
   int32_t units_per_worker;   /* u */
-  int32_t workers;            /* warps that get work */
+  int32_t workers;            /* CTAs that get work */
   int32_t slots;              /* max count(group); P needs slots*M*N floats */
   int32_t grid, block;        /* launch shape used */
 } q_gemm_plan_t;
 
 int q_gemm_plan(int M, int N, int K, q_gemm_plan_t* plan);
 
-int q_gemm_splitk(const void* d_x, const void* d_w, float* d_partials,
+/* Weight tiling, done once at load time (the reference packs at load time too:
+ * engine/mlp.py:12-15, engine/qk_norm_rope.py:25-30). A row-major bf16 [N][K]
+ * matrix (torch Linear layout) becomes q_packed_weight_bytes(N,K) bytes of 1 KB
+ * units (16 rows x 32 k, group-major, rows past N zero) in the order the GEMM
+ * streams them. q_unpack_weight is the inverse. Not capturable-sensitive: plain
+ * kernels on `stream`. */
+int64_t q_packed_weight_bytes(int N, int K);
+int q_pack_weight(const void* d_rowmajor, void* d_tiled, int N, int K, void* stream);
+int q_unpack_weight(const void* d_tiled, void* d_rowmajor, int N, int K, void* stream);
+
+/* d_w_tiled is a weight in the tiled layout above. */
+int q_gemm_splitk(const void* d_x, const void* d_w_tiled, float* d_partials,
                   int M, int N, int K, void* stream);
 
 /* Sums the slots of a plan into one fp32 [M,N] buffer (no rounding). Used
@@ -82,7 +104,8 @@ int q_reduce_partials(const float* d_partials, const q_gemm_plan_t* plan,
 int q_rmsnorm(const void* d_x, const void* d_gain, void* d_out,
               int rows, int cols, float eps, void* stream);
 
-/* engine/decode_step.py:38-39: embedding gather + first RMSNorm.
+/* engine/decode_step.py:38-39: embedding gather + first RMSNorm. d_embed is the
+ * [vocab][cols] table in the TILED weight layout (it is the tied lm_head).
  * d_tokens int64[rows]; writes x (the residual stream) and normed. */
 int q_embed_rmsnorm(const int64_t* d_tokens, const void* d_embed, const void* d_gain,
                     void* d_x, void* d_normed, int rows, int cols, int vocab,
@@ -187,6 +210,7 @@ typedef struct q_config_t {
 } q_config_t;
 
 typedef struct q_layer_weights_t {
+  /* the four matrices are in the tiled layout of q_pack_weight */
   const void* wqkv;     /* [(n_q+2*n_kv)*128][hidden]  q rows | k rows | v rows */
   const void* wo;       /* [hidden][n_q*128] */
   const void* wgu;      /* [2*inter][hidden]  gate rows | up rows */
@@ -200,8 +224,8 @@ typedef struct q_layer_weights_t {
 } q_layer_weights_t;
 
 typedef struct q_state_t {
-  const void* embed;        /* [full_vocab][hidden] */
-  const void* lm_head;      /* [vocab][hidden] (local shard; == embed when tied, tp 1) */
+  const void* embed;        /* [full_vocab][hidden], tiled layout */
+  const void* lm_head;      /* [vocab][hidden] tiled (local shard; == embed when tied, tp 1) */
   const void* ln_final;     /* [hidden] */
   const void* cos;          /* [capacity][128] bf16 */
   const void* sin;
@@ -253,7 +277,7 @@ int q_step_head(q_engine* e, void* stream);
 
 /* Reads the library's device status word of the current device (synchronises
  * the device; not capturable). out[0] != 0 means a bounded wait inside a kernel
- * ran out (1 = attention producer, 2 = attention consumer). */
+ * ran out: out[0] attention (1 producer, 2 consumer), out[1] GEMM ring (1). */
 int q_device_status(int32_t out[4]);
 
 #ifdef __cplusplus

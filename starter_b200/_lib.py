@@ -69,7 +69,12 @@ SIGNATURES = {
     "q_last_error": (C.c_char_p, []),
     "q_version": (_I, []),
     "q_set_pdl": (_I, [_I]),
+    "q_set_option": (_I, [C.c_char_p, _I]),
+    "q_debug_gemm_trace": (_I, [C.POINTER(C.c_uint64), _I]),
     "q_gemm_plan": (_I, [_I, _I, _I, _PLAN]),
+    "q_packed_weight_bytes": (C.c_int64, [_I, _I]),
+    "q_pack_weight": (_I, [_P, _P, _I, _I, _P]),
+    "q_unpack_weight": (_I, [_P, _P, _I, _I, _P]),
     "q_gemm_splitk": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "q_reduce_partials": (_I, [_P, _PLAN, _P, _P]),
     "q_rmsnorm": (_I, [_P, _P, _P, _I, _I, _F, _P]),

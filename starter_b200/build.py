@@ -12,7 +12,7 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
-LIB = ROOT / "libqdecode.so"
+LIB = Path(os.environ.get("QDECODE_LIB", ROOT / "libqdecode.so"))
 SOURCES = ["capi.cu", "gemm_streamk.cu", "fused_ops.cu", "attention.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -36,7 +36,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not _stale():
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc, *NVCC_FLAGS]
+    cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("QDECODE_NVCC_EXTRA", "").split()]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += [str(CSRC / s) for s in SOURCES] + ["-o", str(LIB)]

@@ -370,12 +370,12 @@ k_attn_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml
   const float wgt = l > 0.f ? exp2f(m - M) : 0.f;
   const float L = warp_sum(wgt * l);
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  // every split wrote its (possibly neutral, all-zero) partial, so no branch is needed
+#pragma unroll 4
   for (int s = 0; s < S; ++s) {
     const float ws = __shfl_sync(0xffffffffu, wgt, s);
-    if (ws != 0.f) {
-      const float4 o = *reinterpret_cast<const float4*>(part_o + (base + (size_t)s * R) * 128 + lane * 4);
-      acc[0] += ws * o.x; acc[1] += ws * o.y; acc[2] += ws * o.z; acc[3] += ws * o.w;
-    }
+    const float4 o = *reinterpret_cast<const float4*>(part_o + (base + (size_t)s * R) * 128 + lane * 4);
+    acc[0] += ws * o.x; acc[1] += ws * o.y; acc[2] += ws * o.z; acc[3] += ws * o.w;
   }
   const float inv = L > 0.f ? 1.f / L : 0.f;
   bf16* dst = out + ((size_t)bt * nq + head) * 128 + lane * 4;
@@ -457,9 +457,6 @@ extern "C" int q_attention(const void* d_q, const q_kv_layout_t* kv, const int32
   return Q_OK;
 }
 
-extern "C" int q_device_status(int32_t out[4]) {
-  Q_CHECK_ARG(out != nullptr, "q_device_status: null pointer");
-  Q_CHECK_CUDA(cudaDeviceSynchronize());
-  Q_CHECK_CUDA(cudaMemcpyFromSymbol(out, g_status, sizeof(int) * 4));
-  return Q_OK;
+int q_attn_status_read(int32_t out[4]) {
+  return cudaMemcpyFromSymbol(out, g_status, sizeof(int) * 4) == cudaSuccess ? 0 : -1;
 }

@@ -38,6 +38,41 @@ int q_sm_count() {
   return n;
 }
 
+int g_gemm_prefetch_kb = 640;
+int g_gemm_debug_flags = 0;
+
+extern "C" int q_set_option(const char* name, int value) {
+  Q_CHECK_ARG(name != nullptr, "q_set_option: null name");
+  if (strcmp(name, "gemm_prefetch_kb") == 0) {
+    Q_CHECK_ARG(value >= 0 && value <= 8192, "q_set_option: gemm_prefetch_kb outside 0..8192");
+    g_gemm_prefetch_kb = value;
+    return Q_OK;
+  }
+  if (strcmp(name, "gemm_debug_flags") == 0) {
+    g_gemm_debug_flags = value;     // measurement aid: results are wrong when non-zero
+    return Q_OK;
+  }
+  q_set_error("q_set_option: unknown option '%s'", name);
+  return Q_ERR_ARG;
+}
+
+int q_attn_status_read(int32_t out[4]);
+int q_gemm_status_read(int32_t out[4]);
+
+extern "C" int q_device_status(int32_t out[4]) {
+  Q_CHECK_ARG(out != nullptr, "q_device_status: null pointer");
+  Q_CHECK_CUDA(cudaDeviceSynchronize());
+  int32_t a[4] = {0, 0, 0, 0}, g[4] = {0, 0, 0, 0};
+  if (q_attn_status_read(a) || q_gemm_status_read(g)) {
+    q_set_error("q_device_status: could not read the status words");
+    return Q_ERR_CUDA;
+  }
+  out[0] = a[0];   // attention: 1 producer wait ran out, 2 consumer wait ran out
+  out[1] = g[0];   // GEMM: 1 ring wait ran out
+  out[2] = out[3] = 0;
+  return Q_OK;
+}
+
 extern "C" const char* q_last_error(void) { return g_err; }
 extern "C" int q_version(void) { return 100; }
 extern "C" int q_set_pdl(int enabled) {

@@ -88,21 +88,27 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&p);
 }
 
-// Number of split-K slots that hold a partial for column n, and their sum.
+// Number of split-K slots that hold a partial for column n.
 __device__ __forceinline__ int plan_count(const PlanView& pv, int n) {
   if (pv.u == 0) return 1;
-  long long g = n >> 4;
-  long long first = (g * pv.C) / pv.u;
-  long long last = ((g + 1) * pv.C - 1) / pv.u;
+  const unsigned g = (unsigned)n >> 4, C = (unsigned)pv.C, u = (unsigned)pv.u;
+  const unsigned first = (g * C) / u;
+  const unsigned last = ((g + 1) * C - 1) / u;
   return (int)(last - first + 1);
 }
 
-// Sum of the partial slots of element (m, n) in slot order 0..count-1.
+// Sum of the partial slots of element (m, n) in slot order 0..count-1. Every
+// partial buffer has at least two slots, so slot 1 is loaded unconditionally
+// (in parallel with slot 0) and only used when it holds data.
 __device__ __forceinline__ float plan_sum(const float* __restrict__ P, const PlanView& pv,
                                           long long idx, int n) {
-  int cnt = plan_count(pv, n);
   float s = P[idx];
-  for (int k = 1; k < cnt; ++k) s += P[idx + k * pv.slot_stride];
+  if (pv.u != 0) {
+    const float s1 = P[idx + pv.slot_stride];
+    const int cnt = plan_count(pv, n);
+    if (cnt > 1) s += s1;
+    for (int k = 2; k < cnt; ++k) s += P[idx + k * pv.slot_stride];
+  }
   return s;
 }
 

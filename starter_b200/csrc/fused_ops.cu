@@ -36,6 +36,14 @@ k_rmsnorm(const bf16* __restrict__ X, const bf16* __restrict__ G, bf16* __restri
 }
 
 // ---- embedding gather + RMSNorm --------------------------------------------
+// The table is the (tied) lm_head weight in the tiled GEMM layout: element
+// (row, c) lives in unit (row/16, c/32), half (row%16)/8, piece (row%8)*4 + (c%32)/8.
+__device__ __forceinline__ size_t tiled_offset(long long row, int c, int C) {
+  const long long unit = (row >> 4) * C + (c >> 5);
+  const int piece = (int)(row & 7) * 4 + ((c & 31) >> 3);
+  return (size_t)unit * 512 + (size_t)((row >> 3) & 1) * 256 + piece * 8 + (c & 7);   // in elements
+}
+
 __global__ void __launch_bounds__(256)
 k_embed_rmsnorm(const int64_t* __restrict__ tokens, const bf16* __restrict__ E,
                 const bf16* __restrict__ G, bf16* __restrict__ Xo, bf16* __restrict__ No,
@@ -47,10 +55,10 @@ k_embed_rmsnorm(const int64_t* __restrict__ tokens, const bf16* __restrict__ E,
   long long tok = tokens[row];
   if (tok < 0) tok = 0;
   if (tok >= vocab) tok = vocab - 1;
-  const bf16* x = E + (size_t)tok * cols;
+  const int C = cols >> 5;
   float ss = 0.f;
   for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-    bf16 raw = x[c];
+    bf16 raw = E[tiled_offset(tok, c, C)];
     Xo[row * cols + c] = raw;
     float v = __bfloat162float(raw);
     ss += v * v;
@@ -58,7 +66,7 @@ k_embed_rmsnorm(const int64_t* __restrict__ tokens, const bf16* __restrict__ E,
   ss = block_sum(ss, red);
   const float inv = rsqrtf(ss / (float)cols + eps);
   for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-    float v = bf16_round(__bfloat162float(x[c]) * inv);
+    float v = bf16_round(__bfloat162float(Xo[row * cols + c]) * inv);
     No[row * cols + c] = __float2bfloat16_rn(v * __bfloat162float(G[c]));
   }
 }
@@ -324,8 +332,9 @@ extern "C" int q_rmsnorm(const void* d_x, const void* d_gain, void* d_out, int r
 extern "C" int q_embed_rmsnorm(const int64_t* d_tokens, const void* d_embed, const void* d_gain,
                                void* d_x, void* d_normed, int rows, int cols, int vocab, float eps,
                                void* stream) {
-  Q_CHECK_ARG(d_tokens && d_embed && d_gain && d_x && d_normed && rows >= 1 && cols >= 1 && vocab >= 1,
-              "q_embed_rmsnorm: bad argument");
+  Q_CHECK_ARG(d_tokens && d_embed && d_gain && d_x && d_normed && rows >= 1 && cols >= 32 &&
+                  cols % 32 == 0 && vocab >= 1,
+              "q_embed_rmsnorm: bad argument (cols must be a multiple of 32)");
   Q_CHECK_CUDA(q_launch(k_embed_rmsnorm, dim3(rows), dim3(256), 0, S(stream), d_tokens,
                         (const bf16*)d_embed, (const bf16*)d_gain, (bf16*)d_x, (bf16*)d_normed, cols,
                         vocab, eps));

@@ -1,39 +1,121 @@
-// Split-K weight-streaming GEMM for at most 64 activation rows.
+// Split-K weight-streaming GEMM for at most 64 activation rows, over weights
+// pre-tiled at load time so that every warp streams one contiguous byte range.
 //
 // Y[M,N] = X[M,K] . W[N,K]^T with bf16 operands and fp32 accumulation, written
 // as fp32 partial sums that the fused consumers add and round once
 // (reference: engine/kernels/skinny_gemm.py:28-46 computes the same partials
-// with a fixed split count; the decomposition here is different).
+// with a fixed split count over row-major weights; packing weights at load time
+// is what engine/mlp.py:12-15 and engine/qk_norm_rope.py:25-30 do for gate|up and
+// q|k|v; the tiling here goes further).
 //
-// The weight matrix is cut into units of 16 rows x 32 k (1 KB). Units are
-// numbered group-major and every warp of the grid streams ONE contiguous run of
-// `u` units, so all warps move the same number of bytes whatever N and K are.
-// A warp feeds the weight rows to the tensor cores as the A operand of
-// mma.m16n8k16 straight from its 128-bit global loads (no shared-memory
-// staging): lane (g,t) loads 16 bytes of row g and of row g+8 at k offset 8t and
-// uses them for two MMAs; the k positions inside an MMA are a fixed permutation
-// of the real ones, and the activation fragment is loaded with the same
-// permutation, so the dot products are unchanged. The batch rows sit in the MMA
-// N dimension (8 per tile), which keeps tensor-core padding waste negligible.
+// Tiled layout ("units"). The matrix is cut into units of 16 rows x 32 k = 1 KB,
+// stored group-major (16-row group, then k chunk). Inside a unit the bytes are in
+// the order the tensor-core fragments want them: 32 pieces of 16 B for rows
+// 0..7 (piece l = row l/4, k offset 8*(l%4)), then 32 pieces for rows 8..15.
+// Rows past N are stored as zeros, so there is no ragged edge.
 //
-// A ring of DEPTH chunks per warp is kept in flight. The first DEPTH weight
-// chunks are requested BEFORE griddepcontrol.wait, i.e. while the kernel that
-// produces X is still running.
+// Decomposition. CTA c owns the contiguous run of U units [c*U, (c+1)*U) (same
+// bytes for every CTA, one CTA per SM); warp w of the CTA owns the contiguous
+// 1/8 of that run. A warp therefore streams ONE linear byte range: lane 0 brings
+// it into a private 2-stage shared-memory ring with cp.async.bulk (TMA, 8 KB per
+// copy, mbarrier transaction counts), all lanes read back their own 2 x 16 B per
+// unit as the A fragment of two mma.m16n8k16 (the k positions inside an MMA are a
+// fixed permutation of the real ones and the activation fragment uses the same
+// permutation). The batch rows sit in the MMA N dimension (8 per tile).
+//
+// A warp that covers a 16-row group completely writes that group's result
+// straight to slot 0. The (at most two) ragged ends of a warp's run go to shared
+// memory and are added across the CTA's warps after one __syncthreads, so a group
+// receives one partial per CTA that touches it: at most 2 slots for all Qwen3-4B
+// shapes.
+//
+// Overlap with the producer of X. Before griddepcontrol.wait every warp asks for
+// an L2 prefetch of its run (cp.async.bulk.prefetch.L2) and fills its ring:
+// weights do not depend on the previous kernel, so HBM keeps streaming while the
+// small kernel that produces X is still running. Two GEMM CTAs fit on an SM, which
+// lets the next GEMM start while the current one drains.
+//
+// Every mbarrier wait is bounded; a wait that runs out sets the status word of
+// this file (read by q_device_status) and the warp stops consuming.
 #include "common.cuh"
+
+extern int g_gemm_prefetch_kb;   // set through q_set_option
+extern int g_gemm_debug_flags;   // set through q_set_option: 1 = no MMA/X (stream only), 2 = no X loads
 
 namespace {
 
-constexpr int WARPS = 16;      // warps per CTA
-constexpr int DEPTH = 6;       // weight chunks in flight per warp
+#ifndef QG_WARPS
+#define QG_WARPS 8
+#endif
+#ifndef QG_STAGE_UNITS
+#define QG_STAGE_UNITS 8
+#endif
+#ifndef QG_STAGES
+#define QG_STAGES 2
+#endif
+constexpr int WARPS = QG_WARPS;
+constexpr int THREADS = WARPS * 32;
+constexpr int STAGE_UNITS = QG_STAGE_UNITS;  // units (KB) per bulk copy
+constexpr int STAGES = QG_STAGES;
+constexpr int RING_BYTES = WARPS * STAGES * STAGE_UNITS * 1024;   // 96 KB
+constexpr unsigned WAIT_LIMIT = 1u << 22;
 
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
+__device__ int g_gemm_status[4];
+// Measurement aid (debug flag 4): per CTA {smid, t_start, t_first_data, t_loop_end, t_exit} in ns.
+__device__ unsigned long long g_gemm_trace[256 * 5];
+
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ unsigned smid() {
+  unsigned s;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(s));
+  return s;
 }
 
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (it > 256) __nanosleep(32);
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ uint4 ldg_cached(const void* p) {
   uint4 v;
   asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -41,7 +123,6 @@ __device__ __forceinline__ uint4 ldg_cached(const void* p) {
                : "l"(p));
   return v;
 }
-
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -53,93 +134,186 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 
 // NT = number of 8-row activation tiles (M <= 8*NT).
 template <int NT>
-__global__ void __launch_bounds__(WARPS * 32)
-k_gemm_streamk(const bf16* __restrict__ X, const bf16* __restrict__ W, float* __restrict__ P,
-               int M, int N, int K, int C, long long total, int u) {
+__global__ void __launch_bounds__(THREADS, (RING_BYTES <= 100 * 1024 ? 2 : 1))
+k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
+               float* __restrict__ P, int M, int N, int K, int C, int total, int U,
+               int prefetch_bytes, int dbg) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  float* red = reinterpret_cast<float*>(smem + RING_BYTES);            // [WARPS][2][NT*128]
+  int* tags = reinterpret_cast<int*>(red + WARPS * 2 * NT * 128);      // [WARPS][2] group or -1
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tags + WARPS * 2);      // [WARPS][STAGES]
+
   pdl_launch_dependents();
-  const int lane = threadIdx.x & 31;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const long long w = (long long)blockIdx.x * WARPS + (threadIdx.x >> 5);
-  const long long start = w * u;
-  long long end = start + u;
-  if (end > total) end = total;
-  if (start >= total) {
-    pdl_wait();
-    return;
+  const bool trace = (dbg & 4) && tid == 0 && blockIdx.x < 256;
+  if (trace) {
+    g_gemm_trace[blockIdx.x * 5 + 0] = smid();
+    g_gemm_trace[blockIdx.x * 5 + 1] = gtime();
   }
-  const int n_units = (int)(end - start);
+  const int cs = blockIdx.x * U;
+  const int ce = min(total, cs + U);
+  const int len = ce > cs ? ce - cs : 0;
+  // the warp's contiguous run [ws, we)
+  const int ws = cs + (int)(((long long)warp * len) / WARPS);
+  const int we = cs + (int)(((long long)(warp + 1) * len) / WARPS);
+  const int n_units = we - ws;
+  const unsigned char* src = Wt + (size_t)ws * 1024;
 
-  // Position of the prefetch cursor (unit start+issued): group and chunk.
-  int pf_group = (int)(start / C);
-  int pf_chunk = (int)(start - (long long)pf_group * C);
+  const uint32_t ring = smem_u32(smem) + warp * (STAGES * STAGE_UNITS * 1024);
+  const uint32_t bar0 = smem_u32(&bars[warp * STAGES]);
+  const int n_stages = (n_units + STAGE_UNITS - 1) / STAGE_UNITS;
 
-  uint4 ra[DEPTH], rb[DEPTH];
-  auto issue = [&](int slot) {
-    int r0 = pf_group * 16 + g;
-    int r1 = r0 + 8;
-    r0 = r0 < N ? r0 : N - 1;   // ragged last group: reload a valid row, masked at store
-    r1 = r1 < N ? r1 : N - 1;
-    const bf16* p0 = W + (size_t)r0 * K + pf_chunk * 32 + t * 8;
-    const bf16* p1 = W + (size_t)r1 * K + pf_chunk * 32 + t * 8;
-    ra[slot] = ldg_stream(p0);
-    rb[slot] = ldg_stream(p1);
-    if (++pf_chunk == C) { pf_chunk = 0; ++pf_group; }
-  };
+  if (lane == 0) {
+    if (prefetch_bytes > 0 && n_units > 0)
+      l2_prefetch(src, (uint32_t)min(n_units * 1024, prefetch_bytes));
+    for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (int s = 0; s < STAGES && s < n_stages; ++s) {
+      const uint32_t bytes = (uint32_t)min(STAGE_UNITS, n_units - s * STAGE_UNITS) * 1024u;
+      mbar_expect_tx(bar0 + 8 * s, bytes);
+      bulk_g2s(ring + s * (STAGE_UNITS * 1024), src + (size_t)s * STAGE_UNITS * 1024, bytes, bar0 + 8 * s);
+    }
+  }
+  if (lane < 2) tags[warp * 2 + lane] = -1;
+  __syncwarp();
 
-#pragma unroll
-  for (int j = 0; j < DEPTH; ++j)
-    if (j < n_units) issue(j);
+  pdl_wait();   // X and the previous readers of P are complete from here on
 
-  pdl_wait();   // X (and the partial buffer's previous readers) are complete from here on
+  // Warm L1 with the activation rows (every CTA reads all of X, a few KB).
+  {
+    const int lines = (M * K * 2 + 127) >> 7;
+    if (lines <= 320)
+      for (int i = tid; i < lines; i += THREADS)
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const char*>(X) + ((size_t)i << 7)));
+  }
 
-  int group = (int)(start / C);
-  int chunk = (int)(start - (long long)group * C);
   float acc[NT][4];
 #pragma unroll
-  for (int i = 0; i < NT; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+  for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  int group = ws / C;
+  int chunk = ws - group * C;
+  int seg_first_chunk = chunk;          // first chunk of the current segment
+  int n_boundary = 0;
+  bool alive = true;
 
-  const long long slot_stride = (long long)M * N;
-
-  for (int base = 0; base < n_units; base += DEPTH) {
+  for (int st = 0; st < n_stages && alive; ++st) {
+    const int sidx = st % STAGES;
+    if (!mbar_wait(bar0 + 8 * sidx, (st / STAGES) & 1)) {
+      atomicExch(&g_gemm_status[0], 1);
+      alive = false;
+      break;
+    }
+    if (trace && st == 0) g_gemm_trace[blockIdx.x * 5 + 2] = gtime();
+    const int in_stage = min(STAGE_UNITS, n_units - st * STAGE_UNITS);
+    const uint32_t sbase = ring + sidx * (STAGE_UNITS * 1024) + lane * 16;
+    // activation fragments of the whole stage first, so that their latencies overlap
+    uint4 xs[STAGE_UNITS][NT];
+    {
+      int ch = chunk;
 #pragma unroll
-    for (int j = 0; j < DEPTH; ++j) {
-      const int i = base + j;
-      if (i < n_units) {
-        const uint4 a = ra[j], b = rb[j];
-        if (i + DEPTH < n_units) issue(j);
-        const int koff = chunk * 32 + t * 8;
+      for (int i = 0; i < STAGE_UNITS; ++i) {
+        const int koff = ch * 32 + t * 8;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const int m = nt * 8 + g;
-          uint4 x = make_uint4(0, 0, 0, 0);
-          if (m < M) x = ldg_cached(X + (size_t)m * K + koff);
+          xs[i][nt] = make_uint4(0, 0, 0, 0);
+          if (i < in_stage && m < M && !(dbg & 3)) xs[i][nt] = ldg_cached(X + (size_t)m * K + koff);
+        }
+        ch = ch + 1 == C ? 0 : ch + 1;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < STAGE_UNITS; ++i) {
+      if (i >= in_stage) break;
+      const uint4 a = lds128(sbase + i * 1024), b = lds128(sbase + i * 1024 + 512);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint4 x = xs[i][nt];
+        if (!(dbg & 1)) {
           mma16816(acc[nt], a.x, b.x, a.y, b.y, x.x, x.y);
           mma16816(acc[nt], a.z, b.z, a.w, b.w, x.z, x.w);
+        } else {
+          acc[nt][0] += __uint_as_float(a.x ^ b.w);
         }
-        const bool last_of_group = (chunk == C - 1);
-        if (last_of_group || i == n_units - 1) {
-          // flush this segment: slot = worker index relative to the group's first worker
-          const long long first = ((long long)group * C) / u;
-          float* out = P + (w - first) * slot_stride;
+      }
+      const bool group_end = (chunk == C - 1);
+      const bool run_end = (st * STAGE_UNITS + i == n_units - 1);
+      if (group_end || run_end) {
+        if (group_end && seg_first_chunk == 0) {
+          // the warp covered the whole group: it is the only contributor (slot 0)
           const int n0 = group * 16 + g;
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             const int m0 = nt * 8 + 2 * t;
             if (m0 < M) {
-              if (n0 < N) out[(size_t)m0 * N + n0] = acc[nt][0];
-              if (n0 + 8 < N) out[(size_t)m0 * N + n0 + 8] = acc[nt][2];
+              if (n0 < N) P[(size_t)m0 * N + n0] = acc[nt][0];
+              if (n0 + 8 < N) P[(size_t)m0 * N + n0 + 8] = acc[nt][2];
             }
             if (m0 + 1 < M) {
-              if (n0 < N) out[(size_t)(m0 + 1) * N + n0] = acc[nt][1];
-              if (n0 + 8 < N) out[(size_t)(m0 + 1) * N + n0 + 8] = acc[nt][3];
+              if (n0 < N) P[(size_t)(m0 + 1) * N + n0] = acc[nt][1];
+              if (n0 + 8 < N) P[(size_t)(m0 + 1) * N + n0 + 8] = acc[nt][3];
             }
-            acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
           }
+        } else {
+          // ragged end of the run: park it in shared memory for the CTA reduction
+          float* mine = red + ((size_t)warp * 2 + n_boundary) * (NT * 128);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+            *reinterpret_cast<float4*>(mine + nt * 128 + lane * 4) =
+                make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+          if (lane == 0) tags[warp * 2 + n_boundary] = group;
+          ++n_boundary;
         }
-        if (last_of_group) { chunk = 0; ++group; } else { ++chunk; }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        seg_first_chunk = 0;
       }
+      if (group_end) { chunk = 0; ++group; } else { ++chunk; }
+    }
+    // refill the stage just consumed
+    __syncwarp();
+    const int nxt = st + STAGES;
+    if (lane == 0 && nxt < n_stages) {
+      const uint32_t bytes = (uint32_t)min(STAGE_UNITS, n_units - nxt * STAGE_UNITS) * 1024u;
+      mbar_expect_tx(bar0 + 8 * sidx, bytes);
+      bulk_g2s(ring + sidx * (STAGE_UNITS * 1024), src + (size_t)nxt * STAGE_UNITS * 1024, bytes,
+               bar0 + 8 * sidx);
     }
   }
+
+  if (trace) g_gemm_trace[blockIdx.x * 5 + 3] = gtime();
+  // ---- add the ragged ends across the CTA: one partial per (CTA, group) ----
+  __syncthreads();
+  const long long slot_stride = (long long)M * N;
+  int tg[WARPS * 2];
+#pragma unroll
+  for (int s = 0; s < WARPS * 2; s += 4) {
+    const int4 v = *reinterpret_cast<const int4*>(tags + s);
+    tg[s] = v.x; tg[s + 1] = v.y; tg[s + 2] = v.z; tg[s + 3] = v.w;
+  }
+#pragma unroll
+  for (int s = 0; s < WARPS * 2; ++s) {
+    const int gg = tg[s];
+    bool fresh = gg >= 0;
+#pragma unroll
+    for (int s2 = 0; s2 < s; ++s2) fresh = fresh && (tg[s2] != gg);
+    if (!fresh) continue;
+    const int first = (int)(((long long)gg * C) / U);
+    float* out = P + (long long)(blockIdx.x - first) * slot_stride;
+    for (int r = tid; r < NT * 128; r += THREADS) {
+      float sum = 0.f;
+#pragma unroll
+      for (int s2 = s; s2 < WARPS * 2; ++s2)
+        if (tg[s2] == gg) sum += red[(size_t)s2 * (NT * 128) + r];
+      const int nt = r >> 7, ln = (r & 127) >> 2, e = r & 3;
+      const int n = gg * 16 + (ln >> 2) + 8 * (e >> 1);
+      const int m = nt * 8 + 2 * (ln & 3) + (e & 1);
+      if (n < N && m < M) out[(size_t)m * N + n] = sum;
+    }
+  }
+  if (trace) g_gemm_trace[blockIdx.x * 5 + 4] = gtime();
 }
 
 // Sums the slots of each element into one fp32 value (tensor-parallel path).
@@ -154,67 +328,133 @@ __global__ void k_reduce_partials(const float* __restrict__ P, float* __restrict
   out[i] = plan_sum(P, pv, i, n);
 }
 
+// Row-major [N][K] <-> tiled units. One thread per 16-byte piece of the tiled side.
+__global__ void k_pack_weight(const uint4* __restrict__ src, uint4* __restrict__ dst, int N, int K,
+                              int C, long long pieces, int to_tiled) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= pieces) return;
+  const long long unit = i >> 6;
+  const int piece = (int)(i & 63);
+  const int half = piece >> 5, lane = piece & 31;
+  const int group = (int)(unit / C), chunk = (int)(unit - (long long)group * C);
+  const int row = group * 16 + half * 8 + (lane >> 2);
+  const long long rm = ((long long)row * K + chunk * 32 + (lane & 3) * 8) >> 3;   // in 16-byte pieces
+  if (to_tiled) {
+    dst[i] = row < N ? src[rm] : make_uint4(0, 0, 0, 0);
+  } else if (row < N) {
+    dst[rm] = src[i];
+  }
+}
+
+template <int NT>
+constexpr int gemm_smem() {
+  return RING_BYTES + WARPS * 2 * NT * 128 * 4 + WARPS * 2 * 4 + WARPS * STAGES * 8;
+}
+
+template <int NT>
+cudaError_t launch_gemm(const q_gemm_plan_t& p, const bf16* X, const unsigned char* W, float* P,
+                        cudaStream_t s) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         gemm_smem<NT>());
+    if (e != cudaSuccess) return e;
+    attr_done = true;
+  }
+  return q_launch(k_gemm_streamk<NT>, dim3(p.grid), dim3(p.block), (size_t)gemm_smem<NT>(), s, X, W, P,
+                  p.M, p.N, p.K, p.chunks_per_group, p.groups * p.chunks_per_group,
+                  p.units_per_worker, g_gemm_prefetch_kb * 1024 / WARPS, g_gemm_debug_flags);
+}
+
 }  // namespace
+
+extern "C" int q_debug_gemm_trace(unsigned long long* out, int n_ctas) {
+  Q_CHECK_ARG(out && n_ctas >= 1 && n_ctas <= 256, "q_debug_gemm_trace: bad argument");
+  Q_CHECK_CUDA(cudaDeviceSynchronize());
+  Q_CHECK_CUDA(cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(unsigned long long) * 5 * n_ctas));
+  return Q_OK;
+}
+
+int q_gemm_status_read(int32_t out[4]) {
+  return cudaMemcpyFromSymbol(out, g_gemm_status, sizeof(int) * 4) == cudaSuccess ? 0 : -1;
+}
 
 extern "C" int q_gemm_plan(int M, int N, int K, q_gemm_plan_t* plan) {
   Q_CHECK_ARG(plan != nullptr, "q_gemm_plan: null plan");
   Q_CHECK_ARG(M >= 1 && M <= Q_MAX_ROWS, "q_gemm_plan: rows %d outside 1..%d", M, Q_MAX_ROWS);
   Q_CHECK_ARG(N >= 1 && K >= 32 && K % 32 == 0,
               "q_gemm_plan: need N >= 1 and K a positive multiple of 32 (N=%d K=%d)", N, K);
-  int sms = q_sm_count();
-  if (sms <= 0) return Q_ERR_CUDA;
   const int C = K / 32;
   const int groups = (N + 15) / 16;
+  Q_CHECK_ARG((long long)groups * C < (1ll << 30), "q_gemm_plan: weight too large");
+  int sms = q_sm_count();
+  if (sms <= 0) return Q_ERR_CUDA;
   const long long total = (long long)groups * C;
-  long long warps = (long long)sms * WARPS;
-  long long u = (total + warps - 1) / warps;
+  long long u = (total + sms - 1) / sms;
   if (u < 1) u = 1;
-  long long workers = (total + u - 1) / u;
-  // slots = max over groups of the number of workers that touch the group
-  int slots = 1;
-  for (long long gidx = 0; gidx < groups; ++gidx) {
-    long long first = (gidx * C) / u;
-    long long last = ((gidx + 1) * C - 1) / u;
-    int cnt = (int)(last - first + 1);
-    if (cnt > slots) slots = cnt;
-  }
+  const long long workers = (total + u - 1) / u;
+  // A group of C units is touched by at most ceil((C-1)/u)+1 consecutive CTAs;
+  // consumers may always read two slots, so never report fewer.
+  long long slots = (C - 1 + u - 1) / u + 1;
+  if (slots > workers) slots = workers;
+  if (slots < 2) slots = 2;
   plan->M = M; plan->N = N; plan->K = K;
   plan->chunks_per_group = C;
   plan->groups = groups;
   plan->units_per_worker = (int)u;
   plan->workers = (int)workers;
-  plan->slots = slots;
-  plan->grid = (int)((workers + WARPS - 1) / WARPS);
-  plan->block = WARPS * 32;
+  plan->slots = (int)slots;
+  plan->grid = (int)workers;
+  plan->block = THREADS;
   return Q_OK;
 }
 
-extern "C" int q_gemm_splitk(const void* d_x, const void* d_w, float* d_partials,
+extern "C" int64_t q_packed_weight_bytes(int N, int K) {
+  if (N < 1 || K < 32 || K % 32) return -1;
+  return (int64_t)((N + 15) / 16) * (K / 32) * 1024;
+}
+
+static int pack_common(const void* src, void* dst, int N, int K, int to_tiled, void* stream,
+                       const char* who) {
+  Q_CHECK_ARG(src && dst, "%s: null pointer", who);
+  Q_CHECK_ARG(N >= 1 && K >= 32 && K % 32 == 0, "%s: need N >= 1 and K a multiple of 32", who);
+  Q_CHECK_ARG(((uintptr_t)src & 15) == 0 && ((uintptr_t)dst & 15) == 0,
+              "%s: pointers must be 16-byte aligned", who);
+  const int C = K / 32;
+  const long long pieces = (long long)((N + 15) / 16) * C * 64;
+  const int block = 256;
+  const long long grid = (pieces + block - 1) / block;
+  Q_CHECK_ARG(grid < (1ll << 31), "%s: weight too large", who);
+  k_pack_weight<<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst, N, K,
+                                                                     C, pieces, to_tiled);
+  Q_CHECK_CUDA(cudaGetLastError());
+  return Q_OK;
+}
+
+extern "C" int q_pack_weight(const void* d_rowmajor, void* d_tiled, int N, int K, void* stream) {
+  return pack_common(d_rowmajor, d_tiled, N, K, 1, stream, "q_pack_weight");
+}
+
+extern "C" int q_unpack_weight(const void* d_tiled, void* d_rowmajor, int N, int K, void* stream) {
+  return pack_common(d_tiled, d_rowmajor, N, K, 0, stream, "q_unpack_weight");
+}
+
+extern "C" int q_gemm_splitk(const void* d_x, const void* d_w_tiled, float* d_partials,
                              int M, int N, int K, void* stream) {
-  Q_CHECK_ARG(d_x && d_w && d_partials, "q_gemm_splitk: null pointer");
-  Q_CHECK_ARG(((uintptr_t)d_x & 15) == 0 && ((uintptr_t)d_w & 15) == 0,
+  Q_CHECK_ARG(d_x && d_w_tiled && d_partials, "q_gemm_splitk: null pointer");
+  Q_CHECK_ARG(((uintptr_t)d_x & 15) == 0 && ((uintptr_t)d_w_tiled & 15) == 0,
               "q_gemm_splitk: x and w must be 16-byte aligned");
   q_gemm_plan_t p;
   int rc = q_gemm_plan(M, N, K, &p);
   if (rc) return rc;
-  const long long total = (long long)p.groups * p.chunks_per_group;
   cudaStream_t s = (cudaStream_t)stream;
   const bf16* X = (const bf16*)d_x;
-  const bf16* W = (const bf16*)d_w;
+  const unsigned char* W = (const unsigned char*)d_w_tiled;
   cudaError_t e;
-  dim3 grid(p.grid), block(p.block);
-  if (M <= 8)
-    e = q_launch(k_gemm_streamk<1>, grid, block, 0, s, X, W, d_partials, M, N, K,
-                 p.chunks_per_group, total, p.units_per_worker);
-  else if (M <= 16)
-    e = q_launch(k_gemm_streamk<2>, grid, block, 0, s, X, W, d_partials, M, N, K,
-                 p.chunks_per_group, total, p.units_per_worker);
-  else if (M <= 32)
-    e = q_launch(k_gemm_streamk<4>, grid, block, 0, s, X, W, d_partials, M, N, K,
-                 p.chunks_per_group, total, p.units_per_worker);
-  else
-    e = q_launch(k_gemm_streamk<8>, grid, block, 0, s, X, W, d_partials, M, N, K,
-                 p.chunks_per_group, total, p.units_per_worker);
+  if (M <= 8) e = launch_gemm<1>(p, X, W, d_partials, s);
+  else if (M <= 16) e = launch_gemm<2>(p, X, W, d_partials, s);
+  else if (M <= 32) e = launch_gemm<4>(p, X, W, d_partials, s);
+  else e = launch_gemm<8>(p, X, W, d_partials, s);
   Q_CHECK_CUDA(e);
   return Q_OK;
 }

@@ -50,7 +50,7 @@ class DecodeState:
         self.capacity = prompt_length + max_new_tokens
         if self.capacity > cfg.max_position:
             raise ValueError("prompt + new tokens exceed max_position_embeddings")
-        dev = weights.embed.device
+        dev = weights.device
         self.device = dev
         nq, nkv, inter = weights.local_q_heads, weights.local_kv_heads, weights.local_inter
         self.pages_per_seq = (self.capacity + PAGE_TOKENS - 1) // PAGE_TOKENS
@@ -160,10 +160,19 @@ class DecodeState:
             half = torch.cat((-t[..., HEAD_DIM // 2:], t[..., :HEAD_DIM // 2]), -1)
             return t * cos + half * sin
 
-        x = w.embed[input_ids]                                        # [B, T, H]
+        # Prefill runs on library GEMMs over row-major weights: each tiled matrix is
+        # expanded into a scratch buffer just before use (one layer at a time).
+        embed_rows = w.embed.rows()
+        x = embed_rows[input_ids]                                     # [B, T, H]
+        if w.lm_head.data_ptr() == w.embed.data_ptr() and w.lm_head.shape == w.embed.shape:
+            lm_rows = embed_rows
+        else:
+            del embed_rows
+            lm_rows = None
         for i, lt in enumerate(w.layers):
+            wqkv, wo, wgu, wdown = lt.wqkv.rows(), lt.wo.rows(), lt.wgu.rows(), lt.wdown.rows()
             h = _rms(x, lt.ln_in, eps)
-            qkv = F.linear(h, lt.wqkv)
+            qkv = F.linear(h, wqkv)
             q, k, v = qkv.split((nq * HEAD_DIM, nkv * HEAD_DIM, nkv * HEAD_DIM), -1)
             q = rotate(_rms(q.reshape(B, T, nq, HEAD_DIM), lt.q_gain, eps)).transpose(1, 2)
             k = rotate(_rms(k.reshape(B, T, nkv, HEAD_DIM), lt.k_gain, eps)).transpose(1, 2)
@@ -175,12 +184,16 @@ class DecodeState:
                                    C.c_void_p(torch.cuda.current_stream().cuda_stream)))
             att = F.scaled_dot_product_attention(q, kc, vc, is_causal=True, enable_gqa=True)
             att = att.transpose(1, 2).reshape(B, T, nq * HEAD_DIM)
-            x = x + self._linear_rowpar(att, lt.wo)
+            x = x + self._linear_rowpar(att, wo)
             h = _rms(x, lt.ln_post, eps)
-            gate, up = F.linear(h, lt.wgu).chunk(2, -1)
-            x = x + self._linear_rowpar(F.silu(gate) * up, lt.wdown)
+            gate, up = F.linear(h, wgu).chunk(2, -1)
+            x = x + self._linear_rowpar(F.silu(gate) * up, wdown)
+            del wqkv, wo, wgu, wdown
         last = _rms(x[:, -1], w.ln_final, eps)
-        logits = F.linear(last, w.lm_head)                            # [B, V_local]
+        if lm_rows is None:
+            lm_rows = w.lm_head.rows()
+        logits = F.linear(last, lm_rows)                              # [B, V_local]
+        del lm_rows
         if self.tp == 1:
             self.tokens.copy_(logits.argmax(-1))
         else:

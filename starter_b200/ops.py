@@ -17,6 +17,13 @@ import torch
 
 from . import _lib
 from ._lib import HEAD_DIM, MAX_ROWS, PAGE_TOKENS, GemmPlan, KVLayout, check, lib
+from .weights import TiledWeight
+
+
+def pack_weight(weight: torch.Tensor) -> TiledWeight:
+    """Tiles a row-major BF16 [N, K] Linear weight once (load time), like the
+    reference packs gate|up and q|k|v at load (engine/mlp.py:12-15)."""
+    return TiledWeight.pack(weight)
 
 
 def _stream() -> C.c_void_p:
@@ -51,18 +58,25 @@ class Partials:
         return out
 
 
-def supports(x: torch.Tensor, weight: torch.Tensor) -> bool:
+def supports(x: torch.Tensor, weight) -> bool:
     """Static shape rule, like engine/kernels/skinny_gemm.py:75-83."""
-    return (x.ndim == 2 and weight.ndim == 2 and x.is_cuda and weight.is_cuda
-            and x.dtype == weight.dtype == torch.bfloat16 and 1 <= x.shape[0] <= MAX_ROWS
+    return (x.ndim == 2 and len(weight.shape) == 2 and x.is_cuda
+            and x.dtype == torch.bfloat16 and 1 <= x.shape[0] <= MAX_ROWS
             and x.shape[1] == weight.shape[1] and x.shape[1] % 32 == 0)
 
 
-def linear_partials(x: torch.Tensor, weight: torch.Tensor) -> Partials:
-    """x @ weight.T as FP32 split-K partials (engine/kernels/skinny_gemm.py:100-109)."""
+def linear_partials(x: torch.Tensor, weight) -> Partials:
+    """x @ weight.T as FP32 split-K partials (engine/kernels/skinny_gemm.py:100-109).
+    `weight` is a TiledWeight (see pack_weight) or a row-major BF16 [N, K] tensor,
+    which is tiled on the fly (load-time work done per call: for tests only)."""
     M, K = _bf16_2d(x, "x")
-    N, K2 = _bf16_2d(weight, "weight")
-    if K != K2 or x.device != weight.device:
+    if not isinstance(weight, TiledWeight):
+        _bf16_2d(weight, "weight")
+        if weight.shape[1] % 32:
+            raise ValueError("K must be a multiple of 32")
+        weight = TiledWeight.pack(weight)
+    N, K2 = weight.shape
+    if K != K2 or x.device != weight.data.device:
         raise ValueError("x and weight disagree on K or device")
     if not 1 <= M <= MAX_ROWS:
         raise ValueError(f"at most {MAX_ROWS} rows are supported, got {M}")
@@ -125,10 +139,10 @@ def silu_mul(gate_up, rows: int | None = None) -> torch.Tensor:
     return out
 
 
-def linear_silu_mul(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
+def linear_silu_mul(x: torch.Tensor, gate_up_weight) -> torch.Tensor:
     """BF16 [M, I] = silu(x @ gate.T) * (x @ up.T) for a packed [2I, K] weight
     (engine/kernels/skinny_gemm.py:112-121)."""
-    if gate_up_weight.ndim != 2 or gate_up_weight.shape[0] % 2:
+    if len(gate_up_weight.shape) != 2 or gate_up_weight.shape[0] % 2:
         raise ValueError("packed gate/up weight must have an even number of rows")
     return silu_mul(linear_partials(x, gate_up_weight))
 
@@ -265,7 +279,7 @@ class SmallQueryAttention:
         return out
 
 
-def lm_head_argmax(normed: torch.Tensor, weight: torch.Tensor, return_logits: bool = True):
+def lm_head_argmax(normed: torch.Tensor, weight, return_logits: bool = True):
     """BF16 logits and greedy tokens (engine/decode_step.py:60 + engine/decode.py:106):
     lowest index wins exact ties. Returns (logits or None, tokens int64 [rows])."""
     part = linear_partials(normed, weight)

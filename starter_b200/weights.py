@@ -13,6 +13,7 @@ Tensor-parallel shard of rank r of N (Megatron style):
 """
 from __future__ import annotations
 
+import ctypes as C
 import json
 from dataclasses import dataclass, field
 from pathlib import Path
@@ -20,6 +21,57 @@ from pathlib import Path
 import torch
 
 HEAD_DIM = 128
+
+
+class TiledWeight:
+    """A bf16 [N, K] Linear weight held in the GEMM's tiled unit layout (see
+    q_pack_weight in include/qdecode.h). `data` is a flat uint8 device tensor;
+    `rows()` gives the row-major matrix back (used by prefill, which runs on
+    library GEMMs outside the per-step path)."""
+
+    def __init__(self, data: torch.Tensor, N: int, K: int):
+        self.data, self.N, self.K = data, N, K
+
+    @property
+    def shape(self):
+        return (self.N, self.K)
+
+    def numel(self) -> int:
+        return self.N * self.K
+
+    def data_ptr(self) -> int:
+        return self.data.data_ptr()
+
+    @staticmethod
+    def pack(weight: torch.Tensor) -> "TiledWeight":
+        from ._lib import check, lib
+        if (weight.ndim != 2 or weight.dtype != torch.bfloat16 or not weight.is_cuda
+                or not weight.is_contiguous() or weight.shape[1] % 32):
+            raise ValueError("expected a contiguous BF16 CUDA [N, K] weight with K a multiple of 32")
+        N, K = weight.shape
+        out = torch.empty(lib.q_packed_weight_bytes(N, K), dtype=torch.uint8, device=weight.device)
+        with torch.cuda.device(weight.device):
+            check(lib.q_pack_weight(C.c_void_p(weight.data_ptr()), C.c_void_p(out.data_ptr()), N, K,
+                                    C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return TiledWeight(out, N, K)
+
+    def rows(self, out: torch.Tensor | None = None) -> torch.Tensor:
+        from ._lib import check, lib
+        if out is None:
+            out = torch.empty((self.N, self.K), dtype=torch.bfloat16, device=self.data.device)
+        with torch.cuda.device(self.data.device):
+            check(lib.q_unpack_weight(C.c_void_p(self.data.data_ptr()), C.c_void_p(out.data_ptr()),
+                                      self.N, self.K,
+                                      C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return out
+
+    def row_slice(self, lo: int, hi: int) -> "TiledWeight":
+        """Rows [lo, hi) as a view (no copy); lo must be a multiple of 16."""
+        if lo % 16 or not 0 <= lo < hi <= self.N:
+            raise ValueError("a tiled row slice must start on a 16-row boundary")
+        unit_bytes = (self.K // 32) * 1024
+        groups = (hi - lo + 15) // 16
+        return TiledWeight(self.data[(lo // 16) * unit_bytes:(lo // 16 + groups) * unit_bytes], hi - lo, self.K)
 
 
 @dataclass
@@ -68,10 +120,10 @@ class ModelConfig:
 
 @dataclass
 class LayerTensors:
-    wqkv: torch.Tensor
-    wo: torch.Tensor
-    wgu: torch.Tensor
-    wdown: torch.Tensor
+    wqkv: "torch.Tensor | TiledWeight"
+    wo: "torch.Tensor | TiledWeight"
+    wgu: "torch.Tensor | TiledWeight"
+    wdown: "torch.Tensor | TiledWeight"
     ln_in: torch.Tensor
     ln_post: torch.Tensor
     q_gain: torch.Tensor
@@ -83,9 +135,10 @@ class PackedWeights:
     cfg: ModelConfig
     tp_rank: int
     tp_size: int
-    embed: torch.Tensor            # [V, H] full table (replicated)
-    lm_head: torch.Tensor          # [V/N, H] local vocabulary rows (view of embed when tied, N=1)
+    embed: "torch.Tensor | TiledWeight"     # [V, H] full table (replicated)
+    lm_head: "torch.Tensor | TiledWeight"   # [V/N, H] local vocabulary rows (a view of embed when tied)
     ln_final: torch.Tensor
+    device: torch.device = None
     layers: list[LayerTensors] = field(default_factory=list)
 
     @property
@@ -103,6 +156,26 @@ class PackedWeights:
     @property
     def local_vocab(self) -> int:
         return self.lm_head.shape[0]
+
+    def tile(self) -> "PackedWeights":
+        """Converts every matrix to the tiled GEMM layout in place (device only)."""
+        tied = self.lm_head.data_ptr() == (self.embed.data_ptr() + self.vocab_offset * self.cfg.hidden * 2) \
+            if isinstance(self.embed, torch.Tensor) else False
+        lo = self.vocab_offset
+        rows = self.lm_head.shape[0]
+        if isinstance(self.embed, torch.Tensor):
+            self.embed = TiledWeight.pack(self.embed)
+        if isinstance(self.lm_head, torch.Tensor):
+            if tied and lo % 16 == 0:
+                self.lm_head = self.embed.row_slice(lo, lo + rows)
+            else:
+                self.lm_head = TiledWeight.pack(self.lm_head.contiguous())
+        for lt in self.layers:
+            for name in ("wqkv", "wo", "wgu", "wdown"):
+                t = getattr(lt, name)
+                if isinstance(t, torch.Tensor):
+                    setattr(lt, name, TiledWeight.pack(t))
+        return self
 
     @property
     def vocab_offset(self) -> int:
@@ -159,9 +232,16 @@ def pack(cfg: ModelConfig, get, has, device, tp_rank: int = 0, tp_size: int = 1)
     else:
         lm_head = embed[lo:hi]          # tied: a row view of the table, no second copy
     out = PackedWeights(cfg, tp_rank, tp_size, embed, lm_head,
-                        get("model.norm.weight").to(device=device, dtype=torch.bfloat16).contiguous())
+                        get("model.norm.weight").to(device=device, dtype=torch.bfloat16).contiguous(),
+                        device=torch.device(device))
     for i in range(cfg.n_layers):
         out.layers.append(pack_layer(cfg, get, i, tp_rank, tp_size, device))
+        if out.device.type == "cuda":
+            lt = out.layers[-1]          # tile as we go so that only one layer is held twice
+            for name in ("wqkv", "wo", "wgu", "wdown"):
+                setattr(lt, name, TiledWeight.pack(getattr(lt, name)))
+    if out.device.type == "cuda":
+        out.tile()
     return out
 
 

@@ -62,6 +62,26 @@ def test_split_k_gemm_ragged_and_tiny(ops, M, N, K):
     torch.testing.assert_close(sum_slots(part), O.linear_fp32(x, w), rtol=2e-3, atol=2e-3)
 
 
+@pytest.mark.parametrize("N,K", [(16, 32), (127, 128), (2560, 4096), (100, 9728)])
+def test_weight_tiling_round_trip(ops, N, K):
+    """pack -> unpack returns the matrix bit for bit; rows past N are zero in the
+    tiled form; a 16-row-aligned row slice of the tiled form is the tiling of the slice."""
+    w = randw(N, K, 3).cuda()
+    tiled = ops.pack_weight(w)
+    assert tiled.data.numel() == ((N + 15) // 16) * (K // 32) * 1024
+    assert torch.equal(tiled.rows(), w)
+    if N % 16:
+        pad = torch.zeros(((N + 15) // 16 * 16, K), dtype=torch.bfloat16, device="cuda")
+        pad[:N] = w
+        assert torch.equal(ops.pack_weight(pad).data, tiled.data)
+    if N >= 48:
+        assert torch.equal(tiled.row_slice(16, 48).data, ops.pack_weight(w[16:48].contiguous()).data)
+    x = randx(3, K, 4).cuda()
+    a = ops.linear_partials(x, tiled)
+    b = ops.linear_partials(x, w)
+    assert torch.equal(a.sum(), b.sum())
+
+
 def test_gemm_rejects_bad_operands(ops):
     x, w = randx(2, 64, 1).cuda(), randw(16, 64, 2).cuda()
     with pytest.raises(ValueError):
