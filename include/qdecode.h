@@ -47,7 +47,10 @@ int q_version(void);
 int q_set_pdl(int enabled);
 
 /* Tuning knobs (process-wide, host side only; no reference counterpart).
- *   "gemm_prefetch_kb": L2 prefetch window per GEMM CTA in KB (0 = off).
+ *   "gemm_prefetch_kb": L2 prefetch window per GEMM CTA in KB (0 = off, default).
+ *   "fused_step": 1 = q_decode_step may use the single persistent kernel (default).
+ *   "trace_layer": layer stamped by the whole-step kernel (see q_debug_step_trace), -1 off.
+ *   "gemm_debug_flags": measurement aid, results are wrong when non-zero.
  * Unknown names return Q_ERR_ARG. */
 int q_set_option(const char* name, int value);
 
@@ -55,6 +58,13 @@ int q_set_option(const char* name, int value);
  * {SM id, start, first data, loop end, exit} (ns, %globaltimer); this copies the
  * records of the last launch to the host (5 values per CTA). */
 int q_debug_gemm_trace(unsigned long long* out, int n_ctas);
+
+/* Measurement aid: with option "trace_layer" = l, the whole-step kernel stamps the
+ * phase boundaries of layer l (%globaltimer ns) for CTA 0 (out[0..31]) and CTA 100
+ * (out[32..63]): 0 start, 1 QKV done, 2 barrier, 3 attention, 4 barrier, 5 X staged,
+ * 6 O-proj, 7 barrier, 8 add+norm, 9 gate|up, 10 barrier, 11 SwiGLU, 12 barrier,
+ * 13 X staged, 14 down, 15 barrier, 16 add+norm. */
+int q_debug_step_trace(unsigned long long* out);
 
 /* ---- split-K weight-streaming GEMM --------------------------------------
  * Replaces engine/kernels/skinny_gemm.py:100-109 (linear_partials) and the
@@ -249,6 +259,7 @@ typedef struct q_state_t {
   float* arg_val;           /* [rows] */
   int32_t* arg_idx;         /* [rows] */
   void* arg_scratch;        /* q_argmax_scratch_bytes() bytes, zeroed once */
+  void* fused_scratch;      /* q_fused_scratch_bytes() bytes or NULL: enables the single-kernel step */
 } q_state_t;
 
 typedef struct q_engine q_engine;
@@ -257,9 +268,15 @@ int q_create(const q_config_t* cfg, q_engine** out);
 int q_bind_layer(q_engine* e, int layer, const q_layer_weights_t* w);
 int q_bind_state(q_engine* e, const q_state_t* s);
 int64_t q_engine_partial_floats(const q_engine* e, int rows);
+/* Scratch for the persistent whole-step kernel (layer table, grid barrier, tickets).
+ * q_bind_state fills it (host-to-device copy, synchronous) when all layers are bound. */
+int64_t q_fused_scratch_bytes(const q_engine* e, int rows);
 void q_destroy(q_engine* e);
 
-/* One full step for T=1 on a single GPU: embed .. argmax, tokens and pos updated. */
+/* One full step for T=1 on a single GPU: embed .. argmax, tokens and pos updated.
+ * With at most 8 rows, state.fused_scratch set and enough shared memory, the step
+ * runs as ONE persistent cooperative kernel (option "fused_step", default 1);
+ * otherwise as ~360 dependent-launch kernels. Both produce the same tokens. */
 int q_decode_step(q_engine* e, void* stream);
 
 /* The same step in pieces, for tensor parallelism: the caller all-reduces
@@ -277,7 +294,8 @@ int q_step_head(q_engine* e, void* stream);
 
 /* Reads the library's device status word of the current device (synchronises
  * the device; not capturable). out[0] != 0 means a bounded wait inside a kernel
- * ran out: out[0] attention (1 producer, 2 consumer), out[1] GEMM ring (1). */
+ * ran out: out[0] attention (1 producer, 2 consumer), out[1] GEMM ring (1),
+ * out[2] whole-step kernel (1 grid barrier, 2 GEMM ring, 3/4 attention ring). */
 int q_device_status(int32_t out[4]);
 
 #ifdef __cplusplus

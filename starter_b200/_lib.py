@@ -55,6 +55,7 @@ class State(C.Structure):
         ("act", C.c_void_p), ("partials", C.c_void_p), ("reduced", C.c_void_p),
         ("attn_o", C.c_void_p), ("attn_ml", C.c_void_p), ("logits", C.c_void_p),
         ("arg_val", C.c_void_p), ("arg_idx", C.c_void_p), ("arg_scratch", C.c_void_p),
+        ("fused_scratch", C.c_void_p),
     ]
 
 
@@ -71,6 +72,7 @@ SIGNATURES = {
     "q_set_pdl": (_I, [_I]),
     "q_set_option": (_I, [C.c_char_p, _I]),
     "q_debug_gemm_trace": (_I, [C.POINTER(C.c_uint64), _I]),
+    "q_debug_step_trace": (_I, [C.POINTER(C.c_uint64)]),
     "q_gemm_plan": (_I, [_I, _I, _I, _PLAN]),
     "q_packed_weight_bytes": (C.c_int64, [_I, _I]),
     "q_pack_weight": (_I, [_P, _P, _I, _I, _P]),
@@ -92,6 +94,7 @@ SIGNATURES = {
     "q_bind_layer": (_I, [_P, _I, C.POINTER(LayerWeights)]),
     "q_bind_state": (_I, [_P, C.POINTER(State)]),
     "q_engine_partial_floats": (C.c_int64, [_P, _I]),
+    "q_fused_scratch_bytes": (C.c_int64, [_P, _I]),
     "q_destroy": (None, [_P]),
     "q_decode_step": (_I, [_P, _P]),
     "q_step_begin": (_I, [_P, _P]),

@@ -8,6 +8,7 @@
 #include <new>
 #include <vector>
 #include "common.cuh"
+#include "mega_step.h"
 
 static thread_local char g_err[512] = "";
 static bool g_pdl = true;
@@ -38,14 +39,24 @@ int q_sm_count() {
   return n;
 }
 
-int g_gemm_prefetch_kb = 640;
+int g_gemm_prefetch_kb = 0;
 int g_gemm_debug_flags = 0;
+static int g_fused_step = 1;     // use the persistent whole-step kernel when it applies
+static int g_trace_layer = -1;   // measurement aid: layer whose phases the whole-step kernel stamps
 
 extern "C" int q_set_option(const char* name, int value) {
   Q_CHECK_ARG(name != nullptr, "q_set_option: null name");
   if (strcmp(name, "gemm_prefetch_kb") == 0) {
     Q_CHECK_ARG(value >= 0 && value <= 8192, "q_set_option: gemm_prefetch_kb outside 0..8192");
     g_gemm_prefetch_kb = value;
+    return Q_OK;
+  }
+  if (strcmp(name, "trace_layer") == 0) {
+    g_trace_layer = value;
+    return Q_OK;
+  }
+  if (strcmp(name, "fused_step") == 0) {
+    g_fused_step = value != 0;
     return Q_OK;
   }
   if (strcmp(name, "gemm_debug_flags") == 0) {
@@ -62,14 +73,22 @@ int q_gemm_status_read(int32_t out[4]);
 extern "C" int q_device_status(int32_t out[4]) {
   Q_CHECK_ARG(out != nullptr, "q_device_status: null pointer");
   Q_CHECK_CUDA(cudaDeviceSynchronize());
-  int32_t a[4] = {0, 0, 0, 0}, g[4] = {0, 0, 0, 0};
-  if (q_attn_status_read(a) || q_gemm_status_read(g)) {
+  int32_t a[4] = {0, 0, 0, 0}, g[4] = {0, 0, 0, 0}, m[4] = {0, 0, 0, 0};
+  if (q_attn_status_read(a) || q_gemm_status_read(g) || q_mega_status_read(m)) {
     q_set_error("q_device_status: could not read the status words");
     return Q_ERR_CUDA;
   }
   out[0] = a[0];   // attention: 1 producer wait ran out, 2 consumer wait ran out
   out[1] = g[0];   // GEMM: 1 ring wait ran out
-  out[2] = out[3] = 0;
+  out[2] = m[0];   // whole-step kernel: 1 grid barrier, 2 GEMM ring, 3/4 attention ring
+  out[3] = 0;
+  return Q_OK;
+}
+
+extern "C" int q_debug_step_trace(unsigned long long* out) {
+  Q_CHECK_ARG(out != nullptr, "q_debug_step_trace: null pointer");
+  Q_CHECK_CUDA(cudaDeviceSynchronize());
+  if (q_mega_trace_read(out)) { q_set_error("q_debug_step_trace: read failed"); return Q_ERR_CUDA; }
   return Q_OK;
 }
 
@@ -88,6 +107,9 @@ struct q_engine {
   bool has_state;
   int rows;
   q_gemm_plan_t p_qkv, p_o, p_gu, p_down, p_head;
+  bool mega_ok;
+  int mega_grid;
+  mega_params_t mega;
 };
 
 static int make_plans(q_engine* e, int rows) {
@@ -124,6 +146,8 @@ extern "C" int q_create(const q_config_t* cfg, q_engine** out) {
   memset(&e->st, 0, sizeof(e->st));
   e->has_state = false;
   e->rows = 0;
+  e->mega_ok = false;
+  e->mega_grid = 0;
   *out = e;
   return Q_OK;
 }
@@ -150,7 +174,106 @@ extern "C" int64_t q_engine_partial_floats(const q_engine* e, int rows) {
   if (plan_floats(tmp.p_gu) > m) m = plan_floats(tmp.p_gu);
   if (plan_floats(tmp.p_down) > m) m = plan_floats(tmp.p_down);
   if (plan_floats(tmp.p_head) > m) m = plan_floats(tmp.p_head);
+  // the fused step keeps the O-proj/down partials in a second buffer behind the first
+  long long second = plan_floats(tmp.p_o) > plan_floats(tmp.p_down) ? plan_floats(tmp.p_o) : plan_floats(tmp.p_down);
+  return ((m + 63) / 64) * 64 + second;
+}
+
+static long long first_partial_floats(const q_engine* e) {
+  long long m = plan_floats(e->p_qkv);
+  if (plan_floats(e->p_o) > m) m = plan_floats(e->p_o);
+  if (plan_floats(e->p_gu) > m) m = plan_floats(e->p_gu);
+  if (plan_floats(e->p_down) > m) m = plan_floats(e->p_down);
+  if (plan_floats(e->p_head) > m) m = plan_floats(e->p_head);
+  return ((m + 63) / 64) * 64;
+}
+
+extern "C" int64_t q_fused_scratch_bytes(const q_engine* e, int rows) {
+  if (!e || rows < 1) return -1;
+  const int sms = q_sm_count();
+  return 1024 + (int64_t)e->cfg.n_layers * (int64_t)sizeof(mega_layer_t) + 64 +
+         (int64_t)rows * sms * 8 + 64;
+}
+
+static mega_plan_t lite(const q_gemm_plan_t& p) {
+  mega_plan_t m;
+  m.N = p.N; m.K = p.K; m.C = p.chunks_per_group; m.total = p.groups * p.chunks_per_group;
+  m.U = p.units_per_worker;
   return m;
+}
+
+// Decides whether the persistent whole-step kernel applies and fills its parameters.
+static int setup_fused(q_engine* e) {
+  e->mega_ok = false;
+  const q_config_t& c = e->cfg;
+  const q_state_t& s = e->st;
+  if (c.tp_size != 1 || !s.fused_scratch || e->rows > 8) return Q_OK;
+  const int sms = q_sm_count();
+  const int G = c.n_q_heads / c.n_kv_heads;
+  if (G > 16 || e->rows * c.n_kv_heads > sms) return Q_OK;
+  int xs_cols = c.hidden;
+  if (c.n_q_heads * 128 > xs_cols) xs_cols = c.n_q_heads * 128;
+  if (c.inter > xs_cols) xs_cols = c.inter;
+  int dev = 0, max_smem = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) {
+    cudaGetLastError();
+    return Q_OK;
+  }
+  if (q_mega_smem_bytes(e->rows, c.hidden, xs_cols) > (size_t)max_smem) return Q_OK;
+  int coop = 0;
+  cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+  if (!coop) return Q_OK;
+  // every GEMM must fit the grid (one CTA per SM) and all plans share the grid size
+  int grid = e->p_qkv.grid;
+  const q_gemm_plan_t* plans[5] = {&e->p_qkv, &e->p_o, &e->p_gu, &e->p_down, &e->p_head};
+  for (int i = 0; i < 5; ++i) if (plans[i]->grid > grid) grid = plans[i]->grid;
+  if (grid < e->rows * c.n_kv_heads) grid = e->rows * c.n_kv_heads;   // one CTA per (sequence, kv head) at least
+  if (grid > sms) return Q_OK;
+
+  char* base = (char*)s.fused_scratch;
+  mega_params_t& m = e->mega;
+  memset(&m, 0, sizeof(m));
+  m.sync = (unsigned*)base;
+  mega_layer_t* table = (mega_layer_t*)(base + 1024);
+  char* after = base + 1024 + (size_t)c.n_layers * sizeof(mega_layer_t);
+  after = (char*)(((uintptr_t)after + 63) & ~(uintptr_t)63);
+  m.blk_val = (float*)after;
+  m.blk_idx = (int*)(after + (size_t)e->rows * sms * 4);
+  std::vector<mega_layer_t> host(c.n_layers);
+  for (int i = 0; i < c.n_layers; ++i) {
+    const q_layer_weights_t& w = e->layers[i];
+    if (!e->bound[i]) return Q_OK;       // bind layers first; q_bind_state can be called again
+    host[i].wqkv = (const unsigned char*)w.wqkv; host[i].wo = (const unsigned char*)w.wo;
+    host[i].wgu = (const unsigned char*)w.wgu; host[i].wdown = (const unsigned char*)w.wdown;
+    host[i].ln_in = (const bf16*)w.ln_in; host[i].ln_post = (const bf16*)w.ln_post;
+    host[i].q_gain = (const bf16*)w.q_gain; host[i].k_gain = (const bf16*)w.k_gain;
+    host[i].kpool = (char*)w.kpool; host[i].vpool = (char*)w.vpool;
+  }
+  Q_CHECK_CUDA(cudaMemcpy(table, host.data(), host.size() * sizeof(mega_layer_t), cudaMemcpyHostToDevice));
+  Q_CHECK_CUDA(cudaMemset(m.sync, 0, 1024));
+  m.layers = table;
+  m.M = e->rows; m.H = c.hidden; m.I = c.inter; m.L = c.n_layers; m.nq = c.n_q_heads; m.nkv = c.n_kv_heads;
+  m.V = c.vocab; m.full_vocab = c.full_vocab; m.pages_per_seq = s.pages_per_seq; m.xs_cols = xs_cols;
+  int S = s.attn_splits;
+  const int fit = grid / (e->rows * c.n_kv_heads);
+  if (S > fit) S = fit;
+  if (S < 1) S = 1;
+  m.attn_S = S;
+  m.trace_layer = -1;
+  m.eps = c.rms_eps;
+  m.scale_log2 = c.attn_scale * 1.4426950408889634f;
+  m.embed = (const unsigned char*)s.embed; m.lm_head = (const unsigned char*)s.lm_head;
+  m.ln_final = (const bf16*)s.ln_final; m.cos = (const bf16*)s.cos; m.sin = (const bf16*)s.sin;
+  m.tokens = s.tokens; m.pos = s.pos; m.block_table = s.block_table;
+  m.buf0 = s.partials; m.buf1 = s.partials + first_partial_floats(e);
+  m.attended = (bf16*)s.attended; m.act = (bf16*)s.act; m.attn_o = s.attn_o; m.attn_ml = s.attn_ml;
+  m.logits = (bf16*)s.logits; m.arg_val = s.arg_val; m.arg_idx = s.arg_idx;
+  m.qkv = lite(e->p_qkv); m.o = lite(e->p_o); m.gu = lite(e->p_gu); m.down = lite(e->p_down);
+  m.head = lite(e->p_head);
+  e->mega_grid = grid;
+  e->mega_ok = true;
+  return Q_OK;
 }
 
 extern "C" int q_bind_state(q_engine* e, const q_state_t* s) {
@@ -169,7 +292,7 @@ extern "C" int q_bind_state(q_engine* e, const q_state_t* s) {
   if (rc) return rc;
   e->st = *s;
   e->has_state = true;
-  return Q_OK;
+  return setup_fused(e);
 }
 
 static int ready(q_engine* e, const char* who) {
@@ -276,6 +399,11 @@ extern "C" int q_decode_step(q_engine* e, void* stream) {
   TRY(ready(e, "q_decode_step"));
   Q_CHECK_ARG(e->cfg.tp_size == 1, "q_decode_step: single-GPU entry point called with tp_size %d",
               e->cfg.tp_size);
+  if (e->mega_ok && g_fused_step) {
+    e->mega.trace_layer = g_trace_layer;
+    Q_CHECK_CUDA(q_mega_launch(e->mega, e->mega_grid, (cudaStream_t)stream));
+    return Q_OK;
+  }
   const q_config_t& c = e->cfg;
   const q_state_t& s = e->st;
   TRY(q_step_begin(e, stream));

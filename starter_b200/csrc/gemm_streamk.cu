@@ -189,9 +189,14 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
         asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const char*>(X) + ((size_t)i << 7)));
   }
 
-  float acc[NT][4];
+  // mma.sync has a long latency on this part (~280 cycles): consecutive MMAs go to
+  // SETS independent accumulators, added when a 16-row group (or the run) ends.
+  constexpr int SETS = NT == 1 ? 8 : (NT == 2 ? 4 : 2);
+  float acc[SETS][NT][4];
 #pragma unroll
-  for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  for (int s = 0; s < SETS; ++s)
+#pragma unroll
+    for (int i = 0; i < NT; ++i) acc[s][i][0] = acc[s][i][1] = acc[s][i][2] = acc[s][i][3] = 0.f;
   int group = ws / C;
   int chunk = ws - group * C;
   int seg_first_chunk = chunk;          // first chunk of the current segment
@@ -232,15 +237,25 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
       for (int nt = 0; nt < NT; ++nt) {
         const uint4 x = xs[i][nt];
         if (!(dbg & 1)) {
-          mma16816(acc[nt], a.x, b.x, a.y, b.y, x.x, x.y);
-          mma16816(acc[nt], a.z, b.z, a.w, b.w, x.z, x.w);
+          mma16816(acc[(2 * i) % SETS][nt], a.x, b.x, a.y, b.y, x.x, x.y);
+          mma16816(acc[(2 * i + 1) % SETS][nt], a.z, b.z, a.w, b.w, x.z, x.w);
         } else {
-          acc[nt][0] += __uint_as_float(a.x ^ b.w);
+          acc[0][nt][0] += __uint_as_float(a.x ^ b.w);
         }
       }
       const bool group_end = (chunk == C - 1);
       const bool run_end = (st * STAGE_UNITS + i == n_units - 1);
       if (group_end || run_end) {
+        float tot[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float v = 0.f;
+#pragma unroll
+            for (int s = 0; s < SETS; ++s) { v += acc[s][nt][e]; acc[s][nt][e] = 0.f; }
+            tot[nt][e] = v;
+          }
         if (group_end && seg_first_chunk == 0) {
           // the warp covered the whole group: it is the only contributor (slot 0)
           const int n0 = group * 16 + g;
@@ -248,12 +263,12 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
           for (int nt = 0; nt < NT; ++nt) {
             const int m0 = nt * 8 + 2 * t;
             if (m0 < M) {
-              if (n0 < N) P[(size_t)m0 * N + n0] = acc[nt][0];
-              if (n0 + 8 < N) P[(size_t)m0 * N + n0 + 8] = acc[nt][2];
+              if (n0 < N) P[(size_t)m0 * N + n0] = tot[nt][0];
+              if (n0 + 8 < N) P[(size_t)m0 * N + n0 + 8] = tot[nt][2];
             }
             if (m0 + 1 < M) {
-              if (n0 < N) P[(size_t)(m0 + 1) * N + n0] = acc[nt][1];
-              if (n0 + 8 < N) P[(size_t)(m0 + 1) * N + n0 + 8] = acc[nt][3];
+              if (n0 < N) P[(size_t)(m0 + 1) * N + n0] = tot[nt][1];
+              if (n0 + 8 < N) P[(size_t)(m0 + 1) * N + n0 + 8] = tot[nt][3];
             }
           }
         } else {
@@ -262,12 +277,10 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt)
             *reinterpret_cast<float4*>(mine + nt * 128 + lane * 4) =
-                make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+                make_float4(tot[nt][0], tot[nt][1], tot[nt][2], tot[nt][3]);
           if (lane == 0) tags[warp * 2 + n_boundary] = group;
           ++n_boundary;
         }
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
         seg_first_chunk = 0;
       }
       if (group_end) { chunk = 0; ++group; } else { ++chunk; }
@@ -286,31 +299,36 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
   if (trace) g_gemm_trace[blockIdx.x * 5 + 3] = gtime();
   // ---- add the ragged ends across the CTA: one partial per (CTA, group) ----
   __syncthreads();
+  // The warp that holds the FIRST parked entry of a group adds all entries of that
+  // group in fixed order and writes the CTA's partial of the group.
   const long long slot_stride = (long long)M * N;
-  int tg[WARPS * 2];
-#pragma unroll
-  for (int s = 0; s < WARPS * 2; s += 4) {
-    const int4 v = *reinterpret_cast<const int4*>(tags + s);
-    tg[s] = v.x; tg[s + 1] = v.y; tg[s + 2] = v.z; tg[s + 3] = v.w;
-  }
-#pragma unroll
-  for (int s = 0; s < WARPS * 2; ++s) {
-    const int gg = tg[s];
-    bool fresh = gg >= 0;
-#pragma unroll
-    for (int s2 = 0; s2 < s; ++s2) fresh = fresh && (tg[s2] != gg);
+  for (int mine = warp * 2; mine < warp * 2 + 2; ++mine) {
+    const int gg = tags[mine];
+    if (gg < 0) continue;
+    bool fresh = true;
+    for (int s2 = 0; s2 < mine; ++s2) fresh = fresh && (tags[s2] != gg);
     if (!fresh) continue;
-    const int first = (int)(((long long)gg * C) / U);
-    float* out = P + (long long)(blockIdx.x - first) * slot_stride;
-    for (int r = tid; r < NT * 128; r += THREADS) {
-      float sum = 0.f;
+    const unsigned first = ((unsigned)gg * (unsigned)C) / (unsigned)U;
+    float* out = P + (long long)((int)blockIdx.x - (int)first) * slot_stride;
+    const int n0 = gg * 16 + g;
 #pragma unroll
-      for (int s2 = s; s2 < WARPS * 2; ++s2)
-        if (tg[s2] == gg) sum += red[(size_t)s2 * (NT * 128) + r];
-      const int nt = r >> 7, ln = (r & 127) >> 2, e = r & 3;
-      const int n = gg * 16 + (ln >> 2) + 8 * (e >> 1);
-      const int m = nt * 8 + 2 * (ln & 3) + (e & 1);
-      if (n < N && m < M) out[(size_t)m * N + n] = sum;
+    for (int nt = 0; nt < NT; ++nt) {
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s2 = mine; s2 < WARPS * 2; ++s2) {
+        if (tags[s2] == gg) {
+          const float4 v = *reinterpret_cast<const float4*>(red + (size_t)s2 * (NT * 128) + nt * 128 + lane * 4);
+          sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+      }
+      const int m0 = nt * 8 + 2 * t;
+      if (m0 < M) {
+        if (n0 < N) out[(size_t)m0 * N + n0] = sum.x;
+        if (n0 + 8 < N) out[(size_t)m0 * N + n0 + 8] = sum.z;
+      }
+      if (m0 + 1 < M) {
+        if (n0 < N) out[(size_t)(m0 + 1) * N + n0] = sum.y;
+        if (n0 + 8 < N) out[(size_t)(m0 + 1) * N + n0 + 8] = sum.w;
+      }
     }
   }
   if (trace) g_gemm_trace[blockIdx.x * 5 + 4] = gtime();

@@ -1,0 +1,919 @@
+// Whole decode step as ONE persistent cooperative kernel (small batch).
+//
+// The multi-kernel step (capi.cu) pays a kernel boundary ~360 times per token;
+// at batch 1 the weight stream of a whole layer is only ~31 us long, so those
+// boundaries dominate. Here one CTA per SM stays resident for the whole step and
+// the phases are separated by grid barriers instead (reference: one captured
+// graph of ~335 kernel nodes, engine/decode_step.py:33-60, engine/decode.py:97-108).
+//
+// Per layer:  A  add+RMSNorm (or embedding) -> QKV GEMM            | barrier
+//             B  q/k norm + RoPE + KV write -> split-KV attention,  |
+//                last split of a kv head merges the splits         | barrier
+//             C  O-proj GEMM                                       | barrier
+//             D  add+RMSNorm -> gate|up GEMM                       | barrier
+//             E  SwiGLU (spread over the grid)                     | barrier
+//             F  down GEMM                                         | barrier
+// then the final norm + lm_head GEMM, barrier, and a grid-wide argmax whose last
+// CTA writes the token and bumps the position.
+//
+// What makes the barriers cheap: a CTA issues the TMA copies of its NEXT GEMM's
+// first 128 KB (its whole shared-memory ring) BEFORE it arrives at the barrier,
+// so HBM keeps streaming weights while the CTAs synchronise and run the small
+// prologues. The residual stream lives in every CTA's shared memory (all CTAs
+// compute the same add+norm), so no phase depends on one CTA writing it.
+//
+// The GEMM phases use the same tiled weights, per-warp contiguous runs, mma
+// fragments and slot scheme as k_gemm_streamk; the attention phase is the
+// k_attn_split algorithm with the rope prologue and the merge folded in. Cast
+// boundaries are identical to the multi-kernel step (see fused_ops.cu).
+//
+// Every data item another CTA wrote in this launch is read with ld.global.cg
+// (L1 is not coherent across SMs). Every spin (grid barrier, mbarrier) is
+// bounded: when a limit runs out the kernel records a status code and carries
+// on to the end instead of hanging.
+#include "common.cuh"
+#include "mega_step.h"
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+constexpr int STAGE_UNITS = 8;
+constexpr int STAGES = 2;
+constexpr int STAGE_BYTES = STAGE_UNITS * 1024;
+constexpr int RING_BYTES = WARPS * STAGES * STAGE_BYTES;     // 128 KB
+constexpr int RED_FLOATS = WARPS * 2 * 128;                  // ragged-end accumulators
+constexpr unsigned SPIN_LIMIT = 1u << 22;
+
+constexpr int ATT_TILE = 64 * 128 * 2;                       // one K or V tile
+constexpr int ATT_STAGE = 2 * ATT_TILE;
+constexpr int ATT_NS = 3;
+
+__device__ int g_mega_status[4];
+// Measurement aid: phase time stamps (ns) of layer `trace_layer` for CTAs 0 and 100.
+__device__ unsigned long long g_mega_trace[2 * 32];
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define TRACE(i)                                                                         \
+  do {                                                                                   \
+    if (tracing && threadIdx.x == 0) g_mega_trace[(blockIdx.x == 0 ? 0 : 32) + (i)] = gtime(); \
+  } while (0)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if (it > 256) __nanosleep(32);
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float ldcg_f(const float* p) { return __ldcg(p); }
+
+// Partial-sum read of element idx (column n) written by other CTAs in this launch.
+__device__ __forceinline__ float psum_cg(const float* P, const mega_plan_t& pl, long long stride,
+                                         long long idx, int n) {
+  const unsigned g = (unsigned)n >> 4, C = (unsigned)pl.C, u = (unsigned)pl.U;
+  const unsigned first = (g * C) / u, last = ((g + 1) * C - 1) / u;
+  float s = ldcg_f(P + idx);
+  const float s1 = ldcg_f(P + idx + stride);
+  if (last > first) s += s1;
+  for (unsigned k = 2; k <= last - first; ++k) s += ldcg_f(P + idx + (long long)k * stride);
+  return s;
+}
+
+struct Ctx {
+  unsigned char* ring;        // RING_BYTES (attention reuses it)
+  float* red;                 // RED_FLOATS
+  int* tags;                  // WARPS*2
+  uint64_t* gbars;            // WARPS*STAGES  (GEMM ring)
+  uint64_t* abars;            // 2*ATT_NS      (attention ring)
+  bf16* xs;                   // GEMM activation operand [M][Kmax]
+  bf16* resid;                // residual stream [M][H]
+  float* scratch;             // 64 floats for block reductions + small broadcast
+  bf16* knew;                 // [128] newest key of this CTA's kv head
+  bf16* vnew;                 // [128]
+  uint32_t g_count;           // per-warp GEMM stage counter (mbarrier phase tracking)
+  uint32_t a_count;           // attention stage counter (CTA-wide, same in all threads)
+  int trace_gemm;             // measurement aid: >0 = stamp this GEMM's stages into g_mega_trace[17..]
+  unsigned epoch;             // grid barrier epoch
+};
+
+// ---- grid barrier ----------------------------------------------------------------
+__device__ __noinline__ void grid_barrier(const mega_params_t& p, Ctx& c) {
+  __syncthreads();
+  c.epoch += 1;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(&p.sync[0], 1u);
+    const unsigned target = c.epoch * gridDim.x;
+    unsigned it = 0;
+    // once any wait in this launch has run out, nobody spins again
+    while (*reinterpret_cast<volatile int*>(&g_mega_status[0]) == 0) {
+      unsigned v;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sync) : "memory");
+      if (v >= target) break;
+      if (++it > SPIN_LIMIT) { atomicExch(&g_mega_status[0], 1); break; }
+      if (it > 64) __nanosleep(20);
+    }
+    __threadfence();
+  }
+  __syncthreads();
+}
+
+// ---- GEMM phase --------------------------------------------------------------------
+struct GemmRun {
+  const unsigned char* src;
+  int ws, n_units, n_stages;
+  uint32_t base;              // stage counter value of stage 0 of this GEMM
+};
+
+// Issues the first ring-full of the warp's run. Weights never depend on earlier
+// phases, so this is called BEFORE the barrier that precedes the GEMM.
+__device__ __noinline__ GemmRun gemm_prime(const unsigned char* Wt, const mega_plan_t& pl, Ctx& c) {
+  GemmRun r;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cs = blockIdx.x * pl.U;
+  const int ce = min(pl.total, cs + pl.U);
+  const int len = ce > cs ? ce - cs : 0;
+  r.ws = cs + (int)(((long long)warp * len) / WARPS);
+  const int we = cs + (int)(((long long)(warp + 1) * len) / WARPS);
+  r.n_units = we - r.ws;
+  r.n_stages = (r.n_units + STAGE_UNITS - 1) / STAGE_UNITS;
+  r.src = Wt + (size_t)r.ws * 1024;
+  r.base = c.g_count;
+  if (lane == 0) {
+    // the ring may just have been written through the generic proxy (attention merge)
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    const uint32_t ring = smem_u32(c.ring) + warp * (STAGES * STAGE_BYTES);
+    for (int s = 0; s < STAGES && s < r.n_stages; ++s) {
+      const uint32_t slot = (r.base + s) % STAGES;
+      const uint32_t bar = smem_u32(&c.gbars[warp * STAGES + slot]);
+      const uint32_t bytes = (uint32_t)min(STAGE_UNITS, r.n_units - s * STAGE_UNITS) * 1024u;
+      mbar_expect_tx(bar, bytes);
+      bulk_g2s(ring + slot * STAGE_BYTES, r.src + (size_t)s * STAGE_BYTES, bytes, bar);
+    }
+  }
+  c.g_count += r.n_stages;
+  return r;
+}
+
+// Streams the run, X fragments from shared memory (xs[M][K]), partials to P.
+// mma.sync has a long latency on this part (~280 cycles), so consecutive MMAs go
+// to NSETS independent accumulators that are added when a 16-row group ends.
+constexpr int NSETS = 8;
+
+__device__ __noinline__ void gemm_run(const GemmRun& r, const mega_plan_t& pl, int M, const bf16* xs,
+                                      float* __restrict__ P, Ctx& c) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int C = pl.C, N = pl.N, K = pl.K;
+  const uint32_t ring = smem_u32(c.ring) + warp * (STAGES * STAGE_BYTES);
+  const uint32_t xbase = smem_u32(xs) + (uint32_t)(g * K + t * 8) * 2u;
+  if (lane < 2) c.tags[warp * 2 + lane] = -1;
+  __syncwarp();
+  float acc[NSETS][4];
+#pragma unroll
+  for (int s = 0; s < NSETS; ++s) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.f;
+  const bool tr = c.trace_gemm > 0 && tid == 0;
+  int tri = 17;
+  if (tr) g_mega_trace[(blockIdx.x == 0 ? 0 : 32) + tri++] = gtime();
+  int group = r.ws / C;
+  int chunk = r.ws - group * C;
+  int seg_first = chunk, n_boundary = 0, units_done = 0;
+  for (int st = 0; st < r.n_stages; ++st) {
+    const uint32_t slot = (r.base + st) % STAGES;
+    const uint32_t bar = smem_u32(&c.gbars[warp * STAGES + slot]);
+    if (!mbar_wait(bar, ((r.base + st) / STAGES) & 1)) {
+      atomicExch(&g_mega_status[0], 2);
+      break;
+    }
+    if (tr && tri < 28) g_mega_trace[(blockIdx.x == 0 ? 0 : 32) + tri++] = gtime();
+    const int in_stage = min(STAGE_UNITS, r.n_units - st * STAGE_UNITS);
+    uint32_t sbase = ring + slot * STAGE_BYTES + lane * 16;
+    int done = 0;
+    while (done < in_stage) {
+      const int n = min(in_stage - done, C - chunk);     // units of this stage inside one group
+      const uint32_t xaddr = xbase + (uint32_t)chunk * 64u;
+#pragma unroll
+      for (int j = 0; j < STAGE_UNITS; ++j) {
+        if (j < n) {
+          const uint4 a = lds128(sbase + j * 1024), b = lds128(sbase + j * 1024 + 512);
+          uint4 x = make_uint4(0, 0, 0, 0);
+          if (g < M) x = lds128(xaddr + j * 64);
+          mma16816(acc[(2 * j) % NSETS], a.x, b.x, a.y, b.y, x.x, x.y);
+          mma16816(acc[(2 * j + 1) % NSETS], a.z, b.z, a.w, b.w, x.z, x.w);
+        }
+      }
+      done += n; chunk += n; units_done += n; sbase += n * 1024;
+      const bool group_end = (chunk == C);
+      if (group_end || units_done == r.n_units) {
+        float tot[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = 0.f;
+#pragma unroll
+          for (int s = 0; s < NSETS; ++s) { v += acc[s][e]; acc[s][e] = 0.f; }
+          tot[e] = v;
+        }
+        if (group_end && seg_first == 0) {
+          const int n0 = group * 16 + g, m0 = 2 * t;
+          if (m0 < M) {
+            if (n0 < N) P[(size_t)m0 * N + n0] = tot[0];
+            if (n0 + 8 < N) P[(size_t)m0 * N + n0 + 8] = tot[2];
+          }
+          if (m0 + 1 < M) {
+            if (n0 < N) P[(size_t)(m0 + 1) * N + n0] = tot[1];
+            if (n0 + 8 < N) P[(size_t)(m0 + 1) * N + n0 + 8] = tot[3];
+          }
+        } else {
+          float* mine = c.red + ((size_t)warp * 2 + n_boundary) * 128;
+          *reinterpret_cast<float4*>(mine + lane * 4) = make_float4(tot[0], tot[1], tot[2], tot[3]);
+          if (lane == 0) c.tags[warp * 2 + n_boundary] = group;
+          ++n_boundary;
+        }
+        seg_first = 0;
+        if (group_end) { chunk = 0; ++group; }
+      }
+    }
+    __syncwarp();
+    const int nxt = st + STAGES;
+    if (lane == 0 && nxt < r.n_stages) {
+      const uint32_t bytes = (uint32_t)min(STAGE_UNITS, r.n_units - nxt * STAGE_UNITS) * 1024u;
+      mbar_expect_tx(bar, bytes);
+      bulk_g2s(ring + slot * STAGE_BYTES, r.src + (size_t)nxt * STAGE_BYTES, bytes, bar);
+    }
+  }
+  if (tr) g_mega_trace[(blockIdx.x == 0 ? 0 : 32) + 29] = gtime();
+  __syncthreads();
+  if (tr) g_mega_trace[(blockIdx.x == 0 ? 0 : 32) + 30] = gtime();
+  // Ragged ends: the warp that holds the FIRST parked entry of a group adds all entries
+  // of that group (fixed order) and writes the CTA's partial of the group.
+  const long long stride = (long long)M * N;
+  for (int mine = warp * 2; mine < warp * 2 + 2; ++mine) {
+    const int gg = c.tags[mine];
+    if (gg < 0) continue;
+    bool fresh = true;
+    for (int s2 = 0; s2 < mine; ++s2) fresh = fresh && (c.tags[s2] != gg);
+    if (!fresh) continue;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s2 = mine; s2 < WARPS * 2; ++s2) {
+      if (c.tags[s2] == gg) {
+        const float4 v = *reinterpret_cast<const float4*>(c.red + (size_t)s2 * 128 + lane * 4);
+        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+      }
+    }
+    const unsigned first = ((unsigned)gg * (unsigned)C) / (unsigned)pl.U;
+    float* out = P + (long long)((int)blockIdx.x - (int)first) * stride;
+    const int n0 = gg * 16 + g, m0 = 2 * t;
+    if (m0 < M) {
+      if (n0 < N) out[(size_t)m0 * N + n0] = sum.x;
+      if (n0 + 8 < N) out[(size_t)m0 * N + n0 + 8] = sum.z;
+    }
+    if (m0 + 1 < M) {
+      if (n0 < N) out[(size_t)(m0 + 1) * N + n0] = sum.y;
+      if (n0 + 8 < N) out[(size_t)(m0 + 1) * N + n0 + 8] = sum.w;
+    }
+  }
+  // red/tags are written again only after the next grid barrier (a __syncthreads)
+  if (tr) g_mega_trace[(blockIdx.x == 0 ? 0 : 32) + 31] = gtime();
+}
+
+// ---- block reduction ------------------------------------------------------------------
+__device__ __forceinline__ float block_sum_s(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < WARPS ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+
+// ---- prologues: produce the residual (resid) and the normed GEMM operand (xs) ---------
+__device__ __noinline__ void norm_rows_to_xs(const mega_params_t& p, Ctx& c, const bf16* gain, int K) {
+  // resid[m][*] (shared) -> xs[m][*] = bf16(bf16(resid*inv) * gain)
+  const int H = p.H;
+  for (int m = 0; m < p.M; ++m) {
+    float ss = 0.f;
+    for (int col = threadIdx.x; col < H; col += THREADS) {
+      const float v = __bfloat162float(c.resid[m * H + col]);
+      ss += v * v;
+    }
+    ss = block_sum_s(ss, c.scratch);
+    const float inv = rsqrtf(ss / (float)H + p.eps);
+    for (int col = threadIdx.x; col < H; col += THREADS) {
+      const float v = bf16_round(__bfloat162float(c.resid[m * H + col]) * inv);
+      c.xs[m * K + col] = __float2bfloat16_rn(v * __bfloat162float(gain[col]));
+    }
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ size_t tiled_elem(long long row, int col, int C) {
+  const long long unit = (row >> 4) * C + (col >> 5);
+  const int piece = (int)(row & 7) * 4 + ((col & 31) >> 3);
+  return (size_t)unit * 512 + (size_t)((row >> 3) & 1) * 256 + piece * 8 + (col & 7);
+}
+
+__device__ __forceinline__ void prologue_embed(const mega_params_t& p, Ctx& c, const bf16* gain) {
+  const int H = p.H, C = H >> 5;
+  const bf16* E = reinterpret_cast<const bf16*>(p.embed);
+  for (int m = 0; m < p.M; ++m) {
+    long long tok = p.tokens[m];
+    tok = tok < 0 ? 0 : (tok >= p.full_vocab ? p.full_vocab - 1 : tok);
+    for (int col = threadIdx.x; col < H; col += THREADS) c.resid[m * H + col] = E[tiled_elem(tok, col, C)];
+  }
+  __syncthreads();
+  norm_rows_to_xs(p, c, gain, H);
+}
+
+// resid = bf16(resid + bf16(sum of partial slots)); xs = RMSNorm(resid) * gain
+__device__ __noinline__ void prologue_add_norm(const mega_params_t& p, Ctx& c, const float* P,
+                                                  const mega_plan_t& pl, const bf16* gain) {
+  const int H = p.H;
+  const long long stride = (long long)p.M * H;
+  for (int m = 0; m < p.M; ++m)
+    for (int col = threadIdx.x; col < H; col += THREADS) {
+      const float y = bf16_round(psum_cg(P, pl, stride, (long long)m * H + col, col));
+      c.resid[m * H + col] = __float2bfloat16_rn(__bfloat162float(c.resid[m * H + col]) + y);
+    }
+  __syncthreads();
+  norm_rows_to_xs(p, c, gain, H);
+}
+
+__device__ __noinline__ void stage_x(const mega_params_t& p, Ctx& c, const bf16* src, int K) {
+  const int pieces = p.M * K / 8;
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(c.xs);
+  for (int i = threadIdx.x; i < pieces; i += THREADS) d[i] = __ldcg(s + i);
+  __syncthreads();
+}
+
+// ---- attention phase ----------------------------------------------------------------------
+// CTA `item` = (sequence b, kv head kh, split). T = 1, G <= 16.
+__device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, const mega_layer_t& L,
+                                                const float* PQ) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int S = p.attn_S, nq = p.nq, nkv = p.nkv, G = nq / nkv;
+  const int items = p.M * nkv * S;
+  if ((int)blockIdx.x >= items) return;
+  const int bh = blockIdx.x / S, split = blockIdx.x % S;
+  const int b = bh / nkv, kh = bh % nkv;
+  const int pos = p.pos[0];
+  const int max_limit = pos + 1;
+  const int tiles_used = (max_limit + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
+  const int per = (tiles_used + S - 1) / S;
+  const int tile0 = split * per;
+  const int tile1 = min(tiles_used, tile0 + per);
+  const int ntiles = tile1 > tile0 ? tile1 - tile0 : 0;
+  const int new_tile = pos / Q_PAGE_TOKENS, new_row = pos % Q_PAGE_TOKENS;
+  const bool owns_new = ntiles > 0 && new_tile >= tile0 && new_tile < tile1;
+
+  unsigned char* stages = c.ring;                         // ATT_NS * ATT_STAGE = 96 KB
+  unsigned char* qtile = c.ring + ATT_NS * ATT_STAGE;     // 16 rows * 256 B
+  const uint32_t abar = smem_u32(c.abars);
+  const uint32_t a_base = c.a_count;
+  c.a_count += (uint32_t)ntiles;
+
+  // ---- producer first, so that the KV tiles are in flight during the rope prologue ----
+  if (warp == 4 && lane == 0) {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (int it = 0; it < ntiles && it < ATT_NS; ++it) {
+      const uint32_t slot = (a_base + it) % ATT_NS;
+      const int page = p.block_table[(size_t)b * p.pages_per_seq + tile0 + it];
+      const size_t off = ((size_t)page * nkv + kh) * ATT_TILE;
+      mbar_expect_tx(abar + 8 * slot, ATT_STAGE);
+      bulk_g2s(smem_u32(stages + slot * ATT_STAGE), L.kpool + off, ATT_TILE, abar + 8 * slot);
+      bulk_g2s(smem_u32(stages + slot * ATT_STAGE + ATT_TILE), L.vpool + off, ATT_TILE, abar + 8 * slot);
+    }
+  }
+
+  // ---- q/k head norm + RoPE (+ v), from the QKV partials ----
+  {
+    const int width = (nq + 2 * nkv) * 128;
+    const long long stride = (long long)p.M * width;
+    const float eps = p.eps;
+    for (int h = warp; h < G + 1; h += WARPS) {
+      const bool is_q = h < G;
+      const int head = is_q ? kh * G + h : nq + kh;          // column block in the packed projection
+      const long long src = (long long)b * width + (long long)head * 128;
+      float x[4], ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int d = lane + 32 * j;
+        x[j] = bf16_round(psum_cg(PQ, p.qkv, stride, src + d, head * 128 + d));
+        ss += x[j] * x[j];
+      }
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / 128.f + eps);
+      const bf16* gain = is_q ? L.q_gain : L.k_gain;
+      float n[4], out[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        n[j] = bf16_round(bf16_round(x[j] * inv) * __bfloat162float(gain[lane + 32 * j]));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int d = lane + 32 * j;
+        const float cs = __bfloat162float(p.cos[(size_t)pos * 128 + d]);
+        const float sn = __bfloat162float(p.sin[(size_t)pos * 128 + d]);
+        const float rot = (j < 2) ? -n[j + 2] : n[j - 2];
+        out[j] = bf16_round(n[j] * cs) + bf16_round(rot * sn);
+      }
+      if (is_q) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int d = lane + 32 * j;
+          *reinterpret_cast<bf16*>(qtile + kv_tile_offset_bytes(h, d)) = __float2bfloat16_rn(out[j]);
+        }
+      } else {
+        const long long vsrc = (long long)b * width + (long long)(nq + nkv + kh) * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int d = lane + 32 * j;
+          c.knew[d] = __float2bfloat16_rn(out[j]);
+          c.vnew[d] = __float2bfloat16_rn(psum_cg(PQ, p.qkv, stride, vsrc + d, (nq + nkv + kh) * 128 + d));
+        }
+      }
+    }
+    // rows G..15 of the query tile are zero
+    for (int i = tid; i < (16 - G) * 16; i += THREADS) {
+      const int r = G + (i >> 4), ch = i & 15;
+      *reinterpret_cast<uint4*>(qtile + r * 256 + ((ch ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  __syncthreads();
+  if (owns_new && tid < 32) {
+    // the newest key/value row goes to its page for later steps (16 lanes x 16 B each)
+    const int page = p.block_table[(size_t)b * p.pages_per_seq + new_tile];
+    const size_t tile = ((size_t)page * nkv + kh) * ATT_TILE;
+    if (lane < 16) {
+      const int off = new_row * 256 + ((lane ^ (new_row & 7)) << 4);
+      *reinterpret_cast<uint4*>(L.kpool + tile + off) = *reinterpret_cast<const uint4*>(c.knew + lane * 8);
+      *reinterpret_cast<uint4*>(L.vpool + tile + off) = *reinterpret_cast<const uint4*>(c.vnew + lane * 8);
+    }
+  }
+
+  if (warp == 4) {
+    // ---- producer: remaining tiles ----
+    if (lane == 0) {
+      for (int it = ATT_NS; it < ntiles; ++it) {
+        const uint32_t slot = (a_base + it) % ATT_NS;
+        // wait until the 4 consumers released the previous use of this slot
+        if (!mbar_wait(abar + 8 * (ATT_NS + slot), ((a_base + it) / ATT_NS - 1) & 1)) {
+          atomicExch(&g_mega_status[0], 3);
+          break;
+        }
+        const int page = p.block_table[(size_t)b * p.pages_per_seq + tile0 + it];
+        const size_t off = ((size_t)page * nkv + kh) * ATT_TILE;
+        mbar_expect_tx(abar + 8 * slot, ATT_STAGE);
+        bulk_g2s(smem_u32(stages + slot * ATT_STAGE), L.kpool + off, ATT_TILE, abar + 8 * slot);
+        bulk_g2s(smem_u32(stages + slot * ATT_STAGE + ATT_TILE), L.vpool + off, ATT_TILE, abar + 8 * slot);
+      }
+    }
+  } else if (warp < 4) {
+    // ---- consumers ----
+    const int g = lane >> 2, t4 = lane & 3;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float oacc[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f;
+    const uint32_t q_base = smem_u32(qtile);
+    for (int it = 0; it < ntiles; ++it) {
+      const uint32_t slot = (a_base + it) % ATT_NS;
+      if (!mbar_wait(abar + 8 * slot, ((a_base + it) / ATT_NS) & 1)) {
+        atomicExch(&g_mega_status[0], 4);
+        break;
+      }
+      unsigned char* kt = stages + slot * ATT_STAGE;
+      unsigned char* vt = kt + ATT_TILE;
+      const int key_base = (tile0 + it) * Q_PAGE_TOKENS;
+      const int my_key0 = key_base + warp * 16;
+      if (my_key0 + 16 > max_limit) {
+        for (int i = lane; i < 16 * 16; i += 32) {
+          const int kr = warp * 16 + (i >> 4);
+          if (key_base + kr >= max_limit)
+            *reinterpret_cast<uint4*>(vt + kr * 256 + ((i & 15) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      if (tile0 + it == new_tile && (new_row >> 4) == warp) {
+        // patch the newest key/value row (computed above, not yet visible to the bulk copy)
+        if (lane < 16) {
+          const int off = new_row * 256 + ((lane ^ (new_row & 7)) << 4);
+          *reinterpret_cast<uint4*>(kt + off) = *reinterpret_cast<const uint4*>(c.knew + lane * 8);
+          *reinterpret_cast<uint4*>(vt + off) = *reinterpret_cast<const uint4*>(c.vnew + lane * 8);
+        }
+      }
+      __syncwarp();
+      const uint32_t k_base = smem_u32(kt), v_base = smem_u32(vt);
+      float sacc[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+        {
+          const int row = (lane & 7) + 8 * ((lane >> 3) & 1);
+          const int ch = 2 * ks + (lane >> 4);
+          ldsm_x4(q_base + row * 256 + ((ch ^ (row & 7)) << 4), a0, a1, a2, a3);
+        }
+        {
+          const int mi = lane >> 3;
+          const int key = warp * 16 + 8 * (mi >> 1) + (lane & 7);
+          const int ch = 2 * ks + (mi & 1);
+          ldsm_x4(k_base + key * 256 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+        }
+        mma16816(sacc[0], a0, a1, a2, a3, b0, b1);
+        mma16816(sacc[1], a0, a1, a2, a3, b2, b3);
+      }
+      float pr[2][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = my_key0 + 8 * j + 2 * t4 + e;
+            float v = sacc[j][2 * h + e] * p.scale_log2;
+            v = key < max_limit ? v : -INFINITY;
+            sacc[j][2 * h + e] = v;
+            mx = fmaxf(mx, v);
+          }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[h], mx);
+        const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+        const float resc = exp2f(m_run[h] - m_safe);
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float pv = exp2f(sacc[j][2 * h + e] - m_safe);
+            pr[j][2 * h + e] = pv;
+            sum += pv;
+          }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l_run[h] = l_run[h] * resc + sum;
+        m_run[h] = m_new;
+#pragma unroll
+        for (int n = 0; n < 16; ++n) { oacc[n][2 * h] *= resc; oacc[n][2 * h + 1] *= resc; }
+      }
+      const uint32_t pa0 = pack_bf16(pr[0][0], pr[0][1]), pa1 = pack_bf16(pr[0][2], pr[0][3]);
+      const uint32_t pa2 = pack_bf16(pr[1][0], pr[1][1]), pa3 = pack_bf16(pr[1][2], pr[1][3]);
+#pragma unroll
+      for (int dp = 0; dp < 8; ++dp) {
+        uint32_t b0, b1, b2, b3;
+        const int mi = lane >> 3;
+        const int key = warp * 16 + 8 * (mi & 1) + (lane & 7);
+        const int ch = 2 * dp + (mi >> 1);
+        ldsm_x4_t(v_base + key * 256 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+        mma16816(oacc[2 * dp], pa0, pa1, pa2, pa3, b0, b1);
+        mma16816(oacc[2 * dp + 1], pa0, pa1, pa2, pa3, b2, b3);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(abar + 8 * (ATT_NS + slot));
+    }
+    // park the warp's state for the CTA merge (after the ring is idle)
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    float* mo = reinterpret_cast<float*>(stages);            // [4][16][128]
+    float* mml = mo + 4 * 16 * 128;                          // [4][16][2]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = g + 8 * h;
+      float* dst = mo + ((size_t)warp * 16 + r) * 128;
+#pragma unroll
+      for (int n = 0; n < 16; ++n) {
+        dst[8 * n + 2 * t4] = oacc[n][2 * h];
+        dst[8 * n + 2 * t4 + 1] = oacc[n][2 * h + 1];
+      }
+      if (t4 == 0) {
+        mml[((size_t)warp * 16 + r) * 2] = m_run[h];
+        mml[((size_t)warp * 16 + r) * 2 + 1] = l_run[h];
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const int d = tid;
+    for (int r = 0; r < G; ++r) {
+      float mw[4], Mx = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) { mw[w] = mml[((size_t)w * 16 + r) * 2]; Mx = fmaxf(Mx, mw[w]); }
+      const float Ms = Mx == -INFINITY ? 0.f : Mx;
+      float Lsum = 0.f, O = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float wt = exp2f(mw[w] - Ms);
+        Lsum += wt * mml[((size_t)w * 16 + r) * 2 + 1];
+        O += wt * mo[((size_t)w * 16 + r) * 128 + d];
+      }
+      if (S == 1) {
+        p.attended[((size_t)b * nq + kh * G + r) * 128 + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
+      } else {
+        const size_t row = ((size_t)bh * S + split) * G + r;
+        p.attn_o[row * 128 + d] = O;
+        if (d == 0) { p.attn_ml[row * 2] = Mx; p.attn_ml[row * 2 + 1] = Lsum; }
+      }
+    }
+  }
+  if (S == 1) { __syncthreads(); return; }
+
+  // ---- the last split of this kv head to finish merges all splits ----
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const unsigned ticket = atomicAdd(&p.sync[4 + bh], 1u);
+    reinterpret_cast<volatile int*>(c.scratch)[40] = (ticket == (unsigned)(S - 1));
+    if (ticket == (unsigned)(S - 1)) p.sync[4 + bh] = 0;    // ready for the next layer
+    __threadfence();
+  }
+  __syncthreads();
+  if (reinterpret_cast<volatile int*>(c.scratch)[40]) {
+    for (int r = warp; r < G; r += WARPS) {
+      const size_t base = ((size_t)bh * S) * G + r;           // + split * G
+      float m = -INFINITY, l = 0.f;
+      if (lane < S) {
+        m = __ldcg(p.attn_ml + (base + (size_t)lane * G) * 2);
+        l = __ldcg(p.attn_ml + (base + (size_t)lane * G) * 2 + 1);
+      }
+      float Mx = warp_max(m);
+      if (Mx == -INFINITY) Mx = 0.f;
+      const float wgt = l > 0.f ? exp2f(m - Mx) : 0.f;
+      const float Lsum = warp_sum(wgt * l);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+      for (int s = 0; s < S; ++s) {
+        const float ws = __shfl_sync(0xffffffffu, wgt, s);
+        const float4 o = __ldcg(reinterpret_cast<const float4*>(p.attn_o + (base + (size_t)s * G) * 128) + lane);
+        acc[0] += ws * o.x; acc[1] += ws * o.y; acc[2] += ws * o.z; acc[3] += ws * o.w;
+      }
+      const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
+      uint2 packed;
+      packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+      packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+      *reinterpret_cast<uint2*>(p.attended + ((size_t)b * nq + kh * G + r) * 128 + lane * 4) = packed;
+    }
+  }
+  __syncthreads();
+}
+
+// ---- SwiGLU phase ------------------------------------------------------------------------
+__device__ __noinline__ void swiglu_phase(const mega_params_t& p, const float* PG) {
+  const int I = p.I;
+  const long long total = (long long)p.M * I, stride = (long long)p.M * 2 * I;
+  for (long long i = (long long)blockIdx.x * THREADS + threadIdx.x; i < total; i += (long long)gridDim.x * THREADS) {
+    const int m = (int)(i / I), col = (int)(i % I);
+    const long long base = (long long)m * 2 * I;
+    const float gt = bf16_round(psum_cg(PG, p.gu, stride, base + col, col));
+    const float up = bf16_round(psum_cg(PG, p.gu, stride, base + I + col, I + col));
+    const float a = bf16_round(gt / (1.0f + expf(-gt)));
+    p.act[i] = __float2bfloat16_rn(a * up);
+  }
+}
+
+// ---- logits + argmax phase ----------------------------------------------------------------
+__device__ __forceinline__ void better(float& bv, int& bi, float v, int i) {
+  if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+}
+
+__device__ __forceinline__ void argmax_phase(const mega_params_t& p, Ctx& c, const float* PL) {
+  const int V = p.V, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const long long stride = (long long)p.M * V;
+  const int per = (V + gridDim.x - 1) / gridDim.x;
+  const int c0 = blockIdx.x * per, c1 = min(V, c0 + per);
+  float* sv = c.scratch;
+  int* si = reinterpret_cast<int*>(c.scratch + 16);
+  for (int m = 0; m < p.M; ++m) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int col = c0 + tid; col < c1; col += THREADS) {
+      const long long i = (long long)m * V + col;
+      const bf16 r = __float2bfloat16_rn(psum_cg(PL, p.head, stride, i, col));
+      if (p.logits) p.logits[i] = r;
+      float v = __bfloat162float(r);
+      if (v != v) v = -INFINITY;
+      better(bv, bi, v, col);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      better(bv, bi, ov, oi);
+    }
+    __syncthreads();
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    if (tid == 0) {
+      for (int k = 1; k < WARPS; ++k) better(bv, bi, sv[k], si[k]);
+      p.blk_val[(size_t)m * gridDim.x + blockIdx.x] = bv;
+      p.blk_idx[(size_t)m * gridDim.x + blockIdx.x] = bi;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const unsigned ticket = atomicAdd(&p.sync[2], 1u);
+    reinterpret_cast<volatile int*>(c.scratch)[40] = (ticket == gridDim.x - 1);
+    __threadfence();
+  }
+  __syncthreads();
+  if (!reinterpret_cast<volatile int*>(c.scratch)[40]) return;
+  for (int m = warp; m < p.M; m += WARPS) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int k = lane; k < (int)gridDim.x; k += 32)
+      better(bv, bi, __ldcg(p.blk_val + (size_t)m * gridDim.x + k), __ldcg(p.blk_idx + (size_t)m * gridDim.x + k));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      better(bv, bi, ov, oi);
+    }
+    if (lane == 0) {
+      if (bi == 0x7fffffff) bi = 0;
+      p.arg_val[m] = bv;
+      p.arg_idx[m] = bi;
+      p.tokens[m] = bi;
+    }
+  }
+  if (tid == 0) {
+    p.pos[0] += 1;
+    p.sync[2] = 0;
+    p.sync[0] = 0;      // every CTA is past the last grid barrier: reset for the next launch
+  }
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+k_decode_mega(const __grid_constant__ mega_params_t p) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  Ctx c;
+  c.ring = smem;
+  unsigned char* q = smem + RING_BYTES;
+  c.red = reinterpret_cast<float*>(q); q += RED_FLOATS * 4;
+  c.scratch = reinterpret_cast<float*>(q); q += 64 * 4;
+  c.tags = reinterpret_cast<int*>(q); q += WARPS * 2 * 4;
+  c.gbars = reinterpret_cast<uint64_t*>(q); q += WARPS * STAGES * 8;
+  c.abars = reinterpret_cast<uint64_t*>(q); q += 2 * ATT_NS * 8;
+  c.knew = reinterpret_cast<bf16*>(q); q += 256;
+  c.vnew = reinterpret_cast<bf16*>(q); q += 256;
+  c.resid = reinterpret_cast<bf16*>(q); q += (size_t)p.M * p.H * 2;
+  c.xs = reinterpret_cast<bf16*>(q);
+  c.g_count = 0;
+  c.trace_gemm = 0;
+  c.a_count = 0;
+  c.epoch = 0;
+
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    for (int i = 0; i < WARPS * STAGES; ++i) mbar_init(smem_u32(&c.gbars[i]), 1);
+    for (int i = 0; i < ATT_NS; ++i) {
+      mbar_init(smem_u32(&c.abars[i]), 1);
+      mbar_init(smem_u32(&c.abars[ATT_NS + i]), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int Kmax = p.xs_cols;
+  float* buf0 = p.buf0;
+  float* buf1 = p.buf1;
+
+  GemmRun run = gemm_prime(p.layers[0].wqkv, p.qkv, c);
+  prologue_embed(p, c, p.layers[0].ln_in);
+  for (int l = 0; l < p.L; ++l) {
+    const mega_layer_t& Lw = p.layers[l];
+    const bool tracing = (l == p.trace_layer) && (blockIdx.x == 0 || blockIdx.x == 100);
+    TRACE(0);
+    // A: QKV projection (operand xs = normed hidden, prepared by the previous prologue)
+    c.trace_gemm = tracing ? 1 : 0;
+    gemm_run(run, p.qkv, p.M, c.xs, buf0, c);
+    c.trace_gemm = 0;
+    TRACE(1);
+    grid_barrier(p, c);
+    TRACE(2);
+    // B: attention (reuses the ring), then prime O-proj
+    attention_phase(p, c, Lw, buf0);
+    TRACE(3);
+    run = gemm_prime(Lw.wo, p.o, c);
+    grid_barrier(p, c);
+    TRACE(4);
+    // C: O projection
+    stage_x(p, c, p.attended, p.o.K);
+    TRACE(5);
+    gemm_run(run, p.o, p.M, c.xs, buf1, c);
+    TRACE(6);
+    run = gemm_prime(Lw.wgu, p.gu, c);
+    grid_barrier(p, c);
+    TRACE(7);
+    // D: add + norm, gate|up projection
+    prologue_add_norm(p, c, buf1, p.o, Lw.ln_post);
+    TRACE(8);
+    gemm_run(run, p.gu, p.M, c.xs, buf0, c);
+    TRACE(9);
+    run = gemm_prime(Lw.wdown, p.down, c);
+    grid_barrier(p, c);
+    TRACE(10);
+    // E: SwiGLU
+    swiglu_phase(p, buf0);
+    TRACE(11);
+    grid_barrier(p, c);
+    TRACE(12);
+    // F: down projection
+    stage_x(p, c, p.act, p.down.K);
+    TRACE(13);
+    gemm_run(run, p.down, p.M, c.xs, buf1, c);
+    TRACE(14);
+    const bool last = (l + 1 == p.L);
+    run = last ? gemm_prime(p.lm_head, p.head, c) : gemm_prime(p.layers[l + 1].wqkv, p.qkv, c);
+    grid_barrier(p, c);
+    TRACE(15);
+    prologue_add_norm(p, c, buf1, p.down, last ? p.ln_final : p.layers[l + 1].ln_in);
+    TRACE(16);
+  }
+  (void)Kmax;
+  gemm_run(run, p.head, p.M, c.xs, buf0, c);
+  grid_barrier(p, c);
+  argmax_phase(p, c, buf0);
+}
+
+}  // namespace
+
+int q_mega_trace_read(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_mega_trace, sizeof(unsigned long long) * 64) == cudaSuccess ? 0 : -1;
+}
+
+int q_mega_status_read(int32_t out[4]) {
+  return cudaMemcpyFromSymbol(out, g_mega_status, sizeof(int) * 4) == cudaSuccess ? 0 : -1;
+}
+
+size_t q_mega_smem_bytes(int M, int H, int xs_cols) {
+  return (size_t)RING_BYTES + RED_FLOATS * 4 + 64 * 4 + WARPS * 2 * 4 + WARPS * STAGES * 8 + 2 * ATT_NS * 8 +
+         512 + (size_t)M * H * 2 + (size_t)M * xs_cols * 2 + 64;
+}
+
+cudaError_t q_mega_launch(const mega_params_t& p, int grid, cudaStream_t stream) {
+  const size_t smem = q_mega_smem_bytes(p.M, p.H, p.xs_cols);
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(k_decode_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, k_decode_mega, p);
+}

@@ -100,6 +100,10 @@ class DecodeState:
         self.arg_idx = torch.zeros(batch, dtype=torch.int32, device=dev)
         self.arg_scratch = torch.zeros(lib.q_argmax_scratch_bytes(batch, weights.local_vocab),
                                        dtype=torch.uint8, device=dev)
+        self.fused_scratch = None
+        if self.tp == 1 and batch <= 8:
+            self.fused_scratch = torch.zeros(lib.q_fused_scratch_bytes(handle, batch), dtype=torch.uint8,
+                                             device=dev)
         if self.tp > 1:
             self.gather_val = torch.zeros((self.tp, batch), **f32)
             self.gather_idx = torch.zeros((self.tp, batch), dtype=torch.int32, device=dev)
@@ -111,7 +115,8 @@ class DecodeState:
             self.attended.data_ptr(), self.act.data_ptr(), self.partials.data_ptr(),
             0 if self.reduced is None else self.reduced.data_ptr(), self.attn_o.data_ptr(),
             self.attn_ml.data_ptr(), 0 if self.logits is None else self.logits.data_ptr(),
-            self.arg_val.data_ptr(), self.arg_idx.data_ptr(), self.arg_scratch.data_ptr())
+            self.arg_val.data_ptr(), self.arg_idx.data_ptr(), self.arg_scratch.data_ptr(),
+            0 if self.fused_scratch is None else self.fused_scratch.data_ptr())
         check(lib.q_bind_state(handle, C.byref(st)))
 
     def __del__(self):

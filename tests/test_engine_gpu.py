@@ -143,6 +143,27 @@ def test_zero_lm_head_yields_token_zero_and_never_stops(cuda, golden_dir, tmp_pa
     assert out == [[0, 0]] * 6
 
 
+def test_fused_step_matches_multi_kernel_step(cuda, golden_dir):
+    """The persistent whole-step kernel and the ~360-kernel step implement the same
+    arithmetic: same tokens, logits equal up to fp32 reduction order (one bf16 ulp)."""
+    from starter_b200 import Engine, _lib
+    from starter_b200.ops import device_status
+    path = str(golden_dir / "tiny_qwen3")
+    engine = Engine(path, keep_logits=True)
+    gen = torch.Generator().manual_seed(21)
+    for batch, length, count in ((1, 9, 12), (2, 70, 8), (3, 5, 6)):
+        prompt = torch.randint(0, 127, (batch, length), generator=gen).tolist()
+        fused_tokens, fused_logits = stepwise_logits(engine, prompt, count)
+        _lib.check(_lib.lib.q_set_option(b"fused_step", 0))
+        try:
+            plain_tokens, plain_logits = stepwise_logits(engine, prompt, count)
+        finally:
+            _lib.check(_lib.lib.q_set_option(b"fused_step", 1))
+        assert fused_tokens == plain_tokens
+        torch.testing.assert_close(fused_logits, plain_logits, rtol=1.6e-2, atol=2e-3)
+    assert device_status() == [0, 0, 0, 0]
+
+
 def test_pdl_off_gives_identical_tokens(cuda, golden_dir):
     from starter_b200 import Engine, _lib
     path = str(golden_dir / "tiny_qwen3")
