@@ -401,6 +401,7 @@ extern "C" int q_decode_step(q_engine* e, void* stream) {
               e->cfg.tp_size);
   if (e->mega_ok && g_fused_step) {
     e->mega.trace_layer = g_trace_layer;
+    e->mega.prefetch_units = g_gemm_prefetch_kb / 8;     // per warp (8 warps per CTA), 1 KB units
     Q_CHECK_CUDA(q_mega_launch(e->mega, e->mega_grid, (cudaStream_t)stream));
     return Q_OK;
   }

@@ -57,6 +57,10 @@ __device__ __forceinline__ unsigned long long gtime() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+#define STAMP(i)                                                                        \
+  do {                                                                                   \
+    if (c.trace_gemm > 0 && threadIdx.x == 0) g_mega_trace[(blockIdx.x == 0 ? 0 : 32) + (i)] = gtime(); \
+  } while (0)
 #define TRACE(i)                                                                         \
   do {                                                                                   \
     if (tracing && threadIdx.x == 0) g_mega_trace[(blockIdx.x == 0 ? 0 : 32) + (i)] = gtime(); \
@@ -137,6 +141,9 @@ struct Ctx {
   float* scratch;             // 64 floats for block reductions + small broadcast
   bf16* knew;                 // [128] newest key of this CTA's kv head
   bf16* vnew;                 // [128]
+  bf16* cosrow;               // [128] rotary table row of the current position
+  bf16* sinrow;               // [128]
+  int pos;                    // position of the current token (read once per launch)
   uint32_t g_count;           // per-warp GEMM stage counter (mbarrier phase tracking)
   uint32_t a_count;           // attention stage counter (CTA-wide, same in all threads)
   int trace_gemm;             // measurement aid: >0 = stamp this GEMM's stages into g_mega_trace[17..]
@@ -202,6 +209,27 @@ __device__ __noinline__ GemmRun gemm_prime(const unsigned char* Wt, const mega_p
   return r;
 }
 
+// Asks the TMA unit to pull (part of) this warp's run of a LATER GEMM into L2, so that HBM
+// keeps streaming during the latency-bound phases (attention, norms, barriers). Bytes
+// [skip, skip + cap) of the run; the first RING bytes usually arrive through gemm_prime.
+__device__ __noinline__ void l2_prefetch_run(const unsigned char* Wt, const mega_plan_t& pl, int skip_units,
+                                             int cap_units) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane != 0 || cap_units <= 0) return;
+  const int cs = blockIdx.x * pl.U;
+  const int ce = min(pl.total, cs + pl.U);
+  const int len = ce > cs ? ce - cs : 0;
+  const int ws = cs + (int)(((long long)warp * len) / WARPS);
+  const int we = cs + (int)(((long long)(warp + 1) * len) / WARPS);
+  int lo = ws + skip_units, hi = min(we, lo + cap_units);
+  while (lo < hi) {
+    const int n = min(hi - lo, 32);                      // 32 KB per instruction
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(Wt + (size_t)lo * 1024),
+                 "r"((uint32_t)n * 1024u) : "memory");
+    lo += n;
+  }
+}
+
 // Streams the run, X fragments from shared memory (xs[M][K]), partials to P.
 // mma.sync has a long latency on this part (~280 cycles), so consecutive MMAs go
 // to NSETS independent accumulators that are added when a 16-row group ends.
@@ -219,9 +247,6 @@ __device__ __noinline__ void gemm_run(const GemmRun& r, const mega_plan_t& pl, i
   float acc[NSETS][4];
 #pragma unroll
   for (int s = 0; s < NSETS; ++s) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.f;
-  const bool tr = c.trace_gemm > 0 && tid == 0;
-  int tri = 17;
-  if (tr) g_mega_trace[(blockIdx.x == 0 ? 0 : 32) + tri++] = gtime();
   int group = r.ws / C;
   int chunk = r.ws - group * C;
   int seg_first = chunk, n_boundary = 0, units_done = 0;
@@ -232,7 +257,6 @@ __device__ __noinline__ void gemm_run(const GemmRun& r, const mega_plan_t& pl, i
       atomicExch(&g_mega_status[0], 2);
       break;
     }
-    if (tr && tri < 28) g_mega_trace[(blockIdx.x == 0 ? 0 : 32) + tri++] = gtime();
     const int in_stage = min(STAGE_UNITS, r.n_units - st * STAGE_UNITS);
     uint32_t sbase = ring + slot * STAGE_BYTES + lane * 16;
     int done = 0;
@@ -288,9 +312,7 @@ __device__ __noinline__ void gemm_run(const GemmRun& r, const mega_plan_t& pl, i
       bulk_g2s(ring + slot * STAGE_BYTES, r.src + (size_t)nxt * STAGE_BYTES, bytes, bar);
     }
   }
-  if (tr) g_mega_trace[(blockIdx.x == 0 ? 0 : 32) + 29] = gtime();
   __syncthreads();
-  if (tr) g_mega_trace[(blockIdx.x == 0 ? 0 : 32) + 30] = gtime();
   // Ragged ends: the warp that holds the FIRST parked entry of a group adds all entries
   // of that group (fixed order) and writes the CTA's partial of the group.
   const long long stride = (long long)M * N;
@@ -320,7 +342,6 @@ __device__ __noinline__ void gemm_run(const GemmRun& r, const mega_plan_t& pl, i
     }
   }
   // red/tags are written again only after the next grid barrier (a __syncthreads)
-  if (tr) g_mega_trace[(blockIdx.x == 0 ? 0 : 32) + 31] = gtime();
 }
 
 // ---- block reduction ------------------------------------------------------------------
@@ -335,23 +356,15 @@ __device__ __forceinline__ float block_sum_s(float v, float* red) {
 }
 
 // ---- prologues: produce the residual (resid) and the normed GEMM operand (xs) ---------
-__device__ __noinline__ void norm_rows_to_xs(const mega_params_t& p, Ctx& c, const bf16* gain, int K) {
-  // resid[m][*] (shared) -> xs[m][*] = bf16(bf16(resid*inv) * gain)
+// xs[m][*] = bf16(bf16(resid*inv) * gain) given the per-row sum of squares `ss`.
+__device__ __forceinline__ void scale_row_to_xs(const mega_params_t& p, Ctx& c, const bf16* gain, int K,
+                                                int m, float ss) {
   const int H = p.H;
-  for (int m = 0; m < p.M; ++m) {
-    float ss = 0.f;
-    for (int col = threadIdx.x; col < H; col += THREADS) {
-      const float v = __bfloat162float(c.resid[m * H + col]);
-      ss += v * v;
-    }
-    ss = block_sum_s(ss, c.scratch);
-    const float inv = rsqrtf(ss / (float)H + p.eps);
-    for (int col = threadIdx.x; col < H; col += THREADS) {
-      const float v = bf16_round(__bfloat162float(c.resid[m * H + col]) * inv);
-      c.xs[m * K + col] = __float2bfloat16_rn(v * __bfloat162float(gain[col]));
-    }
+  const float inv = rsqrtf(ss / (float)H + p.eps);
+  for (int col = threadIdx.x; col < H; col += THREADS) {
+    const float v = bf16_round(__bfloat162float(c.resid[m * H + col]) * inv);
+    c.xs[m * K + col] = __float2bfloat16_rn(v * __bfloat162float(gain[col]));
   }
-  __syncthreads();
 }
 
 __device__ __forceinline__ size_t tiled_elem(long long row, int col, int C) {
@@ -360,30 +373,122 @@ __device__ __forceinline__ size_t tiled_elem(long long row, int col, int C) {
   return (size_t)unit * 512 + (size_t)((row >> 3) & 1) * 256 + piece * 8 + (col & 7);
 }
 
-__device__ __forceinline__ void prologue_embed(const mega_params_t& p, Ctx& c, const bf16* gain) {
+constexpr int PB = 12;  // columns per thread whose global loads are issued together (3072 per batch)
+
+__device__ __noinline__ void prologue_embed(const mega_params_t& p, Ctx& c, const bf16* gain) {
   const int H = p.H, C = H >> 5;
   const bf16* E = reinterpret_cast<const bf16*>(p.embed);
   for (int m = 0; m < p.M; ++m) {
     long long tok = p.tokens[m];
     tok = tok < 0 ? 0 : (tok >= p.full_vocab ? p.full_vocab - 1 : tok);
-    for (int col = threadIdx.x; col < H; col += THREADS) c.resid[m * H + col] = E[tiled_elem(tok, col, C)];
+    float ss = 0.f;
+    for (int base = threadIdx.x; base < H; base += THREADS * PB) {
+      bf16 v[PB];
+#pragma unroll
+      for (int j = 0; j < PB; ++j) {
+        const int col = base + j * THREADS;
+        v[j] = col < H ? E[tiled_elem(tok, col, C)] : __float2bfloat16_rn(0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < PB; ++j) {
+        const int col = base + j * THREADS;
+        if (col < H) {
+          c.resid[m * H + col] = v[j];
+          const float f = __bfloat162float(v[j]);
+          ss += f * f;
+        }
+      }
+    }
+    STAMP(18);
+    ss = block_sum_s(ss, c.scratch);
+    STAMP(19);
+    scale_row_to_xs(p, c, gain, H, m, ss);
+    STAMP(20);
   }
   __syncthreads();
-  norm_rows_to_xs(p, c, gain, H);
+  STAMP(21);
 }
 
 // resid = bf16(resid + bf16(sum of partial slots)); xs = RMSNorm(resid) * gain
+// Fast path (H <= 3072): every thread keeps its <= 12 columns in registers, all global
+// loads (two partial slots and the gain) are issued together, one pass.
 __device__ __noinline__ void prologue_add_norm(const mega_params_t& p, Ctx& c, const float* P,
-                                                  const mega_plan_t& pl, const bf16* gain) {
+                                               const mega_plan_t& pl, const bf16* gain) {
   const int H = p.H;
   const long long stride = (long long)p.M * H;
-  for (int m = 0; m < p.M; ++m)
-    for (int col = threadIdx.x; col < H; col += THREADS) {
-      const float y = bf16_round(psum_cg(P, pl, stride, (long long)m * H + col, col));
-      c.resid[m * H + col] = __float2bfloat16_rn(__bfloat162float(c.resid[m * H + col]) + y);
-    }
+  const unsigned C = (unsigned)pl.C, u = (unsigned)pl.U;
+  STAMP(17);
+  // which 16-column groups have a second slot (one division pair per group, not per column)
+  int* two = reinterpret_cast<int*>(c.red);        // red is idle between GEMM phases
+  for (int gi = threadIdx.x; gi < (H >> 4); gi += THREADS) {
+    const unsigned first = ((unsigned)gi * C) / u, last = (((unsigned)gi + 1) * C - 1) / u;
+    two[gi] = (int)(last - first);
+  }
   __syncthreads();
-  norm_rows_to_xs(p, c, gain, H);
+  if (H <= THREADS * PB && (H >> 4) <= RED_FLOATS) {
+    // Every CTA reads the same few KB: start each CTA at a different 128-byte line so that
+    // the requests spread over the L2 slices instead of queueing on one line at a time.
+    const int rot = (int)((blockIdx.x * 37u) % (unsigned)(H >> 5)) << 5;
+    for (int m = 0; m < p.M; ++m) {
+      float s0[PB], s1[PB], gn[PB];
+#pragma unroll
+      for (int j = 0; j < PB; ++j) {
+        int col = threadIdx.x + j * THREADS;
+        col = col < H ? col + rot : rot;
+        if (col >= H) col -= H;
+        const long long idx = (long long)m * H + col;
+        s0[j] = __ldcg(P + idx);
+        s1[j] = __ldcg(P + idx + stride);
+        gn[j] = __bfloat162float(gain[col]);
+      }
+#pragma unroll
+      for (int j = 0; j < PB; ++j) {
+        int col = threadIdx.x + j * THREADS;
+        if (col < H) {
+          col += rot;
+          if (col >= H) col -= H;
+          const int extra = two[col >> 4];
+          float s = s0[j];
+          if (extra > 0) s += s1[j];
+          for (int k = 2; k <= extra; ++k) s += __ldcg(P + (long long)m * H + col + (long long)k * stride);
+          c.resid[m * H + col] =
+              __float2bfloat16_rn(__bfloat162float(c.resid[m * H + col]) + bf16_round(s));
+          c.xs[m * H + col] = __float2bfloat16_rn(gn[j]);        // gain parked next to its column
+        }
+      }
+      __syncthreads();
+      STAMP(18);
+      // fixed column order from here on: every CTA computes bit-identical sums
+      float ss = 0.f;
+      for (int col = threadIdx.x; col < H; col += THREADS) {
+        const float f = __bfloat162float(c.resid[m * H + col]);
+        ss += f * f;
+      }
+      ss = block_sum_s(ss, c.scratch);
+      STAMP(19);
+      const float inv = rsqrtf(ss / (float)H + p.eps);
+      for (int col = threadIdx.x; col < H; col += THREADS) {
+        const float v = bf16_round(__bfloat162float(c.resid[m * H + col]) * inv);
+        c.xs[m * H + col] = __float2bfloat16_rn(v * __bfloat162float(c.xs[m * H + col]));
+      }
+      STAMP(20);
+    }
+  } else {
+    for (int m = 0; m < p.M; ++m) {
+      float ss = 0.f;
+      for (int col = threadIdx.x; col < H; col += THREADS) {
+        const float y = bf16_round(psum_cg(P, pl, stride, (long long)m * H + col, col));
+        const bf16 t = __float2bfloat16_rn(__bfloat162float(c.resid[m * H + col]) + y);
+        c.resid[m * H + col] = t;
+        const float f = __bfloat162float(t);
+        ss += f * f;
+      }
+      ss = block_sum_s(ss, c.scratch);
+      scale_row_to_xs(p, c, gain, H, m, ss);
+    }
+  }
+  __syncthreads();
+  STAMP(21);
 }
 
 __device__ __noinline__ void stage_x(const mega_params_t& p, Ctx& c, const bf16* src, int K) {
@@ -404,7 +509,7 @@ __device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, con
   if ((int)blockIdx.x >= items) return;
   const int bh = blockIdx.x / S, split = blockIdx.x % S;
   const int b = bh / nkv, kh = bh % nkv;
-  const int pos = p.pos[0];
+  const int pos = c.pos;
   const int max_limit = pos + 1;
   const int tiles_used = (max_limit + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
   const int per = (tiles_used + S - 1) / S;
@@ -414,6 +519,7 @@ __device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, con
   const int new_tile = pos / Q_PAGE_TOKENS, new_row = pos % Q_PAGE_TOKENS;
   const bool owns_new = ntiles > 0 && new_tile >= tile0 && new_tile < tile1;
 
+  STAMP(22);
   unsigned char* stages = c.ring;                         // ATT_NS * ATT_STAGE = 96 KB
   unsigned char* qtile = c.ring + ATT_NS * ATT_STAGE;     // 16 rows * 256 B
   const uint32_t abar = smem_u32(c.abars);
@@ -442,25 +548,40 @@ __device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, con
       const bool is_q = h < G;
       const int head = is_q ? kh * G + h : nq + kh;          // column block in the packed projection
       const long long src = (long long)b * width + (long long)head * 128;
-      float x[4], ss = 0.f;
+      float x[4], gv[4], ss = 0.f;
+      {
+        // a head's 128 columns sit in 8 consecutive 16-column groups of one partial plan:
+        // issue the eight loads of this lane together
+        float s0[4], s1[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int d = lane + 32 * j;
-        x[j] = bf16_round(psum_cg(PQ, p.qkv, stride, src + d, head * 128 + d));
-        ss += x[j] * x[j];
+        for (int j = 0; j < 4; ++j) {
+          s0[j] = __ldcg(PQ + src + lane + 32 * j);
+          s1[j] = __ldcg(PQ + src + lane + 32 * j + stride);
+          gv[j] = __bfloat162float((is_q ? L.q_gain : L.k_gain)[lane + 32 * j]);
+        }
+        const unsigned Cq = (unsigned)p.qkv.C, uq = (unsigned)p.qkv.U;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int n = head * 128 + lane + 32 * j;
+          const unsigned gq = (unsigned)n >> 4;
+          const unsigned first = (gq * Cq) / uq, last = ((gq + 1) * Cq - 1) / uq;
+          float s = s0[j];
+          if (last > first) s += s1[j];
+          for (unsigned k = 2; k <= last - first; ++k) s += __ldcg(PQ + src + lane + 32 * j + (long long)k * stride);
+          x[j] = bf16_round(s);
+          ss += x[j] * x[j];
+        }
       }
       ss = warp_sum(ss);
       const float inv = rsqrtf(ss / 128.f + eps);
-      const bf16* gain = is_q ? L.q_gain : L.k_gain;
       float n[4], out[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        n[j] = bf16_round(bf16_round(x[j] * inv) * __bfloat162float(gain[lane + 32 * j]));
+      for (int j = 0; j < 4; ++j) n[j] = bf16_round(bf16_round(x[j] * inv) * gv[j]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int d = lane + 32 * j;
-        const float cs = __bfloat162float(p.cos[(size_t)pos * 128 + d]);
-        const float sn = __bfloat162float(p.sin[(size_t)pos * 128 + d]);
+        const float cs = __bfloat162float(c.cosrow[d]);
+        const float sn = __bfloat162float(c.sinrow[d]);
         const float rot = (j < 2) ? -n[j + 2] : n[j - 2];
         out[j] = bf16_round(n[j] * cs) + bf16_round(rot * sn);
       }
@@ -487,6 +608,7 @@ __device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, con
     }
   }
   __syncthreads();
+  STAMP(23);
   if (owns_new && tid < 32) {
     // the newest key/value row goes to its page for later steps (16 lanes x 16 B each)
     const int page = p.block_table[(size_t)b * p.pages_per_seq + new_tile];
@@ -550,9 +672,12 @@ __device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, con
       }
       __syncwarp();
       const uint32_t k_base = smem_u32(kt), v_base = smem_u32(vt);
-      float sacc[2][4];
+      float sacc[2][4], sodd[2][4];    // even / odd k steps: two independent MMA chains per key tile
 #pragma unroll
-      for (int j = 0; j < 2; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+      for (int j = 0; j < 2; ++j) {
+        sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+        sodd[j][0] = sodd[j][1] = sodd[j][2] = sodd[j][3] = 0.f;
+      }
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
@@ -567,9 +692,18 @@ __device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, con
           const int ch = 2 * ks + (mi & 1);
           ldsm_x4(k_base + key * 256 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
         }
-        mma16816(sacc[0], a0, a1, a2, a3, b0, b1);
-        mma16816(sacc[1], a0, a1, a2, a3, b2, b3);
+        if (ks & 1) {
+          mma16816(sodd[0], a0, a1, a2, a3, b0, b1);
+          mma16816(sodd[1], a0, a1, a2, a3, b2, b3);
+        } else {
+          mma16816(sacc[0], a0, a1, a2, a3, b0, b1);
+          mma16816(sacc[1], a0, a1, a2, a3, b2, b3);
+        }
       }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sacc[j][e] += sodd[j][e];
       float pr[2][4];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -621,6 +755,7 @@ __device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, con
       if (lane == 0) mbar_arrive(abar + 8 * (ATT_NS + slot));
     }
     // park the warp's state for the CTA merge (after the ring is idle)
+    STAMP(24);
     asm volatile("bar.sync 1, 128;" ::: "memory");
     float* mo = reinterpret_cast<float*>(stages);            // [4][16][128]
     float* mml = mo + 4 * 16 * 128;                          // [4][16][2]
@@ -665,6 +800,7 @@ __device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, con
 
   // ---- the last split of this kv head to finish merges all splits ----
   __syncthreads();
+  STAMP(25);
   if (tid == 0) {
     __threadfence();
     const unsigned ticket = atomicAdd(&p.sync[4 + bh], 1u);
@@ -673,6 +809,7 @@ __device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, con
     __threadfence();
   }
   __syncthreads();
+  STAMP(26);
   if (reinterpret_cast<volatile int*>(c.scratch)[40]) {
     for (int r = warp; r < G; r += WARPS) {
       const size_t base = ((size_t)bh * S) * G + r;           // + split * G
@@ -686,11 +823,18 @@ __device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, con
       const float wgt = l > 0.f ? exp2f(m - Mx) : 0.f;
       const float Lsum = warp_sum(wgt * l);
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-      for (int s = 0; s < S; ++s) {
-        const float ws = __shfl_sync(0xffffffffu, wgt, s);
-        const float4 o = __ldcg(reinterpret_cast<const float4*>(p.attn_o + (base + (size_t)s * G) * 128) + lane);
-        acc[0] += ws * o.x; acc[1] += ws * o.y; acc[2] += ws * o.z; acc[3] += ws * o.w;
+      for (int s0 = 0; s0 < S; s0 += 16) {
+        float4 o[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {           // all loads of the batch first
+          const int s = s0 + j < S ? s0 + j : S - 1;
+          o[j] = __ldcg(reinterpret_cast<const float4*>(p.attn_o + (base + (size_t)s * G) * 128) + lane);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float ws = (s0 + j < S) ? __shfl_sync(0xffffffffu, wgt, (s0 + j) & 31) : 0.f;
+          acc[0] += ws * o[j].x; acc[1] += ws * o[j].y; acc[2] += ws * o[j].z; acc[3] += ws * o[j].w;
+        }
       }
       const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
       uint2 packed;
@@ -702,7 +846,7 @@ __device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, con
   __syncthreads();
 }
 
-// ---- SwiGLU phase ------------------------------------------------------------------------
+// ---- SwiGLU phase (spread over the grid) -----------------------------------------------------
 __device__ __noinline__ void swiglu_phase(const mega_params_t& p, const float* PG) {
   const int I = p.I;
   const long long total = (long long)p.M * I, stride = (long long)p.M * 2 * I;
@@ -801,6 +945,8 @@ k_decode_mega(const __grid_constant__ mega_params_t p) {
   c.abars = reinterpret_cast<uint64_t*>(q); q += 2 * ATT_NS * 8;
   c.knew = reinterpret_cast<bf16*>(q); q += 256;
   c.vnew = reinterpret_cast<bf16*>(q); q += 256;
+  c.cosrow = reinterpret_cast<bf16*>(q); q += 256;
+  c.sinrow = reinterpret_cast<bf16*>(q); q += 256;
   c.resid = reinterpret_cast<bf16*>(q); q += (size_t)p.M * p.H * 2;
   c.xs = reinterpret_cast<bf16*>(q);
   c.g_count = 0;
@@ -809,6 +955,11 @@ k_decode_mega(const __grid_constant__ mega_params_t p) {
   c.epoch = 0;
 
   const int tid = threadIdx.x;
+  c.pos = p.pos[0];
+  if (tid < 128) {
+    c.cosrow[tid] = p.cos[(size_t)c.pos * 128 + tid];
+    c.sinrow[tid] = p.sin[(size_t)c.pos * 128 + tid];
+  }
   if (tid == 0) {
     for (int i = 0; i < WARPS * STAGES; ++i) mbar_init(smem_u32(&c.gbars[i]), 1);
     for (int i = 0; i < ATT_NS; ++i) {
@@ -833,7 +984,10 @@ k_decode_mega(const __grid_constant__ mega_params_t p) {
     // A: QKV projection (operand xs = normed hidden, prepared by the previous prologue)
     c.trace_gemm = tracing ? 1 : 0;
     gemm_run(run, p.qkv, p.M, c.xs, buf0, c);
-    c.trace_gemm = 0;
+    if (p.prefetch_units > 0) {          // attention is long: O-proj and gate|up can come in behind it
+      l2_prefetch_run(Lw.wo, p.o, 0, p.prefetch_units);
+      l2_prefetch_run(Lw.wgu, p.gu, 0, p.prefetch_units);
+    }
     TRACE(1);
     grid_barrier(p, c);
     TRACE(2);
@@ -853,10 +1007,12 @@ k_decode_mega(const __grid_constant__ mega_params_t p) {
     TRACE(7);
     // D: add + norm, gate|up projection
     prologue_add_norm(p, c, buf1, p.o, Lw.ln_post);
+    c.trace_gemm = 0;
     TRACE(8);
     gemm_run(run, p.gu, p.M, c.xs, buf0, c);
     TRACE(9);
     run = gemm_prime(Lw.wdown, p.down, c);
+    if (p.prefetch_units > 0) l2_prefetch_run(Lw.wdown, p.down, STAGES * STAGE_UNITS, p.prefetch_units);
     grid_barrier(p, c);
     TRACE(10);
     // E: SwiGLU
@@ -871,6 +1027,10 @@ k_decode_mega(const __grid_constant__ mega_params_t p) {
     TRACE(14);
     const bool last = (l + 1 == p.L);
     run = last ? gemm_prime(p.lm_head, p.head, c) : gemm_prime(p.layers[l + 1].wqkv, p.qkv, c);
+    if (p.prefetch_units > 0) {
+      if (last) l2_prefetch_run(p.lm_head, p.head, STAGES * STAGE_UNITS, p.prefetch_units);
+      else l2_prefetch_run(p.layers[l + 1].wqkv, p.qkv, STAGES * STAGE_UNITS, p.prefetch_units);
+    }
     grid_barrier(p, c);
     TRACE(15);
     prologue_add_norm(p, c, buf1, p.down, last ? p.ln_final : p.layers[l + 1].ln_in);
@@ -894,7 +1054,7 @@ int q_mega_status_read(int32_t out[4]) {
 
 size_t q_mega_smem_bytes(int M, int H, int xs_cols) {
   return (size_t)RING_BYTES + RED_FLOATS * 4 + 64 * 4 + WARPS * 2 * 4 + WARPS * STAGES * 8 + 2 * ATT_NS * 8 +
-         512 + (size_t)M * H * 2 + (size_t)M * xs_cols * 2 + 64;
+         1024 + (size_t)M * H * 2 + (size_t)M * xs_cols * 2 + 64;
 }
 
 cudaError_t q_mega_launch(const mega_params_t& p, int grid, cudaStream_t stream) {

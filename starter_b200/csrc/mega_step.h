@@ -14,7 +14,7 @@ struct mega_layer_t {
 };
 
 struct mega_params_t {
-  int M, H, I, L, nq, nkv, V, full_vocab, pages_per_seq, attn_S, xs_cols, trace_layer;
+  int M, H, I, L, nq, nkv, V, full_vocab, pages_per_seq, attn_S, xs_cols, trace_layer, prefetch_units;
   float eps, scale_log2;
   const mega_layer_t* layers;                        // device array [L]
   const unsigned char* embed;
