@@ -297,6 +297,8 @@ def time_gemm_kernel(state, reps: int = 5):
 
 
 def kernels_per_step(state) -> int:
+    if state.fused_scratch is not None and os.environ.get("QDECODE_FUSED", "1") != "0":
+        return 1                              # the persistent whole-step kernel
     per_layer = 9 + (1 if state.attn_splits > 1 else 0)
     n = 1 + state.cfg.n_layers * per_layer + 2
     if state.tp > 1:
@@ -395,9 +397,22 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                 "tpot_ms": 1e3 * (stamps[-1] - stamps[0]) / max(1, n_new - 1),
             }
 
+    def teardown():
+        """NCCL communicators must not be torn down while captured graphs that hold
+        their kernels are alive; a timer forces the exit if teardown still stalls."""
+        if world == 1:
+            return
+        engine.decode_state = None
+        state.graph = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        threading.Timer(20.0, os._exit, [0]).start()
+        dist.destroy_process_group()
+
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        teardown()
         return
 
     peaks_file = ROOT / "MEASURED_PEAKS.json"
@@ -437,8 +452,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                       f"{min(prompt_len, args.cpu_prompt)} tokens (untimed prefill), {r['steps']} timed decode steps",
         }
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    teardown()
 
 
 def main() -> None:

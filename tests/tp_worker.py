@@ -1,0 +1,45 @@
+"""One rank of a tensor-parallel engine run (launched by tests/test_tp_gpu.py through
+torch.distributed.run). Rank 0 writes the generated tokens as JSON."""
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+
+def main():
+    import faulthandler
+    # a stuck collective shows up as a stack dump instead of a silent wait
+    faulthandler.dump_traceback_later(int(os.environ.get("TP_DUMP_AFTER", "120")), exit=True)
+    model_dir, out_path, cases = sys.argv[1], sys.argv[2], json.loads(sys.argv[3])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    from starter_b200 import Engine, _lib
+    if os.environ.get("TP_NO_PDL"):
+        _lib.check(_lib.lib.q_set_pdl(0))
+    engine = Engine(model_dir, device=f"cuda:{local}", group=dist.group.WORLD)
+    if os.environ.get("TP_NO_GRAPH"):
+        from starter_b200.decode import DecodeState
+        DecodeState.capture = lambda self: None
+    out = []
+    for prompt, n in cases:
+        out.append(list(engine.generate(prompt, n)))
+    if dist.get_rank() == 0:
+        Path(out_path).write_text(json.dumps(out))
+    # captured graphs hold NCCL kernels: drop them before the communicator goes away
+    engine.decode_state = None
+    del engine
+    torch.cuda.synchronize()
+    dist.barrier()
+    import threading
+    threading.Timer(20.0, os._exit, [0]).start()      # a stalled teardown must not hang the test
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
