@@ -108,6 +108,24 @@ int q_gemm_splitk(const void* d_x, const void* d_w_tiled, float* d_partials,
 int q_reduce_partials(const float* d_partials, const q_gemm_plan_t* plan,
                       float* d_out, void* stream);
 
+/* No counterpart in the reference. d_out[M][N] (fp32) = X . W^T, i.e. q_gemm_splitk
+ * followed by q_reduce_partials, for callers that may not allocate device memory
+ * (their own pool owns all of it, their runtime forbids allocator calls, or they
+ * run where cudaMalloc would stall the device): the partial sums live in a static
+ * array inside the library instead of a caller buffer. Limits and rules:
+ *   - slots * M * N must not exceed q_static_scratch_floats() (327,680 floats,
+ *     1.25 MB per GPU, held from library load to process exit); larger shapes
+ *     return Q_ERR_ARG and belong to q_gemm_splitk with a caller buffer;
+ *   - the first call on each device looks up the array's address (with that
+ *     device current) and caches it: make that first call outside any stream
+ *     capture;
+ *   - all calls share the one array, which keeps the previous call's partials:
+ *     calls that overlap on the GPU (different streams) race; order them;
+ *   - it calls no allocator of any kind. */
+int64_t q_static_scratch_floats(void);
+int q_linear_f32_static(const void* d_x, const void* d_w_tiled, float* d_out,
+                        int M, int N, int K, void* stream);
+
 /* ---- fused element-wise consumers ----------------------------------------*/
 
 /* engine/kernels/rmsnorm.py:39-62 (rms_norm): out = bf16(x*rsqrt(mean x^2+eps))*w */

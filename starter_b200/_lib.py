@@ -79,6 +79,8 @@ SIGNATURES = {
     "q_unpack_weight": (_I, [_P, _P, _I, _I, _P]),
     "q_gemm_splitk": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "q_reduce_partials": (_I, [_P, _PLAN, _P, _P]),
+    "q_static_scratch_floats": (C.c_int64, []),
+    "q_linear_f32_static": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "q_rmsnorm": (_I, [_P, _P, _P, _I, _I, _F, _P]),
     "q_embed_rmsnorm": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
     "q_add_rmsnorm": (_I, [_P, _P, _PLAN, _P, _P, _P, _I, _I, _F, _P]),

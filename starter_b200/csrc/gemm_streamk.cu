@@ -477,6 +477,60 @@ extern "C" int q_gemm_splitk(const void* d_x, const void* d_w_tiled, float* d_pa
   return Q_OK;
 }
 
+// ---- projection without any allocation: partials in a library-owned static array ----
+//
+// Some hosts of this library must not allocate device memory at all: a serving
+// loop that has handed every byte to its own pool allocator, a plugin whose
+// runtime gives it buffers but forbids calls into the CUDA allocator, or code that
+// runs while a stream is being captured or inside a latency-critical section,
+// where cudaMalloc/cudaFree would synchronise the whole device. For them the
+// split-K partials (the GEMM's only scratch memory) live in this fixed array
+// instead of a caller buffer. The array costs Q_STATIC_SCRATCH_FLOATS * 4 bytes
+// on every GPU that loads the library, until the process exits.
+#define Q_STATIC_SCRATCH_FLOATS (2 * 8 * 20480)
+static __device__ __align__(256) float g_static_partials[Q_STATIC_SCRATCH_FLOATS];
+
+// In host code `g_static_partials` is only a handle for the runtime, not a device
+// address: the real address is asked for once per device, with that device
+// current, and cached.
+static int static_scratch_address(float** out) {
+  static float* cached[64] = {nullptr};
+  int dev = -1;
+  Q_CHECK_CUDA(cudaGetDevice(&dev));
+  Q_CHECK_ARG(dev >= 0 && dev < 64, "q_linear_f32_static: device index %d not supported", dev);
+  if (!cached[dev]) {
+    void* p = nullptr;
+    Q_CHECK_CUDA(cudaGetSymbolAddress(&p, g_static_partials));
+    Q_CHECK_ARG(p != nullptr, "q_linear_f32_static: no address for the static scratch");
+    cached[dev] = (float*)p;
+  }
+  *out = cached[dev];
+  return Q_OK;
+}
+
+extern "C" int64_t q_static_scratch_floats(void) { return Q_STATIC_SCRATCH_FLOATS; }
+
+extern "C" int q_linear_f32_static(const void* d_x, const void* d_w_tiled, float* d_out, int M, int N,
+                                   int K, void* stream) {
+  Q_CHECK_ARG(d_x && d_w_tiled && d_out, "q_linear_f32_static: null pointer");
+  q_gemm_plan_t p;
+  int rc = q_gemm_plan(M, N, K, &p);
+  if (rc) return rc;
+  const long long need = (long long)p.slots * M * N;
+  Q_CHECK_ARG(need <= Q_STATIC_SCRATCH_FLOATS,
+              "q_linear_f32_static: %d x %d output needs %lld scratch floats, the static array holds %d "
+              "(use q_gemm_splitk with a caller buffer for larger shapes)",
+              M, N, need, Q_STATIC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  // Every slot that a consumer reads is rewritten by the GEMM of this call, so nothing
+  // has to be cleared; the array keeps the last call's partials afterwards.
+  rc = q_gemm_splitk(d_x, d_w_tiled, scratch, M, N, K, stream);
+  if (rc) return rc;
+  return q_reduce_partials(scratch, &p, d_out, stream);
+}
+
 extern "C" int q_reduce_partials(const float* d_partials, const q_gemm_plan_t* plan,
                                  float* d_out, void* stream) {
   Q_CHECK_ARG(d_partials && plan && d_out, "q_reduce_partials: null pointer");
