@@ -374,6 +374,7 @@ __device__ __forceinline__ size_t tiled_elem(long long row, int col, int C) {
 }
 
 constexpr int PB = 12;  // columns per thread whose global loads are issued together (3072 per batch)
+constexpr int VB = 4;   // float4 batches per thread in the add+norm vector path (4096 columns)
 
 __device__ __noinline__ void prologue_embed(const mega_params_t& p, Ctx& c, const bf16* gain) {
   const int H = p.H, C = H >> 5;
@@ -425,51 +426,59 @@ __device__ __noinline__ void prologue_add_norm(const mega_params_t& p, Ctx& c, c
     two[gi] = (int)(last - first);
   }
   __syncthreads();
-  if (H <= THREADS * PB && (H >> 4) <= RED_FLOATS) {
-    // Every CTA reads the same few KB: start each CTA at a different 128-byte line so that
-    // the requests spread over the L2 slices instead of queueing on one line at a time.
-    const int rot = (int)((blockIdx.x * 37u) % (unsigned)(H >> 5)) << 5;
+  if (H <= THREADS * 4 * VB && (H & 3) == 0 && (H >> 4) <= RED_FLOATS) {
+    // Vector path: thread t owns columns 4t..4t+3 (+1024 j): float4 loads of both slots
+    // and an 8-byte load of the gains, all issued before anything is used.
     for (int m = 0; m < p.M; ++m) {
-      float s0[PB], s1[PB], gn[PB];
+      float4 s0[VB], s1[VB];
+      uint2 gn[VB];
 #pragma unroll
-      for (int j = 0; j < PB; ++j) {
-        int col = threadIdx.x + j * THREADS;
-        col = col < H ? col + rot : rot;
-        if (col >= H) col -= H;
-        const long long idx = (long long)m * H + col;
-        s0[j] = __ldcg(P + idx);
-        s1[j] = __ldcg(P + idx + stride);
-        gn[j] = __bfloat162float(gain[col]);
+      for (int j = 0; j < VB; ++j) {
+        const int col = 4 * threadIdx.x + j * THREADS * 4;
+        const int cc = col < H ? col : 0;
+        s0[j] = __ldcg(reinterpret_cast<const float4*>(P + (long long)m * H + cc));
+        s1[j] = __ldcg(reinterpret_cast<const float4*>(P + (long long)m * H + cc + stride));
+        gn[j] = *reinterpret_cast<const uint2*>(gain + cc);
       }
+      float tot[VB][4];
+      float ss = 0.f;
 #pragma unroll
-      for (int j = 0; j < PB; ++j) {
-        int col = threadIdx.x + j * THREADS;
+      for (int j = 0; j < VB; ++j) {
+        const int col = 4 * threadIdx.x + j * THREADS * 4;
         if (col < H) {
-          col += rot;
-          if (col >= H) col -= H;
-          const int extra = two[col >> 4];
-          float s = s0[j];
-          if (extra > 0) s += s1[j];
-          for (int k = 2; k <= extra; ++k) s += __ldcg(P + (long long)m * H + col + (long long)k * stride);
-          c.resid[m * H + col] =
-              __float2bfloat16_rn(__bfloat162float(c.resid[m * H + col]) + bf16_round(s));
-          c.xs[m * H + col] = __float2bfloat16_rn(gn[j]);        // gain parked next to its column
+          const int extra = two[col >> 4];       // the 4 columns share one 16-column group
+          float s[4] = {s0[j].x, s0[j].y, s0[j].z, s0[j].w};
+          if (extra > 0) { s[0] += s1[j].x; s[1] += s1[j].y; s[2] += s1[j].z; s[3] += s1[j].w; }
+          for (int k = 2; k <= extra; ++k) {
+            const float4 sk = __ldcg(reinterpret_cast<const float4*>(P + (long long)m * H + col + (long long)k * stride));
+            s[0] += sk.x; s[1] += sk.y; s[2] += sk.z; s[3] += sk.w;
+          }
+          const uint2 rr = *reinterpret_cast<const uint2*>(c.resid + m * H + col);
+          const float r[4] = {bf_lo(rr.x), bf_hi(rr.x), bf_lo(rr.y), bf_hi(rr.y)};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            tot[j][e] = bf16_round(r[e] + bf16_round(s[e]));
+            ss += tot[j][e] * tot[j][e];
+          }
         }
       }
-      __syncthreads();
       STAMP(18);
-      // fixed column order from here on: every CTA computes bit-identical sums
-      float ss = 0.f;
-      for (int col = threadIdx.x; col < H; col += THREADS) {
-        const float f = __bfloat162float(c.resid[m * H + col]);
-        ss += f * f;
-      }
       ss = block_sum_s(ss, c.scratch);
       STAMP(19);
       const float inv = rsqrtf(ss / (float)H + p.eps);
-      for (int col = threadIdx.x; col < H; col += THREADS) {
-        const float v = bf16_round(__bfloat162float(c.resid[m * H + col]) * inv);
-        c.xs[m * H + col] = __float2bfloat16_rn(v * __bfloat162float(c.xs[m * H + col]));
+#pragma unroll
+      for (int j = 0; j < VB; ++j) {
+        const int col = 4 * threadIdx.x + j * THREADS * 4;
+        if (col < H) {
+          const float g4[4] = {bf_lo(gn[j].x), bf_hi(gn[j].x), bf_lo(gn[j].y), bf_hi(gn[j].y)};
+          uint2 ro, xo;
+          ro.x = pack_bf16(tot[j][0], tot[j][1]);
+          ro.y = pack_bf16(tot[j][2], tot[j][3]);
+          xo.x = pack_bf16(bf16_round(tot[j][0] * inv) * g4[0], bf16_round(tot[j][1] * inv) * g4[1]);
+          xo.y = pack_bf16(bf16_round(tot[j][2] * inv) * g4[2], bf16_round(tot[j][3] * inv) * g4[3]);
+          *reinterpret_cast<uint2*>(c.resid + m * H + col) = ro;
+          *reinterpret_cast<uint2*>(c.xs + m * H + col) = xo;
+        }
       }
       STAMP(20);
     }
@@ -540,65 +549,63 @@ __device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, con
   }
 
   // ---- q/k head norm + RoPE (+ v), from the QKV partials ----
+  // One warp per head; lane l owns dims 4l..4l+3 (one float4 per slot), the rotate-half
+  // partner dims (d +- 64) live in lane l ^ 16.
   {
     const int width = (nq + 2 * nkv) * 128;
     const long long stride = (long long)p.M * width;
     const float eps = p.eps;
-    for (int h = warp; h < G + 1; h += WARPS) {
-      const bool is_q = h < G;
-      const int head = is_q ? kh * G + h : nq + kh;          // column block in the packed projection
-      const long long src = (long long)b * width + (long long)head * 128;
-      float x[4], gv[4], ss = 0.f;
-      {
-        // a head's 128 columns sit in 8 consecutive 16-column groups of one partial plan:
-        // issue the eight loads of this lane together
-        float s0[4], s1[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          s0[j] = __ldcg(PQ + src + lane + 32 * j);
-          s1[j] = __ldcg(PQ + src + lane + 32 * j + stride);
-          gv[j] = __bfloat162float((is_q ? L.q_gain : L.k_gain)[lane + 32 * j]);
-        }
-        const unsigned Cq = (unsigned)p.qkv.C, uq = (unsigned)p.qkv.U;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int n = head * 128 + lane + 32 * j;
-          const unsigned gq = (unsigned)n >> 4;
-          const unsigned first = (gq * Cq) / uq, last = ((gq + 1) * Cq - 1) / uq;
-          float s = s0[j];
-          if (last > first) s += s1[j];
-          for (unsigned k = 2; k <= last - first; ++k) s += __ldcg(PQ + src + lane + 32 * j + (long long)k * stride);
-          x[j] = bf16_round(s);
-          ss += x[j] * x[j];
-        }
+    const unsigned Cq = (unsigned)p.qkv.C, uq = (unsigned)p.qkv.U;
+    for (int h = warp; h < G + 2; h += WARPS) {
+      const bool is_q = h < G, is_v = h == G + 1;
+      const int head = is_q ? kh * G + h : (is_v ? nq + nkv + kh : nq + kh);   // column block
+      const long long src = (long long)b * width + (long long)head * 128 + 4 * lane;
+      const float4 s0 = __ldcg(reinterpret_cast<const float4*>(PQ + src));
+      const float4 s1 = __ldcg(reinterpret_cast<const float4*>(PQ + src + stride));
+      const uint2 graw = is_v ? make_uint2(0, 0)
+                              : *reinterpret_cast<const uint2*>((is_q ? L.q_gain : L.k_gain) + 4 * lane);
+      const unsigned gq = (unsigned)(head * 128 + 4 * lane) >> 4;
+      const unsigned first = (gq * Cq) / uq, last = ((gq + 1) * Cq - 1) / uq;
+      float x[4] = {s0.x, s0.y, s0.z, s0.w};
+      if (last > first) { x[0] += s1.x; x[1] += s1.y; x[2] += s1.z; x[3] += s1.w; }
+      for (unsigned k = 2; k <= last - first; ++k) {
+        const float4 sk = __ldcg(reinterpret_cast<const float4*>(PQ + src + (long long)k * stride));
+        x[0] += sk.x; x[1] += sk.y; x[2] += sk.z; x[3] += sk.w;
       }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x[e] = bf16_round(x[e]);
+      if (is_v) {
+        uint2 o;
+        o.x = pack_bf16(x[0], x[1]);
+        o.y = pack_bf16(x[2], x[3]);
+        *reinterpret_cast<uint2*>(c.vnew + 4 * lane) = o;
+        continue;
+      }
+      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
       ss = warp_sum(ss);
       const float inv = rsqrtf(ss / 128.f + eps);
-      float n[4], out[4];
+      const float gv[4] = {bf_lo(graw.x), bf_hi(graw.x), bf_lo(graw.y), bf_hi(graw.y)};
+      const uint2 craw = *reinterpret_cast<const uint2*>(c.cosrow + 4 * lane);
+      const uint2 sraw = *reinterpret_cast<const uint2*>(c.sinrow + 4 * lane);
+      const float cs[4] = {bf_lo(craw.x), bf_hi(craw.x), bf_lo(craw.y), bf_hi(craw.y)};
+      const float sn[4] = {bf_lo(sraw.x), bf_hi(sraw.x), bf_lo(sraw.y), bf_hi(sraw.y)};
+      float out[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) n[j] = bf16_round(bf16_round(x[j] * inv) * gv[j]);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int d = lane + 32 * j;
-        const float cs = __bfloat162float(c.cosrow[d]);
-        const float sn = __bfloat162float(c.sinrow[d]);
-        const float rot = (j < 2) ? -n[j + 2] : n[j - 2];
-        out[j] = bf16_round(n[j] * cs) + bf16_round(rot * sn);
+      for (int e = 0; e < 4; ++e) {
+        const float n = bf16_round(bf16_round(x[e] * inv) * gv[e]);
+        const float partner = __shfl_xor_sync(0xffffffffu, n, 16);
+        const float rot = lane < 16 ? -partner : partner;     // dims < 64 take -x[d+64]
+        out[e] = bf16_round(n * cs[e]) + bf16_round(rot * sn[e]);
       }
+      uint2 o;
+      o.x = pack_bf16(out[0], out[1]);
+      o.y = pack_bf16(out[2], out[3]);
       if (is_q) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int d = lane + 32 * j;
-          *reinterpret_cast<bf16*>(qtile + kv_tile_offset_bytes(h, d)) = __float2bfloat16_rn(out[j]);
-        }
+        // dims 4l..4l+3 sit in 16-byte chunk l/2 of query row h (rows are swizzled like KV tiles)
+        const int ch = lane >> 1;
+        *reinterpret_cast<uint2*>(qtile + h * 256 + ((ch ^ (h & 7)) << 4) + (lane & 1) * 8) = o;
       } else {
-        const long long vsrc = (long long)b * width + (long long)(nq + nkv + kh) * 128;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int d = lane + 32 * j;
-          c.knew[d] = __float2bfloat16_rn(out[j]);
-          c.vnew[d] = __float2bfloat16_rn(psum_cg(PQ, p.qkv, stride, vsrc + d, (nq + nkv + kh) * 128 + d));
-        }
+        *reinterpret_cast<uint2*>(c.knew + 4 * lane) = o;
       }
     }
     // rows G..15 of the query tile are zero
@@ -849,7 +856,46 @@ __device__ __noinline__ void attention_phase(const mega_params_t& p, Ctx& c, con
 // ---- SwiGLU phase (spread over the grid) -----------------------------------------------------
 __device__ __noinline__ void swiglu_phase(const mega_params_t& p, const float* PG) {
   const int I = p.I;
-  const long long total = (long long)p.M * I, stride = (long long)p.M * 2 * I;
+  const long long stride = (long long)p.M * 2 * I;
+  const unsigned C = (unsigned)p.gu.C, u = (unsigned)p.gu.U;
+  if ((I & 3) == 0) {
+    const long long quads = (long long)p.M * (I >> 2);
+    for (long long qd = (long long)blockIdx.x * THREADS + threadIdx.x; qd < quads;
+         qd += (long long)gridDim.x * THREADS) {
+      const int m = (int)(qd / (I >> 2)), col = (int)(qd % (I >> 2)) * 4;
+      const long long base = (long long)m * 2 * I;
+      const float4 g0 = __ldcg(reinterpret_cast<const float4*>(PG + base + col));
+      const float4 g1 = __ldcg(reinterpret_cast<const float4*>(PG + base + col + stride));
+      const float4 u0 = __ldcg(reinterpret_cast<const float4*>(PG + base + I + col));
+      const float4 u1 = __ldcg(reinterpret_cast<const float4*>(PG + base + I + col + stride));
+      const unsigned gg = (unsigned)col >> 4, gu2 = (unsigned)(I + col) >> 4;
+      const unsigned eg = ((gg + 1) * C - 1) / u - (gg * C) / u;
+      const unsigned eu = ((gu2 + 1) * C - 1) / u - (gu2 * C) / u;
+      float gs[4] = {g0.x, g0.y, g0.z, g0.w}, us[4] = {u0.x, u0.y, u0.z, u0.w};
+      if (eg > 0) { gs[0] += g1.x; gs[1] += g1.y; gs[2] += g1.z; gs[3] += g1.w; }
+      if (eu > 0) { us[0] += u1.x; us[1] += u1.y; us[2] += u1.z; us[3] += u1.w; }
+      for (unsigned k = 2; k <= eg; ++k) {
+        const float4 t = __ldcg(reinterpret_cast<const float4*>(PG + base + col + (long long)k * stride));
+        gs[0] += t.x; gs[1] += t.y; gs[2] += t.z; gs[3] += t.w;
+      }
+      for (unsigned k = 2; k <= eu; ++k) {
+        const float4 t = __ldcg(reinterpret_cast<const float4*>(PG + base + I + col + (long long)k * stride));
+        us[0] += t.x; us[1] += t.y; us[2] += t.z; us[3] += t.w;
+      }
+      float o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float gt = bf16_round(gs[e]), up = bf16_round(us[e]);
+        o[e] = bf16_round(gt / (1.0f + expf(-gt))) * up;
+      }
+      uint2 pk;
+      pk.x = pack_bf16(o[0], o[1]);
+      pk.y = pack_bf16(o[2], o[3]);
+      *reinterpret_cast<uint2*>(p.act + (long long)m * I + col) = pk;
+    }
+    return;
+  }
+  const long long total = (long long)p.M * I;
   for (long long i = (long long)blockIdx.x * THREADS + threadIdx.x; i < total; i += (long long)gridDim.x * THREADS) {
     const int m = (int)(i / I), col = (int)(i % I);
     const long long base = (long long)m * 2 * I;
