@@ -191,7 +191,7 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
 
   // mma.sync has a long latency on this part (~280 cycles): consecutive MMAs go to
   // SETS independent accumulators, added when a 16-row group (or the run) ends.
-  constexpr int SETS = NT == 1 ? 8 : (NT == 2 ? 4 : 2);
+  constexpr int SETS = NT == 1 ? 8 : (NT == 2 ? 4 : 2);   // <= 2 * XB
   float acc[SETS][NT][4];
 #pragma unroll
   for (int s = 0; s < SETS; ++s)
@@ -200,8 +200,9 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
   int group = ws / C;
   int chunk = ws - group * C;
   int seg_first_chunk = chunk;          // first chunk of the current segment
-  int n_boundary = 0;
+  int n_boundary = 0, units_done = 0;
   bool alive = true;
+  constexpr int XB = NT == 1 ? 8 : (NT == 2 ? 4 : (NT == 4 ? 2 : 1));   // units per activation batch
 
   for (int st = 0; st < n_stages && alive; ++st) {
     const int sidx = st % STAGES;
@@ -212,40 +213,42 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
     }
     if (trace && st == 0) g_gemm_trace[blockIdx.x * 5 + 2] = gtime();
     const int in_stage = min(STAGE_UNITS, n_units - st * STAGE_UNITS);
-    const uint32_t sbase = ring + sidx * (STAGE_UNITS * 1024) + lane * 16;
-    // activation fragments of the whole stage first, so that their latencies overlap
-    uint4 xs[STAGE_UNITS][NT];
-    {
-      int ch = chunk;
+    uint32_t sbase = ring + sidx * (STAGE_UNITS * 1024) + lane * 16;
+    int done = 0;
+    while (done < in_stage) {
+      // up to XB units that lie inside one 16-row group; their activation fragments are
+      // requested together so that the (L1/L2) latencies overlap, then the MMAs run
+      const int n = min(min(in_stage - done, C - chunk), XB);
+      uint4 xs[XB][NT];
 #pragma unroll
-      for (int i = 0; i < STAGE_UNITS; ++i) {
-        const int koff = ch * 32 + t * 8;
+      for (int j = 0; j < XB; ++j) {
+        const int koff = (chunk + j) * 32 + t * 8;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const int m = nt * 8 + g;
-          xs[i][nt] = make_uint4(0, 0, 0, 0);
-          if (i < in_stage && m < M && !(dbg & 3)) xs[i][nt] = ldg_cached(X + (size_t)m * K + koff);
-        }
-        ch = ch + 1 == C ? 0 : ch + 1;
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < STAGE_UNITS; ++i) {
-      if (i >= in_stage) break;
-      const uint4 a = lds128(sbase + i * 1024), b = lds128(sbase + i * 1024 + 512);
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const uint4 x = xs[i][nt];
-        if (!(dbg & 1)) {
-          mma16816(acc[(2 * i) % SETS][nt], a.x, b.x, a.y, b.y, x.x, x.y);
-          mma16816(acc[(2 * i + 1) % SETS][nt], a.z, b.z, a.w, b.w, x.z, x.w);
-        } else {
-          acc[0][nt][0] += __uint_as_float(a.x ^ b.w);
+          xs[j][nt] = make_uint4(0, 0, 0, 0);
+          if (j < n && m < M && !(dbg & 3)) xs[j][nt] = ldg_cached(X + (size_t)m * K + koff);
         }
       }
-      const bool group_end = (chunk == C - 1);
-      const bool run_end = (st * STAGE_UNITS + i == n_units - 1);
-      if (group_end || run_end) {
+#pragma unroll
+      for (int j = 0; j < XB; ++j) {
+        if (j < n) {
+          const uint4 a = lds128(sbase + j * 1024), b = lds128(sbase + j * 1024 + 512);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint4 x = xs[j][nt];
+            if (!(dbg & 1)) {
+              mma16816(acc[(2 * j) % SETS][nt], a.x, b.x, a.y, b.y, x.x, x.y);
+              mma16816(acc[(2 * j + 1) % SETS][nt], a.z, b.z, a.w, b.w, x.z, x.w);
+            } else {
+              acc[0][nt][0] += __uint_as_float(a.x ^ b.w);
+            }
+          }
+        }
+      }
+      done += n; chunk += n; units_done += n; sbase += n * 1024;
+      const bool group_end = (chunk == C);
+      if (group_end || units_done == n_units) {
         float tot[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
@@ -282,8 +285,8 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
           ++n_boundary;
         }
         seg_first_chunk = 0;
+        if (group_end) { chunk = 0; ++group; }
       }
-      if (group_end) { chunk = 0; ++group; } else { ++chunk; }
     }
     // refill the stage just consumed
     __syncwarp();
