@@ -50,7 +50,7 @@ int q_set_pdl(int enabled);
  *   "gemm_prefetch_kb": L2 prefetch window per GEMM CTA in KB (0 = off, default).
  *   "fused_step": 1 = q_decode_step may use the single persistent kernel (default).
  *   "trace_layer": layer stamped by the whole-step kernel (see q_debug_step_trace), -1 off.
- *   "gemm_debug_flags": measurement aid, results are wrong when non-zero.
+ *   "gemm_debug_flags": measurement aid, 4 = per-CTA time stamps for q_debug_gemm_trace.
  * Unknown names return Q_ERR_ARG. */
 int q_set_option(const char* name, int value);
 

@@ -40,7 +40,7 @@
 #include "common.cuh"
 
 extern int g_gemm_prefetch_kb;   // set through q_set_option
-extern int g_gemm_debug_flags;   // set through q_set_option: 1 = no MMA/X (stream only), 2 = no X loads
+extern int g_gemm_debug_flags;   // set through q_set_option: 4 = record the per-CTA trace
 
 namespace {
 
@@ -203,6 +203,13 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
   int n_boundary = 0, units_done = 0;
   bool alive = true;
   constexpr int XB = NT == 1 ? 8 : (NT == 2 ? 4 : (NT == 4 ? 2 : 1));   // units per activation batch
+  // activation row pointers of this lane (row nt*8+g, k offset 8t), null past M
+  const bf16* xrow[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int m = nt * 8 + g;
+    xrow[nt] = m < M ? X + (size_t)m * K + t * 8 : nullptr;
+  }
 
   for (int st = 0; st < n_stages && alive; ++st) {
     const int sidx = st % STAGES;
@@ -222,12 +229,11 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
       uint4 xs[XB][NT];
 #pragma unroll
       for (int j = 0; j < XB; ++j) {
-        const int koff = (chunk + j) * 32 + t * 8;
+        const int koff = (chunk + j) * 32;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          const int m = nt * 8 + g;
           xs[j][nt] = make_uint4(0, 0, 0, 0);
-          if (j < n && m < M && !(dbg & 3)) xs[j][nt] = ldg_cached(X + (size_t)m * K + koff);
+          if (j < n && xrow[nt] != nullptr) xs[j][nt] = ldg_cached(xrow[nt] + koff);
         }
       }
 #pragma unroll
@@ -237,12 +243,8 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             const uint4 x = xs[j][nt];
-            if (!(dbg & 1)) {
-              mma16816(acc[(2 * j) % SETS][nt], a.x, b.x, a.y, b.y, x.x, x.y);
-              mma16816(acc[(2 * j + 1) % SETS][nt], a.z, b.z, a.w, b.w, x.z, x.w);
-            } else {
-              acc[0][nt][0] += __uint_as_float(a.x ^ b.w);
-            }
+            mma16816(acc[(2 * j) % SETS][nt], a.x, b.x, a.y, b.y, x.x, x.y);
+            mma16816(acc[(2 * j + 1) % SETS][nt], a.z, b.z, a.w, b.w, x.z, x.w);
           }
         }
       }

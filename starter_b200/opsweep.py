@@ -82,7 +82,7 @@ def main() -> None:
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--prefetch-kb", type=int, default=None)
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches")
-    ap.add_argument("--debug-flags", type=int, default=0, help="measurement aid (wrong results)")
+    ap.add_argument("--debug-flags", type=int, default=0, help="measurement aid (4 = per-CTA trace)")
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
     if args.prefetch_kb is not None:
