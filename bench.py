@@ -437,13 +437,23 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         # duration = the CUDA-event time of the timed region / launches
         roofline = {
             "bound": "hbm", "kernel": "k_decode_mega", "achieved": step_gbs, "peak": peak, "unit": "GB/s",
-            "frac": step_gbs / peak, "traffic": args.traffic_bytes, "peak_source": peak_src,
+            "frac": step_gbs / peak,
+            # DRAM bytes per launch: ncu measured 1.012 x the algorithmic bytes on a 4-layer
+            # capture (profiles/k_decode_mega_c2_batch1.md); traffic grows with the layers
+            "traffic": args.traffic_bytes if args.traffic_bytes else 1.012 * step_bytes_rank,
+            "traffic_source": "scaled from a 4-layer ncu capture",
+            "peak_source": peak_src,
             "avg_launch_us": 1e3 * ms_step, "launches_per_step": 1, "bytes_per_launch": step_bytes_rank,
         }
     else:
         roofline = {
             "bound": "hbm", "kernel": "k_gemm_streamk", "achieved": gemm["gbs"], "peak": peak,
-            "unit": "GB/s", "frac": gemm["gbs"] / peak, "traffic": args.traffic_bytes,
+            "unit": "GB/s", "frac": gemm["gbs"] / peak,
+            # ncu on the gate|up launch: read 99.65 MB + write 5 MB for 99.61 MB of weights
+            # (profiles/k_gemm_streamk_gate_up.md)
+            "traffic": args.traffic_bytes if args.traffic_bytes
+            else 1.05 * gemm["bytes_per_step"] / gemm["launches_per_step"],
+            "traffic_source": "scaled from the ncu capture of one gate|up launch",
             "peak_source": peak_src, "avg_launch_us": gemm["avg_launch_us"],
             "launches_per_step": gemm["launches_per_step"],
             "bytes_per_launch": gemm["bytes_per_step"] / gemm["launches_per_step"],

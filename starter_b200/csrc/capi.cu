@@ -86,7 +86,7 @@ extern "C" int q_device_status(int32_t out[4]) {
 }
 
 extern "C" int q_debug_step_trace(unsigned long long* out) {
-  Q_CHECK_ARG(out != nullptr, "q_debug_step_trace: null pointer");
+  Q_CHECK_ARG(out != nullptr, "q_debug_step_trace: null pointer (needs 704 values)");
   Q_CHECK_CUDA(cudaDeviceSynchronize());
   if (q_mega_trace_read(out)) { q_set_error("q_debug_step_trace: read failed"); return Q_ERR_CUDA; }
   return Q_OK;

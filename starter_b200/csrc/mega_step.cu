@@ -51,7 +51,7 @@ constexpr int ATT_NS = 3;
 
 __device__ int g_mega_status[4];
 // Measurement aid: phase time stamps (ns) of layer `trace_layer` for CTAs 0 and 100.
-__device__ unsigned long long g_mega_trace[2 * 32];
+__device__ unsigned long long g_mega_trace[2 * 32 + 4 * 160];
 __device__ __forceinline__ unsigned long long gtime() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -150,13 +150,18 @@ struct Ctx {
   unsigned epoch;             // grid barrier epoch
 };
 
-// ---- grid barrier ----------------------------------------------------------------
-__device__ __noinline__ void grid_barrier(const mega_params_t& p, Ctx& c) {
+// ---- grid barrier (split: arrive, then do independent work, then wait) ------------------
+__device__ __noinline__ void grid_arrive(const mega_params_t& p, Ctx& c) {
   __syncthreads();
   c.epoch += 1;
   if (threadIdx.x == 0) {
     __threadfence();
     atomicAdd(&p.sync[0], 1u);
+  }
+}
+
+__device__ __noinline__ void grid_wait(const mega_params_t& p, Ctx& c) {
+  if (threadIdx.x == 0) {
     const unsigned target = c.epoch * gridDim.x;
     unsigned it = 0;
     // once any wait in this launch has run out, nobody spins again
@@ -170,6 +175,11 @@ __device__ __noinline__ void grid_barrier(const mega_params_t& p, Ctx& c) {
     __threadfence();
   }
   __syncthreads();
+}
+
+__device__ __forceinline__ void grid_barrier(const mega_params_t& p, Ctx& c) {
+  grid_arrive(p, c);
+  grid_wait(p, c);
 }
 
 // ---- GEMM phase --------------------------------------------------------------------
@@ -316,15 +326,29 @@ __device__ __noinline__ void gemm_run(const GemmRun& r, const mega_plan_t& pl, i
   // Ragged ends: the warp that holds the FIRST parked entry of a group adds all entries
   // of that group (fixed order) and writes the CTA's partial of the group.
   const long long stride = (long long)M * N;
-  for (int mine = warp * 2; mine < warp * 2 + 2; ++mine) {
-    const int gg = c.tags[mine];
-    if (gg < 0) continue;
+  int tg[WARPS * 2];
+#pragma unroll
+  for (int s = 0; s < WARPS * 2; s += 4) {
+    const int4 v = *reinterpret_cast<const int4*>(c.tags + s);
+    tg[s] = v.x; tg[s + 1] = v.y; tg[s + 2] = v.z; tg[s + 3] = v.w;
+  }
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    const int mine = warp * 2 + which;
+    int gg = -1;
     bool fresh = true;
-    for (int s2 = 0; s2 < mine; ++s2) fresh = fresh && (c.tags[s2] != gg);
+#pragma unroll
+    for (int s2 = 0; s2 < WARPS * 2; ++s2) {
+      if (s2 == mine) gg = tg[s2];
+    }
+    if (gg < 0) continue;
+#pragma unroll
+    for (int s2 = 0; s2 < WARPS * 2; ++s2) fresh = fresh && !(s2 < mine && tg[s2] == gg);
     if (!fresh) continue;
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s2 = mine; s2 < WARPS * 2; ++s2) {
-      if (c.tags[s2] == gg) {
+#pragma unroll
+    for (int s2 = 0; s2 < WARPS * 2; ++s2) {
+      if (s2 >= mine && tg[s2] == gg) {
         const float4 v = *reinterpret_cast<const float4*>(c.red + (size_t)s2 * 128 + lane * 4);
         sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
       }
@@ -1040,22 +1064,32 @@ k_decode_mega(const __grid_constant__ mega_params_t p) {
     // B: attention (reuses the ring), then prime O-proj
     attention_phase(p, c, Lw, buf0);
     TRACE(3);
-    run = gemm_prime(Lw.wo, p.o, c);
-    grid_barrier(p, c);
+    grid_arrive(p, c);
+    run = gemm_prime(Lw.wo, p.o, c);         // the copy issue overlaps the barrier wait
+    grid_wait(p, c);
     TRACE(4);
     // C: O projection
     stage_x(p, c, p.attended, p.o.K);
     TRACE(5);
+    if (l == p.trace_layer && threadIdx.x == 0) {
+      unsigned sm;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+      g_mega_trace[64 + blockIdx.x] = sm;
+    }
     gemm_run(run, p.o, p.M, c.xs, buf1, c);
+    if (l == p.trace_layer && threadIdx.x == 0) g_mega_trace[64 + 160 + blockIdx.x] = gtime();
     TRACE(6);
+    grid_arrive(p, c);
     run = gemm_prime(Lw.wgu, p.gu, c);
-    grid_barrier(p, c);
+    grid_wait(p, c);
     TRACE(7);
     // D: add + norm, gate|up projection
     prologue_add_norm(p, c, buf1, p.o, Lw.ln_post);
     c.trace_gemm = 0;
     TRACE(8);
+    if (l == p.trace_layer && threadIdx.x == 0) g_mega_trace[64 + 320 + blockIdx.x] = gtime();
     gemm_run(run, p.gu, p.M, c.xs, buf0, c);
+    if (l == p.trace_layer && threadIdx.x == 0) g_mega_trace[64 + 480 + blockIdx.x] = gtime();
     TRACE(9);
     run = gemm_prime(Lw.wdown, p.down, c);
     if (p.prefetch_units > 0) l2_prefetch_run(Lw.wdown, p.down, STAGES * STAGE_UNITS, p.prefetch_units);
@@ -1091,7 +1125,7 @@ k_decode_mega(const __grid_constant__ mega_params_t p) {
 }  // namespace
 
 int q_mega_trace_read(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, g_mega_trace, sizeof(unsigned long long) * 64) == cudaSuccess ? 0 : -1;
+  return cudaMemcpyFromSymbol(out, g_mega_trace, sizeof(unsigned long long) * (64 + 640)) == cudaSuccess ? 0 : -1;
 }
 
 int q_mega_status_read(int32_t out[4]) {
