@@ -72,11 +72,16 @@ k_embed_rmsnorm(const int64_t* __restrict__ tokens, const bf16* __restrict__ E,
 }
 
 // ---- residual add + RMSNorm on partials ------------------------------------
-// One CTA per row; each thread keeps its elements of the new residual in
-// registers between the two passes (cols <= 256*MAXE).
-constexpr int ADD_MAXE = 40;  // 256 threads * 40 = 10240 columns
+// One CTA per row. Thread t owns columns 4t..4t+3 (+1024 j): both partial slots come in
+// with 16-byte loads that are all issued before anything is used (a row is a few KB in
+// L2, so the kernel is one memory round trip + one block reduction).
+constexpr int ADD_VB = 10;     // 256 threads * 4 columns * 10 = 10240 columns
 
-template <int EPT>
+__device__ __forceinline__ int plan_extra(const PlanView& pv, int n) {   // slots beyond the first
+  return plan_count(pv, n) - 1;
+}
+
+template <int VB>
 __global__ void __launch_bounds__(256)
 k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanView pv,
               const bf16* __restrict__ G, bf16* __restrict__ Tout, bf16* __restrict__ Nout,
@@ -85,28 +90,54 @@ k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanVie
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = blockIdx.x;
-  float keep[EPT];
+  const float* p0 = P + row * cols;
+  const bool two = pv.u != 0;
+  float4 s0[VB], s1[VB];
+  uint2 xr[VB], gn[VB];
+#pragma unroll
+  for (int j = 0; j < VB; ++j) {
+    const int col = 4 * threadIdx.x + j * 1024;
+    const int cc = col < cols ? col : 0;
+    s0[j] = *reinterpret_cast<const float4*>(p0 + cc);
+    s1[j] = two ? *reinterpret_cast<const float4*>(p0 + cc + pv.slot_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+    xr[j] = *reinterpret_cast<const uint2*>(Xin + row * cols + cc);
+    gn[j] = *reinterpret_cast<const uint2*>(G + cc);
+  }
+  float tot[VB][4];
   float ss = 0.f;
 #pragma unroll
-  for (int e = 0; e < EPT; ++e) {
-    int c = threadIdx.x + e * 256;
-    if (c < cols) {
-      float y = bf16_round(plan_sum(P, pv, (long long)row * cols + c, c));
-      float tot = bf16_round(__bfloat162float(Xin[row * cols + c]) + y);
-      keep[e] = tot;
-      ss += tot * tot;
+  for (int j = 0; j < VB; ++j) {
+    const int col = 4 * threadIdx.x + j * 1024;
+    if (col < cols) {
+      const int extra = plan_extra(pv, col);        // the 4 columns share one 16-column group
+      float s[4] = {s0[j].x, s0[j].y, s0[j].z, s0[j].w};
+      if (extra > 0) { s[0] += s1[j].x; s[1] += s1[j].y; s[2] += s1[j].z; s[3] += s1[j].w; }
+      for (int k = 2; k <= extra; ++k) {
+        const float4 sk = *reinterpret_cast<const float4*>(p0 + col + (long long)k * pv.slot_stride);
+        s[0] += sk.x; s[1] += sk.y; s[2] += sk.z; s[3] += sk.w;
+      }
+      const float r[4] = {bf_lo(xr[j].x), bf_hi(xr[j].x), bf_lo(xr[j].y), bf_hi(xr[j].y)};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        tot[j][e] = bf16_round(r[e] + bf16_round(s[e]));
+        ss += tot[j][e] * tot[j][e];
+      }
     }
   }
   ss = block_sum(ss, red);
   const float inv = rsqrtf(ss / (float)cols + eps);
 #pragma unroll
-  for (int e = 0; e < EPT; ++e) {
-    int c = threadIdx.x + e * 256;
-    if (c < cols) {
-      float tot = keep[e];
-      Tout[row * cols + c] = __float2bfloat16_rn(tot);
-      float v = bf16_round(tot * inv);
-      Nout[row * cols + c] = __float2bfloat16_rn(v * __bfloat162float(G[c]));
+  for (int j = 0; j < VB; ++j) {
+    const int col = 4 * threadIdx.x + j * 1024;
+    if (col < cols) {
+      const float g4[4] = {bf_lo(gn[j].x), bf_hi(gn[j].x), bf_lo(gn[j].y), bf_hi(gn[j].y)};
+      uint2 to, no;
+      to.x = pack_bf16(tot[j][0], tot[j][1]);
+      to.y = pack_bf16(tot[j][2], tot[j][3]);
+      no.x = pack_bf16(bf16_round(tot[j][0] * inv) * g4[0], bf16_round(tot[j][1] * inv) * g4[1]);
+      no.y = pack_bf16(bf16_round(tot[j][2] * inv) * g4[2], bf16_round(tot[j][3] * inv) * g4[3]);
+      *reinterpret_cast<uint2*>(Tout + row * cols + col) = to;
+      *reinterpret_cast<uint2*>(Nout + row * cols + col) = no;
     }
   }
 }
@@ -116,20 +147,45 @@ __global__ void __launch_bounds__(256)
 k_swiglu(const float* __restrict__ P, PlanView pv, bf16* __restrict__ O, int rows, int inter) {
   pdl_launch_dependents();
   pdl_wait();
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (long long)rows * inter) return;
-  int m = (int)(i / inter), c = (int)(i % inter);
-  long long base = (long long)m * 2 * inter;
-  float g = bf16_round(plan_sum(P, pv, base + c, c));
-  float u = bf16_round(plan_sum(P, pv, base + inter + c, inter + c));
-  float a = bf16_round(g / (1.0f + expf(-g)));
-  O[i] = __float2bfloat16_rn(a * u);
+  const long long quads = (long long)rows * (inter >> 2);
+  const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (q >= quads) return;
+  const int m = (int)(q / (inter >> 2)), c = (int)(q % (inter >> 2)) * 4;
+  const float* base = P + (long long)m * 2 * inter;
+  const bool two = pv.u != 0;
+  const float4 g0 = *reinterpret_cast<const float4*>(base + c);
+  const float4 u0 = *reinterpret_cast<const float4*>(base + inter + c);
+  const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 g1 = two ? *reinterpret_cast<const float4*>(base + c + pv.slot_stride) : z;
+  const float4 u1 = two ? *reinterpret_cast<const float4*>(base + inter + c + pv.slot_stride) : z;
+  const int eg = plan_count(pv, c) - 1, eu = plan_count(pv, inter + c) - 1;
+  float gs[4] = {g0.x, g0.y, g0.z, g0.w}, us[4] = {u0.x, u0.y, u0.z, u0.w};
+  if (eg > 0) { gs[0] += g1.x; gs[1] += g1.y; gs[2] += g1.z; gs[3] += g1.w; }
+  if (eu > 0) { us[0] += u1.x; us[1] += u1.y; us[2] += u1.z; us[3] += u1.w; }
+  for (int k = 2; k <= eg; ++k) {
+    const float4 t = *reinterpret_cast<const float4*>(base + c + (long long)k * pv.slot_stride);
+    gs[0] += t.x; gs[1] += t.y; gs[2] += t.z; gs[3] += t.w;
+  }
+  for (int k = 2; k <= eu; ++k) {
+    const float4 t = *reinterpret_cast<const float4*>(base + inter + c + (long long)k * pv.slot_stride);
+    us[0] += t.x; us[1] += t.y; us[2] += t.z; us[3] += t.w;
+  }
+  float o[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float g = bf16_round(gs[e]), u = bf16_round(us[e]);
+    o[e] = bf16_round(g / (1.0f + expf(-g))) * u;
+  }
+  uint2 pk;
+  pk.x = pack_bf16(o[0], o[1]);
+  pk.y = pack_bf16(o[2], o[3]);
+  *reinterpret_cast<uint2*>(O + (long long)m * inter + c) = pk;
 }
 
 // ---- q/k head norm + RoPE + KV page write -------------------------------------
-// One warp per (row, head) for q and k heads; lane l owns dims l, l+32, l+64,
-// l+96, so the rotate-half partner (d +- 64) is in the same lane. The warp that
-// handles k head h also copies v head h.
+// One warp per (row, head) for q and k heads and one per v head; lane l owns dims
+// 4l..4l+3 (one 16-byte load per partial slot), the rotate-half partner (d +- 64) is in
+// lane l ^ 16.
 __global__ void __launch_bounds__(128)
 k_qkv_norm_rope_cache(const float* __restrict__ P, PlanView pv, const bf16* __restrict__ QG,
                       const bf16* __restrict__ KG, const bf16* __restrict__ COS,
@@ -141,59 +197,61 @@ k_qkv_norm_rope_cache(const float* __restrict__ P, PlanView pv, const bf16* __re
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
-  const int heads = nq + nkv;
+  const int heads = nq + 2 * nkv;
   if (item >= rows * heads) return;
-  const int m = item / heads, head = item % heads;
+  const int m = item / heads, head = item % heads;       // head indexes the packed column blocks q|k|v
   const int b = m / T, tq = m % T;
   const int pos = pos_ptr[0] + tq;
-  const int width = (nq + 2 * nkv) * 128;
-  const long long src = (long long)m * width + head * 128;  // q heads then k heads
-  float x[4];
-  float ss = 0.f;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    int d = lane + 32 * j;
-    x[j] = bf16_round(plan_sum(P, pv, src + d, head * 128 + d));
-    ss += x[j] * x[j];
+  const int width = heads * 128;
+  const bool is_q = head < nq, is_v = head >= nq + nkv;
+  const long long src = (long long)m * width + (long long)head * 128 + 4 * lane;
+  const float4 s0 = *reinterpret_cast<const float4*>(P + src);
+  const float4 s1 = pv.u != 0 ? *reinterpret_cast<const float4*>(P + src + pv.slot_stride)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+  const uint2 graw = is_v ? make_uint2(0, 0) : *reinterpret_cast<const uint2*>((is_q ? QG : KG) + 4 * lane);
+  const uint2 craw = *reinterpret_cast<const uint2*>(COS + (size_t)pos * 128 + 4 * lane);
+  const uint2 sraw = *reinterpret_cast<const uint2*>(SIN + (size_t)pos * 128 + 4 * lane);
+  const int extra = plan_count(pv, head * 128 + 4 * lane) - 1;
+  float x[4] = {s0.x, s0.y, s0.z, s0.w};
+  if (extra > 0) { x[0] += s1.x; x[1] += s1.y; x[2] += s1.z; x[3] += s1.w; }
+  for (int k = 2; k <= extra; ++k) {
+    const float4 sk = *reinterpret_cast<const float4*>(P + src + (long long)k * pv.slot_stride);
+    x[0] += sk.x; x[1] += sk.y; x[2] += sk.z; x[3] += sk.w;
   }
-  ss = warp_sum(ss);
-  const float inv = rsqrtf(ss / 128.f + eps);
-  const bf16* gain = head < nq ? QG : KG;
-  float n[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    int d = lane + 32 * j;
-    n[j] = bf16_round(bf16_round(x[j] * inv) * __bfloat162float(gain[d]));
-  }
-  float out[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    int d = lane + 32 * j;
-    float c = __bfloat162float(COS[(size_t)pos * 128 + d]);
-    float s = __bfloat162float(SIN[(size_t)pos * 128 + d]);
-    float rot = (j < 2) ? -n[j + 2] : n[j - 2];
-    float left = bf16_round(n[j] * c);
-    float right = bf16_round(rot * s);
-    out[j] = left + right;  // rounded to bf16 at the store
-  }
-  if (head < nq) {
-    bf16* q = Q + ((size_t)m * nq + head) * 128;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) q[lane + 32 * j] = __float2bfloat16_rn(out[j]);
+  for (int e = 0; e < 4; ++e) x[e] = bf16_round(x[e]);
+  uint2 o;
+  if (is_v) {
+    o.x = pack_bf16(x[0], x[1]);
+    o.y = pack_bf16(x[2], x[3]);
   } else {
-    const int kh = head - nq;
+    float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / 128.f + eps);
+    const float gv[4] = {bf_lo(graw.x), bf_hi(graw.x), bf_lo(graw.y), bf_hi(graw.y)};
+    const float cs[4] = {bf_lo(craw.x), bf_hi(craw.x), bf_lo(craw.y), bf_hi(craw.y)};
+    const float sn[4] = {bf_lo(sraw.x), bf_hi(sraw.x), bf_lo(sraw.y), bf_hi(sraw.y)};
+    float out[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float n = bf16_round(bf16_round(x[e] * inv) * gv[e]);
+      const float partner = __shfl_xor_sync(0xffffffffu, n, 16);
+      const float rot = lane < 16 ? -partner : partner;
+      out[e] = bf16_round(n * cs[e]) + bf16_round(rot * sn[e]);   // rounded to bf16 at the store
+    }
+    o.x = pack_bf16(out[0], out[1]);
+    o.y = pack_bf16(out[2], out[3]);
+  }
+  if (is_q) {
+    *reinterpret_cast<uint2*>(Q + ((size_t)m * nq + head) * 128 + 4 * lane) = o;
+  } else {
+    const int kh = is_v ? head - nq - nkv : head - nq;
     const int page = block_table[(size_t)b * pages_per_seq + pos / Q_PAGE_TOKENS];
     const int r = pos % Q_PAGE_TOKENS;
     const size_t tile = ((size_t)page * nkv + kh) * (Q_PAGE_TOKENS * 128 * 2);
-    const long long vsrc = (long long)m * width + (nq + nkv + kh) * 128;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      int d = lane + 32 * j;
-      int off = kv_tile_offset_bytes(r, d);
-      *reinterpret_cast<bf16*>(kpool + tile + off) = __float2bfloat16_rn(out[j]);
-      float v = plan_sum(P, pv, vsrc + d, (nq + nkv + kh) * 128 + d);
-      *reinterpret_cast<bf16*>(vpool + tile + off) = __float2bfloat16_rn(v);
-    }
+    char* pool = is_v ? vpool : kpool;
+    // dims 4l..4l+3 sit in 16-byte chunk l/2 of token row r
+    *reinterpret_cast<uint2*>(pool + tile + r * 256 + (((lane >> 1) ^ (r & 7)) << 4) + (lane & 1) * 8) = o;
   }
 }
 
@@ -246,13 +304,43 @@ k_logits_argmax(const float* __restrict__ P, PlanView pv, bf16* __restrict__ log
   const int c0 = blockIdx.x * ARG_COLS;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int c = c0 + threadIdx.x; c < c0 + ARG_COLS && c < vocab; c += 256) {
-    long long i = (long long)row * vocab + c;
-    bf16 r = __float2bfloat16_rn(plan_sum(P, pv, i, c));
-    if (logits) logits[i] = r;
-    float v = __bfloat162float(r);
-    if (v != v) v = -INFINITY;  // NaN never wins
-    arg_better(bv, bi, v, c);
+  if ((vocab & 3) == 0) {
+    // 4 columns per thread and step, 16-byte loads of both slots issued together
+    const float* p0 = P + (long long)row * vocab;
+    const bool two = pv.u != 0;
+    for (int c = c0 + 4 * threadIdx.x; c < c0 + ARG_COLS && c < vocab; c += 1024) {
+      const float4 a = *reinterpret_cast<const float4*>(p0 + c);
+      const float4 b = two ? *reinterpret_cast<const float4*>(p0 + c + pv.slot_stride)
+                           : make_float4(0.f, 0.f, 0.f, 0.f);
+      const int extra = plan_count(pv, c) - 1;
+      float s[4] = {a.x, a.y, a.z, a.w};
+      if (extra > 0) { s[0] += b.x; s[1] += b.y; s[2] += b.z; s[3] += b.w; }
+      for (int k = 2; k <= extra; ++k) {
+        const float4 t = *reinterpret_cast<const float4*>(p0 + c + (long long)k * pv.slot_stride);
+        s[0] += t.x; s[1] += t.y; s[2] += t.z; s[3] += t.w;
+      }
+      if (logits) {
+        uint2 pk;
+        pk.x = pack_bf16(s[0], s[1]);
+        pk.y = pack_bf16(s[2], s[3]);
+        *reinterpret_cast<uint2*>(logits + (long long)row * vocab + c) = pk;
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = bf16_round(s[e]);
+        if (v != v) v = -INFINITY;  // NaN never wins
+        arg_better(bv, bi, v, c + e);
+      }
+    }
+  } else {
+    for (int c = c0 + threadIdx.x; c < c0 + ARG_COLS && c < vocab; c += 256) {
+      long long i = (long long)row * vocab + c;
+      bf16 r = __float2bfloat16_rn(plan_sum(P, pv, i, c));
+      if (logits) logits[i] = r;
+      float v = __bfloat162float(r);
+      if (v != v) v = -INFINITY;  // NaN never wins
+      arg_better(bv, bi, v, c);
+    }
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -354,11 +442,11 @@ extern "C" int q_add_rmsnorm(const void* d_x_in, const float* d_branch, const q_
                              const void* d_gain, void* d_total_out, void* d_normed_out, int rows,
                              int cols, float eps, void* stream) {
   Q_CHECK_ARG(d_x_in && d_branch && d_gain && d_total_out && d_normed_out, "q_add_rmsnorm: null pointer");
-  Q_CHECK_ARG(rows >= 1 && cols >= 1 && cols <= 256 * ADD_MAXE, "q_add_rmsnorm: cols %d outside 1..%d",
-              cols, 256 * ADD_MAXE);
+  Q_CHECK_ARG(rows >= 1 && cols >= 4 && cols % 4 == 0 && cols <= 1024 * ADD_VB,
+              "q_add_rmsnorm: cols %d must be a multiple of 4 in 4..%d", cols, 1024 * ADD_VB);
   int rc = check_plan(plan, rows, cols, "q_add_rmsnorm");
   if (rc) return rc;
-  auto kern = cols <= 256 * 4 ? k_add_rmsnorm<4> : cols <= 256 * 12 ? k_add_rmsnorm<12> : k_add_rmsnorm<ADD_MAXE>;
+  auto kern = cols <= 1024 ? k_add_rmsnorm<1> : cols <= 3072 ? k_add_rmsnorm<3> : k_add_rmsnorm<ADD_VB>;
   Q_CHECK_CUDA(q_launch(kern, dim3(rows), dim3(256), 0, S(stream), (const bf16*)d_x_in,
                         d_branch, plan_view(plan), (const bf16*)d_gain, (bf16*)d_total_out,
                         (bf16*)d_normed_out, cols, eps));
@@ -367,10 +455,11 @@ extern "C" int q_add_rmsnorm(const void* d_x_in, const float* d_branch, const q_
 
 extern "C" int q_swiglu(const float* d_branch, const q_gemm_plan_t* plan, void* d_out, int rows,
                         int inter, void* stream) {
-  Q_CHECK_ARG(d_branch && d_out && rows >= 1 && inter >= 1, "q_swiglu: bad argument");
+  Q_CHECK_ARG(d_branch && d_out && rows >= 1 && inter >= 4 && inter % 4 == 0,
+              "q_swiglu: bad argument (inter must be a multiple of 4)");
   int rc = check_plan(plan, rows, 2 * inter, "q_swiglu");
   if (rc) return rc;
-  long long total = (long long)rows * inter;
+  long long total = (long long)rows * (inter / 4);
   Q_CHECK_CUDA(q_launch(k_swiglu, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, S(stream),
                         d_branch, plan_view(plan), (bf16*)d_out, rows, inter));
   return Q_OK;
@@ -391,7 +480,7 @@ extern "C" int q_qkv_norm_rope_cache(const float* d_branch, const q_gemm_plan_t*
   const int rows = batch * T, nkv = kv->n_kv_heads;
   int rc = check_plan(plan, rows, (n_q_heads + 2 * nkv) * 128, "q_qkv_norm_rope_cache");
   if (rc) return rc;
-  const int items = rows * (n_q_heads + nkv);
+  const int items = rows * (n_q_heads + 2 * nkv);
   Q_CHECK_CUDA(q_launch(k_qkv_norm_rope_cache, dim3((items + 3) / 4), dim3(128), 0, S(stream),
                         d_branch, plan_view(plan), (const bf16*)d_q_gain, (const bf16*)d_k_gain,
                         (const bf16*)d_cos, (const bf16*)d_sin, d_pos, (bf16*)d_q_out,

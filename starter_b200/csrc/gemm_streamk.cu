@@ -344,10 +344,27 @@ __global__ void k_reduce_partials(const float* __restrict__ P, float* __restrict
                                   PlanView pv, int M, int N) {
   pdl_launch_dependents();
   pdl_wait();
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  long long total = (long long)M * N;
+  const long long total = (long long)M * N;
+  if ((N & 3) == 0) {
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= total) return;
+    const int n = (int)(i % N);
+    const float4 a = *reinterpret_cast<const float4*>(P + i);
+    const float4 b = pv.u != 0 ? *reinterpret_cast<const float4*>(P + i + pv.slot_stride)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+    const int extra = plan_count(pv, n) - 1;
+    float4 s = a;
+    if (extra > 0) { s.x += b.x; s.y += b.y; s.z += b.z; s.w += b.w; }
+    for (int k = 2; k <= extra; ++k) {
+      const float4 t = *reinterpret_cast<const float4*>(P + i + (long long)k * pv.slot_stride);
+      s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+    }
+    *reinterpret_cast<float4*>(out + i) = s;
+    return;
+  }
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
-  int n = (int)(i % N);
+  const int n = (int)(i % N);
   out[i] = plan_sum(P, pv, i, n);
 }
 
@@ -540,6 +557,7 @@ extern "C" int q_reduce_partials(const float* d_partials, const q_gemm_plan_t* p
                                  float* d_out, void* stream) {
   Q_CHECK_ARG(d_partials && plan && d_out, "q_reduce_partials: null pointer");
   long long total = (long long)plan->M * plan->N;
+  if ((plan->N & 3) == 0) total /= 4;
   int block = 256;
   int grid = (int)((total + block - 1) / block);
   Q_CHECK_CUDA(q_launch(k_reduce_partials, dim3(grid), dim3(block), 0, (cudaStream_t)stream,
