@@ -297,8 +297,8 @@ def time_gemm_kernel(state, reps: int = 5):
 
 
 def kernels_per_step(state) -> int:
-    if state.fused_scratch is not None and not os.environ.get("QDECODE_NO_FUSED"):
-        return 1                              # the persistent whole-step kernel
+    if state.fused_scratch is not None and os.environ.get("QDECODE_FUSED") == "1":
+        return 1                              # the persistent whole-step kernel (opt-in)
     per_layer = 9 + (1 if state.attn_splits > 1 else 0)
     n = 1 + state.cfg.n_layers * per_layer + 2
     if state.tp > 1:
@@ -317,8 +317,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         group = dist.group.WORLD
     from starter_b200 import Engine, _lib
 
-    if os.environ.get("QDECODE_NO_FUSED"):          # measure the multi-kernel step instead
-        _lib.check(_lib.lib.q_set_option(b"fused_step", 0))
+    if os.environ.get("QDECODE_FUSED") == "1":      # measure the single persistent kernel instead
+        _lib.check(_lib.lib.q_set_option(b"fused_step", 1))
     batch, prompt_len, new_tokens = WORKLOADS[args.workload]
     cfg = dict(QWEN3_4B)
     if args.layers:

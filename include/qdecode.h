@@ -48,7 +48,8 @@ int q_set_pdl(int enabled);
 
 /* Tuning knobs (process-wide, host side only; no reference counterpart).
  *   "gemm_prefetch_kb": L2 prefetch window per GEMM CTA in KB (0 = off, default).
- *   "fused_step": 1 = q_decode_step may use the single persistent kernel (default).
+ *   "fused_step": 1 = q_decode_step may use the single persistent kernel (default 0: on B200 the
+ *       dependent-launch multi-kernel step measured faster, 2.2 vs 2.8 ms at batch 1).
  *   "trace_layer": layer stamped by the whole-step kernel (see q_debug_step_trace), -1 off.
  *   "gemm_debug_flags": measurement aid, 4 = per-CTA time stamps for q_debug_gemm_trace.
  * Unknown names return Q_ERR_ARG. */
@@ -199,6 +200,19 @@ int q_attention(const void* d_q, const q_kv_layout_t* kv, const int32_t* d_pos,
                 int batch, int T, int n_q_heads, int splits, float scale,
                 void* stream);
 
+/* The three kernels above for the single-token decode step in ONE launch:
+ * engine/kernels/decode_fused.py:172-210 (head norm + RoPE + K/V write into the page
+ * slot *d_pos) + engine/kernels/small_query_attention.py:113-158 (split-KV attention and
+ * merge). Consumes the packed [q|k|v] projection partials directly. d_tickets:
+ * uint32[batch*n_kv], zeroed once by the caller (the last split to finish merges and
+ * resets its ticket). Output [batch][n_q*128]. */
+int q_attention_decode(const float* d_qkv_partials, const q_gemm_plan_t* plan,
+                       const void* d_q_gain, const void* d_k_gain,
+                       const void* d_cos, const void* d_sin, const int32_t* d_pos,
+                       const q_kv_layout_t* kv, float* d_scratch_o, float* d_scratch_ml,
+                       uint32_t* d_tickets, void* d_out, int batch, int n_q_heads,
+                       int splits, float scale, float eps, void* stream);
+
 /* ---- lm_head + argmax -------------------------------------------------------
  * engine/decode_step.py:60 (F.linear on lm_head) + engine/decode.py:106-107
  * (argmax, position += 1). Consumes the lm_head GEMM partials; writes bf16
@@ -273,6 +287,7 @@ typedef struct q_state_t {
   float* reduced;           /* fp32 [rows][hidden] (tensor parallel only, else NULL) */
   float* attn_o;            /* see q_attention */
   float* attn_ml;
+  uint32_t* attn_tickets;   /* uint32[batch*n_kv], zeroed once (q_attention_decode) */
   void* logits;             /* bf16 [rows][vocab] or NULL */
   float* arg_val;           /* [rows] */
   int32_t* arg_idx;         /* [rows] */
@@ -292,9 +307,9 @@ int64_t q_fused_scratch_bytes(const q_engine* e, int rows);
 void q_destroy(q_engine* e);
 
 /* One full step for T=1 on a single GPU: embed .. argmax, tokens and pos updated.
- * With at most 8 rows, state.fused_scratch set and enough shared memory, the step
- * runs as ONE persistent cooperative kernel (option "fused_step", default 1);
- * otherwise as ~360 dependent-launch kernels. Both produce the same tokens. */
+ * Default: ~290 kernels with programmatic dependent launch. With option "fused_step" = 1,
+ * at most 8 rows, state.fused_scratch set and enough shared memory, the step runs as ONE
+ * persistent cooperative kernel instead. Both produce the same tokens. */
 int q_decode_step(q_engine* e, void* stream);
 
 /* The same step in pieces, for tensor parallelism: the caller all-reduces

@@ -53,7 +53,8 @@ class State(C.Structure):
         ("attn_splits", C.c_int32),
         ("x", C.c_void_p), ("normed", C.c_void_p), ("q", C.c_void_p), ("attended", C.c_void_p),
         ("act", C.c_void_p), ("partials", C.c_void_p), ("reduced", C.c_void_p),
-        ("attn_o", C.c_void_p), ("attn_ml", C.c_void_p), ("logits", C.c_void_p),
+        ("attn_o", C.c_void_p), ("attn_ml", C.c_void_p), ("attn_tickets", C.c_void_p),
+        ("logits", C.c_void_p),
         ("arg_val", C.c_void_p), ("arg_idx", C.c_void_p), ("arg_scratch", C.c_void_p),
         ("fused_scratch", C.c_void_p),
     ]
@@ -89,6 +90,7 @@ SIGNATURES = {
     "q_kv_scatter": (_I, [_P, _P, _KV, _I, _I, _I, _P]),
     "q_attention_splits": (_I, [_I, _I, _I]),
     "q_attention": (_I, [_P, _KV, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P]),
+    "q_attention_decode": (_I, [_P, _PLAN, _P, _P, _P, _P, _P, _KV, _P, _P, _P, _P, _I, _I, _I, _F, _F, _P]),
     "q_argmax_scratch_bytes": (C.c_int64, [_I, _I]),
     "q_logits_argmax": (_I, [_P, _PLAN, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _P]),
     "q_argmax_merge": (_I, [_P, _P, _I, _I, _P, _P, _I, _P]),

@@ -119,7 +119,10 @@ k_attn_split(const bf16* __restrict__ Q, const char* __restrict__ kpool,
   }
   __syncthreads();
 
-  pdl_wait();
+  // pos, the block table and every key/value row older than this step's query block were
+  // written by earlier steps (earlier graph launches), so they may be read before the
+  // dependency wait; only tiles that can hold the T newest rows must wait for the kernel
+  // that writes them.
   const int pos = pos_ptr[0];
   const int max_limit = pos + T;                                   // keys visible to the last row
   const int tiles_used = (max_limit + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
@@ -128,12 +131,18 @@ k_attn_split(const bf16* __restrict__ Q, const char* __restrict__ kpool,
   int tile1 = tile0 + per;
   if (tile1 > tiles_used) tile1 = tiles_used;
   const int ntiles = tile1 > tile0 ? tile1 - tile0 : 0;
+  const int first_new_tile = pos / Q_PAGE_TOKENS;                  // tiles >= this may change in this step
 
   if (warp == CONSUMERS) {
     // ---------------- producer ----------------
     if (lane == 0) {
+      bool waited = false;
       for (int it = 0; it < ntiles; ++it) {
         const int s = it % NS;
+        if (!waited && tile0 + it >= first_new_tile) {
+          pdl_wait();
+          waited = true;
+        }
         if (it >= NS) {
           if (!mbar_wait(smem_u32(&bars[NS + s]), ((it / NS) - 1) & 1)) {
             atomicExch(&g_status[0], 1);
@@ -148,9 +157,11 @@ k_attn_split(const bf16* __restrict__ Q, const char* __restrict__ kpool,
         bulk_g2s(smem_u32(stages + s * STAGE_BYTES), kpool + off, TILE_BYTES, bar);
         bulk_g2s(smem_u32(stages + s * STAGE_BYTES + TILE_BYTES), vpool + off, TILE_BYTES, bar);
       }
+      if (!waited) pdl_wait();
     }
   } else {
     // ---------------- consumers ----------------
+    pdl_wait();                 // Q (and the newest K/V rows) come from the previous kernel
     // Q tile -> shared memory (swizzled rows of 256 B); rows >= R are zero.
     for (int c = tid; c < RT * 16 * 16; c += CONSUMERS * 32) {
       const int r = c >> 4, ch = c & 15;
@@ -370,12 +381,19 @@ k_attn_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml
   const float wgt = l > 0.f ? exp2f(m - M) : 0.f;
   const float L = warp_sum(wgt * l);
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  // every split wrote its (possibly neutral, all-zero) partial, so no branch is needed
-#pragma unroll 4
-  for (int s = 0; s < S; ++s) {
-    const float ws = __shfl_sync(0xffffffffu, wgt, s);
-    const float4 o = *reinterpret_cast<const float4*>(part_o + (base + (size_t)s * R) * 128 + lane * 4);
-    acc[0] += ws * o.x; acc[1] += ws * o.y; acc[2] += ws * o.z; acc[3] += ws * o.w;
+  // every split wrote its (possibly neutral, all-zero) partial; 16 loads are issued together
+  for (int s0 = 0; s0 < S; s0 += 16) {
+    float4 o[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int s = s0 + j < S ? s0 + j : S - 1;
+      o[j] = *reinterpret_cast<const float4*>(part_o + (base + (size_t)s * R) * 128 + lane * 4);
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float ws = (s0 + j < S) ? __shfl_sync(0xffffffffu, wgt, (s0 + j) & 31) : 0.f;
+      acc[0] += ws * o[j].x; acc[1] += ws * o[j].y; acc[2] += ws * o[j].z; acc[3] += ws * o[j].w;
+    }
   }
   const float inv = L > 0.f ? 1.f / L : 0.f;
   bf16* dst = out + ((size_t)bt * nq + head) * 128 + lane * 4;
@@ -384,6 +402,349 @@ k_attn_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml
   packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
   *reinterpret_cast<uint2*>(dst) = packed;
 }
+
+
+// ---- single-token decode attention with everything around it folded in -----------------
+// q/k head norm + RoPE + K/V page write (engine/kernels/decode_fused.py:59-118), the
+// split-KV attention above for T = 1, and the split merge (k_attn_merge) as the job of
+// the last split of a kv head to finish (a ticket counter, no spinning): one kernel per
+// layer instead of three. The newest key/value row is computed here, so NOTHING this
+// kernel streams from the KV pages depends on the previous kernel: the producer requests
+// all its tiles before the dependency wait, and the consumer that owns the newest key
+// patches that row into the shared-memory tile (and the owner split writes it to the page
+// for later steps).
+__global__ void __launch_bounds__(THREADS)
+k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict__ QG,
+              const bf16* __restrict__ KG, const bf16* __restrict__ COS, const bf16* __restrict__ SIN,
+              const int32_t* __restrict__ pos_ptr, char* __restrict__ kpool, char* __restrict__ vpool,
+              const int32_t* __restrict__ block_table, int pages_per_seq, float* __restrict__ part_o,
+              float* __restrict__ part_ml, unsigned int* __restrict__ tickets, bf16* __restrict__ out,
+              int rows, int G, int nq, int nkv, int S, float scale_log2, float eps) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* stages = smem;                               // NS * STAGE_BYTES
+  unsigned char* qtile = smem + NS * STAGE_BYTES;             // 16 rows * 256 B
+  uint64_t* bars = reinterpret_cast<uint64_t*>(qtile + 16 * 256);       // full[NS], empty[NS]
+  bf16* knew = reinterpret_cast<bf16*>(bars + 2 * NS);        // [128]
+  bf16* vnew = knew + 128;                                    // [128]
+  __shared__ int s_last;
+
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y, split = blockIdx.x;
+  const int b = bh / nkv, kh = bh % nkv;
+  if (tid == 0) {
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(smem_u32(&bars[i]), 1);
+      mbar_init(smem_u32(&bars[NS + i]), CONSUMERS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  // position and block table were written by earlier steps: safe before the wait
+  const int pos = pos_ptr[0];
+  const int max_limit = pos + 1;
+  const int tiles_used = (max_limit + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
+  const int per = (tiles_used + S - 1) / S;
+  const int tile0 = split * per;
+  const int tile1 = min(tiles_used, tile0 + per);
+  const int ntiles = tile1 > tile0 ? tile1 - tile0 : 0;
+  const int new_tile = pos / Q_PAGE_TOKENS, new_row = pos % Q_PAGE_TOKENS;
+  const bool owns_new = ntiles > 0 && new_tile >= tile0 && new_tile < tile1;
+
+  if (warp == CONSUMERS && lane == 0) {
+    for (int it = 0; it < ntiles && it < NS; ++it) {
+      const int page = block_table[(size_t)b * pages_per_seq + tile0 + it];
+      const size_t off = ((size_t)page * nkv + kh) * TILE_BYTES;
+      const uint32_t bar = smem_u32(&bars[it]);
+      mbar_expect_tx(bar, STAGE_BYTES);
+      bulk_g2s(smem_u32(stages + it * STAGE_BYTES), kpool + off, TILE_BYTES, bar);
+      bulk_g2s(smem_u32(stages + it * STAGE_BYTES + TILE_BYTES), vpool + off, TILE_BYTES, bar);
+    }
+  }
+
+  pdl_wait();          // the QKV partials are complete from here on
+
+  // ---- q/k head norm + RoPE (+ v): one warp per head, lane l owns dims 4l..4l+3 ----
+  {
+    const int width = (nq + 2 * nkv) * 128;
+    for (int h = warp; h < G + 2; h += CONSUMERS + 1) {
+      const bool is_q = h < G, is_v = h == G + 1;
+      const int head = is_q ? kh * G + h : (is_v ? nq + nkv + kh : nq + kh);
+      const long long src = (long long)b * width + (long long)head * 128 + 4 * lane;
+      const float4 s0 = *reinterpret_cast<const float4*>(PQ + src);
+      const float4 s1 = pv.u != 0 ? *reinterpret_cast<const float4*>(PQ + src + pv.slot_stride)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+      const uint2 graw = is_v ? make_uint2(0, 0) : *reinterpret_cast<const uint2*>((is_q ? QG : KG) + 4 * lane);
+      const uint2 craw = *reinterpret_cast<const uint2*>(COS + (size_t)pos * 128 + 4 * lane);
+      const uint2 sraw = *reinterpret_cast<const uint2*>(SIN + (size_t)pos * 128 + 4 * lane);
+      const int extra = plan_count(pv, head * 128 + 4 * lane) - 1;
+      float x[4] = {s0.x, s0.y, s0.z, s0.w};
+      if (extra > 0) { x[0] += s1.x; x[1] += s1.y; x[2] += s1.z; x[3] += s1.w; }
+      for (int k = 2; k <= extra; ++k) {
+        const float4 sk = *reinterpret_cast<const float4*>(PQ + src + (long long)k * pv.slot_stride);
+        x[0] += sk.x; x[1] += sk.y; x[2] += sk.z; x[3] += sk.w;
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x[e] = bf16_round(x[e]);
+      uint2 o;
+      if (is_v) {
+        o.x = pack_bf16(x[0], x[1]);
+        o.y = pack_bf16(x[2], x[3]);
+        *reinterpret_cast<uint2*>(vnew + 4 * lane) = o;
+        continue;
+      }
+      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / 128.f + eps);
+      const float gv[4] = {bf_lo(graw.x), bf_hi(graw.x), bf_lo(graw.y), bf_hi(graw.y)};
+      const float cs[4] = {bf_lo(craw.x), bf_hi(craw.x), bf_lo(craw.y), bf_hi(craw.y)};
+      const float sn[4] = {bf_lo(sraw.x), bf_hi(sraw.x), bf_lo(sraw.y), bf_hi(sraw.y)};
+      float outv[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float n = bf16_round(bf16_round(x[e] * inv) * gv[e]);
+        const float partner = __shfl_xor_sync(0xffffffffu, n, 16);
+        const float rot = lane < 16 ? -partner : partner;
+        outv[e] = bf16_round(n * cs[e]) + bf16_round(rot * sn[e]);
+      }
+      o.x = pack_bf16(outv[0], outv[1]);
+      o.y = pack_bf16(outv[2], outv[3]);
+      if (is_q) {
+        *reinterpret_cast<uint2*>(qtile + h * 256 + (((lane >> 1) ^ (h & 7)) << 4) + (lane & 1) * 8) = o;
+      } else {
+        *reinterpret_cast<uint2*>(knew + 4 * lane) = o;
+      }
+    }
+    for (int i = tid; i < (16 - G) * 16; i += THREADS) {       // query rows G..15 are zero
+      const int r = G + (i >> 4), ch = i & 15;
+      *reinterpret_cast<uint4*>(qtile + r * 256 + ((ch ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  __syncthreads();
+  if (owns_new && tid < 16) {
+    // the newest key/value row goes to its page for later steps
+    const int page = block_table[(size_t)b * pages_per_seq + new_tile];
+    const size_t tile = ((size_t)page * nkv + kh) * TILE_BYTES;
+    const int off = new_row * 256 + ((tid ^ (new_row & 7)) << 4);
+    *reinterpret_cast<uint4*>(kpool + tile + off) = *reinterpret_cast<const uint4*>(knew + tid * 8);
+    *reinterpret_cast<uint4*>(vpool + tile + off) = *reinterpret_cast<const uint4*>(vnew + tid * 8);
+  }
+
+  if (warp == CONSUMERS) {
+    if (lane == 0) {
+      for (int it = NS; it < ntiles; ++it) {
+        const int s = it % NS;
+        if (!mbar_wait(smem_u32(&bars[NS + s]), ((it / NS) - 1) & 1)) {
+          atomicExch(&g_status[0], 1);
+          break;
+        }
+        const int page = block_table[(size_t)b * pages_per_seq + tile0 + it];
+        const size_t off = ((size_t)page * nkv + kh) * TILE_BYTES;
+        const uint32_t bar = smem_u32(&bars[s]);
+        mbar_expect_tx(bar, STAGE_BYTES);
+        bulk_g2s(smem_u32(stages + s * STAGE_BYTES), kpool + off, TILE_BYTES, bar);
+        bulk_g2s(smem_u32(stages + s * STAGE_BYTES + TILE_BYTES), vpool + off, TILE_BYTES, bar);
+      }
+    }
+  } else {
+    const int g = lane >> 2, t4 = lane & 3;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float oacc[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f;
+    const uint32_t q_base = smem_u32(qtile);
+    for (int it = 0; it < ntiles; ++it) {
+      const int s = it % NS;
+      if (!mbar_wait(smem_u32(&bars[s]), (it / NS) & 1)) {
+        atomicExch(&g_status[0], 2);
+        break;
+      }
+      unsigned char* kt = stages + s * STAGE_BYTES;
+      unsigned char* vt = kt + TILE_BYTES;
+      const int key_base = (tile0 + it) * Q_PAGE_TOKENS;
+      const int my_key0 = key_base + warp * 16;
+      if (my_key0 + 16 > max_limit) {
+        for (int i = lane; i < 16 * 16; i += 32) {
+          const int kr = warp * 16 + (i >> 4);
+          if (key_base + kr >= max_limit)
+            *reinterpret_cast<uint4*>(vt + kr * 256 + ((i & 15) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      if (tile0 + it == new_tile && (new_row >> 4) == warp && lane < 16) {
+        const int off = new_row * 256 + ((lane ^ (new_row & 7)) << 4);
+        *reinterpret_cast<uint4*>(kt + off) = *reinterpret_cast<const uint4*>(knew + lane * 8);
+        *reinterpret_cast<uint4*>(vt + off) = *reinterpret_cast<const uint4*>(vnew + lane * 8);
+      }
+      __syncwarp();
+      const uint32_t k_base = smem_u32(kt), v_base = smem_u32(vt);
+      float sacc[2][4], sodd[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+        sodd[j][0] = sodd[j][1] = sodd[j][2] = sodd[j][3] = 0.f;
+      }
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+        {
+          const int row = (lane & 7) + 8 * ((lane >> 3) & 1);
+          const int ch = 2 * ks + (lane >> 4);
+          ldsm_x4(q_base + row * 256 + ((ch ^ (row & 7)) << 4), a0, a1, a2, a3);
+        }
+        {
+          const int mi = lane >> 3;
+          const int key = warp * 16 + 8 * (mi >> 1) + (lane & 7);
+          const int ch = 2 * ks + (mi & 1);
+          ldsm_x4(k_base + key * 256 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+        }
+        if (ks & 1) {
+          mma16816(sodd[0], a0, a1, a2, a3, b0, b1);
+          mma16816(sodd[1], a0, a1, a2, a3, b2, b3);
+        } else {
+          mma16816(sacc[0], a0, a1, a2, a3, b0, b1);
+          mma16816(sacc[1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sacc[j][e] += sodd[j][e];
+      float pr[2][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = my_key0 + 8 * j + 2 * t4 + e;
+            float v = sacc[j][2 * h + e] * scale_log2;
+            v = key < max_limit ? v : -INFINITY;
+            sacc[j][2 * h + e] = v;
+            mx = fmaxf(mx, v);
+          }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[h], mx);
+        const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+        const float resc = exp2f(m_run[h] - m_safe);
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float pv2 = exp2f(sacc[j][2 * h + e] - m_safe);
+            pr[j][2 * h + e] = pv2;
+            sum += pv2;
+          }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l_run[h] = l_run[h] * resc + sum;
+        m_run[h] = m_new;
+#pragma unroll
+        for (int n = 0; n < 16; ++n) { oacc[n][2 * h] *= resc; oacc[n][2 * h + 1] *= resc; }
+      }
+      const uint32_t pa0 = pack_bf16(pr[0][0], pr[0][1]), pa1 = pack_bf16(pr[0][2], pr[0][3]);
+      const uint32_t pa2 = pack_bf16(pr[1][0], pr[1][1]), pa3 = pack_bf16(pr[1][2], pr[1][3]);
+#pragma unroll
+      for (int dp = 0; dp < 8; ++dp) {
+        uint32_t b0, b1, b2, b3;
+        const int mi = lane >> 3;
+        const int key = warp * 16 + 8 * (mi & 1) + (lane & 7);
+        const int ch = 2 * dp + (mi >> 1);
+        ldsm_x4_t(v_base + key * 256 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+        mma16816(oacc[2 * dp], pa0, pa1, pa2, pa3, b0, b1);
+        mma16816(oacc[2 * dp + 1], pa0, pa1, pa2, pa3, b2, b3);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars[NS + s]));
+    }
+    // merge the four consumer states through shared memory (only the G real query rows)
+    consumer_sync();
+    float* mo = reinterpret_cast<float*>(stages);            // [4][16][128]
+    float* mml = mo + CONSUMERS * 16 * 128;                  // [4][16][2]
+    if (g < G) {
+      float* dst = mo + ((size_t)warp * 16 + g) * 128;
+#pragma unroll
+      for (int n = 0; n < 16; ++n)
+        *reinterpret_cast<float2*>(dst + 8 * n + 2 * t4) = make_float2(oacc[n][0], oacc[n][1]);
+      if (t4 == 0) {
+        mml[((size_t)warp * 16 + g) * 2] = m_run[0];
+        mml[((size_t)warp * 16 + g) * 2 + 1] = l_run[0];
+      }
+    }
+    consumer_sync();
+    const int d = tid;
+    for (int r = 0; r < G; ++r) {
+      float mw[CONSUMERS], Mx = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < CONSUMERS; ++w) { mw[w] = mml[((size_t)w * 16 + r) * 2]; Mx = fmaxf(Mx, mw[w]); }
+      const float Ms = Mx == -INFINITY ? 0.f : Mx;
+      float Lsum = 0.f, O = 0.f;
+#pragma unroll
+      for (int w = 0; w < CONSUMERS; ++w) {
+        const float wt = exp2f(mw[w] - Ms);
+        Lsum += wt * mml[((size_t)w * 16 + r) * 2 + 1];
+        O += wt * mo[((size_t)w * 16 + r) * 128 + d];
+      }
+      if (S == 1) {
+        out[((size_t)b * nq + kh * G + r) * 128 + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
+      } else {
+        const size_t row = ((size_t)bh * S + split) * G + r;
+        part_o[row * 128 + d] = O;
+        if (d == 0) { part_ml[row * 2] = Mx; part_ml[row * 2 + 1] = Lsum; }
+      }
+    }
+  }
+  if (S == 1) return;
+
+  // ---- the last split of this kv head to finish merges all splits (fixed split order) ----
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const unsigned ticket = atomicAdd(&tickets[bh], 1u);
+    s_last = (ticket == (unsigned)(S - 1));
+    if (s_last) tickets[bh] = 0;         // ready for the next layer / launch
+    __threadfence();
+  }
+  __syncthreads();
+  if (!s_last) return;
+  for (int r = warp; r < G; r += CONSUMERS + 1) {
+    const size_t base = ((size_t)bh * S) * G + r;
+    float m = -INFINITY, l = 0.f;
+    if (lane < S) {
+      m = __ldcg(part_ml + (base + (size_t)lane * G) * 2);
+      l = __ldcg(part_ml + (base + (size_t)lane * G) * 2 + 1);
+    }
+    float Mx = warp_max(m);
+    if (Mx == -INFINITY) Mx = 0.f;
+    const float wgt = l > 0.f ? exp2f(m - Mx) : 0.f;
+    const float Lsum = warp_sum(wgt * l);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s0 = 0; s0 < S; s0 += 16) {
+      float4 o[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int s = s0 + j < S ? s0 + j : S - 1;
+        o[j] = __ldcg(reinterpret_cast<const float4*>(part_o + (base + (size_t)s * G) * 128) + lane);
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float ws = (s0 + j < S) ? __shfl_sync(0xffffffffu, wgt, (s0 + j) & 31) : 0.f;
+        acc[0] += ws * o[j].x; acc[1] += ws * o[j].y; acc[2] += ws * o[j].z; acc[3] += ws * o[j].w;
+      }
+    }
+    const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
+    uint2 packed;
+    packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+    packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+    *reinterpret_cast<uint2*>(out + ((size_t)b * nq + kh * G + r) * 128 + lane * 4) = packed;
+  }
+}
+
+constexpr size_t attn_decode_smem() { return NS * STAGE_BYTES + 16 * 256 + 2 * NS * 8 + 2 * 128 * 2 + 64; }
 
 template <int RT>
 constexpr size_t attn_smem() { return NS * STAGE_BYTES + RT * 16 * 256 + 2 * NS * 8; }
@@ -454,6 +815,45 @@ extern "C" int q_attention(const void* d_q, const q_kv_layout_t* kv, const int32
     Q_CHECK_CUDA(q_launch(k_attn_merge, dim3((items + 3) / 4), dim3(128), 0, s, d_scratch_o,
                           d_scratch_ml, (bf16*)d_out, batch, T, G, n_q_heads, nkv, splits));
   }
+  return Q_OK;
+}
+
+extern "C" int q_attention_decode(const float* d_qkv_partials, const q_gemm_plan_t* plan,
+                                  const void* d_q_gain, const void* d_k_gain, const void* d_cos,
+                                  const void* d_sin, const int32_t* d_pos, const q_kv_layout_t* kv,
+                                  float* d_scratch_o, float* d_scratch_ml, uint32_t* d_tickets,
+                                  void* d_out, int batch, int n_q_heads, int splits, float scale,
+                                  float eps, void* stream) {
+  Q_CHECK_ARG(d_qkv_partials && d_q_gain && d_k_gain && d_cos && d_sin && d_pos && kv && d_out,
+              "q_attention_decode: null pointer");
+  Q_CHECK_ARG(kv->d_kpool && kv->d_vpool && kv->d_block_table && kv->pages_per_seq >= 1 &&
+                  kv->n_kv_heads >= 1,
+              "q_attention_decode: incomplete KV layout");
+  const int nkv = kv->n_kv_heads;
+  Q_CHECK_ARG(batch >= 1 && batch <= Q_MAX_ROWS && n_q_heads >= nkv && n_q_heads % nkv == 0,
+              "q_attention_decode: bad batch/heads");
+  const int G = n_q_heads / nkv;
+  Q_CHECK_ARG(G <= 16, "q_attention_decode: %d query heads per kv head exceed 16", G);
+  Q_CHECK_ARG(splits >= 1 && splits <= 32, "q_attention_decode: splits %d outside 1..32", splits);
+  Q_CHECK_ARG(splits == 1 || (d_scratch_o && d_scratch_ml && d_tickets),
+              "q_attention_decode: split scratch or tickets missing");
+  Q_CHECK_ARG((long long)batch * nkv <= 65535, "q_attention_decode: too many (sequence, kv head) pairs");
+  if (plan) {
+    Q_CHECK_ARG(plan->M == batch && plan->N == (n_q_heads + 2 * nkv) * 128,
+                "q_attention_decode: plan does not match the packed projection");
+  }
+  static bool attr = false;
+  if (!attr) {
+    Q_CHECK_CUDA(cudaFuncSetAttribute(k_attn_decode, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)attn_decode_smem()));
+    attr = true;
+  }
+  Q_CHECK_CUDA(q_launch(k_attn_decode, dim3(splits, batch * nkv), dim3(THREADS), attn_decode_smem(),
+                        (cudaStream_t)stream, d_qkv_partials, plan_view(plan), (const bf16*)d_q_gain,
+                        (const bf16*)d_k_gain, (const bf16*)d_cos, (const bf16*)d_sin, d_pos,
+                        (char*)kv->d_kpool, (char*)kv->d_vpool, kv->d_block_table, kv->pages_per_seq,
+                        d_scratch_o, d_scratch_ml, d_tickets, (bf16*)d_out, batch, G, n_q_heads, nkv,
+                        splits, scale * 1.4426950408889634f, eps));
   return Q_OK;
 }
 

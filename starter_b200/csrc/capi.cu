@@ -41,7 +41,7 @@ int q_sm_count() {
 
 int g_gemm_prefetch_kb = 0;
 int g_gemm_debug_flags = 0;
-static int g_fused_step = 1;     // use the persistent whole-step kernel when it applies
+static int g_fused_step = 0;     // 1 = use the persistent whole-step kernel when it applies
 static int g_trace_layer = -1;   // measurement aid: layer whose phases the whole-step kernel stamps
 
 extern "C" int q_set_option(const char* name, int value) {
@@ -323,10 +323,17 @@ static int attn_block(q_engine* e, int layer, void* stream) {
   const int rows = e->rows;
   q_kv_layout_t kv = kv_of(e, layer);
   TRY(q_gemm_splitk(s.normed, w.wqkv, s.partials, rows, e->p_qkv.N, c.hidden, stream));
-  TRY(q_qkv_norm_rope_cache(s.partials, &e->p_qkv, w.q_gain, w.k_gain, s.cos, s.sin, s.pos, s.q, &kv,
-                            s.batch, 1, c.n_q_heads, c.rms_eps, stream));
-  TRY(q_attention(s.q, &kv, s.pos, s.attn_o, s.attn_ml, s.attended, s.batch, 1, c.n_q_heads,
-                  s.attn_splits, c.attn_scale, stream));
+  if (s.attn_tickets && c.n_q_heads / c.n_kv_heads <= 16) {
+    // head norm + RoPE + K/V write + attention + split merge in one launch
+    TRY(q_attention_decode(s.partials, &e->p_qkv, w.q_gain, w.k_gain, s.cos, s.sin, s.pos, &kv, s.attn_o,
+                           s.attn_ml, s.attn_tickets, s.attended, s.batch, c.n_q_heads, s.attn_splits,
+                           c.attn_scale, c.rms_eps, stream));
+  } else {
+    TRY(q_qkv_norm_rope_cache(s.partials, &e->p_qkv, w.q_gain, w.k_gain, s.cos, s.sin, s.pos, s.q, &kv,
+                              s.batch, 1, c.n_q_heads, c.rms_eps, stream));
+    TRY(q_attention(s.q, &kv, s.pos, s.attn_o, s.attn_ml, s.attended, s.batch, 1, c.n_q_heads,
+                    s.attn_splits, c.attn_scale, stream));
+  }
   TRY(q_gemm_splitk(s.attended, w.wo, s.partials, rows, c.hidden, c.n_q_heads * 128, stream));
   return Q_OK;
 }

@@ -56,12 +56,17 @@ k_embed_rmsnorm(const int64_t* __restrict__ tokens, const bf16* __restrict__ E,
   if (tok < 0) tok = 0;
   if (tok >= vocab) tok = vocab - 1;
   const int C = cols >> 5;
+  // 8 consecutive columns are one 16-byte piece of the tiled table
   float ss = 0.f;
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-    bf16 raw = E[tiled_offset(tok, c, C)];
-    Xo[row * cols + c] = raw;
-    float v = __bfloat162float(raw);
-    ss += v * v;
+  for (int c8 = threadIdx.x; c8 < (cols >> 3); c8 += blockDim.x) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(E + tiled_offset(tok, c8 * 8, C));
+    *reinterpret_cast<uint4*>(Xo + row * cols + c8 * 8) = raw;
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float lo = bf_lo(w[e]), hi = bf_hi(w[e]);
+      ss += lo * lo + hi * hi;
+    }
   }
   ss = block_sum(ss, red);
   const float inv = rsqrtf(ss / (float)cols + eps);
@@ -298,7 +303,9 @@ k_logits_argmax(const float* __restrict__ P, PlanView pv, bf16* __restrict__ log
   __shared__ float sv[8];
   __shared__ int si[8];
   __shared__ bool is_last;
-  pdl_launch_dependents();
+  // Kernels of the NEXT step read *pos_ptr before their own dependency wait (the
+  // attention producer does), so dependents are released only at the very end, after
+  // the position has been bumped.
   pdl_wait();
   const int row = blockIdx.y, nblk = gridDim.x;
   const int c0 = blockIdx.x * ARG_COLS;
@@ -360,7 +367,10 @@ k_logits_argmax(const float* __restrict__ P, PlanView pv, bf16* __restrict__ log
     is_last = (ticket == (unsigned int)(nblk - 1));
   }
   __syncthreads();
-  if (!is_last) return;
+  if (!is_last) {
+    pdl_launch_dependents();
+    return;
+  }
   __threadfence();
   bv = -INFINITY;
   bi = 0x7fffffff;
@@ -386,13 +396,15 @@ k_logits_argmax(const float* __restrict__ P, PlanView pv, bf16* __restrict__ log
     if (tokens) tokens[row] = (int64_t)(bi + vocab_offset);
     if (pos_ptr && row == 0) pos_ptr[0] += pos_inc;
     tickets[row] = 0;  // ready for the next launch (graph replay)
+    __threadfence();
   }
+  __syncthreads();
+  pdl_launch_dependents();
 }
 
 __global__ void k_argmax_merge(const float* __restrict__ val, const int32_t* __restrict__ idx,
                                int shards, int rows, int64_t* __restrict__ tokens,
                                int32_t* __restrict__ pos_ptr, int pos_inc) {
-  pdl_launch_dependents();
   pdl_wait();
   int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row < rows) {
@@ -403,6 +415,8 @@ __global__ void k_argmax_merge(const float* __restrict__ val, const int32_t* __r
     tokens[row] = bi;
     if (row == 0 && pos_ptr) pos_ptr[0] += pos_inc;
   }
+  __threadfence();
+  pdl_launch_dependents();      // after the position write: see k_logits_argmax
 }
 
 }  // namespace

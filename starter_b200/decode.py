@@ -95,6 +95,7 @@ class DecodeState:
         g = nq // nkv
         self.attn_o = torch.empty((batch * nkv, self.attn_splits, g, HEAD_DIM), **f32)
         self.attn_ml = torch.empty((batch * nkv, self.attn_splits, g, 2), **f32)
+        self.attn_tickets = torch.zeros(batch * nkv, dtype=torch.int32, device=dev)
         self.logits = torch.zeros((batch, weights.local_vocab), **bf) if keep_logits else None
         self.arg_val = torch.zeros(batch, **f32)
         self.arg_idx = torch.zeros(batch, dtype=torch.int32, device=dev)
@@ -114,7 +115,8 @@ class DecodeState:
             self.attn_splits, self.x.data_ptr(), self.normed.data_ptr(), self.q.data_ptr(),
             self.attended.data_ptr(), self.act.data_ptr(), self.partials.data_ptr(),
             0 if self.reduced is None else self.reduced.data_ptr(), self.attn_o.data_ptr(),
-            self.attn_ml.data_ptr(), 0 if self.logits is None else self.logits.data_ptr(),
+            self.attn_ml.data_ptr(), self.attn_tickets.data_ptr(),
+            0 if self.logits is None else self.logits.data_ptr(),
             self.arg_val.data_ptr(), self.arg_idx.data_ptr(), self.arg_scratch.data_ptr(),
             0 if self.fused_scratch is None else self.fused_scratch.data_ptr())
         check(lib.q_bind_state(handle, C.byref(st)))

@@ -279,6 +279,30 @@ class SmallQueryAttention:
         return out
 
 
+def decode_attention(qkv, q_weight, k_weight, eps, cos, sin, position, cache: PagedKV,
+                     attn: SmallQueryAttention, scale) -> torch.Tensor:
+    """qkv_norm_rope_cache + SmallQueryAttention.run for one token per sequence in a single
+    launch (engine/decode_step.py:43-48 does the two calls back to back). Returns the
+    attended rows [batch, Hq*128]; the K/V rows of `position` are written to the pages."""
+    if not isinstance(qkv, Partials):
+        raise ValueError("qkv must be split-K Partials of the packed projection")
+    rows, width = qkv.shape
+    if attn.T != 1 or rows != cache.batch or attn.batch != cache.batch or attn.hk != cache.n_kv:
+        raise ValueError("decode_attention handles one token per sequence")
+    if width != (attn.hq + 2 * attn.hk) * HEAD_DIM:
+        raise ValueError("unsupported packed Q/K/V width")
+    if position.shape != (1,) or position.dtype != torch.int32 or not position.is_cuda:
+        raise ValueError("position must be an int32 CUDA tensor of shape [1]")
+    if not hasattr(attn, "tickets"):
+        attn.tickets = torch.zeros(attn.batch * attn.hk, dtype=torch.int32, device=qkv.data.device)
+    out = torch.empty((rows, attn.hq * HEAD_DIM), dtype=torch.bfloat16, device=qkv.data.device)
+    check(lib.q_attention_decode(_ptr(qkv.data), C.byref(qkv.plan), _ptr(q_weight), _ptr(k_weight),
+                                 _ptr(cos), _ptr(sin), _ptr(position), C.byref(cache.layout),
+                                 _ptr(attn.partials), _ptr(attn.stats), _ptr(attn.tickets), _ptr(out),
+                                 rows, attn.hq, attn.splits, float(scale), float(eps), _stream()))
+    return out
+
+
 def lm_head_argmax(normed: torch.Tensor, weight, return_logits: bool = True):
     """BF16 logits and greedy tokens (engine/decode_step.py:60 + engine/decode.py:106):
     lowest index wins exact ties. Returns (logits or None, tokens int64 [rows])."""

@@ -153,12 +153,12 @@ def test_fused_step_matches_multi_kernel_step(cuda, golden_dir):
     gen = torch.Generator().manual_seed(21)
     for batch, length, count in ((1, 9, 12), (2, 70, 8), (3, 5, 6)):
         prompt = torch.randint(0, 127, (batch, length), generator=gen).tolist()
-        fused_tokens, fused_logits = stepwise_logits(engine, prompt, count)
-        _lib.check(_lib.lib.q_set_option(b"fused_step", 0))
+        plain_tokens, plain_logits = stepwise_logits(engine, prompt, count)
+        _lib.check(_lib.lib.q_set_option(b"fused_step", 1))
         try:
-            plain_tokens, plain_logits = stepwise_logits(engine, prompt, count)
+            fused_tokens, fused_logits = stepwise_logits(engine, prompt, count)
         finally:
-            _lib.check(_lib.lib.q_set_option(b"fused_step", 1))
+            _lib.check(_lib.lib.q_set_option(b"fused_step", 0))
         assert fused_tokens == plain_tokens
         torch.testing.assert_close(fused_logits, plain_logits, rtol=1.6e-2, atol=2e-3)
     assert device_status() == [0, 0, 0, 0]

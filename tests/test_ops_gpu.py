@@ -239,6 +239,44 @@ def test_attention_full_size_block(ops):
     torch.testing.assert_close(out.float(), ref.float(), rtol=0.02, atol=5e-3)
 
 
+@pytest.mark.parametrize("B,nq,nkv,pos", [(1, 32, 8, 0), (1, 32, 8, 1100), (3, 8, 2, 63), (2, 8, 2, 64), (4, 4, 2, 700)])
+def test_fused_decode_attention_equals_the_three_kernels(ops, B, nq, nkv, pos):
+    """One launch (norm + RoPE + K/V write + attention + merge) against the separate
+    kernels on the same inputs: bit-identical pages; the attended rows agree to bf16
+    rounding (the fused kernel adds the QK^T k-steps in two interleaved chains) and both
+    sit within rtol=0.02, atol=5e-3 of each other like every attention check here."""
+    capacity = 1200
+    g = torch.Generator().manual_seed(500 + pos + B)
+    width = (nq + 2 * nkv) * 128
+    w, x = randw(width, 256, 61), randx(B, 256, 62) * 4
+    qg = (1 + 0.1 * torch.randn(128, generator=g)).to(torch.bfloat16).cuda()
+    kg = (1 + 0.1 * torch.randn(128, generator=g)).to(torch.bfloat16).cuda()
+    cos, sin = (t.cuda() for t in O.rotary_tables(1_000_000.0, capacity))
+    part = ops.linear_partials(x.cuda(), w.cuda())
+    position = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    k_old = torch.randn((B, nkv, max(pos, 1), 128), generator=g).to(torch.bfloat16).cuda()
+    v_old = torch.randn((B, nkv, max(pos, 1), 128), generator=g).to(torch.bfloat16).cuda()
+    caches = []
+    for _ in range(2):
+        c = ops.PagedKV(B, nkv, capacity, "cuda", poison=float("nan"))
+        if pos:
+            c.scatter(k_old[:, :, :pos], v_old[:, :, :pos], 0)
+        caches.append(c)
+    attn = ops.SmallQueryAttention(B, nq, nkv, capacity, "cuda")
+    q = ops.qkv_norm_rope_cache(part, qg, kg, 1e-6, 1e-6, cos, sin, position, caches[0])
+    ref = attn.run(q, caches[0], position, 128 ** -0.5)
+    for _ in range(2):                                  # twice: the tickets must reset themselves
+        got = ops.decode_attention(part, qg, kg, 1e-6, cos, sin, position, caches[1], attn, 128 ** -0.5)
+        torch.testing.assert_close(got.float(), ref.float(), rtol=0.02, atol=5e-3)
+        assert bit_equal_fraction(got, ref) > 0.9
+    ka, va = caches[0].gather(pos + 1)
+    kb, vb = caches[1].gather(pos + 1)
+    assert torch.equal(ka.view(torch.int16), kb.view(torch.int16))
+    assert torch.equal(va.view(torch.int16), vb.view(torch.int16))
+    assert not torch.isnan(got.float()).any()
+    assert ops.device_status()[0] == 0
+
+
 def test_attention_rejects_bad_shapes(ops):
     with pytest.raises(ValueError):
         ops.SmallQueryAttention(1, 32, 8, 100, "cuda", tokens_per_seq=9)      # 9*4 > 32 rows
