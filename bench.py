@@ -297,12 +297,18 @@ def time_gemm_kernel(state, reps: int = 5):
 
 
 def kernels_per_step(state) -> int:
+    """Launches of this library's kernels in one decode step (NCCL's are not counted)."""
     if state.fused_scratch is not None and os.environ.get("QDECODE_FUSED") == "1":
         return 1                              # the persistent whole-step kernel (opt-in)
-    per_layer = 9 + (1 if state.attn_splits > 1 else 0)
-    n = 1 + state.cfg.n_layers * per_layer + 2
+    layers = state.cfg.n_layers
+    if state.tp == 1 and state.batch <= 8 and os.environ.get("QDECODE_NORM_IN_GEMM", "1") == "1":
+        # embed, first QKV | attention, O, gate_up (add+norm prologue), SwiGLU, down,
+        # next QKV or lm_head (add+norm prologue) | argmax
+        return 2 + 6 * layers + 1
+    # embed | QKV, attention, O, add+norm, gate_up, SwiGLU, down, add+norm | lm_head, argmax
+    n = 1 + 8 * layers + 2
     if state.tp > 1:
-        n += state.cfg.n_layers * 2 + 1      # partial reductions before each all-reduce, argmax merge
+        n += layers * 2 + 1                   # partial reductions before each all-reduce, argmax merge
     return n
 
 
@@ -319,6 +325,12 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
 
     if os.environ.get("QDECODE_FUSED") == "1":      # measure the single persistent kernel instead
         _lib.check(_lib.lib.q_set_option(b"fused_step", 1))
+    for name in os.environ.get("QDECODE_OPTIONS", "").split(","):      # "name=value,..." tuning knobs
+        if name:
+            key, _, val = name.partition("=")
+            _lib.check(_lib.lib.q_set_option(key.encode(), int(val)))
+    if os.environ.get("QDECODE_NORM_IN_GEMM", "1") != "1":   # separate add+norm launches instead
+        _lib.check(_lib.lib.q_set_option(b"norm_in_gemm", 0))
     batch, prompt_len, new_tokens = WORKLOADS[args.workload]
     cfg = dict(QWEN3_4B)
     if args.layers:

@@ -50,15 +50,29 @@ int q_set_pdl(int enabled);
  *   "gemm_prefetch_kb": L2 prefetch window per GEMM CTA in KB (0 = off, default).
  *   "fused_step": 1 = q_decode_step may use the single persistent kernel (default 0: on B200 the
  *       dependent-launch multi-kernel step measured faster, 2.2 vs 2.8 ms at batch 1).
+ *   "norm_in_gemm": 1 (default) = with up to 8 rows on one GPU, q_decode_step runs residual add +
+ *       RMSNorm as the prologue of the projection that consumes them (q_gemm_splitk_addnorm).
  *   "trace_layer": layer stamped by the whole-step kernel (see q_debug_step_trace), -1 off.
  *   "gemm_debug_flags": measurement aid, 4 = per-CTA time stamps for q_debug_gemm_trace.
+ *   "gemm_trace_launch": measurement aid, n >= 0 = only the n-th GEMM launch from now records
+ *       its CTA trace (so one projection inside a captured step can be looked at), -1 off.
+ *   "timeline": measurement aid, 1 = per-launch time stamps for q_debug_timeline.
  * Unknown names return Q_ERR_ARG. */
 int q_set_option(const char* name, int value);
 
 /* Measurement aid: with option "gemm_debug_flags" bit 4 set, every GEMM CTA records
- * {SM id, start, first data, loop end, exit} (ns, %globaltimer); this copies the
- * records of the last launch to the host (5 values per CTA). */
+ * {SM id, start, past the dependency wait, prologue done, first stage landed, loop end,
+ * exit, 0} (ns, %globaltimer); this copies the records of the last recording launch to the
+ * host (8 values per CTA). */
 int q_debug_gemm_trace(unsigned long long* out, int n_ctas);
+
+/* Measurement aid: with option "timeline" = 1 (set before the launches, and before a graph
+ * capture that should carry it), the kernels of q_decode_step's default path record, per
+ * launch in launch order, {first CTA start, first CTA past its dependency wait, last warp
+ * end, last CTA start} in %globaltimer ns. Copies up to max_records records (4 values each)
+ * of the most recent execution, re-arms the records and returns the count (or a negative
+ * q_status). At most 1024 launches are recorded after the option is set. */
+int q_debug_timeline(unsigned long long* out, int max_records);
 
 /* Measurement aid: with option "trace_layer" = l, the whole-step kernel stamps the
  * phase boundaries of layer l (%globaltimer ns) for CTA 0 (out[0..31]) and CTA 100
@@ -103,6 +117,16 @@ int q_unpack_weight(const void* d_tiled, void* d_rowmajor, int N, int K, void* s
 /* d_w_tiled is a weight in the tiled layout above. */
 int q_gemm_splitk(const void* d_x, const void* d_w_tiled, float* d_partials,
                   int M, int N, int K, void* stream);
+
+/* engine/kernels/decode_fused.py:140-158 (add_rms_norm) folded into the projection that
+ * consumes it (engine/decode_step.py:50-59 calls them back to back): every CTA rebuilds
+ * resid_out = bf16(resid_in + bf16(sum of d_prev slots)) and X = RMSNorm(resid_out) * gain
+ * in shared memory and then streams its weights; d_resid_out (written once, must differ
+ * from d_resid_in) is the new residual. 1..8 rows, K <= 3072. prev_plan NULL = d_prev is
+ * one plain fp32 [M][K] buffer. */
+int q_gemm_splitk_addnorm(const void* d_resid_in, const float* d_prev, const q_gemm_plan_t* prev_plan,
+                          const void* d_gain, void* d_resid_out, const void* d_w_tiled,
+                          float* d_partials, int M, int N, int K, float eps, void* stream);
 
 /* Sums the slots of a plan into one fp32 [M,N] buffer (no rounding). Used
  * before a tensor-parallel all-reduce, which must add fp32 partials. */

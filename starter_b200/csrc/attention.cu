@@ -18,6 +18,8 @@
 // hang the GPU.
 #include "common.cuh"
 
+extern int g_attn_ring_fixed;   // q_set_option "attn_ring_fixed"
+
 namespace {
 
 constexpr int NS = 3;                      // ring stages
@@ -419,7 +421,12 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
               const int32_t* __restrict__ pos_ptr, char* __restrict__ kpool, char* __restrict__ vpool,
               const int32_t* __restrict__ block_table, int pages_per_seq, float* __restrict__ part_o,
               float* __restrict__ part_ml, unsigned int* __restrict__ tickets, bf16* __restrict__ out,
-              int rows, int G, int nq, int nkv, int S, float scale_log2, float eps) {
+              int rows, int G, int nq, int nkv, int S, float scale_log2, float eps, int ring_stages,
+              unsigned long long* tl) {
+  // Ring depth is a launch parameter here: a split that can never see more than one or
+  // two tiles asks for that much shared memory only, so this CTA fits on an SM beside a
+  // weight-streaming GEMM CTA (the next projection primes its ring during the attention).
+  const int NS = ring_stages;
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* stages = smem;                               // NS * STAGE_BYTES
   unsigned char* qtile = smem + NS * STAGE_BYTES;             // 16 rows * 256 B
@@ -428,6 +435,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
   bf16* vnew = knew + 128;                                    // [128]
   __shared__ int s_last;
 
+  tl_begin(tl);
   pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.y, split = blockIdx.x;
@@ -465,6 +473,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
   }
 
   pdl_wait();          // the QKV partials are complete from here on
+  tl_waited(tl);
 
   // ---- q/k head norm + RoPE (+ v): one warp per head, lane l owns dims 4l..4l+3 ----
   {
@@ -663,16 +672,16 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
     }
     // merge the four consumer states through shared memory (only the G real query rows)
     consumer_sync();
-    float* mo = reinterpret_cast<float*>(stages);            // [4][16][128]
-    float* mml = mo + CONSUMERS * 16 * 128;                  // [4][16][2]
+    float* mo = reinterpret_cast<float*>(stages);            // [4][G][128]: fits one stage for G <= 15
+    float* mml = mo + CONSUMERS * G * 128;                   // [4][G][2]
     if (g < G) {
-      float* dst = mo + ((size_t)warp * 16 + g) * 128;
+      float* dst = mo + ((size_t)warp * G + g) * 128;
 #pragma unroll
       for (int n = 0; n < 16; ++n)
         *reinterpret_cast<float2*>(dst + 8 * n + 2 * t4) = make_float2(oacc[n][0], oacc[n][1]);
       if (t4 == 0) {
-        mml[((size_t)warp * 16 + g) * 2] = m_run[0];
-        mml[((size_t)warp * 16 + g) * 2 + 1] = l_run[0];
+        mml[((size_t)warp * G + g) * 2] = m_run[0];
+        mml[((size_t)warp * G + g) * 2 + 1] = l_run[0];
       }
     }
     consumer_sync();
@@ -680,14 +689,14 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
     for (int r = 0; r < G; ++r) {
       float mw[CONSUMERS], Mx = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < CONSUMERS; ++w) { mw[w] = mml[((size_t)w * 16 + r) * 2]; Mx = fmaxf(Mx, mw[w]); }
+      for (int w = 0; w < CONSUMERS; ++w) { mw[w] = mml[((size_t)w * G + r) * 2]; Mx = fmaxf(Mx, mw[w]); }
       const float Ms = Mx == -INFINITY ? 0.f : Mx;
       float Lsum = 0.f, O = 0.f;
 #pragma unroll
       for (int w = 0; w < CONSUMERS; ++w) {
         const float wt = exp2f(mw[w] - Ms);
-        Lsum += wt * mml[((size_t)w * 16 + r) * 2 + 1];
-        O += wt * mo[((size_t)w * 16 + r) * 128 + d];
+        Lsum += wt * mml[((size_t)w * G + r) * 2 + 1];
+        O += wt * mo[((size_t)w * G + r) * 128 + d];
       }
       if (S == 1) {
         out[((size_t)b * nq + kh * G + r) * 128 + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
@@ -698,7 +707,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
       }
     }
   }
-  if (S == 1) return;
+  if (S == 1) { tl_end(tl); return; }
 
   // ---- the last split of this kv head to finish merges all splits (fixed split order) ----
   __syncthreads();
@@ -710,7 +719,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
     __threadfence();
   }
   __syncthreads();
-  if (!s_last) return;
+  if (!s_last) { tl_end(tl); return; }
   for (int r = warp; r < G; r += CONSUMERS + 1) {
     const size_t base = ((size_t)bh * S) * G + r;
     float m = -INFINITY, l = 0.f;
@@ -742,9 +751,10 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
     packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
     *reinterpret_cast<uint2*>(out + ((size_t)b * nq + kh * G + r) * 128 + lane * 4) = packed;
   }
+  tl_end(tl);
 }
 
-constexpr size_t attn_decode_smem() { return NS * STAGE_BYTES + 16 * 256 + 2 * NS * 8 + 2 * 128 * 2 + 64; }
+constexpr size_t attn_decode_smem(int ns) { return ns * STAGE_BYTES + 16 * 256 + 2 * ns * 8 + 2 * 128 * 2 + 64; }
 
 template <int RT>
 constexpr size_t attn_smem() { return NS * STAGE_BYTES + RT * 16 * 256 + 2 * NS * 8; }
@@ -845,15 +855,20 @@ extern "C" int q_attention_decode(const float* d_qkv_partials, const q_gemm_plan
   static bool attr = false;
   if (!attr) {
     Q_CHECK_CUDA(cudaFuncSetAttribute(k_attn_decode, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)attn_decode_smem()));
+                                      (int)attn_decode_smem(NS)));
     attr = true;
   }
-  Q_CHECK_CUDA(q_launch(k_attn_decode, dim3(splits, batch * nkv), dim3(THREADS), attn_decode_smem(),
+  // most tiles one split can be handed: ceil(ceil(tiles / splits)) over the page capacity
+  int ring = (kv->pages_per_seq + splits - 1) / splits;
+  ring = ring < 1 ? 1 : (ring > NS ? NS : ring);
+  if (g_attn_ring_fixed) ring = NS;
+  if (G == 16 && ring < 2) ring = 2;          // the consumers' merge scratch needs 32.5 KB then
+  Q_CHECK_CUDA(q_launch(k_attn_decode, dim3(splits, batch * nkv), dim3(THREADS), attn_decode_smem(ring),
                         (cudaStream_t)stream, d_qkv_partials, plan_view(plan), (const bf16*)d_q_gain,
                         (const bf16*)d_k_gain, (const bf16*)d_cos, (const bf16*)d_sin, d_pos,
                         (char*)kv->d_kpool, (char*)kv->d_vpool, kv->d_block_table, kv->pages_per_seq,
                         d_scratch_o, d_scratch_ml, d_tickets, (bf16*)d_out, batch, G, n_q_heads, nkv,
-                        splits, scale * 1.4426950408889634f, eps));
+                        splits, scale * 1.4426950408889634f, eps, ring, q_tl_next()));
   return Q_OK;
 }
 

@@ -41,11 +41,55 @@ int q_sm_count() {
 
 int g_gemm_prefetch_kb = 0;
 int g_gemm_debug_flags = 0;
+int g_gemm_trace_launch = -1;    // measurement aid: the one GEMM launch that records its CTA trace
+int g_gemm_launches = 0;
+int g_attn_ring_fixed = 0;        // 1 = decode attention always asks for its full 3-stage ring
 static int g_fused_step = 0;     // 1 = use the persistent whole-step kernel when it applies
+static int g_norm_in_gemm = 1;   // 1 = residual add + RMSNorm as the prologue of the next projection
 static int g_trace_layer = -1;   // measurement aid: layer whose phases the whole-step kernel stamps
+
+// Launch timeline (measurement aid): Q_TL_SLOTS records of 4 stamps, handed out in launch order.
+#define Q_TL_SLOTS 1024
+static __device__ unsigned long long g_timeline[Q_TL_SLOTS * 4];
+static int g_tl_on = 0, g_tl_used = 0;
+static unsigned long long* g_tl_base = nullptr;
+
+static int tl_reset() {
+  static unsigned long long init[Q_TL_SLOTS * 4];
+  for (int i = 0; i < Q_TL_SLOTS; ++i) {
+    init[4 * i] = init[4 * i + 1] = ~0ull;
+    init[4 * i + 2] = init[4 * i + 3] = 0ull;
+  }
+  return cudaMemcpyToSymbol(g_timeline, init, sizeof(init)) == cudaSuccess ? 0 : -1;
+}
+
+unsigned long long* q_tl_next() {
+  if (!g_tl_on || g_tl_base == nullptr || g_tl_used >= Q_TL_SLOTS) return nullptr;
+  return g_tl_base + 4 * (g_tl_used++);
+}
+
+extern "C" int q_debug_timeline(unsigned long long* out, int max_records) {
+  Q_CHECK_ARG(out && max_records >= 1, "q_debug_timeline: bad argument");
+  Q_CHECK_CUDA(cudaDeviceSynchronize());
+  const int n = g_tl_used < max_records ? g_tl_used : max_records;
+  if (n > 0) Q_CHECK_CUDA(cudaMemcpyFromSymbol(out, g_timeline, sizeof(unsigned long long) * 4 * n));
+  if (tl_reset()) { q_set_error("q_debug_timeline: reset failed"); return Q_ERR_CUDA; }
+  return n;
+}
 
 extern "C" int q_set_option(const char* name, int value) {
   Q_CHECK_ARG(name != nullptr, "q_set_option: null name");
+  if (strcmp(name, "timeline") == 0) {
+    g_tl_on = value != 0;
+    g_tl_used = 0;
+    if (g_tl_on) {
+      void* p = nullptr;
+      Q_CHECK_CUDA(cudaGetSymbolAddress(&p, g_timeline));
+      g_tl_base = (unsigned long long*)p;
+      if (tl_reset()) { q_set_error("q_set_option: timeline reset failed"); return Q_ERR_CUDA; }
+    }
+    return Q_OK;
+  }
   if (strcmp(name, "gemm_prefetch_kb") == 0) {
     Q_CHECK_ARG(value >= 0 && value <= 8192, "q_set_option: gemm_prefetch_kb outside 0..8192");
     g_gemm_prefetch_kb = value;
@@ -57,6 +101,19 @@ extern "C" int q_set_option(const char* name, int value) {
   }
   if (strcmp(name, "fused_step") == 0) {
     g_fused_step = value != 0;
+    return Q_OK;
+  }
+  if (strcmp(name, "norm_in_gemm") == 0) {
+    g_norm_in_gemm = value != 0;
+    return Q_OK;
+  }
+  if (strcmp(name, "attn_ring_fixed") == 0) {
+    g_attn_ring_fixed = value != 0;
+    return Q_OK;
+  }
+  if (strcmp(name, "gemm_trace_launch") == 0) {
+    g_gemm_trace_launch = value;
+    g_gemm_launches = 0;
     return Q_OK;
   }
   if (strcmp(name, "gemm_debug_flags") == 0) {
@@ -315,14 +372,26 @@ static q_kv_layout_t kv_of(const q_engine* e, int layer) {
   return kv;
 }
 
-// QKV projection .. attention .. O projection (partials left in st.partials).
-static int attn_block(q_engine* e, int layer, void* stream) {
+// Where the hidden-size projections (O, down) leave their partials. With the add+norm
+// prologue the next projection reads them while it writes its own, so they live in the
+// second buffer behind the first (q_engine_partial_floats sizes both).
+static float* hidden_partials(const q_engine* e, bool second) {
+  return second ? e->st.partials + first_partial_floats(e) : e->st.partials;
+}
+
+// Up to 8 rows on one GPU: residual add + RMSNorm run as the prologue of the projection
+// that consumes them, the residual alternating between st.x and st.normed.
+static bool norm_in_gemm(const q_engine* e) {
+  return e->cfg.tp_size == 1 && e->rows <= 8 && e->cfg.hidden % 4 == 0 && e->cfg.hidden <= 3072 &&
+         g_norm_in_gemm;
+}
+
+// attention .. O projection, from the QKV partials in st.partials.
+static int attn_after_qkv(q_engine* e, int layer, float* o_partials, void* stream) {
   const q_config_t& c = e->cfg;
   const q_state_t& s = e->st;
   const q_layer_weights_t& w = e->layers[layer];
-  const int rows = e->rows;
   q_kv_layout_t kv = kv_of(e, layer);
-  TRY(q_gemm_splitk(s.normed, w.wqkv, s.partials, rows, e->p_qkv.N, c.hidden, stream));
   if (s.attn_tickets && c.n_q_heads / c.n_kv_heads <= 16) {
     // head norm + RoPE + K/V write + attention + split merge in one launch
     TRY(q_attention_decode(s.partials, &e->p_qkv, w.q_gain, w.k_gain, s.cos, s.sin, s.pos, &kv, s.attn_o,
@@ -334,19 +403,31 @@ static int attn_block(q_engine* e, int layer, void* stream) {
     TRY(q_attention(s.q, &kv, s.pos, s.attn_o, s.attn_ml, s.attended, s.batch, 1, c.n_q_heads,
                     s.attn_splits, c.attn_scale, stream));
   }
-  TRY(q_gemm_splitk(s.attended, w.wo, s.partials, rows, c.hidden, c.n_q_heads * 128, stream));
+  TRY(q_gemm_splitk(s.attended, w.wo, o_partials, e->rows, c.hidden, c.n_q_heads * 128, stream));
+  return Q_OK;
+}
+
+// QKV projection .. attention .. O projection (partials left in st.partials).
+static int attn_block(q_engine* e, int layer, void* stream) {
+  const q_state_t& s = e->st;
+  TRY(q_gemm_splitk(s.normed, e->layers[layer].wqkv, s.partials, e->rows, e->p_qkv.N, e->cfg.hidden,
+                    stream));
+  return attn_after_qkv(e, layer, s.partials, stream);
+}
+
+static int mlp_after_gate_up(q_engine* e, int layer, float* down_partials, void* stream) {
+  const q_config_t& c = e->cfg;
+  const q_state_t& s = e->st;
+  TRY(q_swiglu(s.partials, &e->p_gu, s.act, e->rows, c.inter, stream));
+  TRY(q_gemm_splitk(s.act, e->layers[layer].wdown, down_partials, e->rows, c.hidden, c.inter, stream));
   return Q_OK;
 }
 
 static int mlp_block(q_engine* e, int layer, void* stream) {
   const q_config_t& c = e->cfg;
   const q_state_t& s = e->st;
-  const q_layer_weights_t& w = e->layers[layer];
-  const int rows = e->rows;
-  TRY(q_gemm_splitk(s.normed, w.wgu, s.partials, rows, 2 * c.inter, c.hidden, stream));
-  TRY(q_swiglu(s.partials, &e->p_gu, s.act, rows, c.inter, stream));
-  TRY(q_gemm_splitk(s.act, w.wdown, s.partials, rows, c.hidden, c.inter, stream));
-  return Q_OK;
+  TRY(q_gemm_splitk(s.normed, e->layers[layer].wgu, s.partials, e->rows, 2 * c.inter, c.hidden, stream));
+  return mlp_after_gate_up(e, layer, s.partials, stream);
 }
 
 static const void* next_gain(const q_engine* e, int layer) {
@@ -391,15 +472,21 @@ extern "C" int q_step_post_mlp(q_engine* e, int layer, void* stream) {
                        c.hidden, c.rms_eps, stream);
 }
 
+static int head_argmax(q_engine* e, void* stream) {
+  const q_config_t& c = e->cfg;
+  const q_state_t& s = e->st;
+  const bool single = c.tp_size == 1;
+  return q_logits_argmax(s.partials, &e->p_head, s.logits, s.arg_val, s.arg_idx,
+                         single ? s.tokens : nullptr, single ? s.pos : nullptr, 1, s.arg_scratch,
+                         e->rows, c.vocab, c.vocab_offset, stream);
+}
+
 extern "C" int q_step_head(q_engine* e, void* stream) {
   TRY(ready(e, "q_step_head"));
   const q_config_t& c = e->cfg;
   const q_state_t& s = e->st;
   TRY(q_gemm_splitk(s.normed, s.lm_head, s.partials, e->rows, c.vocab, c.hidden, stream));
-  const bool single = c.tp_size == 1;
-  return q_logits_argmax(s.partials, &e->p_head, s.logits, s.arg_val, s.arg_idx,
-                         single ? s.tokens : nullptr, single ? s.pos : nullptr, 1, s.arg_scratch,
-                         e->rows, c.vocab, c.vocab_offset, stream);
+  return head_argmax(e, stream);
 }
 
 extern "C" int q_decode_step(q_engine* e, void* stream) {
@@ -415,6 +502,25 @@ extern "C" int q_decode_step(q_engine* e, void* stream) {
   const q_config_t& c = e->cfg;
   const q_state_t& s = e->st;
   TRY(q_step_begin(e, stream));
+  if (norm_in_gemm(e)) {
+    // st.x holds the residual at every layer boundary; st.normed holds it between the
+    // attention and the MLP half. Hidden-size partials go to the second buffer, which no
+    // projection with a prologue writes.
+    float* hp = hidden_partials(e, true);
+    const int rows = e->rows;
+    TRY(q_gemm_splitk(s.normed, e->layers[0].wqkv, s.partials, rows, e->p_qkv.N, c.hidden, stream));
+    for (int l = 0; l < c.n_layers; ++l) {
+      TRY(attn_after_qkv(e, l, hp, stream));
+      TRY(q_gemm_splitk_addnorm(s.x, hp, &e->p_o, e->layers[l].ln_post, s.normed, e->layers[l].wgu,
+                                s.partials, rows, 2 * c.inter, c.hidden, c.rms_eps, stream));
+      TRY(mlp_after_gate_up(e, l, hp, stream));
+      const bool last = l + 1 == c.n_layers;
+      TRY(q_gemm_splitk_addnorm(s.normed, hp, &e->p_down, next_gain(e, l), s.x,
+                                last ? s.lm_head : e->layers[l + 1].wqkv, s.partials, rows,
+                                last ? c.vocab : e->p_qkv.N, c.hidden, c.rms_eps, stream));
+    }
+    return head_argmax(e, stream);
+  }
   for (int l = 0; l < c.n_layers; ++l) {
     TRY(attn_block(e, l, stream));
     TRY(q_add_rmsnorm(s.x, s.partials, &e->p_o, e->layers[l].ln_post, s.x, s.normed, e->rows,

@@ -47,6 +47,11 @@ static inline cudaError_t q_launch(void (*kernel)(KArgs...), dim3 grid, dim3 blo
 
 int q_sm_count();
 
+// Measurement aid: a per-launch record {first CTA start, first CTA past the dependency
+// wait, last warp end, last CTA start} in %globaltimer ns. Launchers pass q_tl_next() as
+// the kernel's last argument: null unless option "timeline" is on, else the next record.
+unsigned long long* q_tl_next();
+
 // Split-K plan passed by value to consumer kernels. u == 0 means "one plain
 // fp32 [rows][cols] buffer".
 struct PlanView {
@@ -69,6 +74,29 @@ static inline PlanView plan_view(const q_gemm_plan_t* p) {
 
 // ---- device side ---------------------------------------------------------------
 #ifdef __CUDACC__
+
+__device__ __forceinline__ unsigned long long tl_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void tl_begin(unsigned long long* tl) {
+  if (tl != nullptr && threadIdx.x == 0) {
+    const unsigned long long t = tl_now();
+    atomicMin(tl, t);
+    atomicMax(tl + 3, t);
+  }
+}
+__device__ __forceinline__ void tl_waited(unsigned long long* tl) {
+  if (tl != nullptr && threadIdx.x == 0) atomicMin(tl + 1, tl_now());
+}
+// Called by every thread of the CTA that is still running at the kernel's end.
+__device__ __forceinline__ void tl_end(unsigned long long* tl) {
+  if (tl != nullptr) {
+    __syncthreads();
+    if (threadIdx.x == 0) atomicMax(tl + 2, tl_now());
+  }
+}
 
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

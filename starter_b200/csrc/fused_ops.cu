@@ -47,10 +47,12 @@ __device__ __forceinline__ size_t tiled_offset(long long row, int c, int C) {
 __global__ void __launch_bounds__(256)
 k_embed_rmsnorm(const int64_t* __restrict__ tokens, const bf16* __restrict__ E,
                 const bf16* __restrict__ G, bf16* __restrict__ Xo, bf16* __restrict__ No,
-                int cols, int vocab, float eps) {
+                int cols, int vocab, float eps, unsigned long long* tl) {
   __shared__ float red[32];
+  tl_begin(tl);
   pdl_launch_dependents();
   pdl_wait();
+  tl_waited(tl);
   const size_t row = blockIdx.x;
   long long tok = tokens[row];
   if (tok < 0) tok = 0;
@@ -74,6 +76,7 @@ k_embed_rmsnorm(const int64_t* __restrict__ tokens, const bf16* __restrict__ E,
     float v = bf16_round(__bfloat162float(Xo[row * cols + c]) * inv);
     No[row * cols + c] = __float2bfloat16_rn(v * __bfloat162float(G[c]));
   }
+  tl_end(tl);
 }
 
 // ---- residual add + RMSNorm on partials ------------------------------------
@@ -90,10 +93,12 @@ template <int VB>
 __global__ void __launch_bounds__(256)
 k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanView pv,
               const bf16* __restrict__ G, bf16* __restrict__ Tout, bf16* __restrict__ Nout,
-              int cols, float eps) {
+              int cols, float eps, unsigned long long* tl) {
   __shared__ float red[32];
+  tl_begin(tl);
   pdl_launch_dependents();
   pdl_wait();
+  tl_waited(tl);
   const size_t row = blockIdx.x;
   const float* p0 = P + row * cols;
   const bool two = pv.u != 0;
@@ -145,13 +150,17 @@ k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanVie
       *reinterpret_cast<uint2*>(Nout + row * cols + col) = no;
     }
   }
+  tl_end(tl);
 }
 
 // ---- SwiGLU on gate|up partials ---------------------------------------------
 __global__ void __launch_bounds__(256)
-k_swiglu(const float* __restrict__ P, PlanView pv, bf16* __restrict__ O, int rows, int inter) {
+k_swiglu(const float* __restrict__ P, PlanView pv, bf16* __restrict__ O, int rows, int inter,
+         unsigned long long* tl) {
+  tl_begin(tl);
   pdl_launch_dependents();
   pdl_wait();
+  tl_waited(tl);
   const long long quads = (long long)rows * (inter >> 2);
   const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (q >= quads) return;
@@ -185,6 +194,7 @@ k_swiglu(const float* __restrict__ P, PlanView pv, bf16* __restrict__ O, int row
   pk.x = pack_bf16(o[0], o[1]);
   pk.y = pack_bf16(o[2], o[3]);
   *reinterpret_cast<uint2*>(O + (long long)m * inter + c) = pk;
+  tl_end(tl);
 }
 
 // ---- q/k head norm + RoPE + KV page write -------------------------------------
@@ -299,14 +309,16 @@ k_logits_argmax(const float* __restrict__ P, PlanView pv, bf16* __restrict__ log
                 float* __restrict__ out_val, int32_t* __restrict__ out_idx,
                 int64_t* __restrict__ tokens, int32_t* __restrict__ pos_ptr, int pos_inc,
                 unsigned int* __restrict__ tickets, float* __restrict__ bval,
-                int* __restrict__ bidx, int vocab, int vocab_offset) {
+                int* __restrict__ bidx, int vocab, int vocab_offset, unsigned long long* tl) {
   __shared__ float sv[8];
   __shared__ int si[8];
   __shared__ bool is_last;
+  tl_begin(tl);
   // Kernels of the NEXT step read *pos_ptr before their own dependency wait (the
   // attention producer does), so dependents are released only at the very end, after
   // the position has been bumped.
   pdl_wait();
+  tl_waited(tl);
   const int row = blockIdx.y, nblk = gridDim.x;
   const int c0 = blockIdx.x * ARG_COLS;
   float bv = -INFINITY;
@@ -399,6 +411,7 @@ k_logits_argmax(const float* __restrict__ P, PlanView pv, bf16* __restrict__ log
     __threadfence();
   }
   __syncthreads();
+  tl_end(tl);
   pdl_launch_dependents();
 }
 
@@ -439,7 +452,7 @@ extern "C" int q_embed_rmsnorm(const int64_t* d_tokens, const void* d_embed, con
               "q_embed_rmsnorm: bad argument (cols must be a multiple of 32)");
   Q_CHECK_CUDA(q_launch(k_embed_rmsnorm, dim3(rows), dim3(256), 0, S(stream), d_tokens,
                         (const bf16*)d_embed, (const bf16*)d_gain, (bf16*)d_x, (bf16*)d_normed, cols,
-                        vocab, eps));
+                        vocab, eps, q_tl_next()));
   return Q_OK;
 }
 
@@ -463,7 +476,7 @@ extern "C" int q_add_rmsnorm(const void* d_x_in, const float* d_branch, const q_
   auto kern = cols <= 1024 ? k_add_rmsnorm<1> : cols <= 3072 ? k_add_rmsnorm<3> : k_add_rmsnorm<ADD_VB>;
   Q_CHECK_CUDA(q_launch(kern, dim3(rows), dim3(256), 0, S(stream), (const bf16*)d_x_in,
                         d_branch, plan_view(plan), (const bf16*)d_gain, (bf16*)d_total_out,
-                        (bf16*)d_normed_out, cols, eps));
+                        (bf16*)d_normed_out, cols, eps, q_tl_next()));
   return Q_OK;
 }
 
@@ -475,7 +488,7 @@ extern "C" int q_swiglu(const float* d_branch, const q_gemm_plan_t* plan, void* 
   if (rc) return rc;
   long long total = (long long)rows * (inter / 4);
   Q_CHECK_CUDA(q_launch(k_swiglu, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, S(stream),
-                        d_branch, plan_view(plan), (bf16*)d_out, rows, inter));
+                        d_branch, plan_view(plan), (bf16*)d_out, rows, inter, q_tl_next()));
   return Q_OK;
 }
 
@@ -543,7 +556,7 @@ extern "C" int q_logits_argmax(const float* d_branch, const q_gemm_plan_t* plan,
   int* bidx = (int*)(base + tick + (int64_t)rows * nblk * 4);
   Q_CHECK_CUDA(q_launch(k_logits_argmax, dim3(nblk, rows), dim3(256), 0, S(stream), d_branch,
                         plan_view(plan), (bf16*)d_logits, d_val, d_idx, d_tokens, d_pos, pos_inc,
-                        tickets, bval, bidx, vocab, vocab_offset));
+                        tickets, bval, bidx, vocab, vocab_offset, q_tl_next()));
   return Q_OK;
 }
 

@@ -41,6 +41,8 @@
 
 extern int g_gemm_prefetch_kb;   // set through q_set_option
 extern int g_gemm_debug_flags;   // set through q_set_option: 4 = record the per-CTA trace
+extern int g_gemm_trace_launch;  // >= 0: only that GEMM launch (counted from when it was set) records
+extern int g_gemm_launches;
 
 namespace {
 
@@ -61,8 +63,9 @@ constexpr int RING_BYTES = WARPS * STAGES * STAGE_UNITS * 1024;   // 96 KB
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 __device__ int g_gemm_status[4];
-// Measurement aid (debug flag 4): per CTA {smid, t_start, t_first_data, t_loop_end, t_exit} in ns.
-__device__ unsigned long long g_gemm_trace[256 * 5];
+// Measurement aid (debug flag 4): per CTA {smid, start, past the dependency wait, prologue done,
+// first stage landed, loop end, exit, 0} in ns.
+__device__ unsigned long long g_gemm_trace[256 * 8];
 
 __device__ __forceinline__ unsigned long long gtime() {
   unsigned long long t;
@@ -132,24 +135,45 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// NT = number of 8-row activation tiles (M <= 8*NT).
-template <int NT>
+// Optional prologue: instead of reading a ready activation matrix, every CTA builds it
+// from the previous projection's partials: resid_out = bf16(resid_in + bf16(sum of
+// slots)); X = RMSNorm(resid_out) * gain (engine/kernels/decode_fused.py:19-44). All CTAs
+// compute the same rows into their shared memory; CTA 0 alone stores resid_out (a different
+// buffer than resid_in, which the other CTAs are still reading). This removes the
+// single-CTA add+norm kernel between two GEMMs, and the prologue's one memory round trip
+// runs while the ring is filling.
+struct NormPrologue {
+  const float* prev;          // partials of the previous projection [slots][M][K]
+  PlanView prev_plan;
+  const bf16* resid_in;       // [M][K]
+  bf16* resid_out;            // [M][K]
+  const bf16* gain;           // [K]
+  float eps;
+};
+
+// NT = number of 8-row activation tiles (M <= 8*NT). PRO: activation rows come from the
+// add+norm prologue (in shared memory) instead of global memory.
+template <int NT, bool PRO>
 __global__ void __launch_bounds__(THREADS, (RING_BYTES <= 100 * 1024 ? 2 : 1))
 k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
                float* __restrict__ P, int M, int N, int K, int C, int total, int U,
-               int prefetch_bytes, int dbg) {
+               int prefetch_bytes, int dbg, NormPrologue pro, unsigned long long* tl) {
   extern __shared__ __align__(1024) unsigned char smem[];
   float* red = reinterpret_cast<float*>(smem + RING_BYTES);            // [WARPS][2][NT*128]
   int* tags = reinterpret_cast<int*>(red + WARPS * 2 * NT * 128);      // [WARPS][2] group or -1
   uint64_t* bars = reinterpret_cast<uint64_t*>(tags + WARPS * 2);      // [WARPS][STAGES]
+  bf16* xsm = reinterpret_cast<bf16*>(bars + WARPS * STAGES);          // PRO: [M][K] activations
+  const int XLD = PRO ? K + 32 : K;        // row stride; +64 B keeps the 8 rows of a fragment off one bank
+  float* psum = reinterpret_cast<float*>(xsm + (PRO ? (size_t)M * XLD : 0));   // PRO: 32 floats
 
+  tl_begin(tl);
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const bool trace = (dbg & 4) && tid == 0 && blockIdx.x < 256;
   if (trace) {
-    g_gemm_trace[blockIdx.x * 5 + 0] = smid();
-    g_gemm_trace[blockIdx.x * 5 + 1] = gtime();
+    g_gemm_trace[blockIdx.x * 8 + 0] = smid();
+    g_gemm_trace[blockIdx.x * 8 + 1] = gtime();
   }
   const int cs = blockIdx.x * U;
   const int ce = min(total, cs + U);
@@ -170,7 +194,10 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
     for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    for (int s = 0; s < STAGES && s < n_stages; ++s) {
+    // With the prologue only the first stage is requested here: the prologue's few KB of
+    // dependent loads would otherwise queue behind the whole ring's worth of bulk copies
+    // (measured: 3.5 us instead of ~1.5 us from the dependency wait to the first MMA).
+    for (int s = 0; s < (PRO ? 1 : STAGES) && s < n_stages; ++s) {
       const uint32_t bytes = (uint32_t)min(STAGE_UNITS, n_units - s * STAGE_UNITS) * 1024u;
       mbar_expect_tx(bar0 + 8 * s, bytes);
       bulk_g2s(ring + s * (STAGE_UNITS * 1024), src + (size_t)s * STAGE_UNITS * 1024, bytes, bar0 + 8 * s);
@@ -180,9 +207,80 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
   __syncwarp();
 
   pdl_wait();   // X and the previous readers of P are complete from here on
+  tl_waited(tl);
+  if (trace) g_gemm_trace[blockIdx.x * 8 + 2] = gtime();
+
+  if (PRO) {
+    // add + norm: thread t owns columns 4t..4t+3 (+1024 j); all loads first
+    constexpr int VB = 3;                       // K <= 3072 (checked on the host)
+    for (int m = 0; m < M; ++m) {
+      float4 s0[VB], s1[VB];
+      uint2 xr[VB], gn[VB];
+#pragma unroll
+      for (int j = 0; j < VB; ++j) {
+        const int col = 4 * tid + j * 1024;
+        const int cc = col < K ? col : 0;
+        s0[j] = *reinterpret_cast<const float4*>(pro.prev + (size_t)m * K + cc);
+        s1[j] = pro.prev_plan.u != 0
+                    ? *reinterpret_cast<const float4*>(pro.prev + (size_t)m * K + cc + pro.prev_plan.slot_stride)
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
+        xr[j] = *reinterpret_cast<const uint2*>(pro.resid_in + (size_t)m * K + cc);
+        gn[j] = *reinterpret_cast<const uint2*>(pro.gain + cc);
+      }
+      if (m == 0 && lane == 0) {
+        // the rest of the ring, behind the prologue's loads in the memory system's queues
+        for (int s = 1; s < STAGES && s < n_stages; ++s) {
+          const uint32_t bytes = (uint32_t)min(STAGE_UNITS, n_units - s * STAGE_UNITS) * 1024u;
+          mbar_expect_tx(bar0 + 8 * s, bytes);
+          bulk_g2s(ring + s * (STAGE_UNITS * 1024), src + (size_t)s * STAGE_UNITS * 1024, bytes,
+                   bar0 + 8 * s);
+        }
+      }
+      float tot[VB][4];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < VB; ++j) {
+        const int col = 4 * tid + j * 1024;
+        if (col < K) {
+          const int extra = plan_count(pro.prev_plan, col) - 1;
+          float s[4] = {s0[j].x, s0[j].y, s0[j].z, s0[j].w};
+          if (extra > 0) { s[0] += s1[j].x; s[1] += s1[j].y; s[2] += s1[j].z; s[3] += s1[j].w; }
+          for (int k = 2; k <= extra; ++k) {
+            const float4 sk = *reinterpret_cast<const float4*>(pro.prev + (size_t)m * K + col +
+                                                               (long long)k * pro.prev_plan.slot_stride);
+            s[0] += sk.x; s[1] += sk.y; s[2] += sk.z; s[3] += sk.w;
+          }
+          const float r[4] = {bf_lo(xr[j].x), bf_hi(xr[j].x), bf_lo(xr[j].y), bf_hi(xr[j].y)};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            tot[j][e] = bf16_round(r[e] + bf16_round(s[e]));
+            ss += tot[j][e] * tot[j][e];
+          }
+        }
+      }
+      ss = block_sum(ss, psum);
+      const float inv = rsqrtf(ss / (float)K + pro.eps);
+#pragma unroll
+      for (int j = 0; j < VB; ++j) {
+        const int col = 4 * tid + j * 1024;
+        if (col < K) {
+          const float g4[4] = {bf_lo(gn[j].x), bf_hi(gn[j].x), bf_lo(gn[j].y), bf_hi(gn[j].y)};
+          uint2 ro, xo;
+          ro.x = pack_bf16(tot[j][0], tot[j][1]);
+          ro.y = pack_bf16(tot[j][2], tot[j][3]);
+          xo.x = pack_bf16(bf16_round(tot[j][0] * inv) * g4[0], bf16_round(tot[j][1] * inv) * g4[1]);
+          xo.y = pack_bf16(bf16_round(tot[j][2] * inv) * g4[2], bf16_round(tot[j][3] * inv) * g4[3]);
+          *reinterpret_cast<uint2*>(xsm + (size_t)m * XLD + col) = xo;
+          if (blockIdx.x == 0) *reinterpret_cast<uint2*>(pro.resid_out + (size_t)m * K + col) = ro;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (trace) g_gemm_trace[blockIdx.x * 8 + 3] = gtime();
 
   // Warm L1 with the activation rows (every CTA reads all of X, a few KB).
-  {
+  if (!PRO) {
     const int lines = (M * K * 2 + 127) >> 7;
     if (lines <= 320)
       for (int i = tid; i < lines; i += THREADS)
@@ -208,7 +306,7 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int m = nt * 8 + g;
-    xrow[nt] = m < M ? X + (size_t)m * K + t * 8 : nullptr;
+    xrow[nt] = m < M ? (PRO ? xsm : X) + (size_t)m * XLD + t * 8 : nullptr;
   }
 
   for (int st = 0; st < n_stages && alive; ++st) {
@@ -218,7 +316,7 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
       alive = false;
       break;
     }
-    if (trace && st == 0) g_gemm_trace[blockIdx.x * 5 + 2] = gtime();
+    if (trace && st == 0) g_gemm_trace[blockIdx.x * 8 + 4] = gtime();
     const int in_stage = min(STAGE_UNITS, n_units - st * STAGE_UNITS);
     uint32_t sbase = ring + sidx * (STAGE_UNITS * 1024) + lane * 16;
     int done = 0;
@@ -233,7 +331,8 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           xs[j][nt] = make_uint4(0, 0, 0, 0);
-          if (j < n && xrow[nt] != nullptr) xs[j][nt] = ldg_cached(xrow[nt] + koff);
+          if (j < n && xrow[nt] != nullptr)
+            xs[j][nt] = PRO ? *reinterpret_cast<const uint4*>(xrow[nt] + koff) : ldg_cached(xrow[nt] + koff);
         }
       }
 #pragma unroll
@@ -301,7 +400,7 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
     }
   }
 
-  if (trace) g_gemm_trace[blockIdx.x * 5 + 3] = gtime();
+  if (trace) g_gemm_trace[blockIdx.x * 8 + 5] = gtime();
   // ---- add the ragged ends across the CTA: one partial per (CTA, group) ----
   __syncthreads();
   // The warp that holds the FIRST parked entry of a group adds all entries of that
@@ -336,7 +435,8 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
       }
     }
   }
-  if (trace) g_gemm_trace[blockIdx.x * 5 + 4] = gtime();
+  if (trace) g_gemm_trace[blockIdx.x * 8 + 6] = gtime();
+  tl_end(tl);
 }
 
 // Sums the slots of each element into one fp32 value (tensor-parallel path).
@@ -391,19 +491,41 @@ constexpr int gemm_smem() {
   return RING_BYTES + WARPS * 2 * NT * 128 * 4 + WARPS * 2 * 4 + WARPS * STAGES * 8;
 }
 
+int debug_flags_of_this_launch() {
+  if (g_gemm_trace_launch < 0) return g_gemm_debug_flags;
+  return g_gemm_launches++ == g_gemm_trace_launch ? 4 : 0;
+}
+
 template <int NT>
 cudaError_t launch_gemm(const q_gemm_plan_t& p, const bf16* X, const unsigned char* W, float* P,
                         cudaStream_t s) {
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         gemm_smem<NT>());
+    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<NT, false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_smem<NT>());
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
-  return q_launch(k_gemm_streamk<NT>, dim3(p.grid), dim3(p.block), (size_t)gemm_smem<NT>(), s, X, W, P,
-                  p.M, p.N, p.K, p.chunks_per_group, p.groups * p.chunks_per_group,
-                  p.units_per_worker, g_gemm_prefetch_kb * 1024 / WARPS, g_gemm_debug_flags);
+  NormPrologue none = {};
+  return q_launch(k_gemm_streamk<NT, false>, dim3(p.grid), dim3(p.block), (size_t)gemm_smem<NT>(), s, X,
+                  W, P, p.M, p.N, p.K, p.chunks_per_group, p.groups * p.chunks_per_group,
+                  p.units_per_worker, g_gemm_prefetch_kb * 1024 / WARPS, debug_flags_of_this_launch(), none,
+                  q_tl_next());
+}
+
+cudaError_t launch_gemm_norm(const q_gemm_plan_t& p, const unsigned char* W, float* P,
+                             const NormPrologue& pro, cudaStream_t s) {
+  const size_t smem = (size_t)gemm_smem<1>() + (size_t)p.M * (p.K + 32) * 2 + 32 * 4;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<1, true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured = smem;
+  }
+  return q_launch(k_gemm_streamk<1, true>, dim3(p.grid), dim3(p.block), smem, s, (const bf16*)nullptr, W,
+                  P, p.M, p.N, p.K, p.chunks_per_group, p.groups * p.chunks_per_group,
+                  p.units_per_worker, 0, debug_flags_of_this_launch(), pro, q_tl_next());
 }
 
 }  // namespace
@@ -411,7 +533,7 @@ cudaError_t launch_gemm(const q_gemm_plan_t& p, const bf16* X, const unsigned ch
 extern "C" int q_debug_gemm_trace(unsigned long long* out, int n_ctas) {
   Q_CHECK_ARG(out && n_ctas >= 1 && n_ctas <= 256, "q_debug_gemm_trace: bad argument");
   Q_CHECK_CUDA(cudaDeviceSynchronize());
-  Q_CHECK_CUDA(cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(unsigned long long) * 5 * n_ctas));
+  Q_CHECK_CUDA(cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(unsigned long long) * 8 * n_ctas));
   return Q_OK;
 }
 
@@ -551,6 +673,31 @@ extern "C" int q_linear_f32_static(const void* d_x, const void* d_w_tiled, float
   rc = q_gemm_splitk(d_x, d_w_tiled, scratch, M, N, K, stream);
   if (rc) return rc;
   return q_reduce_partials(scratch, &p, d_out, stream);
+}
+
+extern "C" int q_gemm_splitk_addnorm(const void* d_resid_in, const float* d_prev, const q_gemm_plan_t* prev_plan,
+                                     const void* d_gain, void* d_resid_out, const void* d_w_tiled,
+                                     float* d_partials, int M, int N, int K, float eps, void* stream) {
+  Q_CHECK_ARG(d_resid_in && d_prev && d_gain && d_resid_out && d_w_tiled && d_partials,
+              "q_gemm_splitk_addnorm: null pointer");
+  Q_CHECK_ARG(d_resid_in != d_resid_out, "q_gemm_splitk_addnorm: the residual cannot be updated in place");
+  Q_CHECK_ARG(M >= 1 && M <= 8 && K % 4 == 0 && K <= 3072,
+              "q_gemm_splitk_addnorm: needs 1..8 rows and K a multiple of 4 up to 3072 (M=%d K=%d)", M, K);
+  if (prev_plan)
+    Q_CHECK_ARG(prev_plan->M == M && prev_plan->N == K, "q_gemm_splitk_addnorm: previous plan is [%d,%d]",
+                prev_plan->M, prev_plan->N);
+  q_gemm_plan_t p;
+  int rc = q_gemm_plan(M, N, K, &p);
+  if (rc) return rc;
+  NormPrologue pro;
+  pro.prev = d_prev;
+  pro.prev_plan = plan_view(prev_plan);
+  pro.resid_in = (const bf16*)d_resid_in;
+  pro.resid_out = (bf16*)d_resid_out;
+  pro.gain = (const bf16*)d_gain;
+  pro.eps = eps;
+  Q_CHECK_CUDA(launch_gemm_norm(p, (const unsigned char*)d_w_tiled, d_partials, pro, (cudaStream_t)stream));
+  return Q_OK;
 }
 
 extern "C" int q_reduce_partials(const float* d_partials, const q_gemm_plan_t* plan,

@@ -126,6 +126,28 @@ def add_rms_norm(residual: torch.Tensor, branch, weight: torch.Tensor, eps: floa
     return total, normed
 
 
+def add_rms_norm_linear(residual: torch.Tensor, branch, gain: torch.Tensor, eps: float, weight):
+    """(residual + branch, RMSNorm(that sum) @ weight.T as split-K partials): add_rms_norm
+    (engine/kernels/decode_fused.py:140-158) run as the prologue of the projection that
+    consumes it (engine/decode_step.py:50-59), one launch. Up to 8 rows, K <= 3072."""
+    rows, cols = _bf16_2d(residual, "residual")
+    if gain.shape != (cols,) or gain.dtype != torch.bfloat16 or gain.device != residual.device:
+        raise ValueError("residual and gain shapes disagree")
+    if not isinstance(weight, TiledWeight):
+        _bf16_2d(weight, "weight")
+        weight = TiledWeight.pack(weight)
+    N, K = weight.shape
+    if K != cols or weight.data.device != residual.device:
+        raise ValueError("residual and weight disagree on K or device")
+    bp, pp = _branch(branch, rows, cols, residual.device)
+    total = torch.empty_like(residual)
+    p = _lib.plan(rows, N, K)
+    data = torch.empty((p.slots, rows, N), dtype=torch.float32, device=residual.device)
+    check(lib.q_gemm_splitk_addnorm(_ptr(residual), bp, pp, _ptr(gain), _ptr(total), _ptr(weight),
+                                    _ptr(data), rows, N, K, float(eps), _stream()))
+    return total, Partials(data, p)
+
+
 def silu_mul(gate_up, rows: int | None = None) -> torch.Tensor:
     """silu(gate) * up for the packed [rows, 2*I] projection given as partials
     (engine/kernels/decode_fused.py:161-169 on the GEMM's FP32 partials)."""

@@ -164,6 +164,27 @@ def test_fused_step_matches_multi_kernel_step(cuda, golden_dir):
     assert device_status() == [0, 0, 0, 0]
 
 
+def test_norm_prologue_step_matches_separate_add_norm_kernels(cuda, golden_dir):
+    """Default step (add + norm inside the consuming projection, up to 8 rows) against the
+    step with separate add+norm launches: same tokens, logits equal up to the reduction
+    order of the sum of squares."""
+    from starter_b200 import Engine, _lib
+    from starter_b200.ops import device_status
+    engine = Engine(str(golden_dir / "tiny_qwen3"), keep_logits=True)
+    gen = torch.Generator().manual_seed(22)
+    for batch, length, count in ((1, 9, 12), (4, 70, 8), (8, 5, 6)):
+        prompt = torch.randint(0, 127, (batch, length), generator=gen).tolist()
+        new_tokens, new_logits = stepwise_logits(engine, prompt, count)
+        _lib.check(_lib.lib.q_set_option(b"norm_in_gemm", 0))
+        try:
+            old_tokens, old_logits = stepwise_logits(engine, prompt, count)
+        finally:
+            _lib.check(_lib.lib.q_set_option(b"norm_in_gemm", 1))
+        assert new_tokens == old_tokens
+        torch.testing.assert_close(new_logits, old_logits, rtol=1.6e-2, atol=2e-3)
+    assert device_status() == [0, 0, 0, 0]
+
+
 def test_pdl_off_gives_identical_tokens(cuda, golden_dir):
     from starter_b200 import Engine, _lib
     path = str(golden_dir / "tiny_qwen3")

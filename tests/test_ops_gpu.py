@@ -112,6 +112,34 @@ def test_add_rms_norm_on_partials(ops, M):
     assert torch.equal(total2, total) and torch.equal(normed2, normed)
 
 
+@pytest.mark.parametrize("M,N", [(1, 2 * I), (3, 6144), (8, 2 * I), (1, 151936)])
+def test_add_rms_norm_as_gemm_prologue(ops, M, N):
+    """One launch (add + norm in every CTA's shared memory, then the projection) against
+    the two-launch sequence: the residual is bit-identical, and so are the projection's
+    summed partials wherever the normed activations agree (the sum of squares is reduced in
+    a different order, so an activation may differ by one bf16 ulp in rare rows)."""
+    w0, x = randw(H, 4096, 121), randx(M, 4096, 122)
+    res = randx(M, H, 123)
+    gain = (1 + 0.1 * torch.randn(H, generator=torch.Generator().manual_seed(124))).to(torch.bfloat16)
+    w1 = randw(N, H, 125).cuda()
+    part = ops.linear_partials(x.cuda(), w0.cuda())
+    total, normed = ops.add_rms_norm(res.cuda(), part, gain.cuda(), 1e-6)
+    want = ops.linear_partials(normed, w1).sum()
+    for branch in (part, part.sum()):
+        total2, got = ops.add_rms_norm_linear(res.cuda(), branch, gain.cuda(), 1e-6, w1)
+        assert torch.equal(total2, total)
+        assert got.plan.slots == ops.linear_partials(normed, w1).plan.slots
+        torch.testing.assert_close(got.sum(), want, rtol=2e-3, atol=2e-3)
+        assert (got.sum() == want).float().mean().item() > 0.9
+    # and against the oracle's chain
+    et, en = O.add_rms_norm(res, sum_slots(part), gain, 1e-6)
+    ref = O.linear_fp32(en, w1.cpu())
+    torch.testing.assert_close(got.sum().cpu(), ref, rtol=2e-2, atol=2e-2)
+    with pytest.raises(ValueError):
+        ops.add_rms_norm_linear(randx(9, H, 126).cuda(), torch.zeros(9, H, device="cuda"), gain.cuda(),
+                                1e-6, w1)
+
+
 @pytest.mark.parametrize("M", [1, 16])
 def test_swiglu_on_partials(ops, M):
     w, x = randw(2 * I, H, 31), randx(M, H, 32) * 3
