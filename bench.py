@@ -263,8 +263,13 @@ def time_gemm_kernel(state, reps: int = 5):
         for lt in w.layers:
             for x, wt in ((state.normed, lt.wqkv), (state.attended, lt.wo), (state.normed, lt.wgu),
                           (state.act, lt.wdown)):
-                check(lib.q_gemm_splitk(C.c_void_p(x.data_ptr()), C.c_void_p(wt.data_ptr()), P, rows,
-                                        wt.shape[0], wt.shape[1], s))
+                if wt is lt.wgu:      # the step runs this one with the SwiGLU epilogue
+                    check(lib.q_gemm_swiglu(C.c_void_p(x.data_ptr()), C.c_void_p(wt.data_ptr()),
+                                            C.c_void_p(state.act.data_ptr()), rows, wt.shape[0] // 2,
+                                            wt.shape[1], s))
+                else:
+                    check(lib.q_gemm_splitk(C.c_void_p(x.data_ptr()), C.c_void_p(wt.data_ptr()), P, rows,
+                                            wt.shape[0], wt.shape[1], s))
                 launches += 1
                 nbytes += wt.numel() * 2
         check(lib.q_gemm_splitk(C.c_void_p(state.normed.data_ptr()), C.c_void_p(w.lm_head.data_ptr()), P,
@@ -302,11 +307,11 @@ def kernels_per_step(state) -> int:
         return 1                              # the persistent whole-step kernel (opt-in)
     layers = state.cfg.n_layers
     if state.tp == 1 and state.batch <= 8 and os.environ.get("QDECODE_NORM_IN_GEMM", "1") == "1":
-        # embed, first QKV | attention, O, gate_up (add+norm prologue), SwiGLU, down,
+        # embed, first QKV | attention, O, gate|up (add+norm prologue, SwiGLU epilogue), down,
         # next QKV or lm_head (add+norm prologue) | argmax
-        return 2 + 6 * layers + 1
-    # embed | QKV, attention, O, add+norm, gate_up, SwiGLU, down, add+norm | lm_head, argmax
-    n = 1 + 8 * layers + 2
+        return 2 + 5 * layers + 1
+    # embed | QKV, attention, O, add+norm, gate|up with SwiGLU, down, add+norm | lm_head, argmax
+    n = 1 + 7 * layers + 2
     if state.tp > 1:
         n += layers * 2 + 1                   # partial reductions before each all-reduce, argmax merge
     return n

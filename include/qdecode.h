@@ -62,7 +62,7 @@ int q_set_option(const char* name, int value);
 
 /* Measurement aid: with option "gemm_debug_flags" bit 4 set, every GEMM CTA records
  * {SM id, start, past the dependency wait, prologue done, first stage landed, loop end,
- * exit, 0} (ns, %globaltimer); this copies the records of the last recording launch to the
+ * exit, prologue operands in registers} (ns, %globaltimer); this copies the records of the last recording launch to the
  * host (8 values per CTA). */
 int q_debug_gemm_trace(unsigned long long* out, int n_ctas);
 
@@ -73,6 +73,11 @@ int q_debug_gemm_trace(unsigned long long* out, int n_ctas);
  * of the most recent execution, re-arms the records and returns the count (or a negative
  * q_status). At most 1024 launches are recorded after the option is set. */
 int q_debug_timeline(unsigned long long* out, int max_records);
+
+/* Measurement aid: with option "timeline" on, CTA (0,0) of the decode-attention kernel stamps
+ * {start, past the dependency wait, heads normed, tiles done, CTA merged, cluster merged, end, 0}
+ * (ns); this copies the stamps of the last such launch (8 values). */
+int q_debug_attn_trace(unsigned long long* out);
 
 /* Measurement aid: with option "trace_layer" = l, the whole-step kernel stamps the
  * phase boundaries of layer l (%globaltimer ns) for CTA 0 (out[0..31]) and CTA 100
@@ -127,6 +132,20 @@ int q_gemm_splitk(const void* d_x, const void* d_w_tiled, float* d_partials,
 int q_gemm_splitk_addnorm(const void* d_resid_in, const float* d_prev, const q_gemm_plan_t* prev_plan,
                           const void* d_gain, void* d_resid_out, const void* d_w_tiled,
                           float* d_partials, int M, int N, int K, float eps, void* stream);
+
+/* engine/kernels/skinny_gemm.py:49-72,112-121 (linear_silu_mul): act[M][inter] (bf16) =
+ * silu(x @ gate.T) * (x @ up.T) in ONE launch, no partials. d_w_tiled is the tiled layout of
+ * the [2*inter, K] matrix whose rows interleave the two projections in blocks of 8: rows
+ * 16i..16i+7 = gate rows 8i..8i+7, rows 16i+8..16i+15 = up rows 8i..8i+7 (so one tensor-core
+ * tile holds a gate row and its up row in the same thread). Every CTA owns whole 16-row
+ * groups. inter must be a multiple of 8. */
+int q_gemm_swiglu(const void* d_x, const void* d_w_tiled, void* d_act, int M, int inter, int K,
+                  void* stream);
+
+/* The same with q_gemm_splitk_addnorm's prologue in front (1..8 rows, K <= 3072). */
+int q_gemm_swiglu_addnorm(const void* d_resid_in, const float* d_prev, const q_gemm_plan_t* prev_plan,
+                          const void* d_gain, void* d_resid_out, const void* d_w_tiled, void* d_act,
+                          int M, int inter, int K, float eps, void* stream);
 
 /* Sums the slots of a plan into one fp32 [M,N] buffer (no rounding). Used
  * before a tensor-parallel all-reduce, which must add fp32 partials. */

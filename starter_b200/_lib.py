@@ -73,6 +73,7 @@ SIGNATURES = {
     "q_set_pdl": (_I, [_I]),
     "q_set_option": (_I, [C.c_char_p, _I]),
     "q_debug_timeline": (_I, [_P, _I]),
+    "q_debug_attn_trace": (_I, [_P]),
     "q_debug_gemm_trace": (_I, [C.POINTER(C.c_uint64), _I]),
     "q_debug_step_trace": (_I, [C.POINTER(C.c_uint64)]),
     "q_gemm_plan": (_I, [_I, _I, _I, _PLAN]),
@@ -81,6 +82,8 @@ SIGNATURES = {
     "q_unpack_weight": (_I, [_P, _P, _I, _I, _P]),
     "q_gemm_splitk": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "q_gemm_splitk_addnorm": (_I, [_P, _P, _PLAN, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
+    "q_gemm_swiglu": (_I, [_P, _P, _P, _I, _I, _I, _P]),
+    "q_gemm_swiglu_addnorm": (_I, [_P, _P, _PLAN, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
     "q_reduce_partials": (_I, [_P, _PLAN, _P, _P]),
     "q_static_scratch_floats": (C.c_int64, []),
     "q_linear_f32_static": (_I, [_P, _P, _P, _I, _I, _I, _P]),

@@ -19,6 +19,7 @@
 #include "common.cuh"
 
 extern int g_attn_ring_fixed;   // q_set_option "attn_ring_fixed"
+extern int g_attn_no_cluster;   // q_set_option "attn_no_cluster": merge splits through global memory
 
 namespace {
 
@@ -30,6 +31,9 @@ constexpr int THREADS = (CONSUMERS + 1) * 32;
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 __device__ int g_status[4];
+// Measurement aid: phase stamps (ns) of CTA (0,0) of the last decode-attention launch that had a
+// timeline record: start, past the wait, heads normed, tiles done, CTA merged, cluster merged, end.
+__device__ unsigned long long g_attn_trace[8];
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -415,6 +419,11 @@ k_attn_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml
 // all its tiles before the dependency wait, and the consumer that owns the newest key
 // patches that row into the shared-memory tile (and the owner split writes it to the page
 // for later steps).
+// CL: the S splits of a kv head are one thread-block cluster (S <= 8) and merge through
+// distributed shared memory: every CTA parks its (max, sum, O) rows in its own shared
+// memory, the cluster synchronises once, and CTA r of the cluster combines 1/S of the
+// (row, dim) outputs from all S CTAs in split order. No global round trips, no tickets.
+template <bool CL>
 __global__ void __launch_bounds__(THREADS)
 k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict__ QG,
               const bf16* __restrict__ KG, const bf16* __restrict__ COS, const bf16* __restrict__ SIN,
@@ -436,6 +445,8 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
   __shared__ int s_last;
 
   tl_begin(tl);
+  const bool stamp = tl != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0;
+  if (stamp) g_attn_trace[0] = tl_now();
   pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.y, split = blockIdx.x;
@@ -474,20 +485,40 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
 
   pdl_wait();          // the QKV partials are complete from here on
   tl_waited(tl);
+  if (stamp) g_attn_trace[1] = tl_now();
 
-  // ---- q/k head norm + RoPE (+ v): one warp per head, lane l owns dims 4l..4l+3 ----
+  // ---- q/k head norm + RoPE (+ v): lane l owns dims 4l..4l+3. Items 0..G-1 are the query
+  // heads; item G is the key head TOGETHER with the value head (its loads ride along), so
+  // that with 4 query heads per kv head every warp has one item and one memory round trip.
   {
     const int width = (nq + 2 * nkv) * 128;
-    for (int h = warp; h < G + 2; h += CONSUMERS + 1) {
-      const bool is_q = h < G, is_v = h == G + 1;
-      const int head = is_q ? kh * G + h : (is_v ? nq + nkv + kh : nq + kh);
+    for (int h = warp; h < G + 1; h += CONSUMERS + 1) {
+      const bool is_q = h < G;
+      const int head = is_q ? kh * G + h : nq + kh;
       const long long src = (long long)b * width + (long long)head * 128 + 4 * lane;
+      const long long vsrc = (long long)b * width + (long long)(nq + nkv + kh) * 128 + 4 * lane;
+      const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
       const float4 s0 = *reinterpret_cast<const float4*>(PQ + src);
-      const float4 s1 = pv.u != 0 ? *reinterpret_cast<const float4*>(PQ + src + pv.slot_stride)
-                                  : make_float4(0.f, 0.f, 0.f, 0.f);
-      const uint2 graw = is_v ? make_uint2(0, 0) : *reinterpret_cast<const uint2*>((is_q ? QG : KG) + 4 * lane);
+      const float4 s1 = pv.u != 0 ? *reinterpret_cast<const float4*>(PQ + src + pv.slot_stride) : z4;
+      const float4 v0 = is_q ? z4 : *reinterpret_cast<const float4*>(PQ + vsrc);
+      const float4 v1 = (is_q || pv.u == 0) ? z4 : *reinterpret_cast<const float4*>(PQ + vsrc + pv.slot_stride);
+      const uint2 graw = *reinterpret_cast<const uint2*>((is_q ? QG : KG) + 4 * lane);
       const uint2 craw = *reinterpret_cast<const uint2*>(COS + (size_t)pos * 128 + 4 * lane);
       const uint2 sraw = *reinterpret_cast<const uint2*>(SIN + (size_t)pos * 128 + 4 * lane);
+      if (!is_q) {
+        const int vcol = (nq + nkv + kh) * 128 + 4 * lane;
+        const int extra = plan_count(pv, vcol) - 1;
+        float x[4] = {v0.x, v0.y, v0.z, v0.w};
+        if (extra > 0) { x[0] += v1.x; x[1] += v1.y; x[2] += v1.z; x[3] += v1.w; }
+        for (int k = 2; k <= extra; ++k) {
+          const float4 sk = *reinterpret_cast<const float4*>(PQ + vsrc + (long long)k * pv.slot_stride);
+          x[0] += sk.x; x[1] += sk.y; x[2] += sk.z; x[3] += sk.w;
+        }
+        uint2 o;
+        o.x = pack_bf16(x[0], x[1]);
+        o.y = pack_bf16(x[2], x[3]);
+        *reinterpret_cast<uint2*>(vnew + 4 * lane) = o;
+      }
       const int extra = plan_count(pv, head * 128 + 4 * lane) - 1;
       float x[4] = {s0.x, s0.y, s0.z, s0.w};
       if (extra > 0) { x[0] += s1.x; x[1] += s1.y; x[2] += s1.z; x[3] += s1.w; }
@@ -497,13 +528,6 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) x[e] = bf16_round(x[e]);
-      uint2 o;
-      if (is_v) {
-        o.x = pack_bf16(x[0], x[1]);
-        o.y = pack_bf16(x[2], x[3]);
-        *reinterpret_cast<uint2*>(vnew + 4 * lane) = o;
-        continue;
-      }
       float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
       ss = warp_sum(ss);
       const float inv = rsqrtf(ss / 128.f + eps);
@@ -518,6 +542,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
         const float rot = lane < 16 ? -partner : partner;
         outv[e] = bf16_round(n * cs[e]) + bf16_round(rot * sn[e]);
       }
+      uint2 o;
       o.x = pack_bf16(outv[0], outv[1]);
       o.y = pack_bf16(outv[2], outv[3]);
       if (is_q) {
@@ -532,6 +557,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
     }
   }
   __syncthreads();
+  if (stamp) g_attn_trace[2] = tl_now();
   if (owns_new && tid < 16) {
     // the newest key/value row goes to its page for later steps
     const int page = block_table[(size_t)b * pages_per_seq + new_tile];
@@ -670,6 +696,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars[NS + s]));
     }
+    if (stamp) g_attn_trace[3] = tl_now();
     // merge the four consumer states through shared memory (only the G real query rows)
     consumer_sync();
     float* mo = reinterpret_cast<float*>(stages);            // [4][G][128]: fits one stage for G <= 15
@@ -700,6 +727,10 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
       }
       if (S == 1) {
         out[((size_t)b * nq + kh * G + r) * 128 + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
+      } else if (CL) {
+        float* fo = mml + CONSUMERS * G * 2;                   // [G][128] then [G][2]
+        fo[r * 128 + d] = O;
+        if (d == 0) { fo[G * 128 + r * 2] = Mx; fo[G * 128 + r * 2 + 1] = Lsum; }
       } else {
         const size_t row = ((size_t)bh * S + split) * G + r;
         part_o[row * 128 + d] = O;
@@ -707,7 +738,53 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
       }
     }
   }
+  if (stamp) g_attn_trace[4] = tl_now();
   if (S == 1) { tl_end(tl); return; }
+  if (CL) {
+    // every thread of every CTA of the cluster arrives (idle splits too: they parked sum 0)
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (stamp) g_attn_trace[5] = tl_now();
+    const uint32_t fo_local = smem_u32(stages) + (uint32_t)(CONSUMERS * G * 130) * 4u;
+    const int total = G * 128;
+    const int share = (total + S - 1) / S;
+    for (int i = tid; i < share; i += THREADS) {
+      const int v = split * share + i;
+      if (v >= total) break;
+      const int r = v >> 7, d = v & 127;
+      float ms[8], ls[8], os[8];
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        ms[s] = -INFINITY; ls[s] = 0.f; os[s] = 0.f;
+        if (s < S) {
+          uint32_t remote;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(fo_local), "r"(s));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ms[s]) : "r"(remote + (uint32_t)(total + r * 2) * 4u));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ls[s]) : "r"(remote + (uint32_t)(total + r * 2 + 1) * 4u));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(os[s]) : "r"(remote + (uint32_t)(r * 128 + d) * 4u));
+        }
+      }
+      float Mx = -INFINITY;
+#pragma unroll
+      for (int s = 0; s < 8; ++s) Mx = fmaxf(Mx, ls[s] > 0.f ? ms[s] : -INFINITY);
+      if (Mx == -INFINITY) Mx = 0.f;
+      float Lsum = 0.f, O = 0.f;
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        const float wgt = ls[s] > 0.f ? exp2f(ms[s] - Mx) : 0.f;
+        Lsum += wgt * ls[s];
+        O += wgt * os[s];
+      }
+      const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
+      out[((size_t)b * nq + kh * G + r) * 128 + d] = __float2bfloat16_rn(O * inv);
+    }
+    // nobody leaves while a peer may still read its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (stamp) g_attn_trace[6] = tl_now();
+    tl_end(tl);
+    return;
+  }
 
   // ---- the last split of this kv head to finish merges all splits (fixed split order) ----
   __syncthreads();
@@ -769,6 +846,9 @@ extern "C" int q_attention_splits(int batch, int n_kv_heads, int capacity) {
   const int tiles = (capacity + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
   int desired = (2 * sms + vh - 1) / vh;
   int s = desired < tiles ? desired : tiles;
+  // Up to 8 splits merge inside a thread-block cluster (no global round trip); that is
+  // worth more than finer splits while a split still sees at most 4 tiles.
+  if (s > 8 && tiles <= 32) s = 8;
   if (s > 32) s = 32;
   if (s < 1) s = 1;
   return s;
@@ -843,10 +923,10 @@ extern "C" int q_attention_decode(const float* d_qkv_partials, const q_gemm_plan
   Q_CHECK_ARG(batch >= 1 && batch <= Q_MAX_ROWS && n_q_heads >= nkv && n_q_heads % nkv == 0,
               "q_attention_decode: bad batch/heads");
   const int G = n_q_heads / nkv;
-  Q_CHECK_ARG(G <= 16, "q_attention_decode: %d query heads per kv head exceed 16", G);
+  Q_CHECK_ARG(G <= 8, "q_attention_decode: %d query heads per kv head exceed 8", G);
   Q_CHECK_ARG(splits >= 1 && splits <= 32, "q_attention_decode: splits %d outside 1..32", splits);
-  Q_CHECK_ARG(splits == 1 || (d_scratch_o && d_scratch_ml && d_tickets),
-              "q_attention_decode: split scratch or tickets missing");
+  Q_CHECK_ARG(splits <= 8 || (d_scratch_o && d_scratch_ml && d_tickets),
+              "q_attention_decode: split scratch or tickets missing (needed above 8 splits)");
   Q_CHECK_ARG((long long)batch * nkv <= 65535, "q_attention_decode: too many (sequence, kv head) pairs");
   if (plan) {
     Q_CHECK_ARG(plan->M == batch && plan->N == (n_q_heads + 2 * nkv) * 128,
@@ -854,21 +934,46 @@ extern "C" int q_attention_decode(const float* d_qkv_partials, const q_gemm_plan
   }
   static bool attr = false;
   if (!attr) {
-    Q_CHECK_CUDA(cudaFuncSetAttribute(k_attn_decode, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    Q_CHECK_CUDA(cudaFuncSetAttribute(k_attn_decode<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)attn_decode_smem(NS)));
+    Q_CHECK_CUDA(cudaFuncSetAttribute(k_attn_decode<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)attn_decode_smem(NS)));
+    Q_CHECK_CUDA(q_prefer_max_smem(k_attn_decode<false>));
+    Q_CHECK_CUDA(q_prefer_max_smem(k_attn_decode<true>));
     attr = true;
   }
-  // most tiles one split can be handed: ceil(ceil(tiles / splits)) over the page capacity
+  // most tiles one split can be handed: ceil(tiles / splits) over the page capacity
   int ring = (kv->pages_per_seq + splits - 1) / splits;
   ring = ring < 1 ? 1 : (ring > NS ? NS : ring);
   if (g_attn_ring_fixed) ring = NS;
-  if (G == 16 && ring < 2) ring = 2;          // the consumers' merge scratch needs 32.5 KB then
-  Q_CHECK_CUDA(q_launch(k_attn_decode, dim3(splits, batch * nkv), dim3(THREADS), attn_decode_smem(ring),
-                        (cudaStream_t)stream, d_qkv_partials, plan_view(plan), (const bf16*)d_q_gain,
-                        (const bf16*)d_k_gain, (const bf16*)d_cos, (const bf16*)d_sin, d_pos,
-                        (char*)kv->d_kpool, (char*)kv->d_vpool, kv->d_block_table, kv->pages_per_seq,
-                        d_scratch_o, d_scratch_ml, d_tickets, (bf16*)d_out, batch, G, n_q_heads, nkv,
-                        splits, scale * 1.4426950408889634f, eps, ring, q_tl_next()));
+  // the merge scratch (consumer states, then the CTA's own rows) reuses the ring
+  const int scratch_stages = (G * 5 * 130 * 4 + STAGE_BYTES - 1) / STAGE_BYTES;
+  if (ring < scratch_stages) ring = scratch_stages;
+  const bool cluster = splits >= 2 && splits <= 8 && !g_attn_no_cluster;
+  const float sl2 = scale * 1.4426950408889634f;
+  if (cluster) {
+    Q_CHECK_CUDA(q_launch_cluster(k_attn_decode<true>, dim3(splits, batch * nkv), dim3(THREADS),
+                                  attn_decode_smem(ring), (cudaStream_t)stream, (unsigned)splits,
+                                  d_qkv_partials, plan_view(plan), (const bf16*)d_q_gain,
+                                  (const bf16*)d_k_gain, (const bf16*)d_cos, (const bf16*)d_sin, d_pos,
+                                  (char*)kv->d_kpool, (char*)kv->d_vpool, kv->d_block_table,
+                                  kv->pages_per_seq, d_scratch_o, d_scratch_ml, d_tickets, (bf16*)d_out,
+                                  batch, G, n_q_heads, nkv, splits, sl2, eps, ring, q_tl_next()));
+  } else {
+    Q_CHECK_CUDA(q_launch(k_attn_decode<false>, dim3(splits, batch * nkv), dim3(THREADS),
+                          attn_decode_smem(ring), (cudaStream_t)stream, d_qkv_partials, plan_view(plan),
+                          (const bf16*)d_q_gain, (const bf16*)d_k_gain, (const bf16*)d_cos,
+                          (const bf16*)d_sin, d_pos, (char*)kv->d_kpool, (char*)kv->d_vpool,
+                          kv->d_block_table, kv->pages_per_seq, d_scratch_o, d_scratch_ml, d_tickets,
+                          (bf16*)d_out, batch, G, n_q_heads, nkv, splits, sl2, eps, ring, q_tl_next()));
+  }
+  return Q_OK;
+}
+
+extern "C" int q_debug_attn_trace(unsigned long long* out) {
+  Q_CHECK_ARG(out != nullptr, "q_debug_attn_trace: null pointer");
+  Q_CHECK_CUDA(cudaDeviceSynchronize());
+  Q_CHECK_CUDA(cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(unsigned long long) * 8));
   return Q_OK;
 }
 

@@ -43,6 +43,15 @@ int g_gemm_prefetch_kb = 0;
 int g_gemm_debug_flags = 0;
 int g_gemm_trace_launch = -1;    // measurement aid: the one GEMM launch that records its CTA trace
 int g_gemm_launches = 0;
+int g_gemm_next_prime_delay_ns = 0;     // set around one launch by the engine (O projection)
+static int g_o_prime_delay_ns = 0;      // option "o_prime_delay_ns"
+static int g_o_idle_sms = 0;            // option "o_idle_sms": SMs the O projection leaves to the attention CTAs
+// An SM's L1/shared split follows the kernels it runs and only changes while the SM is idle,
+// so a CTA of the NEXT kernel that would fit beside a running one by the byte count still
+// waits when the running kernel asked for a smaller carve-out. 1 = the GEMM and decode-attention
+// kernels all ask for the largest carve-out (read when a kernel is first launched).
+int g_smem_carveout_max = 0;
+int g_attn_no_cluster = 0;        // 1 = decode attention merges its splits through global memory
 int g_attn_ring_fixed = 0;        // 1 = decode attention always asks for its full 3-stage ring
 static int g_fused_step = 0;     // 1 = use the persistent whole-step kernel when it applies
 static int g_norm_in_gemm = 1;   // 1 = residual add + RMSNorm as the prologue of the next projection
@@ -105,6 +114,24 @@ extern "C" int q_set_option(const char* name, int value) {
   }
   if (strcmp(name, "norm_in_gemm") == 0) {
     g_norm_in_gemm = value != 0;
+    return Q_OK;
+  }
+  if (strcmp(name, "smem_carveout_max") == 0) {
+    g_smem_carveout_max = value != 0;
+    return Q_OK;
+  }
+  if (strcmp(name, "o_idle_sms") == 0) {
+    Q_CHECK_ARG(value >= 0 && value <= 96, "q_set_option: o_idle_sms outside 0..96");
+    g_o_idle_sms = value;            // read when a state is bound
+    return Q_OK;
+  }
+  if (strcmp(name, "o_prime_delay_ns") == 0) {
+    Q_CHECK_ARG(value >= 0 && value <= 6000, "q_set_option: o_prime_delay_ns outside 0..6000");
+    g_o_prime_delay_ns = value;
+    return Q_OK;
+  }
+  if (strcmp(name, "attn_no_cluster") == 0) {
+    g_attn_no_cluster = value != 0;
     return Q_OK;
   }
   if (strcmp(name, "attn_ring_fixed") == 0) {
@@ -173,7 +200,12 @@ static int make_plans(q_engine* e, int rows) {
   const q_config_t& c = e->cfg;
   int rc;
   if ((rc = q_gemm_plan(rows, (c.n_q_heads + 2 * c.n_kv_heads) * 128, c.hidden, &e->p_qkv))) return rc;
-  if ((rc = q_gemm_plan(rows, c.hidden, c.n_q_heads * 128, &e->p_o))) return rc;
+  // O projection: optionally on fewer CTAs than SMs (see attn_after_qkv)
+  int o_workers = q_sm_count();
+  if (o_workers <= 0) return Q_ERR_CUDA;
+  if (g_o_idle_sms > 0 && c.tp_size == 1 && rows <= 8 && o_workers - g_o_idle_sms >= 64)
+    o_workers -= g_o_idle_sms;
+  if ((rc = q_gemm_plan_workers(rows, c.hidden, c.n_q_heads * 128, o_workers, &e->p_o))) return rc;
   if ((rc = q_gemm_plan(rows, 2 * c.inter, c.hidden, &e->p_gu))) return rc;
   if ((rc = q_gemm_plan(rows, c.hidden, c.inter, &e->p_down))) return rc;
   if ((rc = q_gemm_plan(rows, c.vocab, c.hidden, &e->p_head))) return rc;
@@ -392,7 +424,7 @@ static int attn_after_qkv(q_engine* e, int layer, float* o_partials, void* strea
   const q_state_t& s = e->st;
   const q_layer_weights_t& w = e->layers[layer];
   q_kv_layout_t kv = kv_of(e, layer);
-  if (s.attn_tickets && c.n_q_heads / c.n_kv_heads <= 16) {
+  if (s.attn_tickets && c.n_q_heads / c.n_kv_heads <= 8) {
     // head norm + RoPE + K/V write + attention + split merge in one launch
     TRY(q_attention_decode(s.partials, &e->p_qkv, w.q_gain, w.k_gain, s.cos, s.sin, s.pos, &kv, s.attn_o,
                            s.attn_ml, s.attn_tickets, s.attended, s.batch, c.n_q_heads, s.attn_splits,
@@ -403,8 +435,13 @@ static int attn_after_qkv(q_engine* e, int layer, float* o_partials, void* strea
     TRY(q_attention(s.q, &kv, s.pos, s.attn_o, s.attn_ml, s.attended, s.batch, 1, c.n_q_heads,
                     s.attn_splits, c.attn_scale, stream));
   }
-  TRY(q_gemm_splitk(s.attended, w.wo, o_partials, e->rows, c.hidden, c.n_q_heads * 128, stream));
-  return Q_OK;
+  // The O projection's CTAs become resident while the attention kernel is still loading the
+  // QKV partials; its weights have the whole attention to arrive, so it holds back its
+  // first copies for a moment instead of queueing 19 MB in front of those loads.
+  g_gemm_next_prime_delay_ns = g_o_prime_delay_ns;
+  const int rc = q_gemm_launch_planned(s.attended, w.wo, o_partials, &e->p_o, stream);
+  g_gemm_next_prime_delay_ns = 0;
+  return rc;
 }
 
 // QKV projection .. attention .. O projection (partials left in st.partials).
@@ -415,19 +452,14 @@ static int attn_block(q_engine* e, int layer, void* stream) {
   return attn_after_qkv(e, layer, s.partials, stream);
 }
 
-static int mlp_after_gate_up(q_engine* e, int layer, float* down_partials, void* stream) {
-  const q_config_t& c = e->cfg;
-  const q_state_t& s = e->st;
-  TRY(q_swiglu(s.partials, &e->p_gu, s.act, e->rows, c.inter, stream));
-  TRY(q_gemm_splitk(s.act, e->layers[layer].wdown, down_partials, e->rows, c.hidden, c.inter, stream));
-  return Q_OK;
-}
-
+// gate|up projection with the SwiGLU epilogue (one launch, the layer's gate|up weight is in
+// q_gemm_swiglu's interleaved row order), then the down projection.
 static int mlp_block(q_engine* e, int layer, void* stream) {
   const q_config_t& c = e->cfg;
   const q_state_t& s = e->st;
-  TRY(q_gemm_splitk(s.normed, e->layers[layer].wgu, s.partials, e->rows, 2 * c.inter, c.hidden, stream));
-  return mlp_after_gate_up(e, layer, s.partials, stream);
+  TRY(q_gemm_swiglu(s.normed, e->layers[layer].wgu, s.act, e->rows, c.inter, c.hidden, stream));
+  TRY(q_gemm_splitk(s.act, e->layers[layer].wdown, s.partials, e->rows, c.hidden, c.inter, stream));
+  return Q_OK;
 }
 
 static const void* next_gain(const q_engine* e, int layer) {
@@ -511,9 +543,9 @@ extern "C" int q_decode_step(q_engine* e, void* stream) {
     TRY(q_gemm_splitk(s.normed, e->layers[0].wqkv, s.partials, rows, e->p_qkv.N, c.hidden, stream));
     for (int l = 0; l < c.n_layers; ++l) {
       TRY(attn_after_qkv(e, l, hp, stream));
-      TRY(q_gemm_splitk_addnorm(s.x, hp, &e->p_o, e->layers[l].ln_post, s.normed, e->layers[l].wgu,
-                                s.partials, rows, 2 * c.inter, c.hidden, c.rms_eps, stream));
-      TRY(mlp_after_gate_up(e, l, hp, stream));
+      TRY(q_gemm_swiglu_addnorm(s.x, hp, &e->p_o, e->layers[l].ln_post, s.normed, e->layers[l].wgu,
+                                s.act, rows, c.inter, c.hidden, c.rms_eps, stream));
+      TRY(q_gemm_splitk(s.act, e->layers[l].wdown, hp, rows, c.hidden, c.inter, stream));
       const bool last = l + 1 == c.n_layers;
       TRY(q_gemm_splitk_addnorm(s.normed, hp, &e->p_down, next_gain(e, l), s.x,
                                 last ? s.lm_head : e->layers[l + 1].wqkv, s.partials, rows,

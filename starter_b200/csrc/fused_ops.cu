@@ -450,6 +450,8 @@ extern "C" int q_embed_rmsnorm(const int64_t* d_tokens, const void* d_embed, con
   Q_CHECK_ARG(d_tokens && d_embed && d_gain && d_x && d_normed && rows >= 1 && cols >= 32 &&
                   cols % 32 == 0 && vocab >= 1,
               "q_embed_rmsnorm: bad argument (cols must be a multiple of 32)");
+  static bool pref = false;
+  if (!pref) { Q_CHECK_CUDA(q_prefer_max_smem(k_embed_rmsnorm)); pref = true; }
   Q_CHECK_CUDA(q_launch(k_embed_rmsnorm, dim3(rows), dim3(256), 0, S(stream), d_tokens,
                         (const bf16*)d_embed, (const bf16*)d_gain, (bf16*)d_x, (bf16*)d_normed, cols,
                         vocab, eps, q_tl_next()));
@@ -487,6 +489,8 @@ extern "C" int q_swiglu(const float* d_branch, const q_gemm_plan_t* plan, void* 
   int rc = check_plan(plan, rows, 2 * inter, "q_swiglu");
   if (rc) return rc;
   long long total = (long long)rows * (inter / 4);
+  static bool pref = false;
+  if (!pref) { Q_CHECK_CUDA(q_prefer_max_smem(k_swiglu)); pref = true; }
   Q_CHECK_CUDA(q_launch(k_swiglu, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, S(stream),
                         d_branch, plan_view(plan), (bf16*)d_out, rows, inter, q_tl_next()));
   return Q_OK;
@@ -554,6 +558,8 @@ extern "C" int q_logits_argmax(const float* d_branch, const q_gemm_plan_t* plan,
   unsigned int* tickets = (unsigned int*)base;
   float* bval = (float*)(base + tick);
   int* bidx = (int*)(base + tick + (int64_t)rows * nblk * 4);
+  static bool pref = false;
+  if (!pref) { Q_CHECK_CUDA(q_prefer_max_smem(k_logits_argmax)); pref = true; }
   Q_CHECK_CUDA(q_launch(k_logits_argmax, dim3(nblk, rows), dim3(256), 0, S(stream), d_branch,
                         plan_view(plan), (bf16*)d_logits, d_val, d_idx, d_tokens, d_pos, pos_inc,
                         tickets, bval, bidx, vocab, vocab_offset, q_tl_next()));

@@ -43,6 +43,7 @@ extern int g_gemm_prefetch_kb;   // set through q_set_option
 extern int g_gemm_debug_flags;   // set through q_set_option: 4 = record the per-CTA trace
 extern int g_gemm_trace_launch;  // >= 0: only that GEMM launch (counted from when it was set) records
 extern int g_gemm_launches;
+extern int g_gemm_next_prime_delay_ns;   // how long the plain kernel's CTAs hold back their first copies
 
 namespace {
 
@@ -64,7 +65,7 @@ constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 __device__ int g_gemm_status[4];
 // Measurement aid (debug flag 4): per CTA {smid, start, past the dependency wait, prologue done,
-// first stage landed, loop end, exit, 0} in ns.
+// first stage landed, loop end, exit, prologue operands arrived} in ns.
 __device__ unsigned long long g_gemm_trace[256 * 8];
 
 __device__ __forceinline__ unsigned long long gtime() {
@@ -103,10 +104,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
   return false;
 }
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+// Weights are read once per step and are far larger than L2: their lines are marked
+// evict-first so that they do not push out what the step re-reads (partials, residual,
+// gains, rotary rows, the KV pages of short contexts).
+__device__ __forceinline__ uint64_t stream_policy() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar,
+                                         uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-      "l"(src), "r"(bytes), "r"(bar)
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar), "l"(policy)
       : "memory");
 }
 __device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
@@ -135,6 +145,13 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// silu(gate) * up with the reference's rounding points (engine/kernels/decode_fused.py:161-169):
+// both sums round to bf16, silu rounds, the product rounds.
+__device__ __forceinline__ bf16 swiglu_bf16(float gate, float up) {
+  const float gt = bf16_round(gate), u = bf16_round(up);
+  return __float2bfloat16_rn(bf16_round(gt / (1.0f + expf(-gt))) * u);
+}
+
 // Optional prologue: instead of reading a ready activation matrix, every CTA builds it
 // from the previous projection's partials: resid_out = bf16(resid_in + bf16(sum of
 // slots)); X = RMSNorm(resid_out) * gain (engine/kernels/decode_fused.py:19-44). All CTAs
@@ -152,12 +169,17 @@ struct NormPrologue {
 };
 
 // NT = number of 8-row activation tiles (M <= 8*NT). PRO: activation rows come from the
-// add+norm prologue (in shared memory) instead of global memory.
-template <int NT, bool PRO>
+// add+norm prologue (in shared memory) instead of global memory. ACT: the weight is a
+// gate|up pair interleaved in blocks of 8 rows (rows 16i..16i+7 = gate rows 8i..8i+7, rows
+// 16i+8..16i+15 = the matching up rows), every CTA owns WHOLE 16-row groups, and the
+// epilogue writes silu(gate) * up as bf16 [M][N/2] into P instead of fp32 partials
+// (engine/kernels/skinny_gemm.py:49-72): one MMA tile holds a gate row in c0/c1 and its up
+// row in c2/c3 of the same thread, so no exchange is needed.
+template <int NT, bool PRO, bool ACT>
 __global__ void __launch_bounds__(THREADS, (RING_BYTES <= 100 * 1024 ? 2 : 1))
 k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
                float* __restrict__ P, int M, int N, int K, int C, int total, int U,
-               int prefetch_bytes, int dbg, NormPrologue pro, unsigned long long* tl) {
+               int prefetch_bytes, int dbg, NormPrologue pro, unsigned long long* tl, int prime_delay_ns) {
   extern __shared__ __align__(1024) unsigned char smem[];
   float* red = reinterpret_cast<float*>(smem + RING_BYTES);            // [WARPS][2][NT*128]
   int* tags = reinterpret_cast<int*>(red + WARPS * 2 * NT * 128);      // [WARPS][2] group or -1
@@ -175,8 +197,9 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
     g_gemm_trace[blockIdx.x * 8 + 0] = smid();
     g_gemm_trace[blockIdx.x * 8 + 1] = gtime();
   }
-  const int cs = blockIdx.x * U;
-  const int ce = min(total, cs + U);
+  // stream-K: units [c U, (c+1) U). ACT: groups [c G / grid, (c+1) G / grid) with G = total / C.
+  const int cs = ACT ? (int)(((long long)blockIdx.x * (total / C)) / gridDim.x) * C : blockIdx.x * U;
+  const int ce = ACT ? (int)(((long long)(blockIdx.x + 1) * (total / C)) / gridDim.x) * C : min(total, cs + U);
   const int len = ce > cs ? ce - cs : 0;
   // the warp's contiguous run [ws, we)
   const int ws = cs + (int)(((long long)warp * len) / WARPS);
@@ -187,20 +210,28 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
   const uint32_t ring = smem_u32(smem) + warp * (STAGES * STAGE_UNITS * 1024);
   const uint32_t bar0 = smem_u32(&bars[warp * STAGES]);
   const int n_stages = (n_units + STAGE_UNITS - 1) / STAGE_UNITS;
+  const uint64_t policy = stream_policy();
 
   if (lane == 0) {
     if (prefetch_bytes > 0 && n_units > 0)
       l2_prefetch(src, (uint32_t)min(n_units * 1024, prefetch_bytes));
+    if (prime_delay_ns > 0) {
+      // Let the kernel in front (whose few dependent loads are its critical path) get its
+      // requests into the memory system before this ring's worth of bulk copies.
+      const unsigned long long t0 = gtime();
+      for (int i = 0; i < 64 && gtime() - t0 < (unsigned long long)prime_delay_ns; ++i) __nanosleep(100);
+    }
     for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     // With the prologue only the first stage is requested here: the prologue's few KB of
     // dependent loads would otherwise queue behind the whole ring's worth of bulk copies
     // (measured: 3.5 us instead of ~1.5 us from the dependency wait to the first MMA).
-    for (int s = 0; s < (PRO ? 1 : STAGES) && s < n_stages; ++s) {
+    for (int s = 0; s < (PRO ? ((dbg & 8) ? 0 : 1) : STAGES) && s < n_stages; ++s) {
       const uint32_t bytes = (uint32_t)min(STAGE_UNITS, n_units - s * STAGE_UNITS) * 1024u;
       mbar_expect_tx(bar0 + 8 * s, bytes);
-      bulk_g2s(ring + s * (STAGE_UNITS * 1024), src + (size_t)s * STAGE_UNITS * 1024, bytes, bar0 + 8 * s);
+      bulk_g2s(ring + s * (STAGE_UNITS * 1024), src + (size_t)s * STAGE_UNITS * 1024, bytes, bar0 + 8 * s,
+               policy);
     }
   }
   if (lane < 2) tags[warp * 2 + lane] = -1;
@@ -229,11 +260,11 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
       }
       if (m == 0 && lane == 0) {
         // the rest of the ring, behind the prologue's loads in the memory system's queues
-        for (int s = 1; s < STAGES && s < n_stages; ++s) {
+        for (int s = (dbg & 8) ? 0 : 1; s < STAGES && s < n_stages; ++s) {
           const uint32_t bytes = (uint32_t)min(STAGE_UNITS, n_units - s * STAGE_UNITS) * 1024u;
           mbar_expect_tx(bar0 + 8 * s, bytes);
           bulk_g2s(ring + s * (STAGE_UNITS * 1024), src + (size_t)s * STAGE_UNITS * 1024, bytes,
-                   bar0 + 8 * s);
+                   bar0 + 8 * s, policy);
         }
       }
       float tot[VB][4];
@@ -258,6 +289,7 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
           }
         }
       }
+      if (trace && m == 0) g_gemm_trace[blockIdx.x * 8 + 7] = gtime();    // operands arrived
       ss = block_sum(ss, psum);
       const float inv = rsqrtf(ss / (float)K + pro.eps);
 #pragma unroll
@@ -366,6 +398,15 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             const int m0 = nt * 8 + 2 * t;
+            if (ACT) {
+              bf16* A = reinterpret_cast<bf16*>(P);
+              const int half = N >> 1, col = group * 8 + g;
+              if (col < half) {
+                if (m0 < M) A[(size_t)m0 * half + col] = swiglu_bf16(tot[nt][0], tot[nt][2]);
+                if (m0 + 1 < M) A[(size_t)(m0 + 1) * half + col] = swiglu_bf16(tot[nt][1], tot[nt][3]);
+              }
+              continue;
+            }
             if (m0 < M) {
               if (n0 < N) P[(size_t)m0 * N + n0] = tot[nt][0];
               if (n0 + 8 < N) P[(size_t)m0 * N + n0 + 8] = tot[nt][2];
@@ -396,7 +437,7 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
       const uint32_t bytes = (uint32_t)min(STAGE_UNITS, n_units - nxt * STAGE_UNITS) * 1024u;
       mbar_expect_tx(bar0 + 8 * sidx, bytes);
       bulk_g2s(ring + sidx * (STAGE_UNITS * 1024), src + (size_t)nxt * STAGE_UNITS * 1024, bytes,
-               bar0 + 8 * sidx);
+               bar0 + 8 * sidx, policy);
     }
   }
 
@@ -412,7 +453,7 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
     bool fresh = true;
     for (int s2 = 0; s2 < mine; ++s2) fresh = fresh && (tags[s2] != gg);
     if (!fresh) continue;
-    const unsigned first = ((unsigned)gg * (unsigned)C) / (unsigned)U;
+    const unsigned first = ACT ? blockIdx.x : ((unsigned)gg * (unsigned)C) / (unsigned)U;
     float* out = P + (long long)((int)blockIdx.x - (int)first) * slot_stride;
     const int n0 = gg * 16 + g;
 #pragma unroll
@@ -425,6 +466,15 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
         }
       }
       const int m0 = nt * 8 + 2 * t;
+      if (ACT) {
+        bf16* A = reinterpret_cast<bf16*>(P);
+        const int half = N >> 1, col = gg * 8 + g;
+        if (col < half) {
+          if (m0 < M) A[(size_t)m0 * half + col] = swiglu_bf16(sum.x, sum.z);
+          if (m0 + 1 < M) A[(size_t)(m0 + 1) * half + col] = swiglu_bf16(sum.y, sum.w);
+        }
+        continue;
+      }
       if (m0 < M) {
         if (n0 < N) out[(size_t)m0 * N + n0] = sum.x;
         if (n0 + 8 < N) out[(size_t)m0 * N + n0 + 8] = sum.z;
@@ -493,39 +543,46 @@ constexpr int gemm_smem() {
 
 int debug_flags_of_this_launch() {
   if (g_gemm_trace_launch < 0) return g_gemm_debug_flags;
-  return g_gemm_launches++ == g_gemm_trace_launch ? 4 : 0;
+  return (g_gemm_launches++ == g_gemm_trace_launch ? 4 : 0) | (g_gemm_debug_flags & ~4);
 }
 
-template <int NT>
+template <int NT, bool ACT>
 cudaError_t launch_gemm(const q_gemm_plan_t& p, const bf16* X, const unsigned char* W, float* P,
                         cudaStream_t s) {
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<NT, false>,
+    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<NT, false, ACT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_smem<NT>());
+    if (e != cudaSuccess) return e;
+    e = q_prefer_max_smem(k_gemm_streamk<NT, false, ACT>);
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
   NormPrologue none = {};
-  return q_launch(k_gemm_streamk<NT, false>, dim3(p.grid), dim3(p.block), (size_t)gemm_smem<NT>(), s, X,
+  const int grid = ACT ? (p.groups < p.grid ? p.groups : p.grid) : p.grid;
+  return q_launch(k_gemm_streamk<NT, false, ACT>, dim3(grid), dim3(p.block), (size_t)gemm_smem<NT>(), s, X,
                   W, P, p.M, p.N, p.K, p.chunks_per_group, p.groups * p.chunks_per_group,
                   p.units_per_worker, g_gemm_prefetch_kb * 1024 / WARPS, debug_flags_of_this_launch(), none,
-                  q_tl_next());
+                  q_tl_next(), g_gemm_next_prime_delay_ns);
 }
 
+template <bool ACT>
 cudaError_t launch_gemm_norm(const q_gemm_plan_t& p, const unsigned char* W, float* P,
                              const NormPrologue& pro, cudaStream_t s) {
   const size_t smem = (size_t)gemm_smem<1>() + (size_t)p.M * (p.K + 32) * 2 + 32 * 4;
   static size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<1, true>,
+    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<1, true, ACT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    e = q_prefer_max_smem(k_gemm_streamk<1, true, ACT>);
     if (e != cudaSuccess) return e;
     configured = smem;
   }
-  return q_launch(k_gemm_streamk<1, true>, dim3(p.grid), dim3(p.block), smem, s, (const bf16*)nullptr, W,
+  const int grid = ACT ? (p.groups < p.grid ? p.groups : p.grid) : p.grid;
+  return q_launch(k_gemm_streamk<1, true, ACT>, dim3(grid), dim3(p.block), smem, s, (const bf16*)nullptr, W,
                   P, p.M, p.N, p.K, p.chunks_per_group, p.groups * p.chunks_per_group,
-                  p.units_per_worker, 0, debug_flags_of_this_launch(), pro, q_tl_next());
+                  p.units_per_worker, 0, debug_flags_of_this_launch(), pro, q_tl_next(), 0);
 }
 
 }  // namespace
@@ -542,15 +599,21 @@ int q_gemm_status_read(int32_t out[4]) {
 }
 
 extern "C" int q_gemm_plan(int M, int N, int K, q_gemm_plan_t* plan) {
+  int sms = q_sm_count();
+  if (sms <= 0) return Q_ERR_CUDA;
+  return q_gemm_plan_workers(M, N, K, sms, plan);
+}
+
+int q_gemm_plan_workers(int M, int N, int K, int max_workers, q_gemm_plan_t* plan) {
   Q_CHECK_ARG(plan != nullptr, "q_gemm_plan: null plan");
+  Q_CHECK_ARG(max_workers >= 1, "q_gemm_plan: no workers");
   Q_CHECK_ARG(M >= 1 && M <= Q_MAX_ROWS, "q_gemm_plan: rows %d outside 1..%d", M, Q_MAX_ROWS);
   Q_CHECK_ARG(N >= 1 && K >= 32 && K % 32 == 0,
               "q_gemm_plan: need N >= 1 and K a positive multiple of 32 (N=%d K=%d)", N, K);
   const int C = K / 32;
   const int groups = (N + 15) / 16;
   Q_CHECK_ARG((long long)groups * C < (1ll << 30), "q_gemm_plan: weight too large");
-  int sms = q_sm_count();
-  if (sms <= 0) return Q_ERR_CUDA;
+  const int sms = max_workers;
   const long long total = (long long)groups * C;
   long long u = (total + sms - 1) / sms;
   if (u < 1) u = 1;
@@ -609,14 +672,21 @@ extern "C" int q_gemm_splitk(const void* d_x, const void* d_w_tiled, float* d_pa
   q_gemm_plan_t p;
   int rc = q_gemm_plan(M, N, K, &p);
   if (rc) return rc;
+  return q_gemm_launch_planned(d_x, d_w_tiled, d_partials, &p, stream);
+}
+
+int q_gemm_launch_planned(const void* d_x, const void* d_w_tiled, float* d_partials,
+                          const q_gemm_plan_t* plan, void* stream) {
+  const q_gemm_plan_t& p = *plan;
+  const int M = p.M;
   cudaStream_t s = (cudaStream_t)stream;
   const bf16* X = (const bf16*)d_x;
   const unsigned char* W = (const unsigned char*)d_w_tiled;
   cudaError_t e;
-  if (M <= 8) e = launch_gemm<1>(p, X, W, d_partials, s);
-  else if (M <= 16) e = launch_gemm<2>(p, X, W, d_partials, s);
-  else if (M <= 32) e = launch_gemm<4>(p, X, W, d_partials, s);
-  else e = launch_gemm<8>(p, X, W, d_partials, s);
+  if (M <= 8) e = launch_gemm<1, false>(p, X, W, d_partials, s);
+  else if (M <= 16) e = launch_gemm<2, false>(p, X, W, d_partials, s);
+  else if (M <= 32) e = launch_gemm<4, false>(p, X, W, d_partials, s);
+  else e = launch_gemm<8, false>(p, X, W, d_partials, s);
   Q_CHECK_CUDA(e);
   return Q_OK;
 }
@@ -696,7 +766,65 @@ extern "C" int q_gemm_splitk_addnorm(const void* d_resid_in, const float* d_prev
   pro.resid_out = (bf16*)d_resid_out;
   pro.gain = (const bf16*)d_gain;
   pro.eps = eps;
-  Q_CHECK_CUDA(launch_gemm_norm(p, (const unsigned char*)d_w_tiled, d_partials, pro, (cudaStream_t)stream));
+  Q_CHECK_CUDA(launch_gemm_norm<false>(p, (const unsigned char*)d_w_tiled, d_partials, pro, (cudaStream_t)stream));
+  return Q_OK;
+}
+
+static int swiglu_shape_ok(int M, int inter, int K, const char* who) {
+  Q_CHECK_ARG(M >= 1 && M <= Q_MAX_ROWS && inter >= 8 && inter % 8 == 0 && K >= 32 && K % 32 == 0,
+              "%s: need 1..%d rows, inter a multiple of 8 and K a multiple of 32 (M=%d inter=%d K=%d)", who,
+              Q_MAX_ROWS, M, inter, K);
+  return Q_OK;
+}
+
+extern "C" int q_gemm_swiglu(const void* d_x, const void* d_w_tiled, void* d_act, int M, int inter, int K,
+                             void* stream) {
+  Q_CHECK_ARG(d_x && d_w_tiled && d_act, "q_gemm_swiglu: null pointer");
+  Q_CHECK_ARG(((uintptr_t)d_x & 15) == 0 && ((uintptr_t)d_w_tiled & 15) == 0,
+              "q_gemm_swiglu: x and w must be 16-byte aligned");
+  int rc = swiglu_shape_ok(M, inter, K, "q_gemm_swiglu");
+  if (rc) return rc;
+  q_gemm_plan_t p;
+  rc = q_gemm_plan(M, 2 * inter, K, &p);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  const bf16* X = (const bf16*)d_x;
+  const unsigned char* W = (const unsigned char*)d_w_tiled;
+  float* out = reinterpret_cast<float*>(d_act);
+  cudaError_t e;
+  if (M <= 8) e = launch_gemm<1, true>(p, X, W, out, s);
+  else if (M <= 16) e = launch_gemm<2, true>(p, X, W, out, s);
+  else if (M <= 32) e = launch_gemm<4, true>(p, X, W, out, s);
+  else e = launch_gemm<8, true>(p, X, W, out, s);
+  Q_CHECK_CUDA(e);
+  return Q_OK;
+}
+
+extern "C" int q_gemm_swiglu_addnorm(const void* d_resid_in, const float* d_prev, const q_gemm_plan_t* prev_plan,
+                                     const void* d_gain, void* d_resid_out, const void* d_w_tiled,
+                                     void* d_act, int M, int inter, int K, float eps, void* stream) {
+  Q_CHECK_ARG(d_resid_in && d_prev && d_gain && d_resid_out && d_w_tiled && d_act,
+              "q_gemm_swiglu_addnorm: null pointer");
+  Q_CHECK_ARG(d_resid_in != d_resid_out, "q_gemm_swiglu_addnorm: the residual cannot be updated in place");
+  Q_CHECK_ARG(M >= 1 && M <= 8 && K % 4 == 0 && K <= 3072,
+              "q_gemm_swiglu_addnorm: needs 1..8 rows and K a multiple of 4 up to 3072 (M=%d K=%d)", M, K);
+  int rc = swiglu_shape_ok(M, inter, K, "q_gemm_swiglu_addnorm");
+  if (rc) return rc;
+  if (prev_plan)
+    Q_CHECK_ARG(prev_plan->M == M && prev_plan->N == K, "q_gemm_swiglu_addnorm: previous plan is [%d,%d]",
+                prev_plan->M, prev_plan->N);
+  q_gemm_plan_t p;
+  rc = q_gemm_plan(M, 2 * inter, K, &p);
+  if (rc) return rc;
+  NormPrologue pro;
+  pro.prev = d_prev;
+  pro.prev_plan = plan_view(prev_plan);
+  pro.resid_in = (const bf16*)d_resid_in;
+  pro.resid_out = (bf16*)d_resid_out;
+  pro.gain = (const bf16*)d_gain;
+  pro.eps = eps;
+  Q_CHECK_CUDA(launch_gemm_norm<true>(p, (const unsigned char*)d_w_tiled, reinterpret_cast<float*>(d_act), pro,
+                                      (cudaStream_t)stream));
   return Q_OK;
 }
 

@@ -887,23 +887,26 @@ __device__ __noinline__ void swiglu_phase(const mega_params_t& p, const float* P
     for (long long qd = (long long)blockIdx.x * THREADS + threadIdx.x; qd < quads;
          qd += (long long)gridDim.x * THREADS) {
       const int m = (int)(qd / (I >> 2)), col = (int)(qd % (I >> 2)) * 4;
+      // the layer's gate|up rows are interleaved in blocks of 8 (see q_gemm_swiglu): act
+      // columns col..col+3 have their gate sums at 16*(col/8) + col%8 and their up sums 8 further
       const long long base = (long long)m * 2 * I;
-      const float4 g0 = __ldcg(reinterpret_cast<const float4*>(PG + base + col));
-      const float4 g1 = __ldcg(reinterpret_cast<const float4*>(PG + base + col + stride));
-      const float4 u0 = __ldcg(reinterpret_cast<const float4*>(PG + base + I + col));
-      const float4 u1 = __ldcg(reinterpret_cast<const float4*>(PG + base + I + col + stride));
-      const unsigned gg = (unsigned)col >> 4, gu2 = (unsigned)(I + col) >> 4;
+      const int gcol = 16 * (col >> 3) + (col & 7), ucol = gcol + 8;
+      const float4 g0 = __ldcg(reinterpret_cast<const float4*>(PG + base + gcol));
+      const float4 g1 = __ldcg(reinterpret_cast<const float4*>(PG + base + gcol + stride));
+      const float4 u0 = __ldcg(reinterpret_cast<const float4*>(PG + base + ucol));
+      const float4 u1 = __ldcg(reinterpret_cast<const float4*>(PG + base + ucol + stride));
+      const unsigned gg = (unsigned)gcol >> 4;
       const unsigned eg = ((gg + 1) * C - 1) / u - (gg * C) / u;
-      const unsigned eu = ((gu2 + 1) * C - 1) / u - (gu2 * C) / u;
+      const unsigned eu = eg;
       float gs[4] = {g0.x, g0.y, g0.z, g0.w}, us[4] = {u0.x, u0.y, u0.z, u0.w};
       if (eg > 0) { gs[0] += g1.x; gs[1] += g1.y; gs[2] += g1.z; gs[3] += g1.w; }
       if (eu > 0) { us[0] += u1.x; us[1] += u1.y; us[2] += u1.z; us[3] += u1.w; }
       for (unsigned k = 2; k <= eg; ++k) {
-        const float4 t = __ldcg(reinterpret_cast<const float4*>(PG + base + col + (long long)k * stride));
+        const float4 t = __ldcg(reinterpret_cast<const float4*>(PG + base + gcol + (long long)k * stride));
         gs[0] += t.x; gs[1] += t.y; gs[2] += t.z; gs[3] += t.w;
       }
       for (unsigned k = 2; k <= eu; ++k) {
-        const float4 t = __ldcg(reinterpret_cast<const float4*>(PG + base + I + col + (long long)k * stride));
+        const float4 t = __ldcg(reinterpret_cast<const float4*>(PG + base + ucol + (long long)k * stride));
         us[0] += t.x; us[1] += t.y; us[2] += t.z; us[3] += t.w;
       }
       float o[4];
@@ -923,8 +926,9 @@ __device__ __noinline__ void swiglu_phase(const mega_params_t& p, const float* P
   for (long long i = (long long)blockIdx.x * THREADS + threadIdx.x; i < total; i += (long long)gridDim.x * THREADS) {
     const int m = (int)(i / I), col = (int)(i % I);
     const long long base = (long long)m * 2 * I;
-    const float gt = bf16_round(psum_cg(PG, p.gu, stride, base + col, col));
-    const float up = bf16_round(psum_cg(PG, p.gu, stride, base + I + col, I + col));
+    const int gcol = 16 * (col >> 3) + (col & 7), ucol = gcol + 8;
+    const float gt = bf16_round(psum_cg(PG, p.gu, stride, base + gcol, gcol));
+    const float up = bf16_round(psum_cg(PG, p.gu, stride, base + ucol, ucol));
     const float a = bf16_round(gt / (1.0f + expf(-gt)));
     p.act[i] = __float2bfloat16_rn(a * up);
   }

@@ -161,12 +161,57 @@ def silu_mul(gate_up, rows: int | None = None) -> torch.Tensor:
     return out
 
 
+def _gate_up_operand(gate_up_weight):
+    """The packed [2I, K] gate|up weight in q_gemm_swiglu's interleaved tiled layout, or None
+    when its shape rules it out (I not a multiple of 8)."""
+    if isinstance(gate_up_weight, TiledWeight):
+        return gate_up_weight if gate_up_weight.interleaved8 else None
+    _bf16_2d(gate_up_weight, "weight")
+    if gate_up_weight.shape[0] % 16 or gate_up_weight.shape[1] % 32:
+        return None
+    return TiledWeight.pack(gate_up_weight, interleave8=True)
+
+
 def linear_silu_mul(x: torch.Tensor, gate_up_weight) -> torch.Tensor:
     """BF16 [M, I] = silu(x @ gate.T) * (x @ up.T) for a packed [2I, K] weight
-    (engine/kernels/skinny_gemm.py:112-121)."""
+    (engine/kernels/skinny_gemm.py:112-121). One launch (SwiGLU in the projection's
+    epilogue) when I is a multiple of 8; `gate_up_weight` is the row-major [gate; up] matrix
+    (tiled on the fly: load-time work, for tests) or a TiledWeight packed with
+    interleave8=True. Other shapes take the partials + silu_mul route."""
     if len(gate_up_weight.shape) != 2 or gate_up_weight.shape[0] % 2:
         raise ValueError("packed gate/up weight must have an even number of rows")
-    return silu_mul(linear_partials(x, gate_up_weight))
+    M, K = _bf16_2d(x, "x")
+    w = _gate_up_operand(gate_up_weight)
+    if w is None:
+        return silu_mul(linear_partials(x, gate_up_weight))
+    if w.shape[1] != K or w.data.device != x.device:
+        raise ValueError("x and weight disagree on K or device")
+    if not 1 <= M <= MAX_ROWS:
+        raise ValueError(f"at most {MAX_ROWS} rows are supported, got {M}")
+    inter = w.shape[0] // 2
+    out = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
+    check(lib.q_gemm_swiglu(_ptr(x), _ptr(w), _ptr(out), M, inter, K, _stream()))
+    return out
+
+
+def add_rms_norm_linear_silu_mul(residual: torch.Tensor, branch, gain: torch.Tensor, eps: float,
+                                 gate_up_weight):
+    """(residual + branch, silu(n @ gate.T) * (n @ up.T)) with n = RMSNorm(residual + branch):
+    the post-attention half of a layer up to the SwiGLU (engine/decode_step.py:50-56) in one
+    launch. Up to 8 rows, K <= 3072, I a multiple of 8."""
+    rows, cols = _bf16_2d(residual, "residual")
+    if gain.shape != (cols,) or gain.dtype != torch.bfloat16 or gain.device != residual.device:
+        raise ValueError("residual and gain shapes disagree")
+    w = _gate_up_operand(gate_up_weight)
+    if w is None or w.shape[1] != cols or w.data.device != residual.device:
+        raise ValueError("gate|up weight must be [2I, K] with I a multiple of 8 on the same device")
+    bp, pp = _branch(branch, rows, cols, residual.device)
+    inter = w.shape[0] // 2
+    total = torch.empty_like(residual)
+    out = torch.empty((rows, inter), dtype=torch.bfloat16, device=residual.device)
+    check(lib.q_gemm_swiglu_addnorm(_ptr(residual), bp, pp, _ptr(gain), _ptr(total), _ptr(w), _ptr(out),
+                                    rows, inter, cols, float(eps), _stream()))
+    return total, out
 
 
 class PagedKV:

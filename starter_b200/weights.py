@@ -23,14 +23,33 @@ import torch
 HEAD_DIM = 128
 
 
+def interleave_gate_up(packed: torch.Tensor) -> torch.Tensor:
+    """[gate; up] ([2I, K], engine/mlp.py:12-15) -> rows 16i..16i+7 = gate rows 8i..8i+7,
+    rows 16i+8..16i+15 = up rows 8i..8i+7: the row order q_gemm_swiglu wants."""
+    two_i, K = packed.shape
+    if two_i % 16:
+        raise ValueError("the packed gate|up matrix needs a multiple of 16 rows")
+    inter = two_i // 2
+    gate, up = packed[:inter].view(inter // 8, 8, K), packed[inter:].view(inter // 8, 8, K)
+    return torch.stack((gate, up), 1).reshape(two_i, K).contiguous()
+
+
+def deinterleave_gate_up(mixed: torch.Tensor) -> torch.Tensor:
+    """Inverse of interleave_gate_up."""
+    two_i, K = mixed.shape
+    blocks = mixed.view(two_i // 16, 2, 8, K)
+    return torch.cat((blocks[:, 0].reshape(two_i // 2, K), blocks[:, 1].reshape(two_i // 2, K)), 0).contiguous()
+
+
 class TiledWeight:
     """A bf16 [N, K] Linear weight held in the GEMM's tiled unit layout (see
     q_pack_weight in include/qdecode.h). `data` is a flat uint8 device tensor;
     `rows()` gives the row-major matrix back (used by prefill, which runs on
-    library GEMMs outside the per-step path)."""
+    library GEMMs outside the per-step path). `interleaved8`: the rows were put in
+    q_gemm_swiglu's gate/up order before tiling (rows() undoes it)."""
 
-    def __init__(self, data: torch.Tensor, N: int, K: int):
-        self.data, self.N, self.K = data, N, K
+    def __init__(self, data: torch.Tensor, N: int, K: int, interleaved8: bool = False):
+        self.data, self.N, self.K, self.interleaved8 = data, N, K, interleaved8
 
     @property
     def shape(self):
@@ -43,17 +62,19 @@ class TiledWeight:
         return self.data.data_ptr()
 
     @staticmethod
-    def pack(weight: torch.Tensor) -> "TiledWeight":
+    def pack(weight: torch.Tensor, interleave8: bool = False) -> "TiledWeight":
         from ._lib import check, lib
         if (weight.ndim != 2 or weight.dtype != torch.bfloat16 or not weight.is_cuda
                 or not weight.is_contiguous() or weight.shape[1] % 32):
             raise ValueError("expected a contiguous BF16 CUDA [N, K] weight with K a multiple of 32")
+        if interleave8:
+            weight = interleave_gate_up(weight)
         N, K = weight.shape
         out = torch.empty(lib.q_packed_weight_bytes(N, K), dtype=torch.uint8, device=weight.device)
         with torch.cuda.device(weight.device):
             check(lib.q_pack_weight(C.c_void_p(weight.data_ptr()), C.c_void_p(out.data_ptr()), N, K,
                                     C.c_void_p(torch.cuda.current_stream().cuda_stream)))
-        return TiledWeight(out, N, K)
+        return TiledWeight(out, N, K, interleave8)
 
     def rows(self, out: torch.Tensor | None = None) -> torch.Tensor:
         from ._lib import check, lib
@@ -63,12 +84,14 @@ class TiledWeight:
             check(lib.q_unpack_weight(C.c_void_p(self.data.data_ptr()), C.c_void_p(out.data_ptr()),
                                       self.N, self.K,
                                       C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        if self.interleaved8:
+            out.copy_(deinterleave_gate_up(out))
         return out
 
     def row_slice(self, lo: int, hi: int) -> "TiledWeight":
         """Rows [lo, hi) as a view (no copy); lo must be a multiple of 16."""
-        if lo % 16 or not 0 <= lo < hi <= self.N:
-            raise ValueError("a tiled row slice must start on a 16-row boundary")
+        if lo % 16 or not 0 <= lo < hi <= self.N or self.interleaved8:
+            raise ValueError("a tiled row slice must start on a 16-row boundary (and not be gate/up interleaved)")
         unit_bytes = (self.K // 32) * 1024
         groups = (hi - lo + 15) // 16
         return TiledWeight(self.data[(lo // 16) * unit_bytes:(lo // 16 + groups) * unit_bytes], hi - lo, self.K)
@@ -174,7 +197,7 @@ class PackedWeights:
             for name in ("wqkv", "wo", "wgu", "wdown"):
                 t = getattr(lt, name)
                 if isinstance(t, torch.Tensor):
-                    setattr(lt, name, TiledWeight.pack(t))
+                    setattr(lt, name, TiledWeight.pack(t, interleave8=(name == "wgu")))
         return self
 
     @property
@@ -239,7 +262,7 @@ def pack(cfg: ModelConfig, get, has, device, tp_rank: int = 0, tp_size: int = 1)
         if out.device.type == "cuda":
             lt = out.layers[-1]          # tile as we go so that only one layer is held twice
             for name in ("wqkv", "wo", "wgu", "wdown"):
-                setattr(lt, name, TiledWeight.pack(getattr(lt, name)))
+                setattr(lt, name, TiledWeight.pack(getattr(lt, name), interleave8=(name == "wgu")))
     if out.device.type == "cuda":
         out.tile()
     return out
