@@ -263,7 +263,7 @@ def time_gemm_kernel(state, reps: int = 5):
         for lt in w.layers:
             for x, wt in ((state.normed, lt.wqkv), (state.attended, lt.wo), (state.normed, lt.wgu),
                           (state.act, lt.wdown)):
-                if wt is lt.wgu:      # the step runs this one with the SwiGLU epilogue
+                if wt is lt.wgu and rows <= 8:      # the step runs this one with the SwiGLU epilogue
                     check(lib.q_gemm_swiglu(C.c_void_p(x.data_ptr()), C.c_void_p(wt.data_ptr()),
                                             C.c_void_p(state.act.data_ptr()), rows, wt.shape[0] // 2,
                                             wt.shape[1], s))
@@ -310,8 +310,9 @@ def kernels_per_step(state) -> int:
         # embed, first QKV | attention, O, gate|up (add+norm prologue, SwiGLU epilogue), down,
         # next QKV or lm_head (add+norm prologue) | argmax
         return 2 + 5 * layers + 1
-    # embed | QKV, attention, O, add+norm, gate|up with SwiGLU, down, add+norm | lm_head, argmax
-    n = 1 + 7 * layers + 2
+    # embed | QKV, attention, O, add+norm, gate|up (+ SwiGLU launch above 8 rows), down, add+norm |
+    # lm_head, argmax
+    n = 1 + (7 if state.batch <= 8 else 8) * layers + 2
     if state.tp > 1:
         n += layers * 2 + 1                   # partial reductions before each all-reduce, argmax merge
     return n

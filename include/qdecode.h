@@ -52,8 +52,11 @@ int q_set_pdl(int enabled);
  *       dependent-launch multi-kernel step measured faster, 2.2 vs 2.8 ms at batch 1).
  *   "norm_in_gemm": 1 (default) = with up to 8 rows on one GPU, q_decode_step runs residual add +
  *       RMSNorm as the prologue of the projection that consumes them (q_gemm_splitk_addnorm).
+ *   "attn_no_cluster": 1 = q_attention_decode merges 2..8 key splits through global memory and a
+ *       ticket like it does above 8 splits, instead of inside a thread-block cluster (default 0).
  *   "trace_layer": layer stamped by the whole-step kernel (see q_debug_step_trace), -1 off.
- *   "gemm_debug_flags": measurement aid, 4 = per-CTA time stamps for q_debug_gemm_trace.
+ *   "gemm_debug_flags": measurement aid, 4 = per-CTA time stamps for q_debug_gemm_trace, 8 = a
+ *       projection with the add+norm prologue requests none of its weights before its dependency wait.
  *   "gemm_trace_launch": measurement aid, n >= 0 = only the n-th GEMM launch from now records
  *       its CTA trace (so one projection inside a captured step can be looked at), -1 off.
  *   "timeline": measurement aid, 1 = per-launch time stamps for q_debug_timeline.

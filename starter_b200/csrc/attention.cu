@@ -18,7 +18,6 @@
 // hang the GPU.
 #include "common.cuh"
 
-extern int g_attn_ring_fixed;   // q_set_option "attn_ring_fixed"
 extern int g_attn_no_cluster;   // q_set_option "attn_no_cluster": merge splits through global memory
 
 namespace {
@@ -461,7 +460,11 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
   }
   __syncthreads();
 
-  // position and block table were written by earlier steps: safe before the wait
+  // position and block table were written by earlier steps: safe before the wait. The
+  // producer warp fetches this sequence's block-table row together with the position (one
+  // memory round trip instead of two before the first KV copy can be issued).
+  int my_page = 0;
+  if (warp == CONSUMERS && lane < pages_per_seq) my_page = block_table[(size_t)b * pages_per_seq + lane];
   const int pos = pos_ptr[0];
   const int max_limit = pos + 1;
   const int tiles_used = (max_limit + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
@@ -472,14 +475,18 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
   const int new_tile = pos / Q_PAGE_TOKENS, new_row = pos % Q_PAGE_TOKENS;
   const bool owns_new = ntiles > 0 && new_tile >= tile0 && new_tile < tile1;
 
-  if (warp == CONSUMERS && lane == 0) {
+  if (warp == CONSUMERS) {
     for (int it = 0; it < ntiles && it < NS; ++it) {
-      const int page = block_table[(size_t)b * pages_per_seq + tile0 + it];
-      const size_t off = ((size_t)page * nkv + kh) * TILE_BYTES;
-      const uint32_t bar = smem_u32(&bars[it]);
-      mbar_expect_tx(bar, STAGE_BYTES);
-      bulk_g2s(smem_u32(stages + it * STAGE_BYTES), kpool + off, TILE_BYTES, bar);
-      bulk_g2s(smem_u32(stages + it * STAGE_BYTES + TILE_BYTES), vpool + off, TILE_BYTES, bar);
+      const int tile = tile0 + it;
+      int page = __shfl_sync(0xffffffffu, my_page, tile & 31);
+      if (tile >= 32) page = block_table[(size_t)b * pages_per_seq + tile];
+      if (lane == 0) {
+        const size_t off = ((size_t)page * nkv + kh) * TILE_BYTES;
+        const uint32_t bar = smem_u32(&bars[it]);
+        mbar_expect_tx(bar, STAGE_BYTES);
+        bulk_g2s(smem_u32(stages + it * STAGE_BYTES), kpool + off, TILE_BYTES, bar);
+        bulk_g2s(smem_u32(stages + it * STAGE_BYTES + TILE_BYTES), vpool + off, TILE_BYTES, bar);
+      }
     }
   }
 
@@ -938,14 +945,11 @@ extern "C" int q_attention_decode(const float* d_qkv_partials, const q_gemm_plan
                                       (int)attn_decode_smem(NS)));
     Q_CHECK_CUDA(cudaFuncSetAttribute(k_attn_decode<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)attn_decode_smem(NS)));
-    Q_CHECK_CUDA(q_prefer_max_smem(k_attn_decode<false>));
-    Q_CHECK_CUDA(q_prefer_max_smem(k_attn_decode<true>));
     attr = true;
   }
   // most tiles one split can be handed: ceil(tiles / splits) over the page capacity
   int ring = (kv->pages_per_seq + splits - 1) / splits;
   ring = ring < 1 ? 1 : (ring > NS ? NS : ring);
-  if (g_attn_ring_fixed) ring = NS;
   // the merge scratch (consumer states, then the CTA's own rows) reuses the ring
   const int scratch_stages = (G * 5 * 130 * 4 + STAGE_BYTES - 1) / STAGE_BYTES;
   if (ring < scratch_stages) ring = scratch_stages;

@@ -43,16 +43,7 @@ int g_gemm_prefetch_kb = 0;
 int g_gemm_debug_flags = 0;
 int g_gemm_trace_launch = -1;    // measurement aid: the one GEMM launch that records its CTA trace
 int g_gemm_launches = 0;
-int g_gemm_next_prime_delay_ns = 0;     // set around one launch by the engine (O projection)
-static int g_o_prime_delay_ns = 0;      // option "o_prime_delay_ns"
-static int g_o_idle_sms = 0;            // option "o_idle_sms": SMs the O projection leaves to the attention CTAs
-// An SM's L1/shared split follows the kernels it runs and only changes while the SM is idle,
-// so a CTA of the NEXT kernel that would fit beside a running one by the byte count still
-// waits when the running kernel asked for a smaller carve-out. 1 = the GEMM and decode-attention
-// kernels all ask for the largest carve-out (read when a kernel is first launched).
-int g_smem_carveout_max = 0;
 int g_attn_no_cluster = 0;        // 1 = decode attention merges its splits through global memory
-int g_attn_ring_fixed = 0;        // 1 = decode attention always asks for its full 3-stage ring
 static int g_fused_step = 0;     // 1 = use the persistent whole-step kernel when it applies
 static int g_norm_in_gemm = 1;   // 1 = residual add + RMSNorm as the prologue of the next projection
 static int g_trace_layer = -1;   // measurement aid: layer whose phases the whole-step kernel stamps
@@ -116,26 +107,8 @@ extern "C" int q_set_option(const char* name, int value) {
     g_norm_in_gemm = value != 0;
     return Q_OK;
   }
-  if (strcmp(name, "smem_carveout_max") == 0) {
-    g_smem_carveout_max = value != 0;
-    return Q_OK;
-  }
-  if (strcmp(name, "o_idle_sms") == 0) {
-    Q_CHECK_ARG(value >= 0 && value <= 96, "q_set_option: o_idle_sms outside 0..96");
-    g_o_idle_sms = value;            // read when a state is bound
-    return Q_OK;
-  }
-  if (strcmp(name, "o_prime_delay_ns") == 0) {
-    Q_CHECK_ARG(value >= 0 && value <= 6000, "q_set_option: o_prime_delay_ns outside 0..6000");
-    g_o_prime_delay_ns = value;
-    return Q_OK;
-  }
   if (strcmp(name, "attn_no_cluster") == 0) {
     g_attn_no_cluster = value != 0;
-    return Q_OK;
-  }
-  if (strcmp(name, "attn_ring_fixed") == 0) {
-    g_attn_ring_fixed = value != 0;
     return Q_OK;
   }
   if (strcmp(name, "gemm_trace_launch") == 0) {
@@ -200,12 +173,7 @@ static int make_plans(q_engine* e, int rows) {
   const q_config_t& c = e->cfg;
   int rc;
   if ((rc = q_gemm_plan(rows, (c.n_q_heads + 2 * c.n_kv_heads) * 128, c.hidden, &e->p_qkv))) return rc;
-  // O projection: optionally on fewer CTAs than SMs (see attn_after_qkv)
-  int o_workers = q_sm_count();
-  if (o_workers <= 0) return Q_ERR_CUDA;
-  if (g_o_idle_sms > 0 && c.tp_size == 1 && rows <= 8 && o_workers - g_o_idle_sms >= 64)
-    o_workers -= g_o_idle_sms;
-  if ((rc = q_gemm_plan_workers(rows, c.hidden, c.n_q_heads * 128, o_workers, &e->p_o))) return rc;
+  if ((rc = q_gemm_plan(rows, c.hidden, c.n_q_heads * 128, &e->p_o))) return rc;
   if ((rc = q_gemm_plan(rows, 2 * c.inter, c.hidden, &e->p_gu))) return rc;
   if ((rc = q_gemm_plan(rows, c.hidden, c.inter, &e->p_down))) return rc;
   if ((rc = q_gemm_plan(rows, c.vocab, c.hidden, &e->p_head))) return rc;
@@ -435,13 +403,7 @@ static int attn_after_qkv(q_engine* e, int layer, float* o_partials, void* strea
     TRY(q_attention(s.q, &kv, s.pos, s.attn_o, s.attn_ml, s.attended, s.batch, 1, c.n_q_heads,
                     s.attn_splits, c.attn_scale, stream));
   }
-  // The O projection's CTAs become resident while the attention kernel is still loading the
-  // QKV partials; its weights have the whole attention to arrive, so it holds back its
-  // first copies for a moment instead of queueing 19 MB in front of those loads.
-  g_gemm_next_prime_delay_ns = g_o_prime_delay_ns;
-  const int rc = q_gemm_launch_planned(s.attended, w.wo, o_partials, &e->p_o, stream);
-  g_gemm_next_prime_delay_ns = 0;
-  return rc;
+  return q_gemm_launch_planned(s.attended, w.wo, o_partials, &e->p_o, stream);
 }
 
 // QKV projection .. attention .. O projection (partials left in st.partials).
@@ -452,12 +414,20 @@ static int attn_block(q_engine* e, int layer, void* stream) {
   return attn_after_qkv(e, layer, s.partials, stream);
 }
 
-// gate|up projection with the SwiGLU epilogue (one launch, the layer's gate|up weight is in
-// q_gemm_swiglu's interleaved row order), then the down projection.
+// gate|up projection + SwiGLU (the layer's gate|up weight is in q_gemm_swiglu's interleaved row
+// order), then the down projection.
 static int mlp_block(q_engine* e, int layer, void* stream) {
   const q_config_t& c = e->cfg;
   const q_state_t& s = e->st;
-  TRY(q_gemm_swiglu(s.normed, e->layers[layer].wgu, s.act, e->rows, c.inter, c.hidden, stream));
+  if (e->rows <= 8) {
+    TRY(q_gemm_swiglu(s.normed, e->layers[layer].wgu, s.act, e->rows, c.inter, c.hidden, stream));
+  } else {
+    // Above 8 rows the projection is bound by instruction issue, not by memory, and whole
+    // groups per CTA (8 or 9 of them) cost more than the SwiGLU launch saves: stream-K
+    // partials, then SwiGLU on the interleaved columns.
+    TRY(q_gemm_splitk(s.normed, e->layers[layer].wgu, s.partials, e->rows, 2 * c.inter, c.hidden, stream));
+    TRY(q_swiglu_layout(s.partials, &e->p_gu, s.act, e->rows, c.inter, 1, stream));
+  }
   TRY(q_gemm_splitk(s.act, e->layers[layer].wdown, s.partials, e->rows, c.hidden, c.inter, stream));
   return Q_OK;
 }

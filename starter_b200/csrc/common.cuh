@@ -69,23 +69,15 @@ static inline cudaError_t q_launch_cluster(void (*kernel)(KArgs...), dim3 grid, 
 int q_sm_count();
 
 // Split-K plan over at most `max_workers` CTAs (q_gemm_plan uses the SM count), and the
-// launch of a projection on a given plan. The engine runs the O projection on fewer CTAs
-// than SMs so that all of them fit beside the attention kernel's CTAs.
+// launch of a projection on a plan the caller already holds.
 int q_gemm_plan_workers(int M, int N, int K, int max_workers, q_gemm_plan_t* plan);
 int q_gemm_launch_planned(const void* d_x, const void* d_w_tiled, float* d_partials,
                           const q_gemm_plan_t* plan, void* stream);
 
-// An SM's L1/shared split follows the kernels it runs and is only changed while the SM is
-// idle. All kernels of the step ask for the same (largest) carve-out, so that a CTA of the
-// next kernel can move in beside a running one whenever the byte and register counts allow,
-// and no SM drains just to change its split. Returns 0 or the CUDA error.
-extern int g_smem_carveout_max;
-template <typename K>
-static inline cudaError_t q_prefer_max_smem(K kernel) {
-  if (!g_smem_carveout_max) return cudaSuccess;
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                              cudaSharedmemCarveoutMaxShared);
-}
+// q_swiglu on partials whose columns are in q_gemm_swiglu's interleaved gate/up order
+// (interleaved = 1) or in [gate | up] order (0).
+int q_swiglu_layout(const float* d_branch, const q_gemm_plan_t* plan, void* d_out, int rows, int inter,
+                    int interleaved, void* stream);
 
 // Measurement aid: a per-launch record {first CTA start, first CTA past the dependency
 // wait, last warp end, last CTA start} in %globaltimer ns. Launchers pass q_tl_next() as

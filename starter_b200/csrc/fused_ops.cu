@@ -156,7 +156,7 @@ k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanVie
 // ---- SwiGLU on gate|up partials ---------------------------------------------
 __global__ void __launch_bounds__(256)
 k_swiglu(const float* __restrict__ P, PlanView pv, bf16* __restrict__ O, int rows, int inter,
-         unsigned long long* tl) {
+         int interleaved, unsigned long long* tl) {
   tl_begin(tl);
   pdl_launch_dependents();
   pdl_wait();
@@ -167,21 +167,25 @@ k_swiglu(const float* __restrict__ P, PlanView pv, bf16* __restrict__ O, int row
   const int m = (int)(q / (inter >> 2)), c = (int)(q % (inter >> 2)) * 4;
   const float* base = P + (long long)m * 2 * inter;
   const bool two = pv.u != 0;
-  const float4 g0 = *reinterpret_cast<const float4*>(base + c);
-  const float4 u0 = *reinterpret_cast<const float4*>(base + inter + c);
+  // columns of the gate and up sums of act columns c..c+3: [gate | up], or the layout of
+  // q_gemm_swiglu's weight (blocks of 8 gate rows followed by their 8 up rows)
+  const int gc = interleaved ? 16 * (c >> 3) + (c & 7) : c;
+  const int uc = interleaved ? gc + 8 : inter + c;
+  const float4 g0 = *reinterpret_cast<const float4*>(base + gc);
+  const float4 u0 = *reinterpret_cast<const float4*>(base + uc);
   const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-  const float4 g1 = two ? *reinterpret_cast<const float4*>(base + c + pv.slot_stride) : z;
-  const float4 u1 = two ? *reinterpret_cast<const float4*>(base + inter + c + pv.slot_stride) : z;
-  const int eg = plan_count(pv, c) - 1, eu = plan_count(pv, inter + c) - 1;
+  const float4 g1 = two ? *reinterpret_cast<const float4*>(base + gc + pv.slot_stride) : z;
+  const float4 u1 = two ? *reinterpret_cast<const float4*>(base + uc + pv.slot_stride) : z;
+  const int eg = plan_count(pv, gc) - 1, eu = plan_count(pv, uc) - 1;
   float gs[4] = {g0.x, g0.y, g0.z, g0.w}, us[4] = {u0.x, u0.y, u0.z, u0.w};
   if (eg > 0) { gs[0] += g1.x; gs[1] += g1.y; gs[2] += g1.z; gs[3] += g1.w; }
   if (eu > 0) { us[0] += u1.x; us[1] += u1.y; us[2] += u1.z; us[3] += u1.w; }
   for (int k = 2; k <= eg; ++k) {
-    const float4 t = *reinterpret_cast<const float4*>(base + c + (long long)k * pv.slot_stride);
+    const float4 t = *reinterpret_cast<const float4*>(base + gc + (long long)k * pv.slot_stride);
     gs[0] += t.x; gs[1] += t.y; gs[2] += t.z; gs[3] += t.w;
   }
   for (int k = 2; k <= eu; ++k) {
-    const float4 t = *reinterpret_cast<const float4*>(base + inter + c + (long long)k * pv.slot_stride);
+    const float4 t = *reinterpret_cast<const float4*>(base + uc + (long long)k * pv.slot_stride);
     us[0] += t.x; us[1] += t.y; us[2] += t.z; us[3] += t.w;
   }
   float o[4];
@@ -450,8 +454,6 @@ extern "C" int q_embed_rmsnorm(const int64_t* d_tokens, const void* d_embed, con
   Q_CHECK_ARG(d_tokens && d_embed && d_gain && d_x && d_normed && rows >= 1 && cols >= 32 &&
                   cols % 32 == 0 && vocab >= 1,
               "q_embed_rmsnorm: bad argument (cols must be a multiple of 32)");
-  static bool pref = false;
-  if (!pref) { Q_CHECK_CUDA(q_prefer_max_smem(k_embed_rmsnorm)); pref = true; }
   Q_CHECK_CUDA(q_launch(k_embed_rmsnorm, dim3(rows), dim3(256), 0, S(stream), d_tokens,
                         (const bf16*)d_embed, (const bf16*)d_gain, (bf16*)d_x, (bf16*)d_normed, cols,
                         vocab, eps, q_tl_next()));
@@ -482,18 +484,22 @@ extern "C" int q_add_rmsnorm(const void* d_x_in, const float* d_branch, const q_
   return Q_OK;
 }
 
-extern "C" int q_swiglu(const float* d_branch, const q_gemm_plan_t* plan, void* d_out, int rows,
-                        int inter, void* stream) {
+int q_swiglu_layout(const float* d_branch, const q_gemm_plan_t* plan, void* d_out, int rows, int inter,
+                    int interleaved, void* stream) {
   Q_CHECK_ARG(d_branch && d_out && rows >= 1 && inter >= 4 && inter % 4 == 0,
               "q_swiglu: bad argument (inter must be a multiple of 4)");
+  Q_CHECK_ARG(!interleaved || inter % 8 == 0, "q_swiglu: the interleaved layout needs inter %% 8 == 0");
   int rc = check_plan(plan, rows, 2 * inter, "q_swiglu");
   if (rc) return rc;
   long long total = (long long)rows * (inter / 4);
-  static bool pref = false;
-  if (!pref) { Q_CHECK_CUDA(q_prefer_max_smem(k_swiglu)); pref = true; }
   Q_CHECK_CUDA(q_launch(k_swiglu, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, S(stream),
-                        d_branch, plan_view(plan), (bf16*)d_out, rows, inter, q_tl_next()));
+                        d_branch, plan_view(plan), (bf16*)d_out, rows, inter, interleaved, q_tl_next()));
   return Q_OK;
+}
+
+extern "C" int q_swiglu(const float* d_branch, const q_gemm_plan_t* plan, void* d_out, int rows,
+                        int inter, void* stream) {
+  return q_swiglu_layout(d_branch, plan, d_out, rows, inter, 0, stream);
 }
 
 extern "C" int q_qkv_norm_rope_cache(const float* d_branch, const q_gemm_plan_t* plan,
@@ -558,8 +564,6 @@ extern "C" int q_logits_argmax(const float* d_branch, const q_gemm_plan_t* plan,
   unsigned int* tickets = (unsigned int*)base;
   float* bval = (float*)(base + tick);
   int* bidx = (int*)(base + tick + (int64_t)rows * nblk * 4);
-  static bool pref = false;
-  if (!pref) { Q_CHECK_CUDA(q_prefer_max_smem(k_logits_argmax)); pref = true; }
   Q_CHECK_CUDA(q_launch(k_logits_argmax, dim3(nblk, rows), dim3(256), 0, S(stream), d_branch,
                         plan_view(plan), (bf16*)d_logits, d_val, d_idx, d_tokens, d_pos, pos_inc,
                         tickets, bval, bidx, vocab, vocab_offset, q_tl_next()));

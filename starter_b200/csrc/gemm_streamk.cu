@@ -43,7 +43,6 @@ extern int g_gemm_prefetch_kb;   // set through q_set_option
 extern int g_gemm_debug_flags;   // set through q_set_option: 4 = record the per-CTA trace
 extern int g_gemm_trace_launch;  // >= 0: only that GEMM launch (counted from when it was set) records
 extern int g_gemm_launches;
-extern int g_gemm_next_prime_delay_ns;   // how long the plain kernel's CTAs hold back their first copies
 
 namespace {
 
@@ -175,13 +174,13 @@ struct NormPrologue {
 // epilogue writes silu(gate) * up as bf16 [M][N/2] into P instead of fp32 partials
 // (engine/kernels/skinny_gemm.py:49-72): one MMA tile holds a gate row in c0/c1 and its up
 // row in c2/c3 of the same thread, so no exchange is needed.
-template <int NT, bool PRO, bool ACT>
-__global__ void __launch_bounds__(THREADS, (RING_BYTES <= 100 * 1024 ? 2 : 1))
+template <int NT, bool PRO, bool ACT, int SU>
+__global__ void __launch_bounds__(THREADS, (WARPS * STAGES * SU * 1024 <= 100 * 1024 ? 2 : 1))
 k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
                float* __restrict__ P, int M, int N, int K, int C, int total, int U,
-               int prefetch_bytes, int dbg, NormPrologue pro, unsigned long long* tl, int prime_delay_ns) {
+               int prefetch_bytes, int dbg, NormPrologue pro, unsigned long long* tl) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  float* red = reinterpret_cast<float*>(smem + RING_BYTES);            // [WARPS][2][NT*128]
+  float* red = reinterpret_cast<float*>(smem + WARPS * STAGES * SU * 1024);            // [WARPS][2][NT*128]
   int* tags = reinterpret_cast<int*>(red + WARPS * 2 * NT * 128);      // [WARPS][2] group or -1
   uint64_t* bars = reinterpret_cast<uint64_t*>(tags + WARPS * 2);      // [WARPS][STAGES]
   bf16* xsm = reinterpret_cast<bf16*>(bars + WARPS * STAGES);          // PRO: [M][K] activations
@@ -207,20 +206,14 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
   const int n_units = we - ws;
   const unsigned char* src = Wt + (size_t)ws * 1024;
 
-  const uint32_t ring = smem_u32(smem) + warp * (STAGES * STAGE_UNITS * 1024);
+  const uint32_t ring = smem_u32(smem) + warp * (STAGES * SU * 1024);
   const uint32_t bar0 = smem_u32(&bars[warp * STAGES]);
-  const int n_stages = (n_units + STAGE_UNITS - 1) / STAGE_UNITS;
+  const int n_stages = (n_units + SU - 1) / SU;
   const uint64_t policy = stream_policy();
 
   if (lane == 0) {
     if (prefetch_bytes > 0 && n_units > 0)
       l2_prefetch(src, (uint32_t)min(n_units * 1024, prefetch_bytes));
-    if (prime_delay_ns > 0) {
-      // Let the kernel in front (whose few dependent loads are its critical path) get its
-      // requests into the memory system before this ring's worth of bulk copies.
-      const unsigned long long t0 = gtime();
-      for (int i = 0; i < 64 && gtime() - t0 < (unsigned long long)prime_delay_ns; ++i) __nanosleep(100);
-    }
     for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -228,9 +221,9 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
     // dependent loads would otherwise queue behind the whole ring's worth of bulk copies
     // (measured: 3.5 us instead of ~1.5 us from the dependency wait to the first MMA).
     for (int s = 0; s < (PRO ? ((dbg & 8) ? 0 : 1) : STAGES) && s < n_stages; ++s) {
-      const uint32_t bytes = (uint32_t)min(STAGE_UNITS, n_units - s * STAGE_UNITS) * 1024u;
+      const uint32_t bytes = (uint32_t)min(SU, n_units - s * SU) * 1024u;
       mbar_expect_tx(bar0 + 8 * s, bytes);
-      bulk_g2s(ring + s * (STAGE_UNITS * 1024), src + (size_t)s * STAGE_UNITS * 1024, bytes, bar0 + 8 * s,
+      bulk_g2s(ring + s * (SU * 1024), src + (size_t)s * SU * 1024, bytes, bar0 + 8 * s,
                policy);
     }
   }
@@ -261,9 +254,9 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
       if (m == 0 && lane == 0) {
         // the rest of the ring, behind the prologue's loads in the memory system's queues
         for (int s = (dbg & 8) ? 0 : 1; s < STAGES && s < n_stages; ++s) {
-          const uint32_t bytes = (uint32_t)min(STAGE_UNITS, n_units - s * STAGE_UNITS) * 1024u;
+          const uint32_t bytes = (uint32_t)min(SU, n_units - s * SU) * 1024u;
           mbar_expect_tx(bar0 + 8 * s, bytes);
-          bulk_g2s(ring + s * (STAGE_UNITS * 1024), src + (size_t)s * STAGE_UNITS * 1024, bytes,
+          bulk_g2s(ring + s * (SU * 1024), src + (size_t)s * SU * 1024, bytes,
                    bar0 + 8 * s, policy);
         }
       }
@@ -349,8 +342,8 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
       break;
     }
     if (trace && st == 0) g_gemm_trace[blockIdx.x * 8 + 4] = gtime();
-    const int in_stage = min(STAGE_UNITS, n_units - st * STAGE_UNITS);
-    uint32_t sbase = ring + sidx * (STAGE_UNITS * 1024) + lane * 16;
+    const int in_stage = min(SU, n_units - st * SU);
+    uint32_t sbase = ring + sidx * (SU * 1024) + lane * 16;
     int done = 0;
     while (done < in_stage) {
       // up to XB units that lie inside one 16-row group; their activation fragments are
@@ -434,9 +427,9 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
     __syncwarp();
     const int nxt = st + STAGES;
     if (lane == 0 && nxt < n_stages) {
-      const uint32_t bytes = (uint32_t)min(STAGE_UNITS, n_units - nxt * STAGE_UNITS) * 1024u;
+      const uint32_t bytes = (uint32_t)min(SU, n_units - nxt * SU) * 1024u;
       mbar_expect_tx(bar0 + 8 * sidx, bytes);
-      bulk_g2s(ring + sidx * (STAGE_UNITS * 1024), src + (size_t)nxt * STAGE_UNITS * 1024, bytes,
+      bulk_g2s(ring + sidx * (SU * 1024), src + (size_t)nxt * SU * 1024, bytes,
                bar0 + 8 * sidx, policy);
     }
   }
@@ -536,9 +529,9 @@ __global__ void k_pack_weight(const uint4* __restrict__ src, uint4* __restrict__
   }
 }
 
-template <int NT>
+template <int NT, int SU = STAGE_UNITS>
 constexpr int gemm_smem() {
-  return RING_BYTES + WARPS * 2 * NT * 128 * 4 + WARPS * 2 * 4 + WARPS * STAGES * 8;
+  return WARPS * STAGES * SU * 1024 + WARPS * 2 * NT * 128 * 4 + WARPS * 2 * 4 + WARPS * STAGES * 8;
 }
 
 int debug_flags_of_this_launch() {
@@ -546,24 +539,23 @@ int debug_flags_of_this_launch() {
   return (g_gemm_launches++ == g_gemm_trace_launch ? 4 : 0) | (g_gemm_debug_flags & ~4);
 }
 
-template <int NT, bool ACT>
+// SU = 1 KB units per bulk copy (a warp's ring is STAGES * SU KB)
+template <int NT, bool ACT, int SU = STAGE_UNITS>
 cudaError_t launch_gemm(const q_gemm_plan_t& p, const bf16* X, const unsigned char* W, float* P,
                         cudaStream_t s) {
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<NT, false, ACT>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_smem<NT>());
-    if (e != cudaSuccess) return e;
-    e = q_prefer_max_smem(k_gemm_streamk<NT, false, ACT>);
+    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<NT, false, ACT, SU>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_smem<NT, SU>());
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
   NormPrologue none = {};
   const int grid = ACT ? (p.groups < p.grid ? p.groups : p.grid) : p.grid;
-  return q_launch(k_gemm_streamk<NT, false, ACT>, dim3(grid), dim3(p.block), (size_t)gemm_smem<NT>(), s, X,
+  return q_launch(k_gemm_streamk<NT, false, ACT, SU>, dim3(grid), dim3(p.block), (size_t)gemm_smem<NT, SU>(), s, X,
                   W, P, p.M, p.N, p.K, p.chunks_per_group, p.groups * p.chunks_per_group,
                   p.units_per_worker, g_gemm_prefetch_kb * 1024 / WARPS, debug_flags_of_this_launch(), none,
-                  q_tl_next(), g_gemm_next_prime_delay_ns);
+                  q_tl_next());
 }
 
 template <bool ACT>
@@ -572,17 +564,15 @@ cudaError_t launch_gemm_norm(const q_gemm_plan_t& p, const unsigned char* W, flo
   const size_t smem = (size_t)gemm_smem<1>() + (size_t)p.M * (p.K + 32) * 2 + 32 * 4;
   static size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<1, true, ACT>,
+    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<1, true, ACT, STAGE_UNITS>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    e = q_prefer_max_smem(k_gemm_streamk<1, true, ACT>);
     if (e != cudaSuccess) return e;
     configured = smem;
   }
   const int grid = ACT ? (p.groups < p.grid ? p.groups : p.grid) : p.grid;
-  return q_launch(k_gemm_streamk<1, true, ACT>, dim3(grid), dim3(p.block), smem, s, (const bf16*)nullptr, W,
+  return q_launch(k_gemm_streamk<1, true, ACT, STAGE_UNITS>, dim3(grid), dim3(p.block), smem, s, (const bf16*)nullptr, W,
                   P, p.M, p.N, p.K, p.chunks_per_group, p.groups * p.chunks_per_group,
-                  p.units_per_worker, 0, debug_flags_of_this_launch(), pro, q_tl_next(), 0);
+                  p.units_per_worker, 0, debug_flags_of_this_launch(), pro, q_tl_next());
 }
 
 }  // namespace
