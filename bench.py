@@ -313,6 +313,8 @@ def kernels_per_step(state) -> int:
     # embed | QKV, attention, O, add+norm, gate|up (+ SwiGLU launch above 8 rows), down, add+norm |
     # lm_head, argmax
     n = 1 + (7 if state.batch <= 8 else 8) * layers + 2
+    if state.tp > 1 and getattr(state, "peers", False):
+        return n + 1                          # add+norm reads the peers' partials itself; argmax merge
     if state.tp > 1:
         n += layers * 2 + 1                   # partial reductions before each all-reduce, argmax merge
     return n

@@ -341,6 +341,36 @@ typedef struct q_state_t {
   void* fused_scratch;      /* q_fused_scratch_bytes() bytes or NULL: enables the single-kernel step */
 } q_state_t;
 
+/* Tensor parallel over peer memory (no reference counterpart: the reference is single-GPU).
+ * Every rank keeps the split-K partials of its O and down projections in a buffer the other
+ * ranks can read (CUDA IPC / symmetric memory; q_engine_peer_floats() floats: the O partials
+ * first, the down partials behind them) followed nowhere by anything else, and a small array
+ * of arrival words its peers write. partials[r] / flags[r] are rank r's buffers as mapped
+ * into THIS process (entry `rank` is this rank's own). flags[r] holds `world` uint32 words,
+ * zeroed once before the first step together with *epoch; word p of flags[r] is written by
+ * rank p only. */
+#define Q_MAX_PEERS 8
+typedef struct q_peers_t {
+  int32_t rank, world;
+  float* partials[Q_MAX_PEERS];
+  uint32_t* flags[Q_MAX_PEERS];
+  uint32_t* epoch;          /* this rank's call counter, ordinary device memory, zeroed once */
+} q_peers_t;
+
+/* engine/kernels/decode_fused.py:140-158 with the cross-rank sum folded in: ONE kernel that
+ * (1) tells every peer that this rank's partials at `d_own_branch` (inside partials[rank]) are
+ * complete and waits (bounded) for the same word from every peer, (2) reads every rank's
+ * split-K slots at the same offset through the peer mappings and adds them in rank order,
+ * then slot order, in fp32, (3) rounds the sum once, adds the residual and normalises like
+ * q_add_rmsnorm. It replaces q_reduce_partials + an all-reduce + q_add_rmsnorm. All ranks
+ * must make the same sequence of calls; consecutive calls must use different branch buffers
+ * (the engine alternates the O and the down partials), which is what lets a rank overwrite a
+ * buffer again without a second barrier. A wait that runs out sets q_device_status word 3.
+ * rows <= 8, cols a multiple of 4 up to 3072. */
+int q_add_rmsnorm_peers(const void* d_x_in, const q_peers_t* peers, const float* d_own_branch,
+                        const q_gemm_plan_t* plan, const void* d_gain, void* d_total_out,
+                        void* d_normed_out, int rows, int cols, float eps, void* stream);
+
 typedef struct q_engine q_engine;
 
 int q_create(const q_config_t* cfg, q_engine** out);
@@ -351,6 +381,14 @@ int64_t q_engine_partial_floats(const q_engine* e, int rows);
  * q_bind_state fills it (host-to-device copy, synchronous) when all layers are bound. */
 int64_t q_fused_scratch_bytes(const q_engine* e, int rows);
 void q_destroy(q_engine* e);
+/* Tensor parallel over peer memory: floats of the peer-readable partial buffer for `rows`,
+ * and the binding (after q_bind_state). With peers bound, q_decode_step_peers runs the whole
+ * sharded step - embed .. lm_head shard .. local argmax - with q_add_rmsnorm_peers in place
+ * of the two all-reduces per layer; the caller then gathers (arg_val, arg_idx) over the ranks
+ * and calls q_argmax_merge. */
+int64_t q_engine_peer_floats(const q_engine* e, int rows);
+int q_bind_peers(q_engine* e, const q_peers_t* peers);
+int q_decode_step_peers(q_engine* e, void* stream);
 
 /* One full step for T=1 on a single GPU: embed .. argmax, tokens and pos updated.
  * Default: ~290 kernels with programmatic dependent launch. With option "fused_step" = 1,

@@ -45,6 +45,14 @@ class LayerWeights(C.Structure):
         "wqkv", "wo", "wgu", "wdown", "ln_in", "ln_post", "q_gain", "k_gain", "kpool", "vpool")]
 
 
+MAX_PEERS = 8
+
+
+class Peers(C.Structure):
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("partials", C.c_void_p * MAX_PEERS),
+                ("flags", C.c_void_p * MAX_PEERS), ("epoch", C.c_void_p)]
+
+
 class State(C.Structure):
     _fields_ = [
         ("embed", C.c_void_p), ("lm_head", C.c_void_p), ("ln_final", C.c_void_p),
@@ -85,6 +93,10 @@ SIGNATURES = {
     "q_gemm_swiglu": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "q_gemm_swiglu_addnorm": (_I, [_P, _P, _PLAN, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
     "q_reduce_partials": (_I, [_P, _PLAN, _P, _P]),
+    "q_add_rmsnorm_peers": (_I, [_P, C.POINTER(Peers), _P, _PLAN, _P, _P, _P, _I, _I, _F, _P]),
+    "q_engine_peer_floats": (C.c_int64, [_P, _I]),
+    "q_bind_peers": (_I, [_P, C.POINTER(Peers)]),
+    "q_decode_step_peers": (_I, [_P, _P]),
     "q_static_scratch_floats": (C.c_int64, []),
     "q_linear_f32_static": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "q_rmsnorm": (_I, [_P, _P, _P, _I, _I, _F, _P]),

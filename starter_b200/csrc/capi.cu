@@ -124,6 +124,7 @@ extern "C" int q_set_option(const char* name, int value) {
   return Q_ERR_ARG;
 }
 
+int q_peer_status_read(int32_t* out);
 int q_attn_status_read(int32_t out[4]);
 int q_gemm_status_read(int32_t out[4]);
 
@@ -138,7 +139,9 @@ extern "C" int q_device_status(int32_t out[4]) {
   out[0] = a[0];   // attention: 1 producer wait ran out, 2 consumer wait ran out
   out[1] = g[0];   // GEMM: 1 ring wait ran out
   out[2] = m[0];   // whole-step kernel: 1 grid barrier, 2 GEMM ring, 3/4 attention ring
-  out[3] = 0;
+  int32_t peer = 0;
+  if (q_peer_status_read(&peer)) { q_set_error("q_device_status: could not read the status words"); return Q_ERR_CUDA; }
+  out[3] = peer;   // tensor parallel over peer memory: 1 = a wait for a peer's arrival word ran out
   return Q_OK;
 }
 
@@ -167,6 +170,8 @@ struct q_engine {
   bool mega_ok;
   int mega_grid;
   mega_params_t mega;
+  bool has_peers;
+  q_peers_t peers;
 };
 
 static int make_plans(q_engine* e, int rows) {
@@ -202,6 +207,7 @@ extern "C" int q_create(const q_config_t* cfg, q_engine** out) {
   e->bound.assign(cfg->n_layers, false);
   memset(&e->st, 0, sizeof(e->st));
   e->has_state = false;
+  e->has_peers = false;
   e->rows = 0;
   e->mega_ok = false;
   e->mega_grid = 0;
@@ -487,6 +493,62 @@ extern "C" int q_step_head(q_engine* e, void* stream) {
   TRY(ready(e, "q_step_head"));
   const q_config_t& c = e->cfg;
   const q_state_t& s = e->st;
+  TRY(q_gemm_splitk(s.normed, s.lm_head, s.partials, e->rows, c.vocab, c.hidden, stream));
+  return head_argmax(e, stream);
+}
+
+
+// Peer-readable buffer: [O partials | down partials], each rounded up to 64 floats.
+static long long peer_half_floats(const q_engine* e) {
+  long long m = plan_floats(e->p_o) > plan_floats(e->p_down) ? plan_floats(e->p_o) : plan_floats(e->p_down);
+  return ((m + 63) / 64) * 64;
+}
+
+extern "C" int64_t q_engine_peer_floats(const q_engine* e, int rows) {
+  if (!e || rows < 1 || rows > Q_MAX_ROWS) return -1;
+  q_engine tmp = *e;
+  if (make_plans(&tmp, rows)) return -1;
+  return 2 * peer_half_floats(&tmp);
+}
+
+extern "C" int q_bind_peers(q_engine* e, const q_peers_t* peers) {
+  Q_CHECK_ARG(e && peers, "q_bind_peers: null pointer");
+  Q_CHECK_ARG(e->has_state, "q_bind_peers: bind the state first");
+  Q_CHECK_ARG(peers->world == e->cfg.tp_size && peers->world >= 2 && peers->world <= Q_MAX_PEERS &&
+                  peers->rank >= 0 && peers->rank < peers->world && peers->epoch,
+              "q_bind_peers: world %d does not match tp_size %d (or bad rank / no epoch word)", peers->world,
+              e->cfg.tp_size);
+  Q_CHECK_ARG(e->rows <= 8 && e->cfg.hidden % 4 == 0 && e->cfg.hidden <= 3072,
+              "q_bind_peers: the peer step takes up to 8 rows and hidden <= 3072");
+  for (int r = 0; r < peers->world; ++r)
+    Q_CHECK_ARG(peers->partials[r] && peers->flags[r], "q_bind_peers: rank %d is not mapped", r);
+  e->peers = *peers;
+  e->has_peers = true;
+  return Q_OK;
+}
+
+// The sharded step with the cross-rank sums read from peer memory: per layer QKV, attention,
+// O (partials -> peer buffer half 0), add+norm over all ranks, gate|up + SwiGLU, down (->
+// half 1), add+norm over all ranks. The two halves alternate, which is what
+// q_add_rmsnorm_peers needs; every other projection writes the private partial buffer.
+extern "C" int q_decode_step_peers(q_engine* e, void* stream) {
+  TRY(ready(e, "q_decode_step_peers"));
+  Q_CHECK_ARG(e->has_peers, "q_decode_step_peers: q_bind_peers has not been called");
+  const q_config_t& c = e->cfg;
+  const q_state_t& s = e->st;
+  float* half0 = e->peers.partials[e->peers.rank];
+  float* half1 = half0 + peer_half_floats(e);
+  TRY(q_step_begin(e, stream));
+  for (int l = 0; l < c.n_layers; ++l) {
+    TRY(q_gemm_splitk(s.normed, e->layers[l].wqkv, s.partials, e->rows, e->p_qkv.N, c.hidden, stream));
+    TRY(attn_after_qkv(e, l, half0, stream));
+    TRY(q_add_rmsnorm_peers(s.x, &e->peers, half0, &e->p_o, e->layers[l].ln_post, s.x, s.normed, e->rows,
+                            c.hidden, c.rms_eps, stream));
+    TRY(q_gemm_swiglu(s.normed, e->layers[l].wgu, s.act, e->rows, c.inter, c.hidden, stream));
+    TRY(q_gemm_splitk(s.act, e->layers[l].wdown, half1, e->rows, c.hidden, c.inter, stream));
+    TRY(q_add_rmsnorm_peers(s.x, &e->peers, half1, &e->p_down, next_gain(e, l), s.x, s.normed, e->rows,
+                            c.hidden, c.rms_eps, stream));
+  }
   TRY(q_gemm_splitk(s.normed, s.lm_head, s.partials, e->rows, c.vocab, c.hidden, stream));
   return head_argmax(e, stream);
 }

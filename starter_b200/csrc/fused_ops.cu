@@ -153,6 +153,110 @@ k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanVie
   tl_end(tl);
 }
 
+
+// ---- residual add + RMSNorm on the partials of ALL tensor-parallel ranks ----------------
+// One CTA. Arrival words are written with release / read with acquire at system scope; the
+// value is this rank's call counter, the same on every rank because all ranks make the same
+// calls. Peer data is read with volatile loads (never from a stale local cache line).
+struct PeerView {
+  int rank, world;
+  const float* partials[Q_MAX_PEERS];
+  uint32_t* flags[Q_MAX_PEERS];
+  uint32_t* epoch;
+};
+
+__device__ int g_peer_status;      // 1 = a wait for a peer's arrival word ran out
+
+__device__ __forceinline__ float4 ld_peer(const float* p) {
+  float4 v;
+  asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+
+__global__ void __launch_bounds__(256)
+k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, long long branch_off, PlanView pv,
+                    const bf16* __restrict__ G, bf16* __restrict__ Tout, bf16* __restrict__ Nout,
+                    int rows, int cols, float eps, unsigned long long* tl) {
+  constexpr int VB = 3;
+  __shared__ float red[32];
+  __shared__ unsigned s_epoch;
+  tl_begin(tl);
+  pdl_launch_dependents();
+  pdl_wait();                         // this rank's projection has written its partials
+  tl_waited(tl);
+  const int tid = threadIdx.x;
+  if (tid == 0) s_epoch = *pw.epoch + 1u;
+  __syncthreads();
+  const unsigned e = s_epoch;
+  if (tid < pw.world && tid != pw.rank) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pw.flags[tid] + pw.rank), "r"(e) : "memory");
+    const uint32_t* mine = pw.flags[pw.rank] + tid;
+    bool ok = false;
+    for (int i = 0; i < (1 << 21); ++i) {          // ~1 s at the longest, then give up
+      unsigned v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if ((int)(v - e) >= 0) { ok = true; break; }
+      if (i > 64) __nanosleep(i > 4096 ? 400 : 40);
+    }
+    if (!ok) atomicExch(&g_peer_status, 1);
+  }
+  __syncthreads();
+  for (int row = 0; row < rows; ++row) {
+    float4 acc[VB];
+    uint2 xr[VB], gn[VB];
+#pragma unroll
+    for (int j = 0; j < VB; ++j) {
+      const int col = 4 * tid + j * 1024;
+      const int cc = col < cols ? col : 0;
+      acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      xr[j] = *reinterpret_cast<const uint2*>(Xin + (size_t)row * cols + cc);
+      gn[j] = *reinterpret_cast<const uint2*>(G + cc);
+      const int cnt = plan_count(pv, cc);
+      for (int r = 0; r < pw.world; ++r) {
+        const float* base = pw.partials[r] + branch_off + (size_t)row * cols + cc;
+        for (int k = 0; k < cnt; ++k) {
+          const float4 v = ld_peer(base + (long long)k * pv.slot_stride);
+          acc[j].x += v.x; acc[j].y += v.y; acc[j].z += v.z; acc[j].w += v.w;
+        }
+      }
+    }
+    float tot[VB][4];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VB; ++j) {
+      const int col = 4 * tid + j * 1024;
+      if (col < cols) {
+        const float s[4] = {acc[j].x, acc[j].y, acc[j].z, acc[j].w};
+        const float r4[4] = {bf_lo(xr[j].x), bf_hi(xr[j].x), bf_lo(xr[j].y), bf_hi(xr[j].y)};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          tot[j][q] = bf16_round(r4[q] + bf16_round(s[q]));
+          ss += tot[j][q] * tot[j][q];
+        }
+      }
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)cols + eps);
+#pragma unroll
+    for (int j = 0; j < VB; ++j) {
+      const int col = 4 * tid + j * 1024;
+      if (col < cols) {
+        const float g4[4] = {bf_lo(gn[j].x), bf_hi(gn[j].x), bf_lo(gn[j].y), bf_hi(gn[j].y)};
+        uint2 to, no;
+        to.x = pack_bf16(tot[j][0], tot[j][1]);
+        to.y = pack_bf16(tot[j][2], tot[j][3]);
+        no.x = pack_bf16(bf16_round(tot[j][0] * inv) * g4[0], bf16_round(tot[j][1] * inv) * g4[1]);
+        no.y = pack_bf16(bf16_round(tot[j][2] * inv) * g4[2], bf16_round(tot[j][3] * inv) * g4[3]);
+        *reinterpret_cast<uint2*>(Tout + (size_t)row * cols + col) = to;
+        *reinterpret_cast<uint2*>(Nout + (size_t)row * cols + col) = no;
+      }
+    }
+  }
+  if (tid == 0) *pw.epoch = e;
+  tl_end(tl);
+}
+
 // ---- SwiGLU on gate|up partials ---------------------------------------------
 __global__ void __launch_bounds__(256)
 k_swiglu(const float* __restrict__ P, PlanView pv, bf16* __restrict__ O, int rows, int inter,
@@ -482,6 +586,40 @@ extern "C" int q_add_rmsnorm(const void* d_x_in, const float* d_branch, const q_
                         d_branch, plan_view(plan), (const bf16*)d_gain, (bf16*)d_total_out,
                         (bf16*)d_normed_out, cols, eps, q_tl_next()));
   return Q_OK;
+}
+
+
+extern "C" int q_add_rmsnorm_peers(const void* d_x_in, const q_peers_t* peers, const float* d_own_branch,
+                                   const q_gemm_plan_t* plan, const void* d_gain, void* d_total_out,
+                                   void* d_normed_out, int rows, int cols, float eps, void* stream) {
+  Q_CHECK_ARG(d_x_in && peers && d_own_branch && d_gain && d_total_out && d_normed_out,
+              "q_add_rmsnorm_peers: null pointer");
+  Q_CHECK_ARG(peers->world >= 2 && peers->world <= Q_MAX_PEERS && peers->rank >= 0 &&
+                  peers->rank < peers->world && peers->epoch,
+              "q_add_rmsnorm_peers: bad rank/world or no epoch word");
+  Q_CHECK_ARG(rows >= 1 && rows <= 8 && cols >= 4 && cols % 4 == 0 && cols <= 3072,
+              "q_add_rmsnorm_peers: needs 1..8 rows and cols a multiple of 4 up to 3072");
+  int rc = check_plan(plan, rows, cols, "q_add_rmsnorm_peers");
+  if (rc) return rc;
+  PeerView pw;
+  pw.rank = peers->rank;
+  pw.world = peers->world;
+  pw.epoch = peers->epoch;
+  for (int r = 0; r < Q_MAX_PEERS; ++r) {
+    pw.partials[r] = r < peers->world ? peers->partials[r] : nullptr;
+    pw.flags[r] = r < peers->world ? peers->flags[r] : nullptr;
+    Q_CHECK_ARG(r >= peers->world || (pw.partials[r] && pw.flags[r]), "q_add_rmsnorm_peers: rank %d unmapped", r);
+  }
+  const long long off = d_own_branch - peers->partials[peers->rank];
+  Q_CHECK_ARG(off >= 0 && off % 4 == 0, "q_add_rmsnorm_peers: the branch is not inside this rank's peer buffer");
+  Q_CHECK_CUDA(q_launch(k_add_rmsnorm_peers, dim3(1), dim3(256), 0, S(stream), (const bf16*)d_x_in, pw, off,
+                        plan_view(plan), (const bf16*)d_gain, (bf16*)d_total_out, (bf16*)d_normed_out, rows,
+                        cols, eps, q_tl_next()));
+  return Q_OK;
+}
+
+int q_peer_status_read(int32_t* out) {
+  return cudaMemcpyFromSymbol(out, g_peer_status, sizeof(int)) == cudaSuccess ? 0 : -1;
 }
 
 int q_swiglu_layout(const float* d_branch, const q_gemm_plan_t* plan, void* d_out, int rows, int inter,

@@ -15,6 +15,8 @@ lm_head are all-gathered.
 from __future__ import annotations
 
 import ctypes as C
+import os
+import sys
 
 import torch
 import torch.nn.functional as F
@@ -120,6 +122,53 @@ class DecodeState:
             self.arg_val.data_ptr(), self.arg_idx.data_ptr(), self.arg_scratch.data_ptr(),
             0 if self.fused_scratch is None else self.fused_scratch.data_ptr())
         check(lib.q_bind_state(handle, C.byref(st)))
+        self.peers = False
+        if self.tp > 1 and batch <= 8 and cfg.hidden <= 3072 and os.environ.get("QDECODE_TP_PEERS", "1") == "1":
+            self._bind_peers()
+
+    def _bind_peers(self) -> None:
+        """Puts the O / down split-K partials of every rank into symmetric memory and hands the
+        peer mappings to the library, so that the two cross-rank sums per layer are read from
+        peer memory inside q_add_rmsnorm_peers instead of going through an all-reduce. All
+        ranks agree on the outcome; if any of them cannot map the others, all keep the
+        all-reduce path."""
+        import torch.distributed as dist
+        group = self.group if self.group is not None else dist.group.WORLD
+        ok, err = 1, ""
+        try:
+            # plain peer loads only: no NVLink multicast object is bound to these buffers
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm_mem
+            n = lib.q_engine_peer_floats(self.handle, self.batch)
+            if n <= 0:
+                raise _lib.QDecodeError("could not size the peer partial buffer")
+            buf = symm_mem.empty(n * 4 + 256, dtype=torch.uint8, device=self.device)
+            buf.zero_()
+            hdl = symm_mem.rendezvous(buf, group.group_name)
+            ptrs = list(hdl.buffer_ptrs)
+            if len(ptrs) != self.tp:
+                raise _lib.QDecodeError(f"{len(ptrs)} peer mappings for {self.tp} ranks")
+        except Exception as exc:            # noqa: BLE001 - any failure means "use the all-reduce path"
+            ok, err = 0, f"{type(exc).__name__}: {exc}"
+        agreed = torch.tensor([ok], dtype=torch.int32, device=self.device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+        if int(agreed.item()) == 0:
+            if err:
+                print(f"[starter_b200] peer-memory tensor parallel unavailable ({err}); using all-reduce",
+                      file=sys.stderr)
+            return
+        peers = _lib.Peers()
+        peers.rank, peers.world = dist.get_rank(group), self.tp
+        for r in range(self.tp):
+            peers.partials[r] = ptrs[r]
+            peers.flags[r] = ptrs[r] + n * 4
+        self.peer_epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        peers.epoch = self.peer_epoch.data_ptr()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)              # every rank's arrival words are zero from here on
+        check(lib.q_bind_peers(self.handle, C.byref(peers)))
+        self.peer_buffer, self.peer_handle = buf, hdl
+        self.peers = True
 
     def __del__(self):
         h = getattr(self, "handle", None)
@@ -226,14 +275,17 @@ class DecodeState:
         if self.tp == 1:
             check(lib.q_decode_step(h, s))
             return
-        check(lib.q_step_begin(h, s))
-        for layer in range(self.cfg.n_layers):
-            check(lib.q_step_attn(h, layer, s))
-            torch.distributed.all_reduce(self.reduced, group=self.group)
-            check(lib.q_step_post_attn(h, layer, s))
-            torch.distributed.all_reduce(self.reduced, group=self.group)
-            check(lib.q_step_post_mlp(h, layer, s))
-        check(lib.q_step_head(h, s))
+        if self.peers:
+            check(lib.q_decode_step_peers(h, s))      # cross-rank sums read from peer memory
+        else:
+            check(lib.q_step_begin(h, s))
+            for layer in range(self.cfg.n_layers):
+                check(lib.q_step_attn(h, layer, s))
+                torch.distributed.all_reduce(self.reduced, group=self.group)
+                check(lib.q_step_post_attn(h, layer, s))
+                torch.distributed.all_reduce(self.reduced, group=self.group)
+                check(lib.q_step_post_mlp(h, layer, s))
+            check(lib.q_step_head(h, s))
         torch.distributed.all_gather_into_tensor(self.gather_val, self.arg_val, group=self.group)
         torch.distributed.all_gather_into_tensor(self.gather_idx, self.arg_idx, group=self.group)
         check(lib.q_argmax_merge(_p(self.gather_val), _p(self.gather_idx), self.tp, self.batch,

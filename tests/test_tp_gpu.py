@@ -1,5 +1,6 @@
-"""Tensor-parallel engine on 2 GPUs (NCCL all-reduce inside the captured graph)
-against the single-GPU engine and native Hugging Face."""
+"""Tensor-parallel engine on 2 GPUs against the single-GPU engine and native Hugging Face:
+with the cross-rank sums read from peer memory inside the add+norm kernel (default), and with
+NCCL all-reduces inside the captured graph."""
 import json
 import os
 import subprocess
@@ -16,8 +17,9 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
 
+@pytest.mark.parametrize("peers", ["1", "0"])
 @pytest.mark.parametrize("world", [2])
-def test_tensor_parallel_tokens_match_single_gpu(tmp_path, world):
+def test_tensor_parallel_tokens_match_single_gpu(tmp_path, world, peers):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from transformers import Qwen3Config, Qwen3ForCausalLM
@@ -32,14 +34,17 @@ def test_tensor_parallel_tokens_match_single_gpu(tmp_path, world):
     gen = torch.Generator().manual_seed(2)
     cases = [(torch.randint(0, 512, (b, p), generator=gen).tolist(), n) for b, p, n in ((2, 7, 6), (1, 70, 5), (4, 33, 8))]
     out_path = tmp_path / "tp_tokens.json"
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", QDECODE_TP_PEERS=peers)
     port = 29600 + os.getpid() % 1000
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), str(ROOT / "tests" / "tp_worker.py"),
            str(model_dir), str(out_path), json.dumps(cases)]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
-    tp_tokens = json.loads(out_path.read_text())
+    report = json.loads(out_path.read_text())
+    tp_tokens = report["tokens"]
+    assert report["device_status"] == [0, 0, 0, 0]
+    assert report["peers"] == (peers == "1"), proc.stderr[-2000:]
     single = Engine(str(model_dir))
     native = O.native_model(str(model_dir))
     for (prompt, n), got in zip(cases, tp_tokens):

@@ -26,11 +26,14 @@ def main():
     if os.environ.get("TP_NO_GRAPH"):
         from starter_b200.decode import DecodeState
         DecodeState.capture = lambda self: None
-    out = []
+    out, used_peers = [], True
     for prompt, n in cases:
         out.append(list(engine.generate(prompt, n)))
+        used_peers = used_peers and bool(engine.decode_state.peers)
+    from starter_b200.ops import device_status
+    status = device_status()
     if dist.get_rank() == 0:
-        Path(out_path).write_text(json.dumps(out))
+        Path(out_path).write_text(json.dumps({"tokens": out, "peers": used_peers, "device_status": status}))
     # captured graphs hold NCCL kernels: drop them before the communicator goes away
     engine.decode_state = None
     del engine
