@@ -450,7 +450,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         "kernel": "k_gemm_streamk", "achieved": gemm["gbs"], "unit": "GB/s", "frac": gemm["gbs"] / peak,
         "avg_launch_us": gemm["avg_launch_us"], "launches_per_step": gemm["launches_per_step"],
         "bytes_per_launch": gemm["bytes_per_step"] / gemm["launches_per_step"],
-        "how": "the step's 145 GEMM launches replayed alone as one CUDA graph on the real weights",
+        "how": "the step's projection launches replayed alone, back to back, as one CUDA graph on the real weights",
     }
     if fused:
         # one launch = one whole step: algorithmic bytes = weights + KV of the step,
@@ -469,11 +469,12 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         roofline = {
             "bound": "hbm", "kernel": "k_gemm_streamk", "achieved": gemm["gbs"], "peak": peak,
             "unit": "GB/s", "frac": gemm["gbs"] / peak,
-            # ncu on the gate|up launch: read 99.65 MB + write 5 MB for 99.61 MB of weights
-            # (profiles/k_gemm_streamk_gate_up.md)
             "traffic": args.traffic_bytes if args.traffic_bytes
-            else 1.05 * gemm["bytes_per_step"] / gemm["launches_per_step"],
-            "traffic_source": "scaled from the ncu capture of one gate|up launch",
+            else 1.017 * gemm["bytes_per_step"] / gemm["launches_per_step"],
+            # ncu on a 4-layer step (profiles/k_gemm_streamk_in_step.md): DRAM reads = 1.001 x the
+            # weight bytes of every projection, writes ~3.3 MB per gate|up launch
+            "traffic_source": "1.017 x algorithmic bytes, from the ncu capture of the four projections "
+                              "of a layer inside a 4-layer step",
             "peak_source": peak_src, "avg_launch_us": gemm["avg_launch_us"],
             "launches_per_step": gemm["launches_per_step"],
             "bytes_per_launch": gemm["bytes_per_step"] / gemm["launches_per_step"],

@@ -49,7 +49,7 @@ int q_set_pdl(int enabled);
 /* Tuning knobs (process-wide, host side only; no reference counterpart).
  *   "gemm_prefetch_kb": L2 prefetch window per GEMM CTA in KB (0 = off, default).
  *   "fused_step": 1 = q_decode_step may use the single persistent kernel (default 0: on B200 the
- *       dependent-launch multi-kernel step measured faster, 2.2 vs 2.8 ms at batch 1).
+ *       dependent-launch multi-kernel step measured faster, 2.0 vs 2.8 ms at batch 1).
  *   "norm_in_gemm": 1 (default) = with up to 8 rows on one GPU, q_decode_step runs residual add +
  *       RMSNorm as the prologue of the projection that consumes them (q_gemm_splitk_addnorm).
  *   "attn_no_cluster": 1 = q_attention_decode merges 2..8 key splits through global memory and a
@@ -391,7 +391,8 @@ int q_bind_peers(q_engine* e, const q_peers_t* peers);
 int q_decode_step_peers(q_engine* e, void* stream);
 
 /* One full step for T=1 on a single GPU: embed .. argmax, tokens and pos updated.
- * Default: ~290 kernels with programmatic dependent launch. With option "fused_step" = 1,
+ * Default: 2 + 5 per layer + 1 kernels (up to 8 rows; 1 + 8 per layer + 2 above) with programmatic
+ * dependent launch. With option "fused_step" = 1,
  * at most 8 rows, state.fused_scratch set and enough shared memory, the step runs as ONE
  * persistent cooperative kernel instead. Both produce the same tokens. */
 int q_decode_step(q_engine* e, void* stream);

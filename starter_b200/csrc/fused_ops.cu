@@ -203,8 +203,11 @@ k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, long long branch_
   }
   __syncthreads();
   for (int row = 0; row < rows; ++row) {
+    // All loads of up to four ranks are issued before any is used (a load and its use back
+    // to back would cost one NVLink round trip per load: the pipeline issues in order).
     float4 acc[VB];
     uint2 xr[VB], gn[VB];
+    int cnt[VB];
 #pragma unroll
     for (int j = 0; j < VB; ++j) {
       const int col = 4 * tid + j * 1024;
@@ -212,14 +215,37 @@ k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, long long branch_
       acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
       xr[j] = *reinterpret_cast<const uint2*>(Xin + (size_t)row * cols + cc);
       gn[j] = *reinterpret_cast<const uint2*>(G + cc);
-      const int cnt = plan_count(pv, cc);
-      for (int r = 0; r < pw.world; ++r) {
-        const float* base = pw.partials[r] + branch_off + (size_t)row * cols + cc;
-        for (int k = 0; k < cnt; ++k) {
-          const float4 v = ld_peer(base + (long long)k * pv.slot_stride);
-          acc[j].x += v.x; acc[j].y += v.y; acc[j].z += v.z; acc[j].w += v.w;
+      cnt[j] = plan_count(pv, cc);
+    }
+    for (int r0 = 0; r0 < pw.world; r0 += 4) {
+      float4 v[4][VB][2];
+#pragma unroll
+      for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+        for (int j = 0; j < VB; ++j) {
+          const int col = 4 * tid + j * 1024;
+          const int cc = col < cols ? col : 0;
+          const bool live = r0 + rr < pw.world;
+          const float* base = pw.partials[live ? r0 + rr : pw.rank] + branch_off + (size_t)row * cols + cc;
+          v[rr][j][0] = live ? ld_peer(base) : make_float4(0.f, 0.f, 0.f, 0.f);
+          v[rr][j][1] = (live && cnt[j] > 1) ? ld_peer(base + pv.slot_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-      }
+#pragma unroll
+      for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+        for (int j = 0; j < VB; ++j) {
+          acc[j].x += v[rr][j][0].x; acc[j].y += v[rr][j][0].y; acc[j].z += v[rr][j][0].z; acc[j].w += v[rr][j][0].w;
+          acc[j].x += v[rr][j][1].x; acc[j].y += v[rr][j][1].y; acc[j].z += v[rr][j][1].z; acc[j].w += v[rr][j][1].w;
+          if (r0 + rr < pw.world && cnt[j] > 2) {      // more than two slots: rare, one at a time
+            const int col = 4 * tid + j * 1024;
+            const int cc = col < cols ? col : 0;
+            const float* base = pw.partials[r0 + rr] + branch_off + (size_t)row * cols + cc;
+            for (int k = 2; k < cnt[j]; ++k) {
+              const float4 t = ld_peer(base + (long long)k * pv.slot_stride);
+              acc[j].x += t.x; acc[j].y += t.y; acc[j].z += t.z; acc[j].w += t.w;
+            }
+          }
+        }
     }
     float tot[VB][4];
     float ss = 0.f;
