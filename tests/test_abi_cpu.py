@@ -6,6 +6,7 @@ import re
 from pathlib import Path
 
 import pytest
+import torch
 
 ROOT = Path(__file__).resolve().parents[1]
 
@@ -127,3 +128,32 @@ def test_config_and_tp_shard_shapes(golden_dir):
     assert torch.equal(gate, one.layers[0].wgu[:256])
     assert torch.equal(torch.cat([s.lm_head for s in shards]), one.lm_head)
     assert [s.vocab_offset for s in shards] == [0, 63]
+
+
+def test_gate_up_interleave_is_a_row_permutation():
+    """q_gemm_swiglu's weight order: tiled rows 16i..16i+7 = gate rows 8i..8i+7 and rows
+    16i+8..16i+15 = the matching up rows (engine/mlp.py:12-15 packs [gate; up])."""
+    from starter_b200.weights import deinterleave_gate_up, interleave_gate_up
+    inter, K = 40, 32
+    packed = torch.arange(2 * inter * K, dtype=torch.float32).view(2 * inter, K).to(torch.bfloat16)
+    mixed = interleave_gate_up(packed)
+    assert mixed.shape == packed.shape
+    for i in range(inter // 8):
+        assert torch.equal(mixed[16 * i:16 * i + 8], packed[8 * i:8 * i + 8])                     # gate
+        assert torch.equal(mixed[16 * i + 8:16 * i + 16], packed[inter + 8 * i:inter + 8 * i + 8])  # up
+    assert torch.equal(deinterleave_gate_up(mixed), packed)
+    with pytest.raises(ValueError):
+        interleave_gate_up(packed[:-2])
+
+
+def test_peer_entry_points_reject_bad_arguments():
+    """No GPU needed: the argument checks of the tensor-parallel peer path run on the host."""
+    from starter_b200 import _lib
+    lib = _lib.lib
+    peers = _lib.Peers()
+    peers.rank, peers.world = 0, 1                        # a world of one is not tensor parallel
+    assert lib.q_add_rmsnorm_peers(1, C.byref(peers), 1, None, 1, 1, 1, 1, 128, 1e-6, None) == -1
+    assert b"world" in lib.q_last_error() or b"rank" in lib.q_last_error()
+    assert lib.q_bind_peers(None, C.byref(peers)) == -1
+    assert lib.q_gemm_swiglu(1, 1, 1, 1, 12, 64, None) == -1      # inter must be a multiple of 8
+    assert lib.q_gemm_swiglu_addnorm(1, 1, None, 1, 1, 1, 1, 1, 64, 64, 1e-6, None) == -1   # in place
