@@ -193,11 +193,13 @@ k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, long long branch_
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pw.flags[tid] + pw.rank), "r"(e) : "memory");
     const uint32_t* mine = pw.flags[pw.rank] + tid;
     bool ok = false;
-    for (int i = 0; i < (1 << 21); ++i) {          // ~1 s at the longest, then give up
+    // bounded: ~4 s at the longest (a peer whose host thread was descheduled for a moment
+    // must not look like a dead one), then the status word is set and the kernel goes on
+    for (int i = 0; i < (1 << 21); ++i) {
       unsigned v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
       if ((int)(v - e) >= 0) { ok = true; break; }
-      if (i > 64) __nanosleep(i > 4096 ? 400 : 40);
+      if (i > 64) __nanosleep(i > 65536 ? 2000 : (i > 4096 ? 400 : 40));
     }
     if (!ok) atomicExch(&g_peer_status, 1);
   }
