@@ -344,7 +344,7 @@ typedef struct q_state_t {
 /* Tensor parallel over peer memory (no reference counterpart: the reference is single-GPU).
  * Every rank keeps the split-K partials of its O and down projections in a buffer the other
  * ranks can read (CUDA IPC / symmetric memory; q_engine_peer_floats() floats: the O partials
- * first, the down partials behind them) followed nowhere by anything else, and a small array
+ * first, the down partials behind them), and a small array
  * of arrival words its peers write. partials[r] / flags[r] are rank r's buffers as mapped
  * into THIS process (entry `rank` is this rank's own). flags[r] holds `world` uint32 words,
  * zeroed once before the first step together with *epoch; word p of flags[r] is written by
@@ -385,7 +385,7 @@ void q_destroy(q_engine* e);
  * and the binding (after q_bind_state). With peers bound, q_decode_step_peers runs the whole
  * sharded step - embed .. lm_head shard .. local argmax - with q_add_rmsnorm_peers in place
  * of the two all-reduces per layer; the caller then gathers (arg_val, arg_idx) over the ranks
- * and calls q_argmax_merge. */
+ * and calls q_argmax_merge. q_bind_peers(e, NULL) unbinds. */
 int64_t q_engine_peer_floats(const q_engine* e, int rows);
 int q_bind_peers(q_engine* e, const q_peers_t* peers);
 int q_decode_step_peers(q_engine* e, void* stream);

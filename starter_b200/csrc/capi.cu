@@ -512,7 +512,11 @@ extern "C" int64_t q_engine_peer_floats(const q_engine* e, int rows) {
 }
 
 extern "C" int q_bind_peers(q_engine* e, const q_peers_t* peers) {
-  Q_CHECK_ARG(e && peers, "q_bind_peers: null pointer");
+  Q_CHECK_ARG(e != nullptr, "q_bind_peers: null engine");
+  if (peers == nullptr) {           // unbind: q_decode_step_peers is refused again
+    e->has_peers = false;
+    return Q_OK;
+  }
   Q_CHECK_ARG(e->has_state, "q_bind_peers: bind the state first");
   Q_CHECK_ARG(peers->world == e->cfg.tp_size && peers->world >= 2 && peers->world <= Q_MAX_PEERS &&
                   peers->rank >= 0 && peers->rank < peers->world && peers->epoch,

@@ -168,7 +168,50 @@ class DecodeState:
         dist.barrier(group=group)              # every rank's arrival words are zero from here on
         check(lib.q_bind_peers(self.handle, C.byref(peers)))
         self.peer_buffer, self.peer_handle = buf, hdl
-        self.peers = True
+        self.peers = self._peers_self_test(peers, n, group)
+        if not self.peers:
+            check(lib.q_bind_peers(self.handle, None))
+            print("[starter_b200] peer-memory self-test failed; using all-reduce", file=sys.stderr)
+
+    @staticmethod
+    def _device_status() -> list:
+        out = (C.c_int32 * 4)()
+        check(lib.q_device_status(C.byref(out)))
+        return list(out)
+
+    def _peers_self_test(self, peers, n_floats: int, group) -> bool:
+        """One q_add_rmsnorm_peers call on known data before the path is trusted: every rank
+        fills its buffer with (rank+1)/16, so each output must be a whole multiple (the number of
+        split-K slots of its column, at most plan.slots) of the sum of those over the ranks, and no wait may
+        have run out. All ranks agree on the verdict."""
+        import torch.distributed as dist
+        cfg, dev = self.cfg, self.device
+        rank, world = peers.rank, peers.world
+        half = n_floats // 2
+        own = torch.full((n_floats,), (rank + 1) / 16.0, dtype=torch.float32, device=dev)
+        view = self.peer_buffer[:n_floats * 4].view(torch.float32)
+        view.copy_(own)
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)
+        plan = _lib.plan(self.batch, cfg.hidden, self.w.local_inter)
+        zeros = torch.zeros((self.batch, cfg.hidden), dtype=torch.bfloat16, device=dev)
+        ones = torch.ones(cfg.hidden, dtype=torch.bfloat16, device=dev)
+        total, normed = torch.empty_like(zeros), torch.empty_like(zeros)
+        s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        rc = lib.q_add_rmsnorm_peers(_p(zeros), C.byref(peers), C.c_void_p(view.data_ptr() + half * 4),
+                                     C.byref(plan), _p(ones), _p(total), _p(normed), self.batch, cfg.hidden,
+                                     float(cfg.rms_eps), s)
+        torch.cuda.synchronize(dev)
+        unit = sum(r + 1 for r in range(world)) / 16.0
+        ratio = total.float() / unit
+        whole = (ratio == ratio.round()) & (ratio >= 1) & (ratio <= plan.slots)
+        good = rc == 0 and bool(whole.all()) and self._device_status()[3] == 0
+        verdict = torch.tensor([1 if good else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=group)
+        view.zero_()
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)
+        return bool(int(verdict.item()))
 
     def __del__(self):
         h = getattr(self, "handle", None)
