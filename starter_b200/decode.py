@@ -8,9 +8,10 @@ is enqueued before step k+1 is launched. The KV cache is paged
 
 Tensor parallelism: every rank holds its head / FFN-column / vocabulary shard
 and runs the same step; the fp32 partial sums after O-proj and down-proj are
-all-reduced (so the single bf16 rounding of a Linear output happens after the
-cross-rank sum), and the per-rank (max, index) pairs of the vocabulary-sharded
-lm_head are all-gathered.
+summed over the ranks before the single bf16 rounding of a Linear output - by
+default inside the add+norm kernel, which reads every rank's partials from
+symmetric (peer-mapped) memory, else by an NCCL all-reduce - and the per-rank
+(max, index) pairs of the vocabulary-sharded lm_head are all-gathered.
 """
 from __future__ import annotations
 
