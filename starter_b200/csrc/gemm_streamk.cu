@@ -59,7 +59,6 @@ constexpr int WARPS = QG_WARPS;
 constexpr int THREADS = WARPS * 32;
 constexpr int STAGE_UNITS = QG_STAGE_UNITS;  // units (KB) per bulk copy
 constexpr int STAGES = QG_STAGES;
-constexpr int RING_BYTES = WARPS * STAGES * STAGE_UNITS * 1024;   // 96 KB
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 __device__ int g_gemm_status[4];
