@@ -324,7 +324,7 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
   int seg_first_chunk = chunk;          // first chunk of the current segment
   int n_boundary = 0, units_done = 0;
   bool alive = true;
-  constexpr int XB = NT == 1 ? 8 : (NT == 2 ? 4 : (NT == 4 ? 2 : 1));   // units per activation batch
+  constexpr int XB = NT == 1 ? 8 : (NT == 2 ? 4 : (NT == 4 ? 4 : 2));   // units per activation batch
   // activation row pointers of this lane (row nt*8+g, k offset 8t), null past M
   const bf16* xrow[NT];
 #pragma unroll
