@@ -12,8 +12,11 @@ Rank 0 prints ONE JSON line.
              timed with CUDA events on the launching stream (max over ranks)
   e2e        the same metric through Engine.generate(): host prompt in, host
              tokens out, prefill and all copies inside the timed region
-  roofline   the weight-streaming GEMM kernel (the dominant kernel): algorithmic
-             weight bytes per launch / average launch duration, timed live here
+  step_roofline  algorithmic bytes of a step (weights + KV) / CUDA-event step time
+  roofline   the weight-streaming projection kernel (the dominant kernel) as it runs
+             INSIDE the step: weight bytes / its launches' share of the step
+  gemm_kernel  the same launches replayed alone (CUDA events)
+  c3         the batch-32, prompt-2048 workload measured the same way (rides along)
   cpu_baseline  native Hugging Face on the host cores (bounded sample), N=1 only
 
 --impl reference times the native Hugging Face CPU path alone.
@@ -242,52 +245,51 @@ def workload_config(args, cfg, batch, prompt_len):
 # ----------------------------------------------------------------------------
 # our arm
 # ----------------------------------------------------------------------------
+KIND_NAMES = {1: "k_gemm_streamk", 2: "k_gemm_tc", 3: "k_attn_decode", 4: "k_add_rmsnorm", 5: "k_swiglu",
+              6: "k_embed_rmsnorm", 7: "k_logits_argmax", 8: "k_add_rmsnorm_peers"}
+
+
+def step_projections(state):
+    """(activation tensor, weight) of every projection of one decode step, in step order."""
+    w = state.w
+    out = []
+    for lt in w.layers:
+        out += [(state.normed, lt.wqkv), (state.attended, lt.wo), (state.normed, lt.wgu), (state.act, lt.wdown)]
+    out.append((state.normed, w.lm_head))
+    return out
+
+
 def time_gemm_kernel(state, reps: int = 5):
-    """Average launch duration of the weight-streaming GEMM kernel, timed live with
-    CUDA events on the launching stream: every GEMM of one decode step (4 per
-    layer + lm_head) launched in step order on the real weights (8 GB, far larger
-    than L2), nothing else in between."""
+    """The step's projection launches replayed ALONE, back to back, as one CUDA graph on the
+    real weights (far larger than L2), timed with CUDA events on the launching stream."""
     import ctypes as C
     from starter_b200._lib import lib, check
 
-    w, cfg = state.w, state.cfg
-    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-    rows = state.batch
-    nq, inter = w.local_q_heads, w.local_inter
+    rows = state.rows
     P = C.c_void_p(state.partials.data_ptr())
-    launches, nbytes = 0, 0
+    proj = step_projections(state)
+    nbytes = sum(wt.numel() * 2 for _, wt in proj)
 
-    def seq():
-        nonlocal launches, nbytes
-        launches = nbytes = 0
-        for lt in w.layers:
-            for x, wt in ((state.normed, lt.wqkv), (state.attended, lt.wo), (state.normed, lt.wgu),
-                          (state.act, lt.wdown)):
-                if wt is lt.wgu and rows <= 8:      # the step runs this one with the SwiGLU epilogue
-                    check(lib.q_gemm_swiglu(C.c_void_p(x.data_ptr()), C.c_void_p(wt.data_ptr()),
-                                            C.c_void_p(state.act.data_ptr()), rows, wt.shape[0] // 2,
-                                            wt.shape[1], s))
-                else:
-                    check(lib.q_gemm_splitk(C.c_void_p(x.data_ptr()), C.c_void_p(wt.data_ptr()), P, rows,
-                                            wt.shape[0], wt.shape[1], s))
-                launches += 1
-                nbytes += wt.numel() * 2
-        check(lib.q_gemm_splitk(C.c_void_p(state.normed.data_ptr()), C.c_void_p(w.lm_head.data_ptr()), P,
-                                rows, w.lm_head.shape[0], w.lm_head.shape[1], s))
-        launches += 1
-        nbytes += w.lm_head.numel() * 2
+    def seq(s):
+        for x, wt in proj:
+            xp = C.c_void_p(x.data_ptr())
+            if state.uses_tc:
+                check(lib.q_gemm_tc(xp, C.c_void_p(wt.tc().data_ptr()), P, rows, wt.shape[0], wt.shape[1], s))
+            elif wt.interleaved8 and rows <= 8:      # the step runs this one with the SwiGLU epilogue
+                check(lib.q_gemm_swiglu(xp, C.c_void_p(wt.data_ptr()), C.c_void_p(state.act.data_ptr()), rows,
+                                        wt.shape[0] // 2, wt.shape[1], s))
+            else:
+                check(lib.q_gemm_splitk(xp, C.c_void_p(wt.data_ptr()), P, rows, wt.shape[0], wt.shape[1], s))
 
     for _ in range(2):
-        seq()
+        seq(C.c_void_p(torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
-    # one CUDA graph of the whole sequence: no host launch cost between kernels
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(side):
         with torch.cuda.graph(graph, stream=side):
-            s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-            seq()
+            seq(C.c_void_p(torch.cuda.current_stream().cuda_stream))
     graph.replay()
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -297,27 +299,119 @@ def time_gemm_kernel(state, reps: int = 5):
     b.record()
     torch.cuda.synchronize()
     ms = a.elapsed_time(b) / reps
-    return {"launches_per_step": launches, "bytes_per_step": nbytes,
-            "avg_launch_us": 1e3 * ms / launches, "gbs": nbytes / (ms * 1e-3) / 1e9}
+    return {"launches_per_step": len(proj), "bytes_per_step": nbytes,
+            "avg_launch_us": 1e3 * ms / len(proj), "gbs": nbytes / (ms * 1e-3) / 1e9}
+
+
+def time_in_step(state, reps: int = 8):
+    """Where the time of one decode step goes, per kernel, measured INSIDE the step: with the
+    library's timeline option every kernel stamps %globaltimer at its first CTA's start and its
+    last CTA's end; a kernel's share is (its end - the previous kernel's end), so the overlap
+    that dependent launches give is attributed to the kernel that benefits. One extra graph of
+    the step is recorded with the stamps on and replayed; all ranks do the same."""
+    import ctypes as C
+    from starter_b200._lib import lib, check
+
+    saved = (state.tokens.clone(), state.position.clone())
+    check(lib.q_set_option(b"timeline", 1))
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            state.step()
+        n_max = 4096
+        buf = (C.c_uint64 * (4 * n_max))()
+        kinds = (C.c_int32 * n_max)()
+        shares: dict[int, list[float]] = {}
+        span = []
+        for rep in range(reps + 2):
+            state.tokens.copy_(saved[0])
+            state.position.copy_(saved[1])
+            graph.replay()
+            torch.cuda.synchronize()
+            n = lib.q_debug_timeline(buf, n_max)
+            if n <= 0:
+                return None
+            lib.q_debug_timeline_kinds(kinds, n_max)
+            if rep < 2:
+                continue
+            per = {}
+            for i in range(n):
+                begin, _, end, _ = (int(buf[4 * i + j]) for j in range(4))
+                prev_end = int(buf[4 * (i - 1) + 2]) if i else begin
+                per[kinds[i]] = per.get(kinds[i], 0.0) + max(0.0, (end - prev_end) / 1e3)
+            for k, v in per.items():
+                shares.setdefault(k, []).append(v)
+            span.append((int(buf[4 * (n - 1) + 2]) - int(buf[0])) / 1e3)
+        counts = {}
+        for i in range(n):
+            counts[kinds[i]] = counts.get(kinds[i], 0) + 1
+    finally:
+        check(lib.q_set_option(b"timeline", 0))
+        state.tokens.copy_(saved[0])
+        state.position.copy_(saved[1])
+    med = lambda v: sorted(v)[len(v) // 2]
+    return {"us": {KIND_NAMES.get(k, str(k)): med(v) for k, v in shares.items()},
+            "launches": {KIND_NAMES.get(k, str(k)): c for k, c in counts.items()},
+            "step_span_us": med(span)}
 
 
 def kernels_per_step(state) -> int:
     """Launches of this library's kernels in one decode step (NCCL's are not counted)."""
-    if state.fused_scratch is not None and os.environ.get("QDECODE_FUSED") == "1":
-        return 1                              # the persistent whole-step kernel (opt-in)
-    layers = state.cfg.n_layers
-    if state.tp == 1 and state.batch <= 8 and os.environ.get("QDECODE_NORM_IN_GEMM", "1") == "1":
-        # embed, first QKV | attention, O, gate|up (add+norm prologue, SwiGLU epilogue), down,
-        # next QKV or lm_head (add+norm prologue) | argmax
-        return 2 + 5 * layers + 1
-    # embed | QKV, attention, O, add+norm, gate|up (+ SwiGLU launch above 8 rows), down, add+norm |
-    # lm_head, argmax
-    n = 1 + (7 if state.batch <= 8 else 8) * layers + 2
-    if state.tp > 1 and getattr(state, "peers", False):
-        return n + 1                          # add+norm reads the peers' partials itself; argmax merge
-    if state.tp > 1:
-        n += layers * 2 + 1                   # partial reductions before each all-reduce, argmax merge
-    return n
+    L, rows = state.cfg.n_layers, state.rows
+    if state.tp == 1:
+        if rows <= 8:
+            # embed, first QKV | attention, O, gate|up (add+norm prologue, SwiGLU epilogue), down,
+            # next QKV or lm_head (add+norm prologue) | argmax
+            return 2 + 5 * L + 1
+        # embed | QKV, attention, O, add+norm, gate|up, SwiGLU, down, add+norm | lm_head, argmax
+        return 1 + 8 * L + 2
+    if state.peers:
+        # QKV, attention, O, add+norm over the peers, gate|up (+ SwiGLU launch above 8 rows), down,
+        # add+norm over the peers (+ two slot reductions above 8 rows) | lm_head, argmax, peer merge
+        return 1 + (7 if rows <= 8 else 10) * L + 3
+    # NCCL: slot reductions before each all-reduce, separate add+norm launches, argmax merge
+    return 1 + (9 if rows <= 8 else 10) * L + 3
+
+
+def measure_decode(state, K: int, W: int, world: int, dev, local_rank: int):
+    """W warm-up replays, then K timed replays of the captured step (CUDA events on the launching
+    stream, barrier + synchronize on both sides, max over ranks)."""
+    import torch.distributed as dist
+    for _ in range(W):
+        state.advance()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start_pos = int(state.position.item())
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        a.record()
+        for _ in range(K):
+            state.advance()
+        b.record()
+        torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    end_pos = int(state.position.item())
+    assert end_pos - start_pos == K, (start_pos, end_pos, K)
+    avg_keys = (start_pos + 1 + end_pos) / 2.0
+    return ms, avg_keys, clocks.summary()
+
+
+def tokens_digest(steps) -> str:
+    """sha256 over the first 64 emitted steps' token ids (16 hex digits): equal digests at
+    different GPU counts mean the same tokens were emitted."""
+    import hashlib
+    flat = [int(t) for step in steps[:64] for t in step]
+    return hashlib.sha256(",".join(map(str, flat)).encode()).hexdigest()[:16]
 
 
 def run_ours(args, rank: int, world: int, local_rank: int) -> None:
@@ -330,15 +424,12 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
     from starter_b200 import Engine, _lib
+    from starter_b200.decode import DecodeState
+    from starter_b200.ops import device_status
 
-    if os.environ.get("QDECODE_FUSED") == "1":      # measure the single persistent kernel instead
-        _lib.check(_lib.lib.q_set_option(b"fused_step", 1))
-    for name in os.environ.get("QDECODE_OPTIONS", "").split(","):      # "name=value,..." tuning knobs
-        if name:
-            key, _, val = name.partition("=")
-            _lib.check(_lib.lib.q_set_option(key.encode(), int(val)))
-    if os.environ.get("QDECODE_NORM_IN_GEMM", "1") != "1":   # separate add+norm launches instead
-        _lib.check(_lib.lib.q_set_option(b"norm_in_gemm", 0))
+    for item in args.option:                         # "name=value" tuning knobs of q_set_option
+        key, _, val = item.partition("=")
+        _lib.check(_lib.lib.q_set_option(key.encode(), int(val)))
     batch, prompt_len, new_tokens = WORKLOADS[args.workload]
     cfg = dict(QWEN3_4B)
     if args.layers:
@@ -353,59 +444,43 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         dist.barrier()
     model_dir = checkpoint_dir(cfg)
     t0 = time.perf_counter()
-    engine = Engine(str(model_dir), device=str(dev), group=group)
+    engine = Engine(str(model_dir), device=str(dev), group=group, tp_path=args.tp_path)
     log(f"[bench] rank {rank}: weights loaded in {time.perf_counter() - t0:.1f}s")
     prompt = make_prompt(batch, prompt_len, cfg["vocab_size"])
     prompt_list = prompt.tolist()
 
-    # ---- device-resident timing: K graph replays ----
-    from starter_b200.decode import DecodeState
+    def status_over_ranks():
+        st = torch.tensor(device_status(), dtype=torch.int32, device=dev)
+        if world > 1:
+            dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        return st.tolist()
+
     with torch.inference_mode():
-        state = DecodeState(engine.weights, batch, prompt_len, n_new, group=group)
+        # ---- device-resident timing: K graph replays ----
+        state = DecodeState(engine.weights, batch, prompt_len, n_new, group=group, tp_path=args.tp_path)
         engine.decode_state = state
         state.prefill(prompt.to(dev))
         state.capture()
-        for _ in range(W):
-            state.advance()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        start_pos = int(state.position.item())
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local_rank) as clocks:
-            a.record()
-            for _ in range(K):
-                state.advance()
-            b.record()
-            torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        ms = a.elapsed_time(b)
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-        end_pos = int(state.position.item())
-        assert end_pos - start_pos == K, (start_pos, end_pos, K)
-        avg_keys = (start_pos + 1 + end_pos) / 2.0
+        ms, avg_keys, clocks = measure_decode(state, K, W, world, dev, local_rank)
         step_bytes_rank = state.step_bytes(int(round(avg_keys)))
+        in_step = time_in_step(state)
         gemm = time_gemm_kernel(state) if rank == 0 else None
-        from starter_b200.ops import device_status
-        status = device_status()
+        tp_path = state.tp_path
+        launches = kernels_per_step(state)
 
         # ---- end to end through the public API ----
         e2e = None
         if not args.skip_e2e:
             list(engine.generate(prompt_list, n_new))        # warm-up call (capture already done)
             torch.cuda.synchronize()
+            torch.cuda.reset_peak_memory_stats(dev)
             if world > 1:
                 dist.barrier()
             t_start = time.perf_counter()
-            stamps = []
-            for _tok in engine.generate(prompt_list, n_new):
+            stamps, emitted = [], []
+            for tok in engine.generate(prompt_list, n_new):
                 stamps.append(time.perf_counter())
+                emitted.append(tok)
             torch.cuda.synchronize()
             t_total = time.perf_counter() - t_start
             te = torch.tensor([t_total], dtype=torch.float64, device=dev)
@@ -414,10 +489,42 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             t_total = float(te.item())
             e2e = {
                 "value": batch * n_new / t_total, "unit": "tok/s",
-                "h2d_bytes_per_step": batch * prompt_len * 8 / n_new, "d2h_bytes_per_step": batch * 8,
+                "h2d_bytes_per_step": batch * prompt_len * 8 / n_new, "d2h_bytes_per_step": batch * 8 + 16,
                 "new_tokens": n_new, "ttft_ms": 1e3 * (stamps[0] - t_start),
                 "tpot_ms": 1e3 * (stamps[-1] - stamps[0]) / max(1, n_new - 1),
+                "peak_mem_bytes": int(torch.cuda.max_memory_allocated(dev)),
+                "tokens_sha16": tokens_digest(emitted),
             }
+        status = status_over_ranks()
+
+        # ---- the batch-32 workload next to the headline one (the case tensor parallelism is for) ----
+        c3 = None
+        if args.workload == "c2" and not args.no_c3:
+            engine.decode_state = None
+            state.graph = None
+            del state
+            torch.cuda.empty_cache()
+            b3, p3, n3 = WORKLOADS["c3"]
+            K3 = min(K, 32)
+            st3 = DecodeState(engine.weights, b3, p3, max(n3, K3 + W + 2), group=group, tp_path=args.tp_path)
+            t_pre = time.perf_counter()
+            st3.prefill(make_prompt(b3, p3, cfg["vocab_size"]).to(dev))
+            torch.cuda.synchronize()
+            prefill_ms = 1e3 * (time.perf_counter() - t_pre)
+            first_tokens = st3.tokens.cpu().tolist()
+            st3.capture()
+            ms3, keys3, clocks3 = measure_decode(st3, K3, W, world, dev, local_rank)
+            bytes3 = st3.step_bytes(int(round(keys3)))
+            digest = tokens_digest([first_tokens, st3.tokens.cpu().tolist()])
+            c3 = {"workload": f"c3: batch {b3}, prompt {p3}", "steps": K3, "ms_per_step": ms3 / K3,
+                  "value": b3 * K3 / (ms3 * 1e-3), "unit": "tok/s", "tp_path": st3.tp_path,
+                  "projections": "tcgen05" if st3.uses_tc else "mma.sync",
+                  "bytes_per_step_per_gpu": bytes3, "step_gbs_per_gpu": bytes3 / (ms3 / K3 * 1e-3) / 1e9,
+                  "gpu_launches": kernels_per_step(st3) * K3, "prefill_ms": prefill_ms,
+                  "in_step_us": (time_in_step(st3) or {}).get("us"),
+                  "tokens_sha16": digest, "clocks": clocks3, "device_status": status_over_ranks()}
+            st3.graph = None
+            del st3
 
     def teardown():
         """NCCL communicators must not be torn down while captured graphs that hold
@@ -425,7 +532,6 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         if world == 1:
             return
         engine.decode_state = None
-        state.graph = None
         torch.cuda.synchronize()
         dist.barrier()
         sys.stdout.flush()
@@ -445,53 +551,48 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     ms_step = ms / K
     tok_s = batch * K / (ms * 1e-3)
     step_gbs = step_bytes_rank / (ms_step * 1e-3) / 1e9
-    fused = kernels_per_step(state) == 1
+    kernel = "k_gemm_tc" if tp_path is not None and in_step and "k_gemm_tc" in in_step["us"] else "k_gemm_streamk"
     gemm_info = {
-        "kernel": "k_gemm_streamk", "achieved": gemm["gbs"], "unit": "GB/s", "frac": gemm["gbs"] / peak,
+        "kernel": kernel, "achieved": gemm["gbs"], "unit": "GB/s", "frac": gemm["gbs"] / peak,
         "avg_launch_us": gemm["avg_launch_us"], "launches_per_step": gemm["launches_per_step"],
         "bytes_per_launch": gemm["bytes_per_step"] / gemm["launches_per_step"],
         "how": "the step's projection launches replayed alone, back to back, as one CUDA graph on the real weights",
     }
-    if fused:
-        # one launch = one whole step: algorithmic bytes = weights + KV of the step,
-        # duration = the CUDA-event time of the timed region / launches
-        roofline = {
-            "bound": "hbm", "kernel": "k_decode_mega", "achieved": step_gbs, "peak": peak, "unit": "GB/s",
-            "frac": step_gbs / peak,
-            # DRAM bytes per launch: ncu measured 1.012 x the algorithmic bytes on a 4-layer
-            # capture (profiles/k_decode_mega_c2_batch1.md); traffic grows with the layers
-            "traffic": args.traffic_bytes if args.traffic_bytes else 1.012 * step_bytes_rank,
-            "traffic_source": "scaled from a 4-layer ncu capture",
-            "peak_source": peak_src,
-            "avg_launch_us": 1e3 * ms_step, "launches_per_step": 1, "bytes_per_launch": step_bytes_rank,
-        }
+    # the dominant kernel as it runs INSIDE the step: its launches' share of the step time
+    if in_step and kernel in in_step["us"]:
+        gemm_us = in_step["us"][kernel]
+        n_launch = in_step["launches"][kernel]
+        achieved = gemm["bytes_per_step"] / (gemm_us * 1e-6) / 1e9
+        how = ("weight bytes of the step's projection launches / the sum of their in-step shares "
+               "(each kernel's last-CTA end minus the previous kernel's, %globaltimer stamps inside a replayed graph)")
     else:
-        roofline = {
-            "bound": "hbm", "kernel": "k_gemm_streamk", "achieved": gemm["gbs"], "peak": peak,
-            "unit": "GB/s", "frac": gemm["gbs"] / peak,
-            "traffic": args.traffic_bytes if args.traffic_bytes
-            else 1.017 * gemm["bytes_per_step"] / gemm["launches_per_step"],
-            # ncu on a 4-layer step (profiles/k_gemm_streamk_in_step.md): DRAM reads = 1.001 x the
-            # weight bytes of every projection, writes ~3.3 MB per gate|up launch
-            "traffic_source": "1.017 x algorithmic bytes, from the ncu capture of the four projections "
-                              "of a layer inside a 4-layer step",
-            "peak_source": peak_src, "avg_launch_us": gemm["avg_launch_us"],
-            "launches_per_step": gemm["launches_per_step"],
-            "bytes_per_launch": gemm["bytes_per_step"] / gemm["launches_per_step"],
-        }
+        gemm_us, n_launch, achieved = gemm["avg_launch_us"] * gemm["launches_per_step"], gemm["launches_per_step"], gemm["gbs"]
+        how = "stand-alone replay (no in-step stamps available)"
+    roofline = {
+        "bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "frac": achieved / peak,
+        "traffic": args.traffic_bytes if args.traffic_bytes else 1.017 * gemm["bytes_per_step"] / n_launch,
+        "traffic_source": "1.017 x algorithmic bytes, from the ncu capture of the four projections of a layer "
+                          "inside a 4-layer step",
+        "peak_source": peak_src, "avg_launch_us": gemm_us / n_launch, "launches_per_step": n_launch,
+        "bytes_per_launch": gemm["bytes_per_step"] / n_launch, "how": how,
+    }
     line = {
         "metric": "decode_tok_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args, cfg, batch, prompt_len),
+        "step_roofline": {"bytes_per_step_per_gpu": step_bytes_rank, "achieved": step_gbs, "peak": peak,
+                          "unit": "GB/s", "frac": step_gbs / peak, "avg_visible_keys": avg_keys},
         "roofline": roofline,
         "gemm_kernel": gemm_info,
-        "step_roofline": {"bytes_per_step_per_gpu": step_bytes_rank, "achieved": step_gbs,
-                          "unit": "GB/s", "frac": step_gbs / peak, "avg_visible_keys": avg_keys},
+        "in_step_us": in_step["us"] if in_step else None,
         "e2e": e2e,
-        "gpu_launches": kernels_per_step(state) * K,
-        "clocks": clocks.summary(),
+        "tp_path": tp_path,
+        "gpu_launches": launches * K,
+        "clocks": clocks,
         "device_status": status,
+        "c3": c3,
     }
     if world == 1 and not args.no_cpu_baseline:
         r = cpu_reference(model_dir, batch, min(prompt_len, args.cpu_prompt), args.cpu_steps, 1,
@@ -520,7 +621,13 @@ def main() -> None:
     ap.add_argument("--skip-e2e", action="store_true",
                     help="profiling runs only: skip the Engine.generate leg (e2e becomes null)")
     ap.add_argument("--traffic-bytes", type=float, default=None,
-                    help="DRAM bytes per GEMM launch from an ncu capture (see profiles/)")
+                    help="DRAM bytes per projection launch from an ncu capture, if a newer one is at hand")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="library tuning knob (q_set_option), repeatable")
+    ap.add_argument("--tp-path", choices=("auto", "peers", "nccl"), default="auto",
+                    help="how tensor-parallel ranks exchange partial sums")
+    ap.add_argument("--no-c3", action="store_true",
+                    help="skip the batch-32 record that rides along with the batch-1 headline")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -48,13 +48,14 @@ int q_set_pdl(int enabled);
 
 /* Tuning knobs (process-wide, host side only; no reference counterpart).
  *   "gemm_prefetch_kb": L2 prefetch window per GEMM CTA in KB (0 = off, default).
- *   "fused_step": 1 = q_decode_step may use the single persistent kernel (default 0: on B200 the
- *       dependent-launch multi-kernel step measured faster, 2.0 vs 2.8 ms at batch 1).
  *   "norm_in_gemm": 1 (default) = with up to 8 rows on one GPU, q_decode_step runs residual add +
  *       RMSNorm as the prologue of the projection that consumes them (q_gemm_splitk_addnorm).
  *   "attn_no_cluster": 1 = q_attention_decode merges 2..8 key splits through global memory and a
  *       ticket like it does above 8 splits, instead of inside a thread-block cluster (default 0).
- *   "trace_layer": layer stamped by the whole-step kernel (see q_debug_step_trace), -1 off.
+ *   "peer_wait_iters": polling iterations (about 1 us each once the wait has backed off) after which
+ *       q_add_rmsnorm_peers / q_argmax_merge_peers give up on a peer and set status word 3 (default 2^21).
+ *   "tc_min_rows": fewest rows for which q_decode_step uses the tcgen05 projections when the
+ *       engine has the 128 x 64 tiling of its weights bound (default 9).
  *   "gemm_debug_flags": measurement aid, 4 = per-CTA time stamps for q_debug_gemm_trace, 8 = a
  *       projection with the add+norm prologue requests none of its weights before its dependency wait.
  *   "gemm_trace_launch": measurement aid, n >= 0 = only the n-th GEMM launch from now records
@@ -74,20 +75,17 @@ int q_debug_gemm_trace(unsigned long long* out, int n_ctas);
  * launch in launch order, {first CTA start, first CTA past its dependency wait, last warp
  * end, last CTA start} in %globaltimer ns. Copies up to max_records records (4 values each)
  * of the most recent execution, re-arms the records and returns the count (or a negative
- * q_status). At most 1024 launches are recorded after the option is set. */
+ * q_status). At most 4096 launches are recorded after the option is set.
+ * q_debug_timeline_kinds gives the kernel kind of each record: 1 stream-K projection,
+ * 2 tcgen05 projection, 3 decode attention, 4 add+norm, 5 SwiGLU, 6 embedding + norm,
+ * 7 logits + argmax, 8 add+norm over peer memory. */
 int q_debug_timeline(unsigned long long* out, int max_records);
+int q_debug_timeline_kinds(int32_t* out, int max_records);
 
 /* Measurement aid: with option "timeline" on, CTA (0,0) of the decode-attention kernel stamps
  * {start, past the dependency wait, heads normed, tiles done, CTA merged, cluster merged, end, 0}
  * (ns); this copies the stamps of the last such launch (8 values). */
 int q_debug_attn_trace(unsigned long long* out);
-
-/* Measurement aid: with option "trace_layer" = l, the whole-step kernel stamps the
- * phase boundaries of layer l (%globaltimer ns) for CTA 0 (out[0..31]) and CTA 100
- * (out[32..63]): 0 start, 1 QKV done, 2 barrier, 3 attention, 4 barrier, 5 X staged,
- * 6 O-proj, 7 barrier, 8 add+norm, 9 gate|up, 10 barrier, 11 SwiGLU, 12 barrier,
- * 13 X staged, 14 down, 15 barrier, 16 add+norm. */
-int q_debug_step_trace(unsigned long long* out);
 
 /* ---- split-K weight-streaming GEMM --------------------------------------
  * Replaces engine/kernels/skinny_gemm.py:100-109 (linear_partials) and the
@@ -108,6 +106,7 @@ typedef struct q_gemm_plan_t {
   int32_t workers;            /* CTAs that get work */
   int32_t slots;              /* max count(group); P needs slots*M*N floats */
   int32_t grid, block;        /* launch shape used */
+  int32_t group_rows;         /* weight rows per group: 16 (q_gemm_plan) or 128 (q_gemm_tc_plan) */
 } q_gemm_plan_t;
 
 int q_gemm_plan(int M, int N, int K, q_gemm_plan_t* plan);
@@ -155,6 +154,22 @@ int q_gemm_swiglu_addnorm(const void* d_resid_in, const float* d_prev, const q_g
 int q_reduce_partials(const float* d_partials, const q_gemm_plan_t* plan,
                       float* d_out, void* stream);
 
+/* ---- the same projection on the tcgen05 tensor cores, for 9 rows and more ----------
+ * Replaces engine/kernels/skinny_gemm.py:28-46 at BLOCK_M 32 / 64 and the cuBLAS calls of
+ * the prompt pass (engine/prefill.py:40-52). The weight is tiled a second way: 128 rows x
+ * 64 k tiles of 16 KB, row-block-major then k, each tile stored as the K-major shared-memory
+ * image with 128-byte swizzle that tcgen05.mma reads (rows past N and k past K zero).
+ * q_gemm_tc writes the same kind of partial slots as q_gemm_splitk, with a "group" of 128
+ * weight rows: plan.group_rows = 128, chunks_per_group = k tiles, units_per_worker = tiles
+ * per CTA. Rows are processed in chunks of up to 256 (one weight pass per chunk); X is
+ * row-major [M][K], 16-byte aligned; d_w_tc 1024-byte aligned. */
+int64_t q_packed_weight_bytes_tc(int N, int K);
+int q_pack_weight_tc(const void* d_rowmajor, void* d_tiled, int N, int K, void* stream);
+int q_unpack_weight_tc(const void* d_tiled, void* d_rowmajor, int N, int K, void* stream);
+int q_gemm_tc_plan(int M, int N, int K, q_gemm_plan_t* plan);
+int q_gemm_tc(const void* d_x, const void* d_w_tc, float* d_partials, int M, int N, int K,
+              void* stream);
+
 /* No counterpart in the reference. d_out[M][N] (fp32) = X . W^T, i.e. q_gemm_splitk
  * followed by q_reduce_partials, for callers that may not allocate device memory
  * (their own pool owns all of it, their runtime forbids allocator calls, or they
@@ -200,6 +215,11 @@ int q_add_rmsnorm(const void* d_x_in, const float* d_branch, const q_gemm_plan_t
  * (columns [0,I) gate, [I,2I) up): out = bf16(bf16(silu(bf16 g)) * bf16 u). */
 int q_swiglu(const float* d_branch, const q_gemm_plan_t* plan, void* d_out,
              int rows, int inter, void* stream);
+/* The same on partials whose columns are in q_gemm_swiglu's weight order (blocks of 8 gate
+ * columns followed by their 8 up columns): what the step runs above 8 rows on the stream-K
+ * kernel. inter must be a multiple of 8. */
+int q_swiglu_interleaved(const float* d_branch, const q_gemm_plan_t* plan, void* d_out,
+                         int rows, int inter, void* stream);
 
 /* Paged KV cache of one layer: pool[page][kv_head][64 tokens][128] bf16, the
  * 16-byte chunks of each token row XOR-swizzled by (token & 7) so that a page
@@ -309,6 +329,12 @@ typedef struct q_layer_weights_t {
   const void* k_gain;   /* [128] */
   void* kpool;
   void* vpool;
+  /* optional: the four matrices in q_pack_weight_tc's tiling (wgu_tc = [gate rows | up rows],
+   * not interleaved). All four set = steps with tc_min_rows rows or more use q_gemm_tc. */
+  const void* wqkv_tc;
+  const void* wo_tc;
+  const void* wgu_tc;
+  const void* wdown_tc;
 } q_layer_weights_t;
 
 typedef struct q_state_t {
@@ -323,6 +349,9 @@ typedef struct q_state_t {
   int32_t pages_per_seq;
   int32_t batch;
   int32_t attn_splits;
+  int32_t q_tokens;         /* query tokens per sequence T (0 or 1 = the plain decode step); rows =
+                               batch * T: every row buffer below is sized for that many rows, tokens
+                               holds batch * T candidate ids, row b*T + t sits at position *pos + t */
   /* scratch, all caller-allocated */
   void* x;                  /* bf16 [rows][hidden] residual stream */
   void* normed;             /* bf16 [rows][hidden] */
@@ -338,7 +367,10 @@ typedef struct q_state_t {
   float* arg_val;           /* [rows] */
   int32_t* arg_idx;         /* [rows] */
   void* arg_scratch;        /* q_argmax_scratch_bytes() bytes, zeroed once */
-  void* fused_scratch;      /* q_fused_scratch_bytes() bytes or NULL: enables the single-kernel step */
+  const void* lm_head_tc;   /* lm_head in q_pack_weight_tc's tiling, or NULL */
+  int32_t* status_out;      /* int32[4] or NULL: the step's last kernel copies the four status
+                               words of q_device_status here, so the host can read them with the
+                               tokens instead of synchronising */
 } q_state_t;
 
 /* Tensor parallel over peer memory (no reference counterpart: the reference is single-GPU).
@@ -354,8 +386,15 @@ typedef struct q_peers_t {
   int32_t rank, world;
   float* partials[Q_MAX_PEERS];
   uint32_t* flags[Q_MAX_PEERS];
-  uint32_t* epoch;          /* this rank's call counter, ordinary device memory, zeroed once */
+  uint32_t* epoch;          /* uint32[4] of this rank, ordinary device memory, zeroed once: call
+                               counter and CTA ticket of the add+norm exchange, call counter of the
+                               token exchange */
 } q_peers_t;
+
+/* Bytes of the region flags[r] points to (zeroed once before the first step): 512 bytes of
+ * arrival words (uint32 [p] for q_add_rmsnorm_peers, [64 + p] for q_argmax_merge_peers), then
+ * the (value, index) pairs of the token exchange, [parity][shard][row]. */
+int64_t q_peer_flag_bytes(void);
 
 /* engine/kernels/decode_fused.py:140-158 with the cross-rank sum folded in: ONE kernel that
  * (1) tells every peer that this rank's partials at `d_own_branch` (inside partials[rank]) are
@@ -366,10 +405,19 @@ typedef struct q_peers_t {
  * must make the same sequence of calls; consecutive calls must use different branch buffers
  * (the engine alternates the O and the down partials), which is what lets a rank overwrite a
  * buffer again without a second barrier. A wait that runs out sets q_device_status word 3.
- * rows <= 8, cols a multiple of 4 up to 3072. */
+ * One CTA per row (the first one tells the peers, all wait for them). rows <= Q_MAX_ROWS,
+ * cols a multiple of 4 up to 3072; plan NULL = one fp32 [rows][cols] sum per rank. */
 int q_add_rmsnorm_peers(const void* d_x_in, const q_peers_t* peers, const float* d_own_branch,
                         const q_gemm_plan_t* plan, const void* d_gain, void* d_total_out,
                         void* d_normed_out, int rows, int cols, float eps, void* stream);
+
+/* engine/decode.py:106-107 (argmax, position += 1) over vocabulary shards held by different
+ * ranks, without a collective library call: every rank stores its per-row (value, index) pair
+ * (d_val / d_idx, as q_logits_argmax leaves them) into every rank's exchange area with plain
+ * peer stores, signals, waits (bounded, status word 3) for the others and picks the largest
+ * value with the lowest index; tokens are written and *d_pos += pos_inc on every rank. */
+int q_argmax_merge_peers(const float* d_val, const int32_t* d_idx, const q_peers_t* peers, int rows,
+                         int64_t* d_tokens, int32_t* d_pos, int pos_inc, void* stream);
 
 typedef struct q_engine q_engine;
 
@@ -377,24 +425,20 @@ int q_create(const q_config_t* cfg, q_engine** out);
 int q_bind_layer(q_engine* e, int layer, const q_layer_weights_t* w);
 int q_bind_state(q_engine* e, const q_state_t* s);
 int64_t q_engine_partial_floats(const q_engine* e, int rows);
-/* Scratch for the persistent whole-step kernel (layer table, grid barrier, tickets).
- * q_bind_state fills it (host-to-device copy, synchronous) when all layers are bound. */
-int64_t q_fused_scratch_bytes(const q_engine* e, int rows);
 void q_destroy(q_engine* e);
 /* Tensor parallel over peer memory: floats of the peer-readable partial buffer for `rows`,
  * and the binding (after q_bind_state). With peers bound, q_decode_step_peers runs the whole
- * sharded step - embed .. lm_head shard .. local argmax - with q_add_rmsnorm_peers in place
- * of the two all-reduces per layer; the caller then gathers (arg_val, arg_idx) over the ranks
- * and calls q_argmax_merge. q_bind_peers(e, NULL) unbinds. */
+ * sharded step - embed .. lm_head shard .. local argmax .. q_argmax_merge_peers - with
+ * q_add_rmsnorm_peers in place of the two all-reduces per layer (above 8 rows a rank adds its
+ * own split-K slots first, so that the peers fetch every element once). No collective library
+ * call is left in the step. q_bind_peers(e, NULL) unbinds; q_bind_state unbinds too. */
 int64_t q_engine_peer_floats(const q_engine* e, int rows);
 int q_bind_peers(q_engine* e, const q_peers_t* peers);
 int q_decode_step_peers(q_engine* e, void* stream);
 
-/* One full step for T=1 on a single GPU: embed .. argmax, tokens and pos updated.
- * Default: 2 + 5 per layer + 1 kernels (up to 8 rows; 1 + 8 per layer + 2 above) with programmatic
- * dependent launch. With option "fused_step" = 1,
- * at most 8 rows, state.fused_scratch set and enough shared memory, the step runs as ONE
- * persistent cooperative kernel instead. Both produce the same tokens. */
+/* One full step for T=1 on a single GPU: embed .. argmax, tokens and pos updated:
+ * 2 + 5 per layer + 1 kernels up to 8 rows (add+norm and SwiGLU folded into the projections),
+ * 1 + 8 per layer + 2 above, all with programmatic dependent launch. */
 int q_decode_step(q_engine* e, void* stream);
 
 /* The same step in pieces, for tensor parallelism: the caller all-reduces
@@ -409,12 +453,27 @@ int q_step_attn(q_engine* e, int layer, void* stream);
 int q_step_post_attn(q_engine* e, int layer, void* stream);
 int q_step_post_mlp(q_engine* e, int layer, void* stream);
 int q_step_head(q_engine* e, void* stream);
+/* ... and after the caller has all-gathered (arg_val, arg_idx) into [tp_size][rows] buffers:
+ * the pick over the shards (q_argmax_merge) into state.tokens, position += 1. */
+int q_step_merge(q_engine* e, const float* d_val, const int32_t* d_idx, void* stream);
 
-/* Reads the library's device status word of the current device (synchronises
- * the device; not capturable). out[0] != 0 means a bounded wait inside a kernel
- * ran out: out[0] attention (1 producer, 2 consumer), out[1] GEMM ring (1),
- * out[2] whole-step kernel (1 grid barrier, 2 GEMM ring, 3/4 attention ring). */
+/* The exact-verification step (the idea recorded at AGENTS.md:93-95 of the reference): with
+ * state.q_tokens = T >= 1, runs T candidate tokens per sequence through all layers in one
+ * pass over the weights - rows = batch * T through the same projections, q_qkv_norm_rope_cache
+ * and q_attention with T tokens per sequence - and leaves, for every row, the greedy successor
+ * of that row's prefix in state.arg_idx (and the logits in state.logits if set). Tokens and
+ * position are NOT advanced: the caller accepts the longest prefix whose candidates equal the
+ * successors before them, then sets state.tokens / *pos. Single GPU. */
+int q_verify_step(q_engine* e, void* stream);
+
+/* Reads the library's device status words of the current device (synchronises the device;
+ * not capturable). A non-zero word means a bounded wait inside a kernel ran out and the
+ * results since then are not to be trusted: out[0] attention (1 producer, 2 consumer),
+ * out[1] stream-K GEMM ring (1), out[2] tcgen05 GEMM (1 producer, 2 MMA issuer, 3 epilogue,
+ * 4 drain), out[3] tensor parallel over peer memory (1 = a peer's arrival word never came).
+ * The words are sticky; q_clear_status zeroes them (synchronises too). */
 int q_device_status(int32_t out[4]);
+int q_clear_status(void);
 
 #ifdef __cplusplus
 }

@@ -13,6 +13,7 @@ from . import build as _build
 PAGE_TOKENS = 64
 HEAD_DIM = 128
 MAX_ROWS = 64
+ERR_DEVICE = -4      # q_status Q_ERR_DEVICE: a device status word reported a wait that ran out
 
 
 class GemmPlan(C.Structure):
@@ -21,6 +22,7 @@ class GemmPlan(C.Structure):
         ("chunks_per_group", C.c_int32), ("groups", C.c_int32),
         ("units_per_worker", C.c_int32), ("workers", C.c_int32),
         ("slots", C.c_int32), ("grid", C.c_int32), ("block", C.c_int32),
+        ("group_rows", C.c_int32),
     ]
 
 
@@ -42,7 +44,8 @@ class Config(C.Structure):
 
 class LayerWeights(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
-        "wqkv", "wo", "wgu", "wdown", "ln_in", "ln_post", "q_gain", "k_gain", "kpool", "vpool")]
+        "wqkv", "wo", "wgu", "wdown", "ln_in", "ln_post", "q_gain", "k_gain", "kpool", "vpool",
+        "wqkv_tc", "wo_tc", "wgu_tc", "wdown_tc")]
 
 
 MAX_PEERS = 8
@@ -58,13 +61,13 @@ class State(C.Structure):
         ("embed", C.c_void_p), ("lm_head", C.c_void_p), ("ln_final", C.c_void_p),
         ("cos", C.c_void_p), ("sin", C.c_void_p), ("tokens", C.c_void_p), ("pos", C.c_void_p),
         ("block_table", C.c_void_p), ("pages_per_seq", C.c_int32), ("batch", C.c_int32),
-        ("attn_splits", C.c_int32),
+        ("attn_splits", C.c_int32), ("q_tokens", C.c_int32),
         ("x", C.c_void_p), ("normed", C.c_void_p), ("q", C.c_void_p), ("attended", C.c_void_p),
         ("act", C.c_void_p), ("partials", C.c_void_p), ("reduced", C.c_void_p),
         ("attn_o", C.c_void_p), ("attn_ml", C.c_void_p), ("attn_tickets", C.c_void_p),
         ("logits", C.c_void_p),
         ("arg_val", C.c_void_p), ("arg_idx", C.c_void_p), ("arg_scratch", C.c_void_p),
-        ("fused_scratch", C.c_void_p),
+        ("lm_head_tc", C.c_void_p), ("status_out", C.c_void_p),
     ]
 
 
@@ -81,9 +84,9 @@ SIGNATURES = {
     "q_set_pdl": (_I, [_I]),
     "q_set_option": (_I, [C.c_char_p, _I]),
     "q_debug_timeline": (_I, [_P, _I]),
+    "q_debug_timeline_kinds": (_I, [_P, _I]),
     "q_debug_attn_trace": (_I, [_P]),
     "q_debug_gemm_trace": (_I, [C.POINTER(C.c_uint64), _I]),
-    "q_debug_step_trace": (_I, [C.POINTER(C.c_uint64)]),
     "q_gemm_plan": (_I, [_I, _I, _I, _PLAN]),
     "q_packed_weight_bytes": (C.c_int64, [_I, _I]),
     "q_pack_weight": (_I, [_P, _P, _I, _I, _P]),
@@ -93,6 +96,16 @@ SIGNATURES = {
     "q_gemm_swiglu": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "q_gemm_swiglu_addnorm": (_I, [_P, _P, _PLAN, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
     "q_reduce_partials": (_I, [_P, _PLAN, _P, _P]),
+    "q_packed_weight_bytes_tc": (C.c_int64, [_I, _I]),
+    "q_pack_weight_tc": (_I, [_P, _P, _I, _I, _P]),
+    "q_unpack_weight_tc": (_I, [_P, _P, _I, _I, _P]),
+    "q_gemm_tc_plan": (_I, [_I, _I, _I, _PLAN]),
+    "q_gemm_tc": (_I, [_P, _P, _P, _I, _I, _I, _P]),
+    "q_peer_flag_bytes": (C.c_int64, []),
+    "q_argmax_merge_peers": (_I, [_P, _P, C.POINTER(Peers), _I, _P, _P, _I, _P]),
+    "q_step_merge": (_I, [_P, _P, _P, _P]),
+    "q_verify_step": (_I, [_P, _P]),
+    "q_clear_status": (_I, []),
     "q_add_rmsnorm_peers": (_I, [_P, C.POINTER(Peers), _P, _PLAN, _P, _P, _P, _I, _I, _F, _P]),
     "q_engine_peer_floats": (C.c_int64, [_P, _I]),
     "q_bind_peers": (_I, [_P, C.POINTER(Peers)]),
@@ -103,6 +116,7 @@ SIGNATURES = {
     "q_embed_rmsnorm": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
     "q_add_rmsnorm": (_I, [_P, _P, _PLAN, _P, _P, _P, _I, _I, _F, _P]),
     "q_swiglu": (_I, [_P, _PLAN, _P, _I, _I, _P]),
+    "q_swiglu_interleaved": (_I, [_P, _PLAN, _P, _I, _I, _P]),
     "q_qkv_norm_rope_cache": (_I, [_P, _PLAN, _P, _P, _P, _P, _P, _P, _KV, _I, _I, _I, _F, _P]),
     "q_kv_scatter": (_I, [_P, _P, _KV, _I, _I, _I, _P]),
     "q_attention_splits": (_I, [_I, _I, _I]),
@@ -115,7 +129,6 @@ SIGNATURES = {
     "q_bind_layer": (_I, [_P, _I, C.POINTER(LayerWeights)]),
     "q_bind_state": (_I, [_P, C.POINTER(State)]),
     "q_engine_partial_floats": (C.c_int64, [_P, _I]),
-    "q_fused_scratch_bytes": (C.c_int64, [_P, _I]),
     "q_destroy": (None, [_P]),
     "q_decode_step": (_I, [_P, _P]),
     "q_step_begin": (_I, [_P, _P]),
@@ -158,7 +171,8 @@ def check(rc: int) -> None:
     raise QDecodeError(f"qdecode status {rc}: {msg}")
 
 
-def plan(M: int, N: int, K: int) -> GemmPlan:
+def plan(M: int, N: int, K: int, tc: bool = False) -> GemmPlan:
+    """Split-K plan of the stream-K kernel, or (tc) of the tcgen05 kernel."""
     p = GemmPlan()
-    check(lib.q_gemm_plan(M, N, K, C.byref(p)))
+    check((lib.q_gemm_tc_plan if tc else lib.q_gemm_plan)(M, N, K, C.byref(p)))
     return p

@@ -13,7 +13,7 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
 LIB = Path(os.environ.get("QDECODE_LIB", ROOT / "libqdecode.so"))
-SOURCES = ["capi.cu", "gemm_streamk.cu", "fused_ops.cu", "attention.cu", "mega_step.cu"]
+SOURCES = ["capi.cu", "gemm_streamk.cu", "gemm_tc.cu", "fused_ops.cu", "attention.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-lineinfo", "-std=c++17",

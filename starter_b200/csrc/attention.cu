@@ -879,28 +879,21 @@ extern "C" int q_attention(const void* d_q, const q_kv_layout_t* kv, const int32
   Q_CHECK_ARG(((uintptr_t)kv->d_kpool & 15) == 0 && ((uintptr_t)kv->d_vpool & 15) == 0 &&
                   ((uintptr_t)d_q & 15) == 0,
               "q_attention: pools and q must be 16-byte aligned");
+  Q_CHECK_ALIGN(d_scratch_o, 16, "q_attention"); Q_CHECK_ALIGN(d_scratch_ml, 8, "q_attention");
+  Q_CHECK_ALIGN(d_out, 8, "q_attention");
   cudaStream_t s = (cudaStream_t)stream;
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(splits, batch * nkv), block(THREADS);
   cudaError_t e;
+  static size_t done1[64] = {0}, done2[64] = {0};
   if (T * G <= 16) {
-    static bool attr1 = false;
-    if (!attr1) {
-      Q_CHECK_CUDA(cudaFuncSetAttribute(k_attn_split<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)attn_smem<1>()));
-      attr1 = true;
-    }
+    Q_CHECK_CUDA(q_ensure_smem(k_attn_split<1>, attn_smem<1>(), done1));
     e = q_launch(k_attn_split<1>, grid, block, attn_smem<1>(), s, (const bf16*)d_q,
                  (const char*)kv->d_kpool, (const char*)kv->d_vpool, kv->d_block_table,
                  kv->pages_per_seq, d_pos, d_scratch_o, d_scratch_ml, (bf16*)d_out, T, G, n_q_heads,
                  nkv, splits, scale_log2);
   } else {
-    static bool attr2 = false;
-    if (!attr2) {
-      Q_CHECK_CUDA(cudaFuncSetAttribute(k_attn_split<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)attn_smem<2>()));
-      attr2 = true;
-    }
+    Q_CHECK_CUDA(q_ensure_smem(k_attn_split<2>, attn_smem<2>(), done2));
     e = q_launch(k_attn_split<2>, grid, block, attn_smem<2>(), s, (const bf16*)d_q,
                  (const char*)kv->d_kpool, (const char*)kv->d_vpool, kv->d_block_table,
                  kv->pages_per_seq, d_pos, d_scratch_o, d_scratch_ml, (bf16*)d_out, T, G, n_q_heads,
@@ -939,14 +932,14 @@ extern "C" int q_attention_decode(const float* d_qkv_partials, const q_gemm_plan
     Q_CHECK_ARG(plan->M == batch && plan->N == (n_q_heads + 2 * nkv) * 128,
                 "q_attention_decode: plan does not match the packed projection");
   }
-  static bool attr = false;
-  if (!attr) {
-    Q_CHECK_CUDA(cudaFuncSetAttribute(k_attn_decode<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)attn_decode_smem(NS)));
-    Q_CHECK_CUDA(cudaFuncSetAttribute(k_attn_decode<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)attn_decode_smem(NS)));
-    attr = true;
-  }
+  Q_CHECK_ALIGN(d_qkv_partials, 16, "q_attention_decode"); Q_CHECK_ALIGN(d_q_gain, 8, "q_attention_decode");
+  Q_CHECK_ALIGN(d_k_gain, 8, "q_attention_decode"); Q_CHECK_ALIGN(d_cos, 8, "q_attention_decode");
+  Q_CHECK_ALIGN(d_sin, 8, "q_attention_decode"); Q_CHECK_ALIGN(kv->d_kpool, 16, "q_attention_decode");
+  Q_CHECK_ALIGN(kv->d_vpool, 16, "q_attention_decode"); Q_CHECK_ALIGN(d_scratch_o, 16, "q_attention_decode");
+  Q_CHECK_ALIGN(d_scratch_ml, 8, "q_attention_decode"); Q_CHECK_ALIGN(d_out, 8, "q_attention_decode");
+  static size_t done_plain[64] = {0}, done_cluster[64] = {0};
+  Q_CHECK_CUDA(q_ensure_smem(k_attn_decode<false>, attn_decode_smem(NS), done_plain));
+  Q_CHECK_CUDA(q_ensure_smem(k_attn_decode<true>, attn_decode_smem(NS), done_cluster));
   // most tiles one split can be handed: ceil(tiles / splits) over the page capacity
   int ring = (kv->pages_per_seq + splits - 1) / splits;
   ring = ring < 1 ? 1 : (ring > NS ? NS : ring);
@@ -962,14 +955,14 @@ extern "C" int q_attention_decode(const float* d_qkv_partials, const q_gemm_plan
                                   (const bf16*)d_k_gain, (const bf16*)d_cos, (const bf16*)d_sin, d_pos,
                                   (char*)kv->d_kpool, (char*)kv->d_vpool, kv->d_block_table,
                                   kv->pages_per_seq, d_scratch_o, d_scratch_ml, d_tickets, (bf16*)d_out,
-                                  batch, G, n_q_heads, nkv, splits, sl2, eps, ring, q_tl_next()));
+                                  batch, G, n_q_heads, nkv, splits, sl2, eps, ring, q_tl_next(Q_TL_ATTENTION)));
   } else {
     Q_CHECK_CUDA(q_launch(k_attn_decode<false>, dim3(splits, batch * nkv), dim3(THREADS),
                           attn_decode_smem(ring), (cudaStream_t)stream, d_qkv_partials, plan_view(plan),
                           (const bf16*)d_q_gain, (const bf16*)d_k_gain, (const bf16*)d_cos,
                           (const bf16*)d_sin, d_pos, (char*)kv->d_kpool, (char*)kv->d_vpool,
                           kv->d_block_table, kv->pages_per_seq, d_scratch_o, d_scratch_ml, d_tickets,
-                          (bf16*)d_out, batch, G, n_q_heads, nkv, splits, sl2, eps, ring, q_tl_next()));
+                          (bf16*)d_out, batch, G, n_q_heads, nkv, splits, sl2, eps, ring, q_tl_next(Q_TL_ATTENTION)));
   }
   return Q_OK;
 }
@@ -981,6 +974,4 @@ extern "C" int q_debug_attn_trace(unsigned long long* out) {
   return Q_OK;
 }
 
-int q_attn_status_read(int32_t out[4]) {
-  return cudaMemcpyFromSymbol(out, g_status, sizeof(int) * 4) == cudaSuccess ? 0 : -1;
-}
+Q_DEFINE_STATUS_ADDR(q_attn_status_addr, g_status)

@@ -17,6 +17,11 @@ bool q_pdl_enabled();
     if (!(cond)) { q_set_error(__VA_ARGS__); return Q_ERR_ARG; } \
   } while (0)
 
+// Vectorised kernels load and store 8 or 16 bytes at a time: a pointer that is not aligned
+// would fault on the device, so it is refused on the host. Null passes (optional operands).
+#define Q_CHECK_ALIGN(ptr, bytes, who)                                                        \
+  Q_CHECK_ARG((((uintptr_t)(ptr)) & ((bytes) - 1)) == 0, "%s: %s must be %d-byte aligned", who, #ptr, (int)(bytes))
+
 #define Q_CHECK_CUDA(expr)                                                     \
   do {                                                                         \
     cudaError_t _e = (expr);                                                   \
@@ -68,11 +73,64 @@ static inline cudaError_t q_launch_cluster(void (*kernel)(KArgs...), dim3 grid, 
 
 int q_sm_count();
 
+// Device index of the calling thread's current device, or -1 (also -1 above 63: the
+// per-device caches below hold 64 entries).
+static inline int q_device_index() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return -1; }
+  return (dev >= 0 && dev < 64) ? dev : -1;
+}
+
+// Defines `int* fn()`: the device address of a file-scope __device__ status word on the
+// current device (looked up once per device and cached), or null.
+#define Q_DEFINE_STATUS_ADDR(fn, symbol)                                             \
+  int* fn() {                                                                        \
+    static int* cached[64] = {nullptr};                                              \
+    const int dev = q_device_index();                                                \
+    if (dev < 0) return nullptr;                                                     \
+    if (!cached[dev]) {                                                              \
+      void* p = nullptr;                                                             \
+      if (cudaGetSymbolAddress(&p, symbol) != cudaSuccess) { cudaGetLastError(); return nullptr; } \
+      cached[dev] = (int*)p;                                                         \
+    }                                                                                \
+    return cached[dev];                                                              \
+  }
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is a per-device setting: `done` is a
+// static size_t[64] of the largest size configured so far on each device.
+template <typename F>
+static inline cudaError_t q_ensure_smem(F* kernel, size_t bytes, size_t* done) {
+  const int dev = q_device_index();
+  if (dev < 0) return cudaErrorInvalidDevice;
+  if (bytes <= done[dev]) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess) done[dev] = bytes;
+  return e;
+}
+
+// The step's last kernel copies the four status words (see q_device_status) to out, so
+// that the host can read them with the tokens instead of synchronising the device.
+struct StatusTap {
+  const int* src[4];
+  int32_t* out;      // null = no copy
+};
+int q_logits_argmax_tap(const float* d_branch, const q_gemm_plan_t* plan, void* d_logits, float* d_val,
+                        int32_t* d_idx, int64_t* d_tokens, int32_t* d_pos, int pos_inc,
+                        void* d_block_scratch, int rows, int vocab, int vocab_offset, StatusTap tap,
+                        void* stream);
+int q_argmax_merge_tap(const float* d_val, const int32_t* d_idx, int shards, int rows, int64_t* d_tokens,
+                       int32_t* d_pos, int pos_inc, StatusTap tap, void* stream);
+int q_argmax_merge_peers_tap(const float* d_val, const int32_t* d_idx, const q_peers_t* peers, int rows,
+                             int64_t* d_tokens, int32_t* d_pos, int pos_inc, StatusTap tap, void* stream);
+
 // Split-K plan over at most `max_workers` CTAs (q_gemm_plan uses the SM count), and the
 // launch of a projection on a plan the caller already holds.
 int q_gemm_plan_workers(int M, int N, int K, int max_workers, q_gemm_plan_t* plan);
 int q_gemm_launch_planned(const void* d_x, const void* d_w_tiled, float* d_partials,
                           const q_gemm_plan_t* plan, void* stream);
+// The same for the tcgen05 kernel (plan from q_gemm_tc_plan, weight in the 128 x 64 tiling).
+int q_gemm_tc_launch(const void* d_x, const void* d_w_tc, float* d_partials, const q_gemm_plan_t* plan,
+                     void* stream);
 
 // q_swiglu on partials whose columns are in q_gemm_swiglu's interleaved gate/up order
 // (interleaved = 1) or in [gate | up] order (0).
@@ -80,15 +138,18 @@ int q_swiglu_layout(const float* d_branch, const q_gemm_plan_t* plan, void* d_ou
                     int interleaved, void* stream);
 
 // Measurement aid: a per-launch record {first CTA start, first CTA past the dependency
-// wait, last warp end, last CTA start} in %globaltimer ns. Launchers pass q_tl_next() as
+// wait, last warp end, last CTA start} in %globaltimer ns. Launchers pass q_tl_next(kind) as
 // the kernel's last argument: null unless option "timeline" is on, else the next record.
-unsigned long long* q_tl_next();
+enum q_tl_kind { Q_TL_GEMM = 1, Q_TL_GEMM_TC = 2, Q_TL_ATTENTION = 3, Q_TL_ADD_NORM = 4, Q_TL_SWIGLU = 5,
+                 Q_TL_EMBED = 6, Q_TL_ARGMAX = 7, Q_TL_PEER_ADD_NORM = 8 };
+unsigned long long* q_tl_next(int kind);
 
 // Split-K plan passed by value to consumer kernels. u == 0 means "one plain
 // fp32 [rows][cols] buffer".
 struct PlanView {
   int u;       // units per worker
-  int C;       // chunks per 16-row group
+  int C;       // chunks per group
+  int gshift;  // log2(weight rows per group): 4 (stream-K units) or 7 (tcgen05 tiles)
   long long slot_stride;  // M*N floats
 };
 
@@ -97,9 +158,10 @@ static inline PlanView plan_view(const q_gemm_plan_t* p) {
   if (p) {
     v.u = p->units_per_worker;
     v.C = p->chunks_per_group;
+    v.gshift = p->group_rows == 128 ? 7 : 4;
     v.slot_stride = (long long)p->M * p->N;
   } else {
-    v.u = 0; v.C = 0; v.slot_stride = 0;
+    v.u = 0; v.C = 0; v.gshift = 4; v.slot_stride = 0;
   }
   return v;
 }
@@ -151,7 +213,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Number of split-K slots that hold a partial for column n.
 __device__ __forceinline__ int plan_count(const PlanView& pv, int n) {
   if (pv.u == 0) return 1;
-  const unsigned g = (unsigned)n >> 4, C = (unsigned)pv.C, u = (unsigned)pv.u;
+  const unsigned g = (unsigned)n >> pv.gshift, C = (unsigned)pv.C, u = (unsigned)pv.u;
   const unsigned first = (g * C) / u;
   const unsigned last = ((g + 1) * C - 1) / u;
   return (int)(last - first + 1);

@@ -11,7 +11,14 @@
 // (reference: engine/kernels/decode_fused.py:19-118, engine/kernels/rmsnorm.py:12-36)
 #include "common.cuh"
 
+extern int g_peer_wait_iters;   // q_set_option "peer_wait_iters"
+
 namespace {
+
+// Greedy pick: larger value wins, equal values go to the lower index.
+__device__ __forceinline__ void arg_better(float& bv, int& bi, float v, int i) {
+  if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+}
 
 // ---- RMSNorm (plain) -------------------------------------------------------
 __global__ void __launch_bounds__(256)
@@ -113,16 +120,38 @@ k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanVie
     xr[j] = *reinterpret_cast<const uint2*>(Xin + row * cols + cc);
     gn[j] = *reinterpret_cast<const uint2*>(G + cc);
   }
+  // A projection whose output is narrow and whose K is long (O, down on the tcgen05 path) is
+  // split up to ~10 ways: slots 2..9 are requested together as well (narrow rows only, the
+  // registers of a wide row would not hold them); anything beyond comes one at a time.
+  constexpr int EX = VB <= 3 ? 8 : 0;
+  float4 sx[VB][EX > 0 ? EX : 1];
+  if (EX > 0 && two) {
+#pragma unroll
+    for (int j = 0; j < VB; ++j) {
+      const int col = 4 * threadIdx.x + j * 1024;
+      const int cc = col < cols ? col : 0;
+      const int extra = plan_extra(pv, cc);
+#pragma unroll
+      for (int k = 0; k < EX; ++k)
+        sx[j][k] = (k + 2 <= extra) ? *reinterpret_cast<const float4*>(p0 + cc + (long long)(k + 2) * pv.slot_stride)
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
   float tot[VB][4];
   float ss = 0.f;
 #pragma unroll
   for (int j = 0; j < VB; ++j) {
     const int col = 4 * threadIdx.x + j * 1024;
     if (col < cols) {
-      const int extra = plan_extra(pv, col);        // the 4 columns share one 16-column group
+      const int extra = plan_extra(pv, col);        // the 4 columns share one group
       float s[4] = {s0[j].x, s0[j].y, s0[j].z, s0[j].w};
       if (extra > 0) { s[0] += s1[j].x; s[1] += s1[j].y; s[2] += s1[j].z; s[3] += s1[j].w; }
-      for (int k = 2; k <= extra; ++k) {
+      if (EX > 0 && two) {
+#pragma unroll
+        for (int k = 0; k < EX; ++k)
+          if (k + 2 <= extra) { s[0] += sx[j][k].x; s[1] += sx[j][k].y; s[2] += sx[j][k].z; s[3] += sx[j][k].w; }
+      }
+      for (int k = 2 + EX; k <= extra; ++k) {
         const float4 sk = *reinterpret_cast<const float4*>(p0 + col + (long long)k * pv.slot_stride);
         s[0] += sk.x; s[1] += sk.y; s[2] += sk.z; s[3] += sk.w;
       }
@@ -155,14 +184,17 @@ k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanVie
 
 
 // ---- residual add + RMSNorm on the partials of ALL tensor-parallel ranks ----------------
-// One CTA. Arrival words are written with release / read with acquire at system scope; the
-// value is this rank's call counter, the same on every rank because all ranks make the same
-// calls. Peer data is read with volatile loads (never from a stale local cache line).
+// One CTA per row. Arrival words are written with release / read with acquire at system
+// scope; the value is this rank's call counter, the same on every rank because all ranks make
+// the same calls. CTA 0 tells the peers that this rank's partials are complete; every CTA
+// waits (bounded) for the peers' words, which live in this rank's own memory. Peer data is
+// read with volatile loads (never from a stale local cache line). The call counter is bumped
+// by the last CTA to finish (a ticket), so every CTA of a call reads the same value.
 struct PeerView {
   int rank, world;
   const float* partials[Q_MAX_PEERS];
   uint32_t* flags[Q_MAX_PEERS];
-  uint32_t* epoch;
+  uint32_t* epoch;     // [0] call counter of the add+norm exchange, [1] its ticket, [2] counter of the argmax exchange
 };
 
 __device__ int g_peer_status;      // 1 = a wait for a peer's arrival word ran out
@@ -173,10 +205,23 @@ __device__ __forceinline__ float4 ld_peer(const float* p) {
   return v;
 }
 
+// Bounded wait for `word` to reach `e` (wrap-around safe). The limit is in polling
+// iterations; the back-off grows to 2 us per poll, so the default 2^21 is about 4 s: a peer
+// whose host thread was descheduled for a moment must not look like a dead one.
+__device__ __forceinline__ bool wait_arrival(const uint32_t* word, unsigned e, int limit) {
+  for (int i = 0; i < limit; ++i) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
+    if ((int)(v - e) >= 0) return true;
+    if (i > 64) __nanosleep(i > 65536 ? 2000 : (i > 4096 ? 400 : 40));
+  }
+  return false;
+}
+
 __global__ void __launch_bounds__(256)
 k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, long long branch_off, PlanView pv,
                     const bf16* __restrict__ G, bf16* __restrict__ Tout, bf16* __restrict__ Nout,
-                    int rows, int cols, float eps, unsigned long long* tl) {
+                    int rows, int cols, float eps, int wait_iters, unsigned long long* tl) {
   constexpr int VB = 3;
   __shared__ float red[32];
   __shared__ unsigned s_epoch;
@@ -185,26 +230,19 @@ k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, long long branch_
   pdl_wait();                         // this rank's projection has written its partials
   tl_waited(tl);
   const int tid = threadIdx.x;
-  if (tid == 0) s_epoch = *pw.epoch + 1u;
+  const int row = blockIdx.x;
+  if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned*>(pw.epoch) + 1u;
   __syncthreads();
   const unsigned e = s_epoch;
   if (tid < pw.world && tid != pw.rank) {
-    __threadfence_system();
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pw.flags[tid] + pw.rank), "r"(e) : "memory");
-    const uint32_t* mine = pw.flags[pw.rank] + tid;
-    bool ok = false;
-    // bounded: ~4 s at the longest (a peer whose host thread was descheduled for a moment
-    // must not look like a dead one), then the status word is set and the kernel goes on
-    for (int i = 0; i < (1 << 21); ++i) {
-      unsigned v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-      if ((int)(v - e) >= 0) { ok = true; break; }
-      if (i > 64) __nanosleep(i > 65536 ? 2000 : (i > 4096 ? 400 : 40));
+    if (row == 0) {
+      __threadfence_system();
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pw.flags[tid] + pw.rank), "r"(e) : "memory");
     }
-    if (!ok) atomicExch(&g_peer_status, 1);
+    if (!wait_arrival(pw.flags[pw.rank] + tid, e, wait_iters)) atomicExch(&g_peer_status, 1);
   }
   __syncthreads();
-  for (int row = 0; row < rows; ++row) {
+  {
     // All loads of up to four ranks are issued before any is used (a load and its use back
     // to back would cost one NVLink round trip per load: the pipeline issues in order).
     float4 acc[VB];
@@ -281,8 +319,77 @@ k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, long long branch_
       }
     }
   }
-  if (tid == 0) *pw.epoch = e;
+  // the last CTA of the call publishes the new call counter
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const unsigned ticket = atomicAdd(pw.epoch + 1, 1u);
+    if (ticket == gridDim.x - 1) {
+      pw.epoch[1] = 0;
+      *reinterpret_cast<volatile unsigned*>(pw.epoch) = e;
+      __threadfence();
+    }
+  }
   tl_end(tl);
+}
+
+// ---- final token pick over the vocabulary shards, exchanged through peer memory ----------
+// Every rank stores its per-row (max logit, index) pair into every rank's exchange area
+// (plain peer stores), tells the peers with an arrival word and waits (bounded) for theirs;
+// then each rank picks, per row, the largest value with the lowest index over the shards in
+// its own area, writes the token and bumps the position. The area is double-buffered by the
+// parity of the call counter, so a rank may run one call ahead of a peer that is still
+// reading. Exchange area of rank r (inside its flag region, see q_peer_flag_bytes):
+// arrival words at uint32 [64 + p], pairs at byte 512: [parity][shard][row] {float, int32}.
+__global__ void __launch_bounds__(64)
+k_argmax_merge_peers(const float* __restrict__ val, const int32_t* __restrict__ idx, PeerView pw, int rows,
+                     int64_t* __restrict__ tokens, int32_t* __restrict__ pos_ptr, int pos_inc, int wait_iters,
+                     StatusTap tap) {
+  pdl_wait();
+  const int tid = threadIdx.x;
+  const unsigned e = *reinterpret_cast<volatile unsigned*>(pw.epoch + 2) + 1u;
+  const int parity = (int)(e & 1u);
+  if (tid < rows) {
+    const float v = val[tid];
+    const int i = idx[tid];
+    for (int p = 0; p < pw.world; ++p) {
+      char* area = reinterpret_cast<char*>(pw.flags[p]) + 512;
+      float2* slot = reinterpret_cast<float2*>(area) + ((size_t)parity * pw.world + pw.rank) * Q_MAX_ROWS + tid;
+      asm volatile("st.volatile.global.v2.f32 [%0], {%1, %2};" ::"l"(slot), "f"(v), "f"(__int_as_float(i)) : "memory");
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (tid < pw.world && tid != pw.rank) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pw.flags[tid] + 64 + pw.rank), "r"(e) : "memory");
+    if (!wait_arrival(pw.flags[pw.rank] + 64 + tid, e, wait_iters)) atomicExch(&g_peer_status, 1);
+  }
+  __syncthreads();
+  if (tid < rows) {
+    const char* area = reinterpret_cast<const char*>(pw.flags[pw.rank]) + 512;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int s = 0; s < pw.world; ++s) {
+      const float2* slot = reinterpret_cast<const float2*>(area) + ((size_t)parity * pw.world + s) * Q_MAX_ROWS + tid;
+      float a, b;
+      asm volatile("ld.volatile.global.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(b) : "l"(slot));
+      arg_better(bv, bi, a, __float_as_int(b));
+    }
+    if (bi == 0x7fffffff) bi = 0;
+    tokens[tid] = bi;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    if (pos_ptr) pos_ptr[0] += pos_inc;
+    pw.epoch[2] = e;
+    if (tap.out) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) tap.out[k] = *reinterpret_cast<const volatile int*>(tap.src[k]);
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  pdl_launch_dependents();      // after the position write: the next step reads it early
 }
 
 // ---- SwiGLU on gate|up partials ---------------------------------------------
@@ -436,16 +543,14 @@ struct ArgScratch {
   int* idx;
 };
 
-__device__ __forceinline__ void arg_better(float& bv, int& bi, float v, int i) {
-  if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
-}
 
 __global__ void __launch_bounds__(256)
 k_logits_argmax(const float* __restrict__ P, PlanView pv, bf16* __restrict__ logits,
                 float* __restrict__ out_val, int32_t* __restrict__ out_idx,
                 int64_t* __restrict__ tokens, int32_t* __restrict__ pos_ptr, int pos_inc,
                 unsigned int* __restrict__ tickets, float* __restrict__ bval,
-                int* __restrict__ bidx, int vocab, int vocab_offset, unsigned long long* tl) {
+                int* __restrict__ bidx, int vocab, int vocab_offset, StatusTap tap,
+                unsigned long long* tl) {
   __shared__ float sv[8];
   __shared__ int si[8];
   __shared__ bool is_last;
@@ -543,6 +648,10 @@ k_logits_argmax(const float* __restrict__ P, PlanView pv, bf16* __restrict__ log
     out_idx[row] = bi + vocab_offset;
     if (tokens) tokens[row] = (int64_t)(bi + vocab_offset);
     if (pos_ptr && row == 0) pos_ptr[0] += pos_inc;
+    if (tap.out && row == 0) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) tap.out[k] = *reinterpret_cast<const volatile int*>(tap.src[k]);
+    }
     tickets[row] = 0;  // ready for the next launch (graph replay)
     __threadfence();
   }
@@ -553,7 +662,7 @@ k_logits_argmax(const float* __restrict__ P, PlanView pv, bf16* __restrict__ log
 
 __global__ void k_argmax_merge(const float* __restrict__ val, const int32_t* __restrict__ idx,
                                int shards, int rows, int64_t* __restrict__ tokens,
-                               int32_t* __restrict__ pos_ptr, int pos_inc) {
+                               int32_t* __restrict__ pos_ptr, int pos_inc, StatusTap tap) {
   pdl_wait();
   int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row < rows) {
@@ -563,6 +672,10 @@ __global__ void k_argmax_merge(const float* __restrict__ val, const int32_t* __r
     if (bi == 0x7fffffff) bi = 0;
     tokens[row] = bi;
     if (row == 0 && pos_ptr) pos_ptr[0] += pos_inc;
+    if (row == 0 && tap.out) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) tap.out[k] = *reinterpret_cast<const volatile int*>(tap.src[k]);
+    }
   }
   __threadfence();
   pdl_launch_dependents();      // after the position write: see k_logits_argmax
@@ -575,6 +688,7 @@ __global__ void k_argmax_merge(const float* __restrict__ val, const int32_t* __r
 extern "C" int q_rmsnorm(const void* d_x, const void* d_gain, void* d_out, int rows, int cols,
                          float eps, void* stream) {
   Q_CHECK_ARG(d_x && d_gain && d_out && rows >= 1 && cols >= 1, "q_rmsnorm: bad argument");
+  Q_CHECK_ALIGN(d_x, 2, "q_rmsnorm"); Q_CHECK_ALIGN(d_gain, 2, "q_rmsnorm"); Q_CHECK_ALIGN(d_out, 2, "q_rmsnorm");
   Q_CHECK_CUDA(q_launch(k_rmsnorm, dim3(rows), dim3(256), 0, S(stream), (const bf16*)d_x,
                         (const bf16*)d_gain, (bf16*)d_out, cols, eps));
   return Q_OK;
@@ -586,9 +700,12 @@ extern "C" int q_embed_rmsnorm(const int64_t* d_tokens, const void* d_embed, con
   Q_CHECK_ARG(d_tokens && d_embed && d_gain && d_x && d_normed && rows >= 1 && cols >= 32 &&
                   cols % 32 == 0 && vocab >= 1,
               "q_embed_rmsnorm: bad argument (cols must be a multiple of 32)");
+  Q_CHECK_ALIGN(d_tokens, 8, "q_embed_rmsnorm"); Q_CHECK_ALIGN(d_embed, 16, "q_embed_rmsnorm");
+  Q_CHECK_ALIGN(d_x, 16, "q_embed_rmsnorm"); Q_CHECK_ALIGN(d_normed, 2, "q_embed_rmsnorm");
+  Q_CHECK_ALIGN(d_gain, 2, "q_embed_rmsnorm");
   Q_CHECK_CUDA(q_launch(k_embed_rmsnorm, dim3(rows), dim3(256), 0, S(stream), d_tokens,
                         (const bf16*)d_embed, (const bf16*)d_gain, (bf16*)d_x, (bf16*)d_normed, cols,
-                        vocab, eps, q_tl_next()));
+                        vocab, eps, q_tl_next(Q_TL_EMBED)));
   return Q_OK;
 }
 
@@ -607,65 +724,106 @@ extern "C" int q_add_rmsnorm(const void* d_x_in, const float* d_branch, const q_
   Q_CHECK_ARG(d_x_in && d_branch && d_gain && d_total_out && d_normed_out, "q_add_rmsnorm: null pointer");
   Q_CHECK_ARG(rows >= 1 && cols >= 4 && cols % 4 == 0 && cols <= 1024 * ADD_VB,
               "q_add_rmsnorm: cols %d must be a multiple of 4 in 4..%d", cols, 1024 * ADD_VB);
+  Q_CHECK_ALIGN(d_branch, 16, "q_add_rmsnorm"); Q_CHECK_ALIGN(d_x_in, 8, "q_add_rmsnorm");
+  Q_CHECK_ALIGN(d_gain, 8, "q_add_rmsnorm"); Q_CHECK_ALIGN(d_total_out, 8, "q_add_rmsnorm");
+  Q_CHECK_ALIGN(d_normed_out, 8, "q_add_rmsnorm");
   int rc = check_plan(plan, rows, cols, "q_add_rmsnorm");
   if (rc) return rc;
   auto kern = cols <= 1024 ? k_add_rmsnorm<1> : cols <= 3072 ? k_add_rmsnorm<3> : k_add_rmsnorm<ADD_VB>;
   Q_CHECK_CUDA(q_launch(kern, dim3(rows), dim3(256), 0, S(stream), (const bf16*)d_x_in,
                         d_branch, plan_view(plan), (const bf16*)d_gain, (bf16*)d_total_out,
-                        (bf16*)d_normed_out, cols, eps, q_tl_next()));
+                        (bf16*)d_normed_out, cols, eps, q_tl_next(Q_TL_ADD_NORM)));
   return Q_OK;
 }
 
+
+static int peer_view(const q_peers_t* peers, PeerView* out, const char* who) {
+  Q_CHECK_ARG(peers->world >= 2 && peers->world <= Q_MAX_PEERS && peers->rank >= 0 &&
+                  peers->rank < peers->world && peers->epoch,
+              "%s: bad rank/world or no counter words", who);
+  out->rank = peers->rank;
+  out->world = peers->world;
+  out->epoch = peers->epoch;
+  for (int r = 0; r < Q_MAX_PEERS; ++r) {
+    out->partials[r] = r < peers->world ? peers->partials[r] : nullptr;
+    out->flags[r] = r < peers->world ? peers->flags[r] : nullptr;
+    Q_CHECK_ARG(r >= peers->world || (out->partials[r] && out->flags[r]), "%s: rank %d unmapped", who, r);
+    Q_CHECK_ARG(((uintptr_t)out->partials[r] & 15) == 0 && ((uintptr_t)out->flags[r] & 15) == 0,
+                "%s: peer buffers must be 16-byte aligned", who);
+  }
+  return Q_OK;
+}
 
 extern "C" int q_add_rmsnorm_peers(const void* d_x_in, const q_peers_t* peers, const float* d_own_branch,
                                    const q_gemm_plan_t* plan, const void* d_gain, void* d_total_out,
                                    void* d_normed_out, int rows, int cols, float eps, void* stream) {
   Q_CHECK_ARG(d_x_in && peers && d_own_branch && d_gain && d_total_out && d_normed_out,
               "q_add_rmsnorm_peers: null pointer");
-  Q_CHECK_ARG(peers->world >= 2 && peers->world <= Q_MAX_PEERS && peers->rank >= 0 &&
-                  peers->rank < peers->world && peers->epoch,
-              "q_add_rmsnorm_peers: bad rank/world or no epoch word");
-  Q_CHECK_ARG(rows >= 1 && rows <= 8 && cols >= 4 && cols % 4 == 0 && cols <= 3072,
-              "q_add_rmsnorm_peers: needs 1..8 rows and cols a multiple of 4 up to 3072");
+  Q_CHECK_ARG(rows >= 1 && rows <= Q_MAX_ROWS && cols >= 4 && cols % 4 == 0 && cols <= 3072,
+              "q_add_rmsnorm_peers: needs 1..%d rows and cols a multiple of 4 up to 3072", Q_MAX_ROWS);
+  Q_CHECK_ARG((((uintptr_t)d_x_in | (uintptr_t)d_gain | (uintptr_t)d_total_out | (uintptr_t)d_normed_out) & 7) == 0,
+              "q_add_rmsnorm_peers: bf16 operands must be 8-byte aligned");
   int rc = check_plan(plan, rows, cols, "q_add_rmsnorm_peers");
   if (rc) return rc;
   PeerView pw;
-  pw.rank = peers->rank;
-  pw.world = peers->world;
-  pw.epoch = peers->epoch;
-  for (int r = 0; r < Q_MAX_PEERS; ++r) {
-    pw.partials[r] = r < peers->world ? peers->partials[r] : nullptr;
-    pw.flags[r] = r < peers->world ? peers->flags[r] : nullptr;
-    Q_CHECK_ARG(r >= peers->world || (pw.partials[r] && pw.flags[r]), "q_add_rmsnorm_peers: rank %d unmapped", r);
-  }
+  rc = peer_view(peers, &pw, "q_add_rmsnorm_peers");
+  if (rc) return rc;
   const long long off = d_own_branch - peers->partials[peers->rank];
   Q_CHECK_ARG(off >= 0 && off % 4 == 0, "q_add_rmsnorm_peers: the branch is not inside this rank's peer buffer");
-  Q_CHECK_CUDA(q_launch(k_add_rmsnorm_peers, dim3(1), dim3(256), 0, S(stream), (const bf16*)d_x_in, pw, off,
+  Q_CHECK_CUDA(q_launch(k_add_rmsnorm_peers, dim3(rows), dim3(256), 0, S(stream), (const bf16*)d_x_in, pw, off,
                         plan_view(plan), (const bf16*)d_gain, (bf16*)d_total_out, (bf16*)d_normed_out, rows,
-                        cols, eps, q_tl_next()));
+                        cols, eps, g_peer_wait_iters, q_tl_next(Q_TL_PEER_ADD_NORM)));
   return Q_OK;
 }
 
-int q_peer_status_read(int32_t* out) {
-  return cudaMemcpyFromSymbol(out, g_peer_status, sizeof(int)) == cudaSuccess ? 0 : -1;
+extern "C" int64_t q_peer_flag_bytes(void) {
+  // 512 bytes of arrival words, then [2 parities][Q_MAX_PEERS shards][Q_MAX_ROWS] pairs of 8 bytes
+  return 512 + 2ll * Q_MAX_PEERS * Q_MAX_ROWS * 8;
 }
+
+int q_argmax_merge_peers_tap(const float* d_val, const int32_t* d_idx, const q_peers_t* peers, int rows,
+                             int64_t* d_tokens, int32_t* d_pos, int pos_inc, StatusTap tap, void* stream) {
+  Q_CHECK_ARG(d_val && d_idx && peers && d_tokens && rows >= 1 && rows <= Q_MAX_ROWS,
+              "q_argmax_merge_peers: bad argument");
+  PeerView pw;
+  int rc = peer_view(peers, &pw, "q_argmax_merge_peers");
+  if (rc) return rc;
+  Q_CHECK_CUDA(q_launch(k_argmax_merge_peers, dim3(1), dim3(64), 0, S(stream), d_val, d_idx, pw, rows, d_tokens,
+                        d_pos, pos_inc, g_peer_wait_iters, tap));
+  return Q_OK;
+}
+
+extern "C" int q_argmax_merge_peers(const float* d_val, const int32_t* d_idx, const q_peers_t* peers, int rows,
+                                    int64_t* d_tokens, int32_t* d_pos, int pos_inc, void* stream) {
+  StatusTap none = {};
+  return q_argmax_merge_peers_tap(d_val, d_idx, peers, rows, d_tokens, d_pos, pos_inc, none, stream);
+}
+
+Q_DEFINE_STATUS_ADDR(q_peer_status_addr, g_peer_status)
 
 int q_swiglu_layout(const float* d_branch, const q_gemm_plan_t* plan, void* d_out, int rows, int inter,
                     int interleaved, void* stream) {
   Q_CHECK_ARG(d_branch && d_out && rows >= 1 && inter >= 4 && inter % 4 == 0,
               "q_swiglu: bad argument (inter must be a multiple of 4)");
+  Q_CHECK_ARG(((uintptr_t)d_branch & 15) == 0 && ((uintptr_t)d_out & 7) == 0,
+              "q_swiglu: the partials must be 16-byte and the output 8-byte aligned");
   Q_CHECK_ARG(!interleaved || inter % 8 == 0, "q_swiglu: the interleaved layout needs inter %% 8 == 0");
   int rc = check_plan(plan, rows, 2 * inter, "q_swiglu");
   if (rc) return rc;
   long long total = (long long)rows * (inter / 4);
   Q_CHECK_CUDA(q_launch(k_swiglu, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, S(stream),
-                        d_branch, plan_view(plan), (bf16*)d_out, rows, inter, interleaved, q_tl_next()));
+                        d_branch, plan_view(plan), (bf16*)d_out, rows, inter, interleaved, q_tl_next(Q_TL_SWIGLU)));
   return Q_OK;
 }
 
 extern "C" int q_swiglu(const float* d_branch, const q_gemm_plan_t* plan, void* d_out, int rows,
                         int inter, void* stream) {
   return q_swiglu_layout(d_branch, plan, d_out, rows, inter, 0, stream);
+}
+
+extern "C" int q_swiglu_interleaved(const float* d_branch, const q_gemm_plan_t* plan, void* d_out, int rows,
+                                    int inter, void* stream) {
+  return q_swiglu_layout(d_branch, plan, d_out, rows, inter, 1, stream);
 }
 
 extern "C" int q_qkv_norm_rope_cache(const float* d_branch, const q_gemm_plan_t* plan,
@@ -678,9 +836,13 @@ extern "C" int q_qkv_norm_rope_cache(const float* d_branch, const q_gemm_plan_t*
   Q_CHECK_ARG(kv->d_kpool && kv->d_vpool && kv->d_block_table && kv->pages_per_seq >= 1 &&
                   kv->n_kv_heads >= 1,
               "q_qkv_norm_rope_cache: incomplete KV layout");
-  Q_CHECK_ARG(batch >= 1 && T >= 1 && n_q_heads >= 1 && batch * T <= Q_MAX_ROWS,
+  Q_CHECK_ARG(batch >= 1 && T >= 1 && n_q_heads >= 1 && (long long)batch * T <= (1 << 20),
               "q_qkv_norm_rope_cache: bad batch/T");
   const int rows = batch * T, nkv = kv->n_kv_heads;
+  Q_CHECK_ALIGN(d_branch, 16, "q_qkv_norm_rope_cache"); Q_CHECK_ALIGN(d_q_gain, 8, "q_qkv_norm_rope_cache");
+  Q_CHECK_ALIGN(d_k_gain, 8, "q_qkv_norm_rope_cache"); Q_CHECK_ALIGN(d_cos, 8, "q_qkv_norm_rope_cache");
+  Q_CHECK_ALIGN(d_sin, 8, "q_qkv_norm_rope_cache"); Q_CHECK_ALIGN(d_q_out, 8, "q_qkv_norm_rope_cache");
+  Q_CHECK_ALIGN(kv->d_kpool, 16, "q_qkv_norm_rope_cache"); Q_CHECK_ALIGN(kv->d_vpool, 16, "q_qkv_norm_rope_cache");
   int rc = check_plan(plan, rows, (n_q_heads + 2 * nkv) * 128, "q_qkv_norm_rope_cache");
   if (rc) return rc;
   const int items = rows * (n_q_heads + 2 * nkv);
@@ -720,8 +882,19 @@ extern "C" int q_logits_argmax(const float* d_branch, const q_gemm_plan_t* plan,
                                float* d_val, int32_t* d_idx, int64_t* d_tokens, int32_t* d_pos,
                                int pos_inc, void* d_block_scratch, int rows, int vocab,
                                int vocab_offset, void* stream) {
+  StatusTap none = {};
+  return q_logits_argmax_tap(d_branch, plan, d_logits, d_val, d_idx, d_tokens, d_pos, pos_inc,
+                             d_block_scratch, rows, vocab, vocab_offset, none, stream);
+}
+
+int q_logits_argmax_tap(const float* d_branch, const q_gemm_plan_t* plan, void* d_logits, float* d_val,
+                        int32_t* d_idx, int64_t* d_tokens, int32_t* d_pos, int pos_inc,
+                        void* d_block_scratch, int rows, int vocab, int vocab_offset, StatusTap tap,
+                        void* stream) {
   Q_CHECK_ARG(d_branch && d_val && d_idx && d_block_scratch, "q_logits_argmax: null pointer");
   Q_CHECK_ARG(rows >= 1 && rows <= Q_MAX_ROWS && vocab >= 1, "q_logits_argmax: bad sizes");
+  Q_CHECK_ALIGN(d_branch, 16, "q_logits_argmax"); Q_CHECK_ALIGN(d_logits, 8, "q_logits_argmax");
+  Q_CHECK_ALIGN(d_block_scratch, 4, "q_logits_argmax"); Q_CHECK_ALIGN(d_tokens, 8, "q_logits_argmax");
   int rc = check_plan(plan, rows, vocab, "q_logits_argmax");
   if (rc) return rc;
   const int nblk = arg_blocks(vocab);
@@ -732,14 +905,20 @@ extern "C" int q_logits_argmax(const float* d_branch, const q_gemm_plan_t* plan,
   int* bidx = (int*)(base + tick + (int64_t)rows * nblk * 4);
   Q_CHECK_CUDA(q_launch(k_logits_argmax, dim3(nblk, rows), dim3(256), 0, S(stream), d_branch,
                         plan_view(plan), (bf16*)d_logits, d_val, d_idx, d_tokens, d_pos, pos_inc,
-                        tickets, bval, bidx, vocab, vocab_offset, q_tl_next()));
+                        tickets, bval, bidx, vocab, vocab_offset, tap, q_tl_next(Q_TL_ARGMAX)));
+  return Q_OK;
+}
+
+int q_argmax_merge_tap(const float* d_val, const int32_t* d_idx, int shards, int rows, int64_t* d_tokens,
+                       int32_t* d_pos, int pos_inc, StatusTap tap, void* stream) {
+  Q_CHECK_ARG(d_val && d_idx && d_tokens && shards >= 1 && rows >= 1, "q_argmax_merge: bad argument");
+  Q_CHECK_CUDA(q_launch(k_argmax_merge, dim3((rows + 63) / 64), dim3(64), 0, S(stream), d_val, d_idx,
+                        shards, rows, d_tokens, d_pos, pos_inc, tap));
   return Q_OK;
 }
 
 extern "C" int q_argmax_merge(const float* d_val, const int32_t* d_idx, int shards, int rows,
                               int64_t* d_tokens, int32_t* d_pos, int pos_inc, void* stream) {
-  Q_CHECK_ARG(d_val && d_idx && d_tokens && shards >= 1 && rows >= 1, "q_argmax_merge: bad argument");
-  Q_CHECK_CUDA(q_launch(k_argmax_merge, dim3((rows + 63) / 64), dim3(64), 0, S(stream), d_val, d_idx,
-                        shards, rows, d_tokens, d_pos, pos_inc));
-  return Q_OK;
+  StatusTap none = {};
+  return q_argmax_merge_tap(d_val, d_idx, shards, rows, d_tokens, d_pos, pos_inc, none, stream);
 }

@@ -29,11 +29,12 @@
 // receives one partial per CTA that touches it: at most 2 slots for all Qwen3-4B
 // shapes.
 //
-// Overlap with the producer of X. Before griddepcontrol.wait every warp asks for
-// an L2 prefetch of its run (cp.async.bulk.prefetch.L2) and fills its ring:
-// weights do not depend on the previous kernel, so HBM keeps streaming while the
-// small kernel that produces X is still running. Two GEMM CTAs fit on an SM, which
-// lets the next GEMM start while the current one drains.
+// Overlap with the producer of X. Before griddepcontrol.wait every warp fills its ring:
+// weights do not depend on the previous kernel, so HBM keeps streaming while the kernel
+// that produces X is still running (with the add+norm prologue only the first stage is
+// requested that early, see below). One CTA per SM: a second co-resident CTA measured
+// slower, its copies queue in front of the running kernel's. An L2 prefetch of the run
+// (cp.async.bulk.prefetch.L2) is an option that is off by default for the same reason.
 //
 // Every mbarrier wait is bounded; a wait that runs out sets the status word of
 // this file (read by q_device_status) and the warp stops consuming.
@@ -497,7 +498,16 @@ __global__ void k_reduce_partials(const float* __restrict__ P, float* __restrict
     const int extra = plan_count(pv, n) - 1;
     float4 s = a;
     if (extra > 0) { s.x += b.x; s.y += b.y; s.z += b.z; s.w += b.w; }
-    for (int k = 2; k <= extra; ++k) {
+    // slots 2..9 are requested together (the tcgen05 plan splits long-K projections ~10 ways)
+    float4 t8[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      t8[k] = (k + 2 <= extra) ? *reinterpret_cast<const float4*>(P + i + (long long)(k + 2) * pv.slot_stride)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k + 2 <= extra) { s.x += t8[k].x; s.y += t8[k].y; s.z += t8[k].z; s.w += t8[k].w; }
+    for (int k = 10; k <= extra; ++k) {
       const float4 t = *reinterpret_cast<const float4*>(P + i + (long long)k * pv.slot_stride);
       s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
     }
@@ -542,36 +552,28 @@ int debug_flags_of_this_launch() {
 template <int NT, bool ACT, int SU = STAGE_UNITS>
 cudaError_t launch_gemm(const q_gemm_plan_t& p, const bf16* X, const unsigned char* W, float* P,
                         cudaStream_t s) {
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<NT, false, ACT, SU>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_smem<NT, SU>());
-    if (e != cudaSuccess) return e;
-    attr_done = true;
-  }
+  static size_t done[64] = {0};          // the attribute is a per-device setting
+  cudaError_t e0 = q_ensure_smem(k_gemm_streamk<NT, false, ACT, SU>, (size_t)gemm_smem<NT, SU>(), done);
+  if (e0 != cudaSuccess) return e0;
   NormPrologue none = {};
   const int grid = ACT ? (p.groups < p.grid ? p.groups : p.grid) : p.grid;
   return q_launch(k_gemm_streamk<NT, false, ACT, SU>, dim3(grid), dim3(p.block), (size_t)gemm_smem<NT, SU>(), s, X,
                   W, P, p.M, p.N, p.K, p.chunks_per_group, p.groups * p.chunks_per_group,
                   p.units_per_worker, g_gemm_prefetch_kb * 1024 / WARPS, debug_flags_of_this_launch(), none,
-                  q_tl_next());
+                  q_tl_next(Q_TL_GEMM));
 }
 
 template <bool ACT>
 cudaError_t launch_gemm_norm(const q_gemm_plan_t& p, const unsigned char* W, float* P,
                              const NormPrologue& pro, cudaStream_t s) {
   const size_t smem = (size_t)gemm_smem<1>() + (size_t)p.M * (p.K + 32) * 2 + 32 * 4;
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(k_gemm_streamk<1, true, ACT, STAGE_UNITS>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    configured = smem;
-  }
+  static size_t done[64] = {0};
+  cudaError_t e0 = q_ensure_smem(k_gemm_streamk<1, true, ACT, STAGE_UNITS>, smem, done);
+  if (e0 != cudaSuccess) return e0;
   const int grid = ACT ? (p.groups < p.grid ? p.groups : p.grid) : p.grid;
   return q_launch(k_gemm_streamk<1, true, ACT, STAGE_UNITS>, dim3(grid), dim3(p.block), smem, s, (const bf16*)nullptr, W,
                   P, p.M, p.N, p.K, p.chunks_per_group, p.groups * p.chunks_per_group,
-                  p.units_per_worker, 0, debug_flags_of_this_launch(), pro, q_tl_next());
+                  p.units_per_worker, 0, debug_flags_of_this_launch(), pro, q_tl_next(Q_TL_GEMM));
 }
 
 }  // namespace
@@ -583,9 +585,7 @@ extern "C" int q_debug_gemm_trace(unsigned long long* out, int n_ctas) {
   return Q_OK;
 }
 
-int q_gemm_status_read(int32_t out[4]) {
-  return cudaMemcpyFromSymbol(out, g_gemm_status, sizeof(int) * 4) == cudaSuccess ? 0 : -1;
-}
+Q_DEFINE_STATUS_ADDR(q_gemm_status_addr, g_gemm_status)
 
 extern "C" int q_gemm_plan(int M, int N, int K, q_gemm_plan_t* plan) {
   int sms = q_sm_count();
@@ -620,6 +620,7 @@ int q_gemm_plan_workers(int M, int N, int K, int max_workers, q_gemm_plan_t* pla
   plan->slots = (int)slots;
   plan->grid = (int)workers;
   plan->block = THREADS;
+  plan->group_rows = 16;
   return Q_OK;
 }
 
@@ -716,6 +717,7 @@ extern "C" int64_t q_static_scratch_floats(void) { return Q_STATIC_SCRATCH_FLOAT
 extern "C" int q_linear_f32_static(const void* d_x, const void* d_w_tiled, float* d_out, int M, int N,
                                    int K, void* stream) {
   Q_CHECK_ARG(d_x && d_w_tiled && d_out, "q_linear_f32_static: null pointer");
+  Q_CHECK_ALIGN(d_out, 16, "q_linear_f32_static");
   q_gemm_plan_t p;
   int rc = q_gemm_plan(M, N, K, &p);
   if (rc) return rc;
@@ -740,6 +742,9 @@ extern "C" int q_gemm_splitk_addnorm(const void* d_resid_in, const float* d_prev
   Q_CHECK_ARG(d_resid_in && d_prev && d_gain && d_resid_out && d_w_tiled && d_partials,
               "q_gemm_splitk_addnorm: null pointer");
   Q_CHECK_ARG(d_resid_in != d_resid_out, "q_gemm_splitk_addnorm: the residual cannot be updated in place");
+  Q_CHECK_ALIGN(d_resid_in, 8, "q_gemm_splitk_addnorm"); Q_CHECK_ALIGN(d_prev, 16, "q_gemm_splitk_addnorm");
+  Q_CHECK_ALIGN(d_gain, 8, "q_gemm_splitk_addnorm"); Q_CHECK_ALIGN(d_resid_out, 8, "q_gemm_splitk_addnorm");
+  Q_CHECK_ALIGN(d_w_tiled, 16, "q_gemm_splitk_addnorm"); Q_CHECK_ALIGN(d_partials, 4, "q_gemm_splitk_addnorm");
   Q_CHECK_ARG(M >= 1 && M <= 8 && K % 4 == 0 && K <= 3072,
               "q_gemm_splitk_addnorm: needs 1..8 rows and K a multiple of 4 up to 3072 (M=%d K=%d)", M, K);
   if (prev_plan)
@@ -795,6 +800,9 @@ extern "C" int q_gemm_swiglu_addnorm(const void* d_resid_in, const float* d_prev
   Q_CHECK_ARG(d_resid_in && d_prev && d_gain && d_resid_out && d_w_tiled && d_act,
               "q_gemm_swiglu_addnorm: null pointer");
   Q_CHECK_ARG(d_resid_in != d_resid_out, "q_gemm_swiglu_addnorm: the residual cannot be updated in place");
+  Q_CHECK_ALIGN(d_resid_in, 8, "q_gemm_swiglu_addnorm"); Q_CHECK_ALIGN(d_prev, 16, "q_gemm_swiglu_addnorm");
+  Q_CHECK_ALIGN(d_gain, 8, "q_gemm_swiglu_addnorm"); Q_CHECK_ALIGN(d_resid_out, 8, "q_gemm_swiglu_addnorm");
+  Q_CHECK_ALIGN(d_w_tiled, 16, "q_gemm_swiglu_addnorm"); Q_CHECK_ALIGN(d_act, 2, "q_gemm_swiglu_addnorm");
   Q_CHECK_ARG(M >= 1 && M <= 8 && K % 4 == 0 && K <= 3072,
               "q_gemm_swiglu_addnorm: needs 1..8 rows and K a multiple of 4 up to 3072 (M=%d K=%d)", M, K);
   int rc = swiglu_shape_ok(M, inter, K, "q_gemm_swiglu_addnorm");
@@ -820,6 +828,7 @@ extern "C" int q_gemm_swiglu_addnorm(const void* d_resid_in, const float* d_prev
 extern "C" int q_reduce_partials(const float* d_partials, const q_gemm_plan_t* plan,
                                  float* d_out, void* stream) {
   Q_CHECK_ARG(d_partials && plan && d_out, "q_reduce_partials: null pointer");
+  Q_CHECK_ALIGN(d_partials, 16, "q_reduce_partials"); Q_CHECK_ALIGN(d_out, 16, "q_reduce_partials");
   long long total = (long long)plan->M * plan->N;
   if ((plan->N & 3) == 0) total /= 4;
   int block = 256;

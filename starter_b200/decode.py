@@ -11,13 +11,20 @@ and runs the same step; the fp32 partial sums after O-proj and down-proj are
 summed over the ranks before the single bf16 rounding of a Linear output - by
 default inside the add+norm kernel, which reads every rank's partials from
 symmetric (peer-mapped) memory, else by an NCCL all-reduce - and the per-rank
-(max, index) pairs of the vocabulary-sharded lm_head are all-gathered.
+(max, index) pairs of the vocabulary-sharded lm_head are exchanged through peer
+memory as well (else all-gathered).
+
+Every step's last kernel copies the library's device status words next to the
+tokens; emit() reads them from pinned host memory with the tokens and raises
+when a bounded wait inside a kernel ran out, so such a step never hands wrong
+tokens to the caller.
 """
 from __future__ import annotations
 
 import ctypes as C
 import os
 import sys
+import weakref
 
 import torch
 import torch.nn.functional as F
@@ -36,13 +43,26 @@ def _rms(x, w, eps):
     return (f * torch.rsqrt(f.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
 
 
+TC_MIN_ROWS = 9     # rows from which the projections run on the tcgen05 kernel
+
+
 class DecodeState:
     def __init__(self, weights: PackedWeights, batch: int, prompt_length: int, max_new_tokens: int,
-                 group=None, keep_logits: bool = False):
-        if batch < 1 or prompt_length < 1 or max_new_tokens < 1:
+                 group=None, keep_logits: bool = False, tp_path: str = "auto", q_tokens: int = 1,
+                 share: "DecodeState | None" = None):
+        """tp_path: "auto" (peer memory if every rank can map the others, else NCCL), "peers"
+        (the same, but an error if it cannot be used) or "nccl". q_tokens > 1 makes this the
+        state of the multi-token verification step (verify()); `share` = a state whose KV pages,
+        block table, rotary tables and position this one uses instead of allocating its own."""
+        if batch < 1 or prompt_length < 1 or max_new_tokens < 1 or q_tokens < 1:
             raise ValueError("positive batch, prompt length and token count required")
-        if batch > _lib.MAX_ROWS:
-            raise ValueError(f"batch {batch} exceeds {_lib.MAX_ROWS} rows")
+        rows = batch * q_tokens
+        if rows > _lib.MAX_ROWS:
+            raise ValueError(f"batch {batch} x {q_tokens} tokens exceeds {_lib.MAX_ROWS} rows")
+        if tp_path not in ("auto", "peers", "nccl"):
+            raise ValueError("tp_path must be 'auto', 'peers' or 'nccl'")
+        if q_tokens > 1 and weights.tp_size > 1:
+            raise ValueError("the multi-token verification step runs on one GPU")
         self.w = weights
         cfg = weights.cfg
         self.cfg = cfg
@@ -50,27 +70,42 @@ class DecodeState:
         self.tp = weights.tp_size
         self.shape = (batch, prompt_length, max_new_tokens)
         self.batch = batch
-        self.capacity = prompt_length + max_new_tokens
+        self.q_tokens = q_tokens
+        self.rows = rows
+        self.capacity = prompt_length + max_new_tokens + (q_tokens - 1 if share is None else 0)
         if self.capacity > cfg.max_position:
             raise ValueError("prompt + new tokens exceed max_position_embeddings")
         dev = weights.device
         self.device = dev
         nq, nkv, inter = weights.local_q_heads, weights.local_kv_heads, weights.local_inter
-        self.pages_per_seq = (self.capacity + PAGE_TOKENS - 1) // PAGE_TOKENS
-        n_pages = batch * self.pages_per_seq
-        self.block_table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(batch, -1).contiguous()
-        pool = (n_pages, nkv, PAGE_TOKENS, HEAD_DIM)
-        self.kpools = [torch.zeros(pool, dtype=torch.bfloat16, device=dev) for _ in range(cfg.n_layers)]
-        self.vpools = [torch.zeros(pool, dtype=torch.bfloat16, device=dev) for _ in range(cfg.n_layers)]
-        self.cos, self.sin = rotary_tables(cfg, self.capacity, dev)
-        self.tokens = torch.zeros(batch, dtype=torch.int64, device=dev)
-        self.position = torch.zeros(1, dtype=torch.int32, device=dev)
+        if share is not None:
+            if share.batch != batch or share.capacity < self.capacity or share.w is not weights:
+                raise ValueError("the shared state has another batch, weights or a smaller capacity")
+            self.capacity = share.capacity
+            self.pages_per_seq, self.block_table = share.pages_per_seq, share.block_table
+            self.kpools, self.vpools = share.kpools, share.vpools
+            self.cos, self.sin, self.position = share.cos, share.sin, share.position
+        else:
+            self.pages_per_seq = (self.capacity + PAGE_TOKENS - 1) // PAGE_TOKENS
+            n_pages = batch * self.pages_per_seq
+            self.block_table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(batch, -1).contiguous()
+            pool = (n_pages, nkv, PAGE_TOKENS, HEAD_DIM)
+            self.kpools = [torch.zeros(pool, dtype=torch.bfloat16, device=dev) for _ in range(cfg.n_layers)]
+            self.vpools = [torch.zeros(pool, dtype=torch.bfloat16, device=dev) for _ in range(cfg.n_layers)]
+            self.cos, self.sin = rotary_tables(cfg, self.capacity, dev)
+            self.position = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.tokens = torch.zeros(rows, dtype=torch.int64, device=dev)
         self.host = torch.empty(batch, dtype=torch.int64).pin_memory()
+        self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.host_status = torch.zeros(4, dtype=torch.int32).pin_memory()
         self.ready = torch.cuda.Event()
         self.graph = None
+        use_tc = rows >= TC_MIN_ROWS
+        if use_tc:
+            weights.ensure_tc()           # second tiling of the weights, built once per engine
 
         ccfg = _lib.Config(cfg.hidden, inter, cfg.n_layers, nq, nkv, weights.local_vocab,
-                           weights.vocab_offset, cfg.vocab, self.tp, batch, cfg.rms_eps,
+                           weights.vocab_offset, cfg.vocab, self.tp, rows, cfg.rms_eps,
                            float(HEAD_DIM) ** -0.5)
         handle = C.c_void_p()
         check(lib.q_create(C.byref(ccfg), C.byref(handle)))
@@ -79,35 +114,33 @@ class DecodeState:
             lw = _lib.LayerWeights(lt.wqkv.data_ptr(), lt.wo.data_ptr(), lt.wgu.data_ptr(),
                                    lt.wdown.data_ptr(), lt.ln_in.data_ptr(), lt.ln_post.data_ptr(),
                                    lt.q_gain.data_ptr(), lt.k_gain.data_ptr(),
-                                   self.kpools[i].data_ptr(), self.vpools[i].data_ptr())
+                                   self.kpools[i].data_ptr(), self.vpools[i].data_ptr(),
+                                   *((lt.wqkv.tc().data_ptr(), lt.wo.tc().data_ptr(), lt.wgu.tc().data_ptr(),
+                                      lt.wdown.tc().data_ptr()) if use_tc else (0, 0, 0, 0)))
             check(lib.q_bind_layer(handle, i, C.byref(lw)))
 
         bf = dict(dtype=torch.bfloat16, device=dev)
         f32 = dict(dtype=torch.float32, device=dev)
-        self.x = torch.zeros((batch, cfg.hidden), **bf)
-        self.normed = torch.zeros((batch, cfg.hidden), **bf)
-        self.q = torch.zeros((batch, nq * HEAD_DIM), **bf)
-        self.attended = torch.zeros((batch, nq * HEAD_DIM), **bf)
-        self.act = torch.zeros((batch, inter), **bf)
-        n_part = lib.q_engine_partial_floats(handle, batch)
+        self.x = torch.zeros((rows, cfg.hidden), **bf)
+        self.normed = torch.zeros((rows, cfg.hidden), **bf)
+        self.q = torch.zeros((rows, nq * HEAD_DIM), **bf)
+        self.attended = torch.zeros((rows, nq * HEAD_DIM), **bf)
+        self.act = torch.zeros((rows, inter), **bf)
+        n_part = lib.q_engine_partial_floats(handle, rows)
         if n_part <= 0:
             raise _lib.QDecodeError("could not size the split-K partial buffer")
         self.partials = torch.empty(n_part, **f32)
-        self.reduced = torch.zeros((batch, cfg.hidden), **f32) if self.tp > 1 else None
+        self.reduced = torch.zeros((rows, cfg.hidden), **f32) if self.tp > 1 else None
         self.attn_splits = lib.q_attention_splits(batch, nkv, self.capacity)
         g = nq // nkv
-        self.attn_o = torch.empty((batch * nkv, self.attn_splits, g, HEAD_DIM), **f32)
-        self.attn_ml = torch.empty((batch * nkv, self.attn_splits, g, 2), **f32)
+        self.attn_o = torch.empty((batch * nkv, self.attn_splits, q_tokens * g, HEAD_DIM), **f32)
+        self.attn_ml = torch.empty((batch * nkv, self.attn_splits, q_tokens * g, 2), **f32)
         self.attn_tickets = torch.zeros(batch * nkv, dtype=torch.int32, device=dev)
-        self.logits = torch.zeros((batch, weights.local_vocab), **bf) if keep_logits else None
-        self.arg_val = torch.zeros(batch, **f32)
-        self.arg_idx = torch.zeros(batch, dtype=torch.int32, device=dev)
-        self.arg_scratch = torch.zeros(lib.q_argmax_scratch_bytes(batch, weights.local_vocab),
+        self.logits = torch.zeros((rows, weights.local_vocab), **bf) if keep_logits else None
+        self.arg_val = torch.zeros(rows, **f32)
+        self.arg_idx = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self.arg_scratch = torch.zeros(lib.q_argmax_scratch_bytes(rows, weights.local_vocab),
                                        dtype=torch.uint8, device=dev)
-        self.fused_scratch = None
-        if self.tp == 1 and batch <= 8:
-            self.fused_scratch = torch.zeros(lib.q_fused_scratch_bytes(handle, batch), dtype=torch.uint8,
-                                             device=dev)
         if self.tp > 1:
             self.gather_val = torch.zeros((self.tp, batch), **f32)
             self.gather_idx = torch.zeros((self.tp, batch), dtype=torch.int32, device=dev)
@@ -115,17 +148,22 @@ class DecodeState:
             weights.embed.data_ptr(), weights.lm_head.data_ptr(), weights.ln_final.data_ptr(),
             self.cos.data_ptr(), self.sin.data_ptr(), self.tokens.data_ptr(),
             self.position.data_ptr(), self.block_table.data_ptr(), self.pages_per_seq, batch,
-            self.attn_splits, self.x.data_ptr(), self.normed.data_ptr(), self.q.data_ptr(),
+            self.attn_splits, q_tokens, self.x.data_ptr(), self.normed.data_ptr(), self.q.data_ptr(),
             self.attended.data_ptr(), self.act.data_ptr(), self.partials.data_ptr(),
             0 if self.reduced is None else self.reduced.data_ptr(), self.attn_o.data_ptr(),
             self.attn_ml.data_ptr(), self.attn_tickets.data_ptr(),
             0 if self.logits is None else self.logits.data_ptr(),
             self.arg_val.data_ptr(), self.arg_idx.data_ptr(), self.arg_scratch.data_ptr(),
-            0 if self.fused_scratch is None else self.fused_scratch.data_ptr())
+            weights.lm_head.tc().data_ptr() if use_tc else 0, self.status.data_ptr())
         check(lib.q_bind_state(handle, C.byref(st)))
+        self.uses_tc = use_tc
         self.peers = False
-        if self.tp > 1 and batch <= 8 and cfg.hidden <= 3072 and os.environ.get("QDECODE_TP_PEERS", "1") == "1":
-            self._bind_peers()
+        if self.tp > 1 and tp_path != "nccl":
+            if cfg.hidden <= 3072:
+                self._bind_peers()
+            if tp_path == "peers" and not self.peers:
+                raise _lib.QDecodeError("tensor parallel over peer memory was asked for and is unavailable")
+        self.tp_path = "single" if self.tp == 1 else ("peers" if self.peers else "nccl")
 
     def _bind_peers(self) -> None:
         """Puts the O / down split-K partials of every rank into symmetric memory and hands the
@@ -140,10 +178,10 @@ class DecodeState:
             # plain peer loads only: no NVLink multicast object is bound to these buffers
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             import torch.distributed._symmetric_memory as symm_mem
-            n = lib.q_engine_peer_floats(self.handle, self.batch)
+            n = lib.q_engine_peer_floats(self.handle, self.rows)
             if n <= 0:
                 raise _lib.QDecodeError("could not size the peer partial buffer")
-            buf = symm_mem.empty(n * 4 + 256, dtype=torch.uint8, device=self.device)
+            buf = symm_mem.empty(n * 4 + lib.q_peer_flag_bytes(), dtype=torch.uint8, device=self.device)
             buf.zero_()
             hdl = symm_mem.rendezvous(buf, group.group_name)
             ptrs = list(hdl.buffer_ptrs)
@@ -163,7 +201,7 @@ class DecodeState:
         for r in range(self.tp):
             peers.partials[r] = ptrs[r]
             peers.flags[r] = ptrs[r] + n * 4
-        self.peer_epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.peer_epoch = torch.zeros(4, dtype=torch.int32, device=self.device)
         peers.epoch = self.peer_epoch.data_ptr()
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)              # every rank's arrival words are zero from here on
@@ -182,9 +220,8 @@ class DecodeState:
 
     def _peers_self_test(self, peers, n_floats: int, group) -> bool:
         """One q_add_rmsnorm_peers call on known data before the path is trusted: every rank
-        fills its buffer with (rank+1)/16, so each output must be a whole multiple (the number of
-        split-K slots of its column, at most plan.slots) of the sum of those over the ranks, and no wait may
-        have run out. All ranks agree on the verdict."""
+        fills its buffer with (rank+1)/16, so every output element must equal the sum of those
+        over the ranks, and no wait may have run out. All ranks agree on the verdict."""
         import torch.distributed as dist
         cfg, dev = self.cfg, self.device
         rank, world = peers.rank, peers.world
@@ -194,19 +231,16 @@ class DecodeState:
         view.copy_(own)
         torch.cuda.synchronize(dev)
         dist.barrier(group=group)
-        plan = _lib.plan(self.batch, cfg.hidden, self.w.local_inter)
-        zeros = torch.zeros((self.batch, cfg.hidden), dtype=torch.bfloat16, device=dev)
+        zeros = torch.zeros((self.rows, cfg.hidden), dtype=torch.bfloat16, device=dev)
         ones = torch.ones(cfg.hidden, dtype=torch.bfloat16, device=dev)
         total, normed = torch.empty_like(zeros), torch.empty_like(zeros)
         s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         rc = lib.q_add_rmsnorm_peers(_p(zeros), C.byref(peers), C.c_void_p(view.data_ptr() + half * 4),
-                                     C.byref(plan), _p(ones), _p(total), _p(normed), self.batch, cfg.hidden,
+                                     None, _p(ones), _p(total), _p(normed), self.rows, cfg.hidden,
                                      float(cfg.rms_eps), s)
         torch.cuda.synchronize(dev)
         unit = sum(r + 1 for r in range(world)) / 16.0
-        ratio = total.float() / unit
-        whole = (ratio == ratio.round()) & (ratio >= 1) & (ratio <= plan.slots)
-        good = rc == 0 and bool(whole.all()) and self._device_status()[3] == 0
+        good = rc == 0 and bool((total.float() == unit).all()) and self._device_status()[3] == 0
         verdict = torch.tensor([1 if good else 0], dtype=torch.int32, device=dev)
         dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=group)
         view.zero_()
@@ -316,46 +350,63 @@ class DecodeState:
     def step(self) -> None:
         s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         h = self.handle
+        if self.q_tokens > 1:
+            raise ValueError("this state runs verify(), not step()")
         if self.tp == 1:
             check(lib.q_decode_step(h, s))
             return
         if self.peers:
-            check(lib.q_decode_step_peers(h, s))      # cross-rank sums read from peer memory
-        else:
-            check(lib.q_step_begin(h, s))
-            for layer in range(self.cfg.n_layers):
-                check(lib.q_step_attn(h, layer, s))
-                torch.distributed.all_reduce(self.reduced, group=self.group)
-                check(lib.q_step_post_attn(h, layer, s))
-                torch.distributed.all_reduce(self.reduced, group=self.group)
-                check(lib.q_step_post_mlp(h, layer, s))
-            check(lib.q_step_head(h, s))
+            check(lib.q_decode_step_peers(h, s))      # every cross-rank exchange goes through peer memory
+            return
+        check(lib.q_step_begin(h, s))
+        for layer in range(self.cfg.n_layers):
+            check(lib.q_step_attn(h, layer, s))
+            torch.distributed.all_reduce(self.reduced, group=self.group)
+            check(lib.q_step_post_attn(h, layer, s))
+            torch.distributed.all_reduce(self.reduced, group=self.group)
+            check(lib.q_step_post_mlp(h, layer, s))
+        check(lib.q_step_head(h, s))
         torch.distributed.all_gather_into_tensor(self.gather_val, self.arg_val, group=self.group)
         torch.distributed.all_gather_into_tensor(self.gather_idx, self.arg_idx, group=self.group)
-        check(lib.q_argmax_merge(_p(self.gather_val), _p(self.gather_idx), self.tp, self.batch,
-                                 _p(self.tokens), _p(self.position), 1, s))
+        check(lib.q_step_merge(h, _p(self.gather_val), _p(self.gather_idx), s))
+
+    def verify(self, candidates: torch.Tensor) -> torch.Tensor:
+        """The multi-token verification step: candidates int64 [batch, T] (device) sit at
+        positions position .. position + T - 1; returns int32 [batch, T], the greedy successor of
+        every candidate's prefix. Neither tokens nor position advance."""
+        if candidates.shape != (self.batch, self.q_tokens) or candidates.dtype != torch.int64:
+            raise ValueError(f"candidates must be int64 [{self.batch}, {self.q_tokens}]")
+        self.tokens.copy_(candidates.reshape(-1))
+        check(lib.q_verify_step(self.handle, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return self.arg_idx.view(self.batch, self.q_tokens)
 
     def capture(self) -> None:
-        """Three warm-up steps on a side stream, then one captured step
-        (engine/decode.py:130-148). Warm-up writes land in KV slots at or after the
-        current position, which the real steps overwrite before reading."""
-        tokens, position = self.tokens.clone(), self.position.clone()
-        current = torch.cuda.current_stream()
+        """Warm-up steps on a side stream, then one step recorded as a CUDA graph; tokens and
+        position are put back afterwards (engine/decode.py:130-148 does the same around its
+        capture). Warm-up writes land in KV slots at or after the current position, which the
+        real steps overwrite before they read them. Under tensor parallelism over peer memory
+        the call counters of the exchange kernels advance in the warm-up steps on every rank
+        alike, so the recorded step continues the same sequence."""
+        saved = (self.tokens.clone(), self.position.clone())
+
+        def restore():
+            self.tokens.copy_(saved[0])
+            self.position.copy_(saved[1])
+
+        launch_stream = torch.cuda.current_stream()
         side = torch.cuda.Stream()
-        side.wait_stream(current)
+        side.wait_stream(launch_stream)
         with torch.cuda.stream(side):
             for _ in range(3):
-                self.tokens.copy_(tokens)
-                self.position.copy_(position)
+                restore()
                 self.step()
-        current.wait_stream(side)
-        self.tokens.copy_(tokens)
-        self.position.copy_(position)
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, stream=side):
+            restore()
+        launch_stream.wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
             self.step()
-        self.tokens.copy_(tokens)
-        self.position.copy_(position)
+        restore()
+        self.graph = graph
 
     def advance(self) -> None:
         if self.graph is None:
@@ -363,13 +414,25 @@ class DecodeState:
         else:
             self.graph.replay()
 
+    def check_status(self, words) -> None:
+        """Raises when a bounded wait inside a kernel ran out (the status words are sticky
+        until q_clear_status): what such a step computed is not to be trusted."""
+        if any(words):
+            names = ("attention", "stream-K GEMM", "tcgen05 GEMM", "tensor-parallel peer exchange")
+            what = ", ".join(f"{n} (code {w})" for n, w in zip(names, words) if w)
+            raise _lib.QDecodeError(f"qdecode status {_lib.ERR_DEVICE}: a bounded wait inside a kernel ran out: {what}")
+
     def emit(self, max_new_tokens: int):
-        """Yields one host list per output step; exactly max_new_tokens - 1 decode
-        steps run (engine/decode.py:110-128)."""
+        """Yields one host list per output step; exactly max_new_tokens - 1 decode steps run
+        (engine/decode.py:110-128). The device-to-host copy of step k (tokens and the status
+        words its last kernel left) is enqueued before step k + 1 is launched, and awaited
+        after."""
         for step in range(max_new_tokens):
             self.host.copy_(self.tokens, non_blocking=True)
+            self.host_status.copy_(self.status, non_blocking=True)
             self.ready.record()
             if step + 1 < max_new_tokens:
                 self.advance()
             self.ready.synchronize()
+            self.check_status(self.host_status.tolist())
             yield self.host.tolist()

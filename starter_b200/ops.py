@@ -387,6 +387,41 @@ def lm_head_argmax(normed: torch.Tensor, weight, return_logits: bool = True):
 
 
 def device_status() -> list[int]:
+    """The four status words of the current device (synchronises): non-zero = a bounded wait
+    inside a kernel ran out (attention, stream-K GEMM, tcgen05 GEMM, peer exchange)."""
     out = (C.c_int32 * 4)()
     check(lib.q_device_status(C.byref(out)))
     return list(out)
+
+
+def clear_status() -> None:
+    check(lib.q_clear_status())
+
+
+def pack_weight_tc(weight: torch.Tensor):
+    """Tiles a row-major BF16 [N, K] weight for the tcgen05 projection (load time)."""
+    from .weights import TcWeight
+    return TcWeight.pack(weight)
+
+
+def linear_partials_tc(x: torch.Tensor, weight) -> Partials:
+    """x @ weight.T as FP32 split-K partials on the tcgen05 kernel
+    (engine/kernels/skinny_gemm.py:100-109 at 9 rows and more; any row count up to the
+    prompt pass's). `weight` is a TcWeight or a row-major BF16 [N, K] tensor (tiled on the
+    fly: load-time work done per call, for tests)."""
+    from .weights import TcWeight
+    M, K = _bf16_2d(x, "x")
+    if not isinstance(weight, TcWeight):
+        _bf16_2d(weight, "weight")
+        if weight.shape[1] % 32:
+            raise ValueError("K must be a multiple of 32")
+        weight = TcWeight.pack(weight)
+    N, K2 = weight.shape
+    if K != K2 or x.device != weight.data.device:
+        raise ValueError("x and weight disagree on K or device")
+    if M < 1:
+        raise ValueError("at least one row")
+    p = _lib.plan(M, N, K, tc=True)
+    data = torch.empty((p.slots, M, N), dtype=torch.float32, device=x.device)
+    check(lib.q_gemm_tc(_ptr(x), _ptr(weight), _ptr(data), M, N, K, _stream()))
+    return Partials(data, p)

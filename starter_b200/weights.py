@@ -50,6 +50,15 @@ class TiledWeight:
 
     def __init__(self, data: torch.Tensor, N: int, K: int, interleaved8: bool = False):
         self.data, self.N, self.K, self.interleaved8 = data, N, K, interleaved8
+        self._tc: "TcWeight | None" = None
+
+    def tc(self) -> "TcWeight":
+        """The same matrix in the tcgen05 kernel's 128 x 64 tiling (built on first use from
+        the row-major form, then kept: a second copy of the weight in HBM). A gate|up matrix
+        comes out as plain [gate; up]."""
+        if self._tc is None:
+            self._tc = TcWeight.pack(self.rows())
+        return self._tc
 
     @property
     def shape(self):
@@ -95,6 +104,51 @@ class TiledWeight:
         unit_bytes = (self.K // 32) * 1024
         groups = (hi - lo + 15) // 16
         return TiledWeight(self.data[(lo // 16) * unit_bytes:(lo // 16 + groups) * unit_bytes], hi - lo, self.K)
+
+
+class TcWeight:
+    """A bf16 [N, K] Linear weight in the tcgen05 GEMM's tiling (q_pack_weight_tc in
+    include/qdecode.h): 128-row x 64-k tiles of 16 KB, each the swizzled K-major
+    shared-memory image of the tile."""
+
+    def __init__(self, data: torch.Tensor, N: int, K: int):
+        self.data, self.N, self.K = data, N, K
+
+    @property
+    def shape(self):
+        return (self.N, self.K)
+
+    def numel(self) -> int:
+        return self.N * self.K
+
+    def data_ptr(self) -> int:
+        return self.data.data_ptr()
+
+    @staticmethod
+    def pack(weight: torch.Tensor) -> "TcWeight":
+        from ._lib import check, lib
+        if (weight.ndim != 2 or weight.dtype != torch.bfloat16 or not weight.is_cuda
+                or not weight.is_contiguous() or weight.shape[1] % 32):
+            raise ValueError("expected a contiguous BF16 CUDA [N, K] weight with K a multiple of 32")
+        N, K = weight.shape
+        nbytes = lib.q_packed_weight_bytes_tc(N, K)
+        # 1024-byte alignment of every tile: over-allocate and slice
+        raw = torch.empty(nbytes + 1024, dtype=torch.uint8, device=weight.device)
+        off = (-raw.data_ptr()) % 1024
+        out = raw[off:off + nbytes]
+        with torch.cuda.device(weight.device):
+            check(lib.q_pack_weight_tc(C.c_void_p(weight.data_ptr()), C.c_void_p(out.data_ptr()), N, K,
+                                       C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return TcWeight(out, N, K)
+
+    def rows(self) -> torch.Tensor:
+        from ._lib import check, lib
+        out = torch.empty((self.N, self.K), dtype=torch.bfloat16, device=self.data.device)
+        with torch.cuda.device(self.data.device):
+            check(lib.q_unpack_weight_tc(C.c_void_p(self.data.data_ptr()), C.c_void_p(out.data_ptr()),
+                                         self.N, self.K,
+                                         C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return out
 
 
 @dataclass
@@ -203,6 +257,19 @@ class PackedWeights:
     @property
     def vocab_offset(self) -> int:
         return self.tp_rank * (self.cfg.vocab // self.tp_size)
+
+    def ensure_tc(self) -> None:
+        """Builds the tcgen05 tiling of every matrix (steps with 9 rows and more, the prompt
+        pass). Doubles the weight bytes held in HBM."""
+        for lt in self.layers:
+            for name in ("wqkv", "wo", "wgu", "wdown"):
+                getattr(lt, name).tc()
+        self.lm_head.tc()
+
+    @property
+    def has_tc(self) -> bool:
+        return self.lm_head._tc is not None and all(
+            getattr(lt, n)._tc is not None for lt in self.layers for n in ("wqkv", "wo", "wgu", "wdown"))
 
 
 def check_tp(cfg: ModelConfig, tp_size: int) -> None:

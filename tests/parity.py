@@ -8,7 +8,7 @@ def sum_slots(partials):
     p = partials.plan
     data = partials.data.detach().cpu()
     Cg, u = p.chunks_per_group, p.units_per_worker
-    g = torch.arange(p.N) // 16
+    g = torch.arange(p.N) // p.group_rows
     cnt = ((g + 1) * Cg - 1) // u - (g * Cg) // u + 1
     total = torch.zeros((p.M, p.N), dtype=torch.float32)
     for k in range(p.slots):

@@ -40,7 +40,7 @@ def test_plan_covers_every_unit_once(M, N, K):
     p = _lib.plan(M, N, K)
     Cg, u = p.chunks_per_group, p.units_per_worker
     total = p.groups * Cg
-    assert p.groups == (N + 15) // 16 and Cg == K // 32
+    assert p.groups == (N + 15) // 16 and Cg == K // 32 and p.group_rows == 16
     assert p.workers == (total + u - 1) // u
     assert p.workers <= p.grid * (p.block // 32)
     covered = 0
@@ -152,8 +152,57 @@ def test_peer_entry_points_reject_bad_arguments():
     lib = _lib.lib
     peers = _lib.Peers()
     peers.rank, peers.world = 0, 1                        # a world of one is not tensor parallel
-    assert lib.q_add_rmsnorm_peers(1, C.byref(peers), 1, None, 1, 1, 1, 1, 128, 1e-6, None) == -1
+    A = 4096                                              # a made-up, aligned address: nothing is launched
+    assert lib.q_add_rmsnorm_peers(A, C.byref(peers), A, None, A, A, A, 1, 128, 1e-6, None) == -1
     assert b"world" in lib.q_last_error() or b"rank" in lib.q_last_error()
     assert lib.q_bind_peers(None, C.byref(peers)) == -1
-    assert lib.q_gemm_swiglu(1, 1, 1, 1, 12, 64, None) == -1      # inter must be a multiple of 8
-    assert lib.q_gemm_swiglu_addnorm(1, 1, None, 1, 1, 1, 1, 1, 64, 64, 1e-6, None) == -1   # in place
+    assert lib.q_gemm_swiglu(A, A, A, 1, 12, 64, None) == -1      # inter must be a multiple of 8
+    assert lib.q_gemm_swiglu_addnorm(A, A, None, A, A, A, A, 1, 64, 64, 1e-6, None) == -1   # in place
+    assert lib.q_argmax_merge_peers(A, A, C.byref(peers), 1, A, A, 1, None) == -1
+    assert lib.q_peer_flag_bytes() >= 512 + 2 * 8 * 64 * 8
+
+
+def test_misaligned_pointers_are_argument_errors():
+    """Kernels that load or store 8 / 16 bytes at a time refuse pointers that would fault on the
+    device: the check runs on the host, before any launch."""
+    from starter_b200 import _lib
+    lib = _lib.lib
+    A = 4096
+    p = _lib.plan(2, 64, 64)
+    cases = [
+        lib.q_gemm_splitk(A + 2, A, A, 2, 64, 64, None),
+        lib.q_gemm_tc(A, A + 512, A, 12, 64, 64, None),
+        lib.q_reduce_partials(A + 4, C.byref(p), A, None),
+        lib.q_reduce_partials(A, C.byref(p), A + 8, None),
+        lib.q_linear_f32_static(A, A, A + 4, 2, 64, 64, None),
+        lib.q_add_rmsnorm(A + 2, A, None, A, A, A, 2, 64, 1e-6, None),
+        lib.q_add_rmsnorm(A, A + 4, None, A, A, A, 2, 64, 1e-6, None),
+        lib.q_swiglu(A + 8, C.byref(_lib.plan(2, 128, 64)), A, 2, 64, None),
+        lib.q_logits_argmax(A + 4, C.byref(p), None, A, A, None, None, 0, A, 2, 64, 0, None),
+        lib.q_gemm_splitk_addnorm(A, A + 4, None, A, A + 64, A, A, 2, 64, 64, 1e-6, None),
+    ]
+    assert cases == [-1] * len(cases), cases
+    assert b"aligned" in lib.q_last_error()
+
+
+@pytest.mark.parametrize("M,N,K", [(32, 19456, 2560), (64, 2560, 9728), (9, 6144, 2560), (16, 151936, 2560),
+                                   (12, 127, 128), (300, 48, 96), (1, 16, 32)])
+def test_tc_plan_covers_every_tile_once(M, N, K):
+    """The tcgen05 kernel's stream-K split: every (128-row block, 64-k tile) belongs to exactly
+    one CTA, and the slot a CTA writes for a block is below `slots`."""
+    from starter_b200 import _lib
+    p = _lib.plan(M, N, K, tc=True)
+    KT, u = p.chunks_per_group, p.units_per_worker
+    assert p.group_rows == 128 and p.groups == (N + 127) // 128 and KT == (K + 63) // 64
+    total = p.groups * KT
+    assert p.workers == (total + u - 1) // u == p.grid
+    covered, max_slot = 0, 0
+    for w in range(p.workers):
+        start, end = w * u, min(total, (w + 1) * u)
+        covered += end - start
+        for g in range(start // KT, (end - 1) // KT + 1):
+            first, last = (g * KT) // u, ((g + 1) * KT - 1) // u
+            assert first <= w <= last
+            max_slot = max(max_slot, last - first + 1)
+    assert covered == total and max_slot <= p.slots
+    assert _lib.lib.q_packed_weight_bytes_tc(N, K) == total * 16384

@@ -35,6 +35,7 @@ def stepwise_logits(engine, prompt, n):
     ids = torch.tensor(prompt, dtype=torch.int64, device="cuda")
     with torch.inference_mode():
         state = DecodeState(engine.weights, ids.shape[0], ids.shape[1], n, keep_logits=True)
+        stepwise_logits.last_state = state
         first = state.prefill(ids)
         tokens = [state.tokens.cpu().tolist()]
         logits = [first.float().cpu()]
@@ -143,27 +144,6 @@ def test_zero_lm_head_yields_token_zero_and_never_stops(cuda, golden_dir, tmp_pa
     assert out == [[0, 0]] * 6
 
 
-def test_fused_step_matches_multi_kernel_step(cuda, golden_dir):
-    """The persistent whole-step kernel and the ~360-kernel step implement the same
-    arithmetic: same tokens, logits equal up to fp32 reduction order (one bf16 ulp)."""
-    from starter_b200 import Engine, _lib
-    from starter_b200.ops import device_status
-    path = str(golden_dir / "tiny_qwen3")
-    engine = Engine(path, keep_logits=True)
-    gen = torch.Generator().manual_seed(21)
-    for batch, length, count in ((1, 9, 12), (2, 70, 8), (3, 5, 6)):
-        prompt = torch.randint(0, 127, (batch, length), generator=gen).tolist()
-        plain_tokens, plain_logits = stepwise_logits(engine, prompt, count)
-        _lib.check(_lib.lib.q_set_option(b"fused_step", 1))
-        try:
-            fused_tokens, fused_logits = stepwise_logits(engine, prompt, count)
-        finally:
-            _lib.check(_lib.lib.q_set_option(b"fused_step", 0))
-        assert fused_tokens == plain_tokens
-        torch.testing.assert_close(fused_logits, plain_logits, rtol=1.6e-2, atol=2e-3)
-    assert device_status() == [0, 0, 0, 0]
-
-
 def test_norm_prologue_step_matches_separate_add_norm_kernels(cuda, golden_dir):
     """Default step (add + norm inside the consuming projection, up to 8 rows) against the
     step with separate add+norm launches: same tokens, logits equal up to the reduction
@@ -196,3 +176,146 @@ def test_pdl_off_gives_identical_tokens(cuda, golden_dir):
     finally:
         _lib.lib.q_set_pdl(1)
     assert a == b
+
+
+def _live_model(tmp_path, nq, nkv, hidden, inter, vocab, layers, seed):
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    torch.manual_seed(seed)
+    cfg = Qwen3Config(vocab_size=vocab, hidden_size=hidden, intermediate_size=inter,
+                      num_hidden_layers=layers, num_attention_heads=nq, num_key_value_heads=nkv,
+                      head_dim=128, max_position_embeddings=512, rope_theta=1_000_000.0,
+                      tie_word_embeddings=True, sliding_window=None)
+    Qwen3ForCausalLM(cfg).eval().to(torch.bfloat16).save_pretrained(tmp_path, safe_serialization=True)
+    return str(tmp_path)
+
+
+@pytest.mark.parametrize("route", ["tcgen05", "mma"])
+def test_steps_above_8_rows_match_native(cuda, golden_dir, tmp_path, route):
+    """The step for 9..64 sequences - projections on the tcgen05 kernel (default) or, with the
+    option tc_min_rows out of reach, on the stream-K kernel with SwiGLU and add+norm as
+    separate launches - against native Hugging Face at the 2e-2 bar, on the golden tiny model
+    and a live model with 4 query heads per kv head (the own-prefix check of reference
+    tests/test_skinny_gemm.py:549-588)."""
+    from starter_b200 import Engine, _lib
+    from starter_b200.ops import device_status
+    if route == "mma":
+        _lib.check(_lib.lib.q_set_option(b"tc_min_rows", 1000))
+    try:
+        gen = torch.Generator().manual_seed(31)
+        path = str(golden_dir / "tiny_qwen3")
+        engine, native = Engine(path, keep_logits=True), O.native_model(path)
+        for batch, length, count in ((9, 7, 4), (16, 40, 4), (32, 70, 5), (64, 3, 3)):
+            prompt = torch.randint(0, 127, (batch, length), generator=gen).tolist()
+            tokens, logits = stepwise_logits(engine, prompt, count)
+            assert stepwise_logits.last_state.uses_tc
+            assert_parity(native, prompt, tokens, logits)
+            assert list(engine.generate(prompt, count)) == tokens          # graph replay, same route
+        live = _live_model(tmp_path, 8, 2, 384, 1024, 1000, 3, 77)
+        engine, native = Engine(live, keep_logits=True), O.native_model(live)
+        for batch, length, count in ((12, 33, 4), (32, 130, 4)):
+            prompt = torch.randint(0, 1000, (batch, length), generator=gen).tolist()
+            tokens, logits = stepwise_logits(engine, prompt, count)
+            assert_parity(native, prompt, tokens, logits)
+    finally:
+        _lib.check(_lib.lib.q_set_option(b"tc_min_rows", 9))
+    assert device_status() == [0, 0, 0, 0]
+
+
+def test_both_routes_above_8_rows_agree(cuda, golden_dir):
+    """tcgen05 route against the stream-K route at 32 rows: same tokens, logits equal up to the
+    fp32 summation order of the projections (one bf16 ulp)."""
+    from starter_b200 import Engine, _lib
+    engine = Engine(str(golden_dir / "tiny_qwen3"), keep_logits=True)
+    prompt = torch.randint(0, 127, (32, 50), generator=torch.Generator().manual_seed(41)).tolist()
+    tc_tokens, tc_logits = stepwise_logits(engine, prompt, 6)
+    _lib.check(_lib.lib.q_set_option(b"tc_min_rows", 1000))
+    try:
+        mma_tokens, mma_logits = stepwise_logits(engine, prompt, 6)
+    finally:
+        _lib.check(_lib.lib.q_set_option(b"tc_min_rows", 9))
+    torch.testing.assert_close(tc_logits[:2], mma_logits[:2], rtol=1.6e-2, atol=4e-3)
+    assert tc_tokens[:2] == mma_tokens[:2]
+
+
+@pytest.mark.parametrize("batch,T", [(1, 4), (2, 8), (8, 8), (3, 2)])
+def test_verify_step_equals_single_token_steps(cuda, golden_dir, batch, T):
+    """q_verify_step on T candidate tokens per sequence gives, for every row, the token that T
+    single-token steps produce (the candidates ARE the greedy continuation here), and wrong
+    candidates change nothing before them."""
+    from starter_b200 import Engine
+    from starter_b200.decode import DecodeState
+    engine = Engine(str(golden_dir / "tiny_qwen3"))
+    gen = torch.Generator().manual_seed(51 + batch)
+    length, count = 20, T + 1
+    prompt = torch.randint(0, 127, (batch, length), generator=gen)
+    greedy = torch.tensor(list(engine.generate(prompt.tolist(), count)))          # [count, batch]
+    with torch.inference_mode():
+        state = DecodeState(engine.weights, batch, length, count)
+        state.prefill(prompt.cuda())
+        assert state.tokens.cpu().tolist() == greedy[0].tolist()
+        ver = DecodeState(engine.weights, batch, length, count, q_tokens=T, share=state)
+        cand = greedy[:T].t().contiguous().cuda()                                  # [batch, T]
+        nxt = ver.verify(cand).cpu()
+        assert nxt.tolist() == greedy[1:T + 1].t().tolist()
+        assert int(state.position.item()) == length                              # nothing advanced
+        # corrupt the last candidate: successors of the earlier rows stay
+        bad = cand.clone()
+        bad[:, -1] = (bad[:, -1] + 1) % 127
+        nxt2 = ver.verify(bad).cpu()
+        assert nxt2[:, :T - 1].tolist() == greedy[1:T].t().tolist()
+
+
+def test_speculative_generate_is_exact(cuda, golden_dir):
+    """The accept-prefix loop over q_verify_step emits exactly the greedy tokens, whatever the
+    drafts are; a repetitive prompt makes the prompt-lookup drafter hit."""
+    from starter_b200 import Engine
+    from starter_b200.speculative import generate_speculative
+    engine = Engine(str(golden_dir / "tiny_qwen3"))
+    gen = torch.Generator().manual_seed(61)
+    base = torch.randint(0, 127, (2, 6), generator=gen)
+    prompt = base.repeat(1, 5).tolist()
+    want = list(engine.generate(prompt, 24))
+    for T in (2, 4, 8):
+        got, stats = generate_speculative(engine, prompt, 24, draft_tokens=T)
+        assert got == want
+        assert stats["verify_calls"] >= 1 and stats["emitted"] == 24
+
+
+def test_device_status_is_surfaced_and_cleared(cuda, golden_dir):
+    """A wait that ran out must reach the caller as an error: the peer add+norm is called on ONE
+    GPU with a world of two whose second arrival word nobody writes and a short wait limit. The
+    kernel returns, status word 3 is set, the engine's next step raises, and q_clear_status
+    re-arms. Nothing faults or hangs: the wait gives up and the kernel finishes."""
+    import ctypes as C
+    from starter_b200 import Engine, _lib
+    from starter_b200.ops import clear_status, device_status
+    lib, check = _lib.lib, _lib.check
+    clear_status()
+    rows, cols = 2, 256
+    buf = torch.zeros(rows * cols * 2 + lib.q_peer_flag_bytes() // 4, dtype=torch.float32, device="cuda")
+    counters = torch.zeros(4, dtype=torch.int32, device="cuda")
+    peers = _lib.Peers()
+    peers.rank, peers.world = 0, 2
+    for r in range(2):
+        peers.partials[r] = buf.data_ptr()
+        peers.flags[r] = buf.data_ptr() + rows * cols * 2 * 4
+    peers.epoch = counters.data_ptr()
+    x = torch.zeros((rows, cols), dtype=torch.bfloat16, device="cuda")
+    gain = torch.ones(cols, dtype=torch.bfloat16, device="cuda")
+    total, normed = torch.empty_like(x), torch.empty_like(x)
+    check(lib.q_set_option(b"peer_wait_iters", 2000))
+    try:
+        check(lib.q_add_rmsnorm_peers(C.c_void_p(x.data_ptr()), C.byref(peers), C.c_void_p(buf.data_ptr()), None,
+                                      C.c_void_p(gain.data_ptr()), C.c_void_p(total.data_ptr()),
+                                      C.c_void_p(normed.data_ptr()), rows, cols, 1e-6, None))
+        torch.cuda.synchronize()
+    finally:
+        check(lib.q_set_option(b"peer_wait_iters", 1 << 21))
+    assert device_status() == [0, 0, 0, 1]
+    assert counters[0].item() == 1 and counters[1].item() == 0          # the call completed
+    engine = Engine(str(golden_dir / "tiny_qwen3"))
+    with pytest.raises(_lib.QDecodeError, match="peer exchange"):
+        list(engine.generate([[1, 2, 3]], 4))
+    clear_status()
+    assert device_status() == [0, 0, 0, 0]
+    assert len(list(engine.generate([[1, 2, 3]], 4))) == 4

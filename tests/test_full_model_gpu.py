@@ -49,6 +49,13 @@ def test_qwen3_4b_logits_and_tokens_vs_native_cpu():
     print(f"max abs logit diff {float(diff.max()):.4f}; native self-noise {noise:.4f}; "
           f"largest top-1 gap of an emitted token {float(gaps.max()):.4f}; "
           f"tokens equal to native cached loop for {agree}/16 steps")
+    from tests.test_full_width_gpu import write_parity_record
+    write_parity_record("c1_full_model", {
+        "workload": "Qwen3-4B architecture, 36 layers, batch 1, prompt 64, 16 new tokens",
+        "max_abs_vs_native": float(diff.max()), "native_self_noise": noise,
+        "tokens_equal_native_cached": agree, "steps": 16,
+        "largest_top1_gap_of_emitted": float(gaps.max()),
+        "near_tie_gaps": [float(g) for g in gaps.flatten() if g > 0]})
     tol = max(2e-2, 1.5 * noise)
     assert float(diff.max()) <= tol, (float(diff.max()), tol)
     assert float(gaps.max()) <= tol

@@ -111,3 +111,89 @@ def test_argmax_merge_prefers_lowest_global_index():
     best = vals.max(0).values
     token = torch.where(vals == best[None], idxs, torch.full_like(idxs, 2 ** 40)).min(0).values
     assert token.tolist() == [4, 200]
+
+
+# ---- failure detection on the host: a rank that raises, a wrong shard, a rank that never joins ----
+def _failure_worker(rank, world, port, result, case):
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    from datetime import timedelta
+    from starter_b200 import tp, weights as W
+    try:
+        if case == "absent" and rank == 1:
+            # this rank reaches the rendezvous but never the arrival point
+            store = dist.TCPStore("127.0.0.1", port, world, is_master=False, timeout=timedelta(seconds=20))
+            result.put((rank, "skipped"))
+            return
+        if case == "absent":
+            store = dist.TCPStore("127.0.0.1", port, world, is_master=True, timeout=timedelta(seconds=20))
+            try:
+                tp.join_or_fail(store, rank, world, "step0", 1.0)
+                result.put((rank, "no error"))
+            except tp.TensorParallelError as exc:
+                result.put((rank, str(exc)))
+            return
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=30))
+        group = dist.group.WORLD
+        gold = ROOT / "tests" / "golden" / "tiny_qwen3"
+        try:
+            if case == "raises":
+                def load():
+                    if rank == 1:
+                        raise FileNotFoundError("shard 1 is missing")
+                    return 7
+                tp.guarded(group, load, "loading the checkpoint shard")
+            elif case == "shape":
+                from safetensors.torch import load_file
+                import json
+                sd = load_file(str(gold / "model.safetensors"))
+                sd["model.embed_tokens.weight"] = sd["model.embed_tokens.weight"][:126].contiguous()
+                hf_cfg = json.loads((gold / "config.json").read_text())
+                hf_cfg["vocab_size"] = 126
+                cfg = W.ModelConfig.from_hf(hf_cfg)
+                # rank 1 cuts its shard as if it were alone
+                pw = W.pack(cfg, sd.__getitem__, sd.__contains__, "cpu", *((rank, world) if rank == 0 else (0, 1)))
+                tp.check_shards(group, pw)
+            elif case == "fine":
+                assert tp.guarded(group, lambda: rank + 1, "a step that works") == rank + 1
+            result.put((rank, "no error"))
+        except tp.TensorParallelError as exc:
+            result.put((rank, str(exc)))
+        finally:
+            dist.destroy_process_group()
+    except Exception as exc:             # noqa: BLE001 - the test reads it
+        result.put((rank, f"unexpected {type(exc).__name__}: {exc}"))
+
+
+def _run_failure_case(case):
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = 31500 + (os.getpid() * 7 + hash(case)) % 2000
+    procs = [ctx.Process(target=_failure_worker, args=(r, 2, port, result, case)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    out = dict(result.get(timeout=5) for _ in range(2))
+    return out
+
+
+def test_a_rank_that_raises_fails_every_rank():
+    out = _run_failure_case("raises")
+    for rank in (0, 1):
+        assert "failed on rank(s) [1] of 2" in out[rank], out
+    assert "shard 1 is missing" in out[1]
+    assert _run_failure_case("fine") == {0: "no error", 1: "no error"}
+
+
+def test_a_wrong_shard_fails_every_rank():
+    out = _run_failure_case("shape")
+    for rank in (0, 1):
+        assert "shards disagree" in out[rank], out
+
+
+def test_a_rank_that_never_arrives_is_named():
+    out = _run_failure_case("absent")
+    assert "rank(s) [1] of 2 did not arrive at 'step0'" in out[0], out

@@ -17,9 +17,9 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
 
-@pytest.mark.parametrize("peers", ["1", "0"])
+@pytest.mark.parametrize("tp_path", ["peers", "nccl"])
 @pytest.mark.parametrize("world", [2])
-def test_tensor_parallel_tokens_match_single_gpu(tmp_path, world, peers):
+def test_tensor_parallel_tokens_match_single_gpu(tmp_path, world, tp_path):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from transformers import Qwen3Config, Qwen3ForCausalLM
@@ -32,19 +32,22 @@ def test_tensor_parallel_tokens_match_single_gpu(tmp_path, world, peers):
     model_dir = tmp_path / "model"
     Qwen3ForCausalLM(cfg).eval().to(torch.bfloat16).save_pretrained(model_dir, safe_serialization=True)
     gen = torch.Generator().manual_seed(2)
-    cases = [(torch.randint(0, 512, (b, p), generator=gen).tolist(), n) for b, p, n in ((2, 7, 6), (1, 70, 5), (4, 33, 8))]
+    # up to 8 rows the peers read the split-K slots directly; above, every rank adds its own
+    # slots first and the projections run on the tcgen05 kernel
+    cases = [(torch.randint(0, 512, (b, p), generator=gen).tolist(), n)
+             for b, p, n in ((2, 7, 6), (1, 70, 5), (4, 33, 8), (12, 20, 5), (32, 66, 4))]
     out_path = tmp_path / "tp_tokens.json"
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", QDECODE_TP_PEERS=peers)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     port = 29600 + os.getpid() % 1000
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), str(ROOT / "tests" / "tp_worker.py"),
-           str(model_dir), str(out_path), json.dumps(cases)]
+           str(model_dir), str(out_path), json.dumps(cases), tp_path]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
     report = json.loads(out_path.read_text())
     tp_tokens = report["tokens"]
     assert report["device_status"] == [0, 0, 0, 0]
-    assert report["peers"] == (peers == "1"), proc.stderr[-2000:]
+    assert report["tp_path"] == tp_path, proc.stderr[-2000:]
     single = Engine(str(model_dir))
     native = O.native_model(str(model_dir))
     for (prompt, n), got in zip(cases, tp_tokens):

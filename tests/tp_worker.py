@@ -16,24 +16,26 @@ def main():
     # a stuck collective shows up as a stack dump instead of a silent wait
     faulthandler.dump_traceback_later(int(os.environ.get("TP_DUMP_AFTER", "120")), exit=True)
     model_dir, out_path, cases = sys.argv[1], sys.argv[2], json.loads(sys.argv[3])
+    tp_path = sys.argv[4] if len(sys.argv) > 4 else "auto"
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     from starter_b200 import Engine, _lib
     if os.environ.get("TP_NO_PDL"):
         _lib.check(_lib.lib.q_set_pdl(0))
-    engine = Engine(model_dir, device=f"cuda:{local}", group=dist.group.WORLD)
+    engine = Engine(model_dir, device=f"cuda:{local}", group=dist.group.WORLD, tp_path=tp_path)
     if os.environ.get("TP_NO_GRAPH"):
         from starter_b200.decode import DecodeState
         DecodeState.capture = lambda self: None
-    out, used_peers = [], True
+    out, paths = [], set()
     for prompt, n in cases:
         out.append(list(engine.generate(prompt, n)))
-        used_peers = used_peers and bool(engine.decode_state.peers)
+        paths.add(engine.decode_state.tp_path)
     from starter_b200.ops import device_status
     status = device_status()
     if dist.get_rank() == 0:
-        Path(out_path).write_text(json.dumps({"tokens": out, "peers": used_peers, "device_status": status}))
+        Path(out_path).write_text(json.dumps({"tokens": out, "tp_path": "/".join(sorted(paths)),
+                                              "device_status": status}))
     # captured graphs hold NCCL kernels: drop them before the communicator goes away
     engine.decode_state = None
     del engine
