@@ -69,6 +69,10 @@ int q_set_option(const char* name, int value);
  * exit, prologue operands in registers} (ns, %globaltimer); this copies the records of the last recording launch to the
  * host (8 values per CTA). */
 int q_debug_gemm_trace(unsigned long long* out, int n_ctas);
+/* The same for the tcgen05 projection: {start, set-up done, producer past the dependency wait,
+ * first stage landed, last MMA issued, last accumulator stored, exit, tiles of the CTA}. With
+ * "gemm_debug_flags" bit 16 the kernel issues no MMA (copies only: the load pipeline alone). */
+int q_debug_tc_trace(unsigned long long* out, int n_ctas);
 
 /* Measurement aid: with option "timeline" = 1 (set before the launches, and before a graph
  * capture that should carry it), the kernels of q_decode_step's default path record, per

@@ -87,6 +87,7 @@ SIGNATURES = {
     "q_debug_timeline_kinds": (_I, [_P, _I]),
     "q_debug_attn_trace": (_I, [_P]),
     "q_debug_gemm_trace": (_I, [C.POINTER(C.c_uint64), _I]),
+    "q_debug_tc_trace": (_I, [C.POINTER(C.c_uint64), _I]),
     "q_gemm_plan": (_I, [_I, _I, _I, _PLAN]),
     "q_packed_weight_bytes": (C.c_int64, [_I, _I]),
     "q_pack_weight": (_I, [_P, _P, _I, _I, _P]),

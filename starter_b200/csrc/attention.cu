@@ -131,11 +131,11 @@ k_attn_split(const bf16* __restrict__ Q, const char* __restrict__ kpool,
   const int pos = pos_ptr[0];
   const int max_limit = pos + T;                                   // keys visible to the last row
   const int tiles_used = (max_limit + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
-  const int per = (tiles_used + S - 1) / S;
-  const int tile0 = split * per;
-  int tile1 = tile0 + per;
-  if (tile1 > tiles_used) tile1 = tiles_used;
-  const int ntiles = tile1 > tile0 ? tile1 - tile0 : 0;
+  // tiles are dealt out evenly: the first (tiles_used % S) splits get one more
+  const int tbase = tiles_used / S, trem = tiles_used - tbase * S;
+  const int tile0 = split * tbase + min(split, trem);
+  const int tile1 = tile0 + tbase + (split < trem ? 1 : 0);
+  const int ntiles = tile1 - tile0;
   const int first_new_tile = pos / Q_PAGE_TOKENS;                  // tiles >= this may change in this step
 
   if (warp == CONSUMERS) {
@@ -468,10 +468,11 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
   const int pos = pos_ptr[0];
   const int max_limit = pos + 1;
   const int tiles_used = (max_limit + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
-  const int per = (tiles_used + S - 1) / S;
-  const int tile0 = split * per;
-  const int tile1 = min(tiles_used, tile0 + per);
-  const int ntiles = tile1 > tile0 ? tile1 - tile0 : 0;
+  // tiles are dealt out evenly: the first (tiles_used % S) splits get one more
+  const int tbase = tiles_used / S, trem = tiles_used - tbase * S;
+  const int tile0 = split * tbase + min(split, trem);
+  const int tile1 = tile0 + tbase + (split < trem ? 1 : 0);
+  const int ntiles = tile1 - tile0;
   const int new_tile = pos / Q_PAGE_TOKENS, new_row = pos % Q_PAGE_TOKENS;
   const bool owns_new = ntiles > 0 && new_tile >= tile0 && new_tile < tile1;
 
@@ -851,7 +852,11 @@ extern "C" int q_attention_splits(int batch, int n_kv_heads, int capacity) {
   if (sms <= 0) sms = 148;
   const int vh = batch * n_kv_heads;
   const int tiles = (capacity + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
-  int desired = (2 * sms + vh - 1) / vh;
+  // Two CTAs fit on an SM. All CTAs of a launch should be resident at once: a second wave
+  // cannot request its K/V tiles before a slot frees, and measured ~15 % at 32 sequences of
+  // 2 K keys (two splits per kv head = 1.7 waves) against one split per kv head in one wave.
+  int desired = (2 * sms) / vh;
+  if (desired < 1) desired = 1;
   int s = desired < tiles ? desired : tiles;
   // Up to 8 splits merge inside a thread-block cluster (no global round trip); that is
   // worth more than finer splits while a split still sees at most 4 tiles.

@@ -33,16 +33,26 @@
 #include <cuda.h>
 #include "common.cuh"
 
+extern int g_gemm_debug_flags;   // q_set_option "gemm_debug_flags": 4 = per-CTA stamps, 16 = no MMA issue
+
 namespace {
 
 constexpr int TC_THREADS = 192;
 constexpr int TILE_ROWS = 128;
 constexpr int TILE_K = 64;
 constexpr int W_TILE_BYTES = TILE_ROWS * TILE_K * 2;      // 16 KB
-constexpr int SMEM_BUDGET = 200 * 1024;                   // ring bytes at most
+constexpr int SMEM_BUDGET = 222 * 1024;                   // ring bytes at most
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 __device__ int g_tc_status[4];
+// Measurement aid (debug flag 4): per CTA {start, set-up done, producer past the dependency
+// wait, first stage landed, last MMA issued, last accumulator stored, exit, tiles} in ns.
+__device__ unsigned long long g_tc_trace[256 * 8];
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -160,7 +170,7 @@ struct TcShape {
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restrict__ W, float* __restrict__ P,
-          TcShape sh, unsigned long long* tl) {
+          TcShape sh, int dbg, unsigned long long* tl) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;            // tiles need 1024-byte alignment
@@ -176,12 +186,17 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restr
   tl_begin(tl);
   pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool trace = (dbg & 4) && blockIdx.x < 256;
+  unsigned long long* tr = g_tc_trace + blockIdx.x * 8;
+  if (trace && tid == 0) tr[0] = gtime();
   const int t0 = blockIdx.x * sh.U;
   const int t1 = min(sh.total, t0 + sh.U);
   const int n_tiles = t1 > t0 ? t1 - t0 : 0;
-  // tensor-memory columns: two accumulator buffers, a power of two >= 32
+  // tensor-memory columns: two accumulator buffers of m_pad columns, a power of two >= 32
+  // (spreading the k-steps of a tile over several accumulators measured no faster)
+  const int acc_cols = sh.m_pad;
   uint32_t ncols = 32;
-  while (ncols < 2u * sh.m_pad) ncols <<= 1;
+  while (ncols < 2u * acc_cols) ncols <<= 1;
 
   if (tid == 0) {
     for (int s = 0; s < sh.stages; ++s) {
@@ -205,6 +220,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restr
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (trace && tid == 0) { tr[1] = gtime(); tr[7] = (unsigned long long)n_tiles; }
 
   if (warp == 0) {
     // ---------------- producer ----------------
@@ -218,26 +234,41 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restr
       }
       pdl_wait();                       // the activations are complete from here on
       tl_waited(tl);
+      if (trace) tr[2] = gtime();
       for (int i = 0; i < first; ++i) {
         const int kt = (t0 + i) % sh.KT;
         tma_load_2d(base + i * stage_bytes + W_TILE_BYTES, &xmap, kt * TILE_K, sh.row0, bar_full + 8 * i);
       }
+      // Refill loop. One thread issues everything, so its instruction count per tile is what
+      // bounds the copy rate: stage index, barrier parity and k tile are carried along instead
+      // of being divided out of the tile number.
       bool ok = true;
       int issued_tiles = first;
-      for (int i = first; i < n_tiles && ok; ++i) {
-        const int s = i % sh.stages;
-        if (!mbar_wait(bar_empty + 8 * s, ((i / sh.stages) - 1) & 1, abort_flag)) {
-          atomicExch(&g_tc_status[0], 1);
-          *abort_flag = 1;
-          ok = false;
-          break;
+      {
+        int st = 0;                                        // stage of tile `first`
+        uint32_t parity = 0;                               // phase of empty[st] to wait for
+        int kt = (t0 + first) % sh.KT;
+        uint32_t dst = base, full = bar_full, empty = bar_empty;
+        const unsigned char* src = W + (size_t)(t0 + first) * W_TILE_BYTES;
+        for (int i = first; i < n_tiles; ++i) {
+          if (!mbar_wait(empty, parity, abort_flag)) {
+            atomicExch(&g_tc_status[0], 1);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(full, stage_bytes);
+          bulk_g2s(dst, src, W_TILE_BYTES, full, policy);
+          tma_load_2d(dst + W_TILE_BYTES, &xmap, kt * TILE_K, sh.row0, full);
+          issued_tiles = i + 1;
+          src += W_TILE_BYTES;
+          if (++kt == sh.KT) kt = 0;
+          if (++st == sh.stages) {
+            st = 0; parity ^= 1u; dst = base; full = bar_full; empty = bar_empty;
+          } else {
+            dst += stage_bytes; full += 8; empty += 8;
+          }
         }
-        const int kt = (t0 + i) % sh.KT;
-        mbar_expect_tx(bar_full + 8 * s, stage_bytes);
-        bulk_g2s(base + s * stage_bytes, W + (size_t)(t0 + i) * W_TILE_BYTES, W_TILE_BYTES, bar_full + 8 * s,
-                 policy);
-        tma_load_2d(base + s * stage_bytes + W_TILE_BYTES, &xmap, kt * TILE_K, sh.row0, bar_full + 8 * s);
-        issued_tiles = i + 1;
       }
       // Copies in flight must land before the CTA may exit, also when a role gave up: the
       // last fill of every stage flips that stage's `full` barrier once more.
@@ -253,39 +284,58 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restr
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(sh.m_pad >> 3) << 17) |
                              ((uint32_t)(TILE_ROWS >> 4) << 24);     // f32 accum, bf16 x bf16, K-major both
-      int seg = 0, buf = 0;
+      // Like the producer, this thread's instruction count per tile matters (a loop with
+      // three integer divisions per tile made the tensor pipe look like the bottleneck): all
+      // indices are carried along, the four k-steps are unrolled.
+      const uint32_t stage_units = stage_bytes >> 4;       // descriptor address units (16 B)
+      const uint64_t desc0 = smem_desc(base);
+      int seg = 0;
+      int st = 0;
+      int kt = t0 % sh.KT;
+      uint32_t full_parity = 0;
+      uint32_t full = bar_full, empty = bar_empty;
+      uint64_t a_desc = desc0;
+      uint32_t dacc = tmem_base;
+      uint32_t acc_full_bar = bar_acc_full;
       for (int i = 0; i < n_tiles; ++i) {
-        const int s = i % sh.stages;
-        const int kt = (t0 + i) % sh.KT;
         const bool seg_start = (i == 0) || kt == 0;
         if (seg_start) {
-          buf = seg & 1;
+          const int buf = seg & 1;
           // the epilogue has drained this buffer (passes at once for the first two segments)
           if (!mbar_wait(bar_acc_empty + 8 * buf, ((seg >> 1) & 1) ^ 1, abort_flag)) {
             atomicExch(&g_tc_status[0], 2);
             *abort_flag = 1;
             break;
           }
+          dacc = tmem_base + (uint32_t)(buf * acc_cols);
+          acc_full_bar = bar_acc_full + 8 * buf;
         }
-        if (!mbar_wait(bar_full + 8 * s, (i / sh.stages) & 1, abort_flag)) {
+        if (!mbar_wait(full, full_parity, abort_flag)) {
           atomicExch(&g_tc_status[0], 2);
           *abort_flag = 1;
           break;
         }
         tc_fence_after();
-        const uint64_t a0 = smem_desc(base + s * stage_bytes);
-        const uint64_t b0 = smem_desc(base + s * stage_bytes + W_TILE_BYTES);
-        const uint32_t d = tmem_base + (uint32_t)(buf * sh.m_pad);
+        if (trace && i == 0) tr[3] = gtime();
+        const uint64_t b_desc = a_desc + (W_TILE_BYTES >> 4);
+        if (!(dbg & 16)) {
 #pragma unroll
-        for (int k = 0; k < TILE_K / 16; ++k)
-          tc_mma(d, a0 + 2u * k, b0 + 2u * k, idesc, (seg_start && k == 0) ? 0u : 1u);
-        tc_commit(bar_empty + 8 * s);                 // the stage is free when these MMAs are done
-        const bool seg_end = (i == n_tiles - 1) || kt == sh.KT - 1;
-        if (seg_end) {
-          tc_commit(bar_acc_full + 8 * buf);          // ... and so is the accumulator
+          for (int k = 0; k < TILE_K / 16; ++k)
+            tc_mma(dacc, a_desc + 2u * k, b_desc + 2u * k, idesc, (seg_start && k == 0) ? 0u : 1u);
+        }
+        tc_commit(empty);                             // the stage is free when these MMAs are done
+        if (++kt == sh.KT) kt = 0;
+        if (kt == 0 || i == n_tiles - 1) {
+          tc_commit(acc_full_bar);                    // ... and so is the accumulator
           ++seg;
         }
+        if (++st == sh.stages) {
+          st = 0; full_parity ^= 1u; full = bar_full; empty = bar_empty; a_desc = desc0;
+        } else {
+          full += 8; empty += 8; a_desc += stage_units;
+        }
       }
+      if (trace) tr[4] = gtime();
     }
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
@@ -311,7 +361,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restr
       const int first_cta = (int)(((long long)block * sh.KT) / sh.U);
       float* out = P + (long long)((int)blockIdx.x - first_cta) * sh.slot_stride;
       const int n = block * TILE_ROWS + q * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * sh.m_pad);
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * acc_cols);
       for (int c0 = 0; c0 < sh.m_pad; c0 += 16) {
         if (c0 >= sh.M) break;          // warp-uniform
         float v[16];
@@ -330,6 +380,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restr
       i += len;
       ++seg;
     }
+    if (trace && warp == 2 && lane == 0) tr[5] = gtime();
   }
 
   tc_fence_before();
@@ -339,6 +390,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restr
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ncols) : "memory");
   }
+  if (trace && tid == 0) tr[6] = gtime();
   tl_end(tl);
 }
 
@@ -392,7 +444,7 @@ int pad_rows(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 1
 int stages_for(int m_pad) {
   const int stage = W_TILE_BYTES + m_pad * 128;
   int s = SMEM_BUDGET / stage;
-  return s > 10 ? 10 : s;
+  return s > 12 ? 12 : s;
 }
 
 size_t tc_smem(int m_pad, int stages) {
@@ -402,6 +454,13 @@ size_t tc_smem(int m_pad, int stages) {
 }  // namespace
 
 Q_DEFINE_STATUS_ADDR(q_tc_status_addr, g_tc_status)
+
+extern "C" int q_debug_tc_trace(unsigned long long* out, int n_ctas) {
+  Q_CHECK_ARG(out && n_ctas >= 1 && n_ctas <= 256, "q_debug_tc_trace: bad argument");
+  Q_CHECK_CUDA(cudaDeviceSynchronize());
+  Q_CHECK_CUDA(cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(unsigned long long) * 8 * n_ctas));
+  return Q_OK;
+}
 
 extern "C" int64_t q_packed_weight_bytes_tc(int N, int K) {
   if (N < 1 || K < 32 || K % 32) return -1;
@@ -488,7 +547,8 @@ int q_gemm_tc_launch(const void* d_x, const void* d_w_tc, float* d_partials, con
     const size_t smem = tc_smem(m_pad, stages);
     Q_CHECK_CUDA(q_ensure_smem(k_gemm_tc, smem, smem_done));
     Q_CHECK_CUDA(q_launch(k_gemm_tc, dim3(p.grid), dim3(TC_THREADS), smem, (cudaStream_t)stream, map,
-                          (const unsigned char*)d_w_tc, d_partials, sh, q_tl_next(Q_TL_GEMM_TC)));
+                          (const unsigned char*)d_w_tc, d_partials, sh, g_gemm_debug_flags,
+                          q_tl_next(Q_TL_GEMM_TC)));
   }
   return Q_OK;
 }

@@ -427,6 +427,7 @@ class DecodeState:
         (engine/decode.py:110-128). The device-to-host copy of step k (tokens and the status
         words its last kernel left) is enqueued before step k + 1 is launched, and awaited
         after."""
+        self.status.zero_()          # what an earlier call left; a word that is still set comes back with the first step
         for step in range(max_new_tokens):
             self.host.copy_(self.tokens, non_blocking=True)
             self.host_status.copy_(self.status, non_blocking=True)
