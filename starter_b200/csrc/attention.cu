@@ -505,20 +505,27 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
       const int head = is_q ? kh * G + h : nq + kh;
       const long long src = (long long)b * width + (long long)head * 128 + 4 * lane;
       const long long vsrc = (long long)b * width + (long long)(nq + nkv + kh) * 128 + 4 * lane;
+      // Up to four partial slots per column (the tcgen05 plan splits the packed projection
+      // four ways) are requested together; anything beyond comes one at a time.
       const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      const float4 s0 = *reinterpret_cast<const float4*>(PQ + src);
-      const float4 s1 = pv.u != 0 ? *reinterpret_cast<const float4*>(PQ + src + pv.slot_stride) : z4;
-      const float4 v0 = is_q ? z4 : *reinterpret_cast<const float4*>(PQ + vsrc);
-      const float4 v1 = (is_q || pv.u == 0) ? z4 : *reinterpret_cast<const float4*>(PQ + vsrc + pv.slot_stride);
+      const int extra = plan_count(pv, head * 128 + 4 * lane) - 1;
+      const int vextra = is_q ? 0 : plan_count(pv, (nq + nkv + kh) * 128 + 4 * lane) - 1;
+      float4 sq[4], sv[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        sq[k] = (k == 0 || (pv.u != 0 && k <= extra)) ? *reinterpret_cast<const float4*>(PQ + src + (long long)k * pv.slot_stride) : z4;
+        sv[k] = (!is_q && (k == 0 || (pv.u != 0 && k <= vextra)))
+                    ? *reinterpret_cast<const float4*>(PQ + vsrc + (long long)k * pv.slot_stride) : z4;
+      }
       const uint2 graw = *reinterpret_cast<const uint2*>((is_q ? QG : KG) + 4 * lane);
       const uint2 craw = *reinterpret_cast<const uint2*>(COS + (size_t)pos * 128 + 4 * lane);
       const uint2 sraw = *reinterpret_cast<const uint2*>(SIN + (size_t)pos * 128 + 4 * lane);
       if (!is_q) {
-        const int vcol = (nq + nkv + kh) * 128 + 4 * lane;
-        const int extra = plan_count(pv, vcol) - 1;
-        float x[4] = {v0.x, v0.y, v0.z, v0.w};
-        if (extra > 0) { x[0] += v1.x; x[1] += v1.y; x[2] += v1.z; x[3] += v1.w; }
-        for (int k = 2; k <= extra; ++k) {
+        float x[4] = {sv[0].x, sv[0].y, sv[0].z, sv[0].w};
+#pragma unroll
+        for (int k = 1; k < 4; ++k)
+          if (k <= vextra) { x[0] += sv[k].x; x[1] += sv[k].y; x[2] += sv[k].z; x[3] += sv[k].w; }
+        for (int k = 4; k <= vextra; ++k) {
           const float4 sk = *reinterpret_cast<const float4*>(PQ + vsrc + (long long)k * pv.slot_stride);
           x[0] += sk.x; x[1] += sk.y; x[2] += sk.z; x[3] += sk.w;
         }
@@ -527,10 +534,11 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
         o.y = pack_bf16(x[2], x[3]);
         *reinterpret_cast<uint2*>(vnew + 4 * lane) = o;
       }
-      const int extra = plan_count(pv, head * 128 + 4 * lane) - 1;
-      float x[4] = {s0.x, s0.y, s0.z, s0.w};
-      if (extra > 0) { x[0] += s1.x; x[1] += s1.y; x[2] += s1.z; x[3] += s1.w; }
-      for (int k = 2; k <= extra; ++k) {
+      float x[4] = {sq[0].x, sq[0].y, sq[0].z, sq[0].w};
+#pragma unroll
+      for (int k = 1; k < 4; ++k)
+        if (k <= extra) { x[0] += sq[k].x; x[1] += sq[k].y; x[2] += sq[k].z; x[3] += sq[k].w; }
+      for (int k = 4; k <= extra; ++k) {
         const float4 sk = *reinterpret_cast<const float4*>(PQ + src + (long long)k * pv.slot_stride);
         x[0] += sk.x; x[1] += sk.y; x[2] += sk.z; x[3] += sk.w;
       }

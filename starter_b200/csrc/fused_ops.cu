@@ -96,8 +96,10 @@ __device__ __forceinline__ int plan_extra(const PlanView& pv, int n) {   // slot
   return plan_count(pv, n) - 1;
 }
 
-template <int VB>
-__global__ void __launch_bounds__(256)
+// THREADS = 256, or 1024 for rows of up to 4096 columns (VB = 1): a row is then spread over
+// four times the threads, each with a third of the loads in flight.
+template <int VB, int THREADS = 256>
+__global__ void __launch_bounds__(THREADS)
 k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanView pv,
               const bf16* __restrict__ G, bf16* __restrict__ Tout, bf16* __restrict__ Nout,
               int cols, float eps, unsigned long long* tl) {
@@ -729,8 +731,10 @@ extern "C" int q_add_rmsnorm(const void* d_x_in, const float* d_branch, const q_
   Q_CHECK_ALIGN(d_normed_out, 8, "q_add_rmsnorm");
   int rc = check_plan(plan, rows, cols, "q_add_rmsnorm");
   if (rc) return rc;
-  auto kern = cols <= 1024 ? k_add_rmsnorm<1> : cols <= 3072 ? k_add_rmsnorm<3> : k_add_rmsnorm<ADD_VB>;
-  Q_CHECK_CUDA(q_launch(kern, dim3(rows), dim3(256), 0, S(stream), (const bf16*)d_x_in,
+  const bool wide = cols > 1024 && cols <= 4096 && plan != nullptr && plan->slots > 2;
+  auto kern = wide ? k_add_rmsnorm<1, 1024>
+                   : cols <= 1024 ? k_add_rmsnorm<1> : cols <= 3072 ? k_add_rmsnorm<3> : k_add_rmsnorm<ADD_VB>;
+  Q_CHECK_CUDA(q_launch(kern, dim3(rows), dim3(wide ? 1024 : 256), 0, S(stream), (const bf16*)d_x_in,
                         d_branch, plan_view(plan), (const bf16*)d_gain, (bf16*)d_total_out,
                         (bf16*)d_normed_out, cols, eps, q_tl_next(Q_TL_ADD_NORM)));
   return Q_OK;
