@@ -378,13 +378,12 @@ typedef struct q_state_t {
 } q_state_t;
 
 /* Tensor parallel over peer memory (no reference counterpart: the reference is single-GPU).
- * Every rank keeps the split-K partials of its O and down projections in a buffer the other
- * ranks can read (CUDA IPC / symmetric memory; q_engine_peer_floats() floats: the O partials
- * first, the down partials behind them), and a small array
- * of arrival words its peers write. partials[r] / flags[r] are rank r's buffers as mapped
- * into THIS process (entry `rank` is this rank's own). flags[r] holds `world` uint32 words,
- * zeroed once before the first step together with *epoch; word p of flags[r] is written by
- * rank p only. */
+ * Every rank owns a receive area the other ranks can write (CUDA IPC / symmetric memory;
+ * q_engine_peer_floats() floats: [2 halves][world][rows][hidden] pairs {fp32 sum, call
+ * counter}, 8 bytes each, the halves used by alternate calls) and a flag region (q_peer_flag_bytes() bytes) of arrival words and the
+ * token-exchange pairs. partials[r] / flags[r] are rank r's receive area and flag region as
+ * mapped into THIS process (entry `rank` is this rank's own); both are zeroed once before
+ * the first step together with the counter words. */
 #define Q_MAX_PEERS 8
 typedef struct q_peers_t {
   int32_t rank, world;
@@ -401,16 +400,16 @@ typedef struct q_peers_t {
 int64_t q_peer_flag_bytes(void);
 
 /* engine/kernels/decode_fused.py:140-158 with the cross-rank sum folded in: ONE kernel that
- * (1) tells every peer that this rank's partials at `d_own_branch` (inside partials[rank]) are
- * complete and waits (bounded) for the same word from every peer, (2) reads every rank's
- * split-K slots at the same offset through the peer mappings and adds them in rank order,
- * then slot order, in fp32, (3) rounds the sum once, adds the residual and normalises like
- * q_add_rmsnorm. It replaces q_reduce_partials + an all-reduce + q_add_rmsnorm. All ranks
- * must make the same sequence of calls; consecutive calls must use different branch buffers
- * (the engine alternates the O and the down partials), which is what lets a rank overwrite a
- * buffer again without a second barrier. A wait that runs out sets q_device_status word 3.
- * One CTA per row (the first one tells the peers, all wait for them). rows <= Q_MAX_ROWS,
- * cols a multiple of 4 up to 3072; plan NULL = one fp32 [rows][cols] sum per rank. */
+ * (1) adds this rank's split-K slots (d_own_branch: ordinary device memory, described by
+ * `plan`; plan NULL = one fp32 [rows][cols] buffer) and stores every sum, paired with this
+ * rank's call counter in one 8-byte store, into every peer's receive area (plain peer stores,
+ * no fence and no separate flag: a pair that carries this call's counter HAS arrived),
+ * (2) polls (bounded) its OWN receive area for the peers' pairs, (3) adds all ranks' sums in
+ * rank order in fp32, rounds the total once, adds the residual and normalises like
+ * q_add_rmsnorm. It
+ * replaces q_reduce_partials + an all-reduce + q_add_rmsnorm. All ranks must make the same
+ * sequence of calls. A wait that runs out sets q_device_status word 3. One CTA per row.
+ * rows <= Q_MAX_ROWS, cols a multiple of 4 up to 4096. */
 int q_add_rmsnorm_peers(const void* d_x_in, const q_peers_t* peers, const float* d_own_branch,
                         const q_gemm_plan_t* plan, const void* d_gain, void* d_total_out,
                         void* d_normed_out, int rows, int cols, float eps, void* stream);
@@ -433,9 +432,8 @@ void q_destroy(q_engine* e);
 /* Tensor parallel over peer memory: floats of the peer-readable partial buffer for `rows`,
  * and the binding (after q_bind_state). With peers bound, q_decode_step_peers runs the whole
  * sharded step - embed .. lm_head shard .. local argmax .. q_argmax_merge_peers - with
- * q_add_rmsnorm_peers in place of the two all-reduces per layer (above 8 rows a rank adds its
- * own split-K slots first, so that the peers fetch every element once). No collective library
- * call is left in the step. q_bind_peers(e, NULL) unbinds; q_bind_state unbinds too. */
+ * q_add_rmsnorm_peers in place of the two all-reduces per layer. No collective library call
+ * is left in the step. q_bind_peers(e, NULL) unbinds; q_bind_state unbinds too. */
 int64_t q_engine_peer_floats(const q_engine* e, int rows);
 int q_bind_peers(q_engine* e, const q_peers_t* peers);
 int q_decode_step_peers(q_engine* e, void* stream);

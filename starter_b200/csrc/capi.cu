@@ -501,27 +501,11 @@ extern "C" int q_step_merge(q_engine* e, const float* d_val, const int32_t* d_id
   return q_argmax_merge_tap(d_val, d_idx, e->cfg.tp_size, e->rows, s.tokens, s.pos, 1, status_tap(e), stream);
 }
 
-// Peer-readable buffer: [O partials | down partials], each rounded up to 64 floats. Above 8
-// rows each half holds ONE fp32 sum per element (the rank's own slots are added first, so
-// that the peers fetch each element once); up to 8 rows it holds the split-K slots.
-static bool peers_presum(const q_engine* e) { return e->rows > 8 || e->tc; }
-
-static long long peer_half_floats(const q_engine* e) {
-  const long long slots = hidden_plan_floats(e);
-  const long long sums = (((long long)e->rows * e->cfg.hidden + 63) / 64) * 64;
-  return slots > sums ? slots : sums;
-}
-
+// Receive area of the cross-rank sums: [2 halves][world][rows][hidden] pairs {fp32 sum, call
+// counter} of 8 bytes per rank, counted in floats.
 extern "C" int64_t q_engine_peer_floats(const q_engine* e, int rows) {
   if (!e || rows < 1 || rows > Q_MAX_ROWS) return -1;
-  long long need = 0;
-  for (int tc = 0; tc < 2; ++tc) {
-    q_engine tmp = *e;
-    if (make_plans(&tmp, rows, tc != 0)) return -1;
-    const long long n = 2 * peer_half_floats(&tmp);
-    if (n > need) need = n;
-  }
-  return need;
+  return 2ll * 2ll * e->cfg.tp_size * rows * e->cfg.hidden;
 }
 
 extern "C" int q_bind_peers(q_engine* e, const q_peers_t* peers) {
@@ -535,7 +519,7 @@ extern "C" int q_bind_peers(q_engine* e, const q_peers_t* peers) {
                   peers->rank >= 0 && peers->rank < peers->world && peers->epoch,
               "q_bind_peers: world %d does not match tp_size %d (or bad rank / no counter words)", peers->world,
               e->cfg.tp_size);
-  Q_CHECK_ARG(e->cfg.hidden % 4 == 0 && e->cfg.hidden <= 3072, "q_bind_peers: the peer step needs hidden <= 3072");
+  Q_CHECK_ARG(e->cfg.hidden % 4 == 0 && e->cfg.hidden <= 4096, "q_bind_peers: the peer step needs hidden <= 4096");
   for (int r = 0; r < peers->world; ++r)
     Q_CHECK_ARG(peers->partials[r] && peers->flags[r], "q_bind_peers: rank %d is not mapped", r);
   e->peers = *peers;
@@ -543,39 +527,24 @@ extern "C" int q_bind_peers(q_engine* e, const q_peers_t* peers) {
   return Q_OK;
 }
 
-// Cross-rank add+norm of one hidden-size projection whose partials sit in `mine` (a half of
-// this rank's peer buffer, or private memory when the slots are added up first).
-static int peers_add_norm(q_engine* e, float* half, const q_gemm_plan_t& plan, const void* gain, void* stream) {
-  const q_config_t& c = e->cfg;
-  const q_state_t& s = e->st;
-  if (peers_presum(e)) {
-    TRY(q_reduce_partials(s.partials, &plan, half, stream));
-    return q_add_rmsnorm_peers(s.x, &e->peers, half, nullptr, gain, s.x, s.normed, e->rows, c.hidden, c.rms_eps,
-                               stream);
-  }
-  return q_add_rmsnorm_peers(s.x, &e->peers, half, &plan, gain, s.x, s.normed, e->rows, c.hidden, c.rms_eps,
-                             stream);
-}
-
-// The sharded step with the cross-rank sums read from peer memory: per layer QKV, attention,
-// O, add+norm over all ranks, gate|up + SwiGLU, down, add+norm over all ranks; then the
-// lm_head shard, the local pick and the pick over the shards exchanged through peer memory.
-// The two halves of the peer buffer alternate, which is what q_add_rmsnorm_peers needs.
+// The sharded step with the cross-rank sums exchanged through peer memory: per layer QKV,
+// attention, O, add+norm over all ranks, gate|up + SwiGLU, down, add+norm over all ranks; then
+// the lm_head shard, the local pick and the pick over the shards, exchanged the same way. No
+// collective library call, and no launch besides the single-GPU step's own.
 extern "C" int q_decode_step_peers(q_engine* e, void* stream) {
   TRY(ready(e, "q_decode_step_peers"));
   Q_CHECK_ARG(e->has_peers, "q_decode_step_peers: q_bind_peers has not been called");
   Q_CHECK_ARG(e->T == 1, "q_decode_step_peers: one query token per sequence");
   const q_config_t& c = e->cfg;
   const q_state_t& s = e->st;
-  float* half0 = e->peers.partials[e->peers.rank];
-  float* half1 = half0 + peer_half_floats(e);
-  const bool presum = peers_presum(e);
   TRY(q_step_begin(e, stream));
   for (int l = 0; l < c.n_layers; ++l) {
-    TRY(attn_block(e, l, presum ? s.partials : half0, stream));
-    TRY(peers_add_norm(e, half0, e->p_o, e->layers[l].ln_post, stream));
-    TRY(mlp_block(e, l, presum ? s.partials : half1, stream));
-    TRY(peers_add_norm(e, half1, e->p_down, next_gain(e, l), stream));
+    TRY(attn_block(e, l, s.partials, stream));
+    TRY(q_add_rmsnorm_peers(s.x, &e->peers, s.partials, &e->p_o, e->layers[l].ln_post, s.x, s.normed, e->rows,
+                            c.hidden, c.rms_eps, stream));
+    TRY(mlp_block(e, l, s.partials, stream));
+    TRY(q_add_rmsnorm_peers(s.x, &e->peers, s.partials, &e->p_down, next_gain(e, l), s.x, s.normed, e->rows,
+                            c.hidden, c.rms_eps, stream));
   }
   TRY(head(e, false, stream));
   return q_argmax_merge_peers_tap(s.arg_val, s.arg_idx, &e->peers, e->rows, s.tokens, s.pos, 1, status_tap(e),

@@ -186,26 +186,28 @@ k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanVie
 
 
 // ---- residual add + RMSNorm on the partials of ALL tensor-parallel ranks ----------------
-// One CTA per row. Arrival words are written with release / read with acquire at system
-// scope; the value is this rank's call counter, the same on every rank because all ranks make
-// the same calls. CTA 0 tells the peers that this rank's partials are complete; every CTA
-// waits (bounded) for the peers' words, which live in this rank's own memory. Peer data is
-// read with volatile loads (never from a stale local cache line). The call counter is bumped
-// by the last CTA to finish (a ticket), so every CTA of a call reads the same value.
+// One CTA per row, one thread per four columns. The exchange carries its own arrival
+// signal: every fp32 sum travels as an 8-byte pair {value, call counter}, stored with one
+// 8-byte store (single-copy atomic), so there is no fence, no flag and no second trip:
+//   1. the CTA adds this rank's split-K slots of its row (fp32, slot order) and stores the
+//      pairs into EVERY peer's receive area through the peer mappings (posted writes);
+//   2. it polls (bounded) its OWN receive area until the pairs of its row carry this call's
+//      counter for every peer, adds all ranks' sums in rank order, rounds once, adds the
+//      residual and normalises.
+// The receive area has two halves used by alternate calls, so a rank may already push the
+// next call's pairs while a slower peer still reads this call's; a half is written again two
+// calls later, which a rank reaches only after every peer's pairs of the call between have
+// arrived, i.e. after every peer finished this call. A stale pair can never look fresh: it
+// carries an older counter. The call counter is bumped by the last CTA to finish (a
+// ticket), so every CTA of a call reads the same value. All ranks make the same calls.
 struct PeerView {
   int rank, world;
-  const float* partials[Q_MAX_PEERS];
+  float* recv[Q_MAX_PEERS];      // rank r's receive area [2 halves][world][rows][cols] pairs of 8 bytes
   uint32_t* flags[Q_MAX_PEERS];
-  uint32_t* epoch;     // [0] call counter of the add+norm exchange, [1] its ticket, [2] counter of the argmax exchange
+  uint32_t* epoch;     // [0] call counter of the add+norm exchange, [1] its ticket, [2] counter of the token exchange
 };
 
-__device__ int g_peer_status;      // 1 = a wait for a peer's arrival word ran out
-
-__device__ __forceinline__ float4 ld_peer(const float* p) {
-  float4 v;
-  asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-  return v;
-}
+__device__ int g_peer_status;      // 1 = a wait for a peer ran out
 
 // Bounded wait for `word` to reach `e` (wrap-around safe). The limit is in polling
 // iterations; the back-off grows to 2 us per poll, so the default 2^21 is about 4 s: a peer
@@ -220,11 +222,22 @@ __device__ __forceinline__ bool wait_arrival(const uint32_t* word, unsigned e, i
   return false;
 }
 
-__global__ void __launch_bounds__(256)
-k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, long long branch_off, PlanView pv,
+__device__ __forceinline__ void st_pair2(void* p, float a, float b, unsigned e) {
+  // two {value, counter} pairs, each element an 8-byte single-copy-atomic store
+  asm volatile("st.volatile.global.v2.b64 [%0], {%1, %2};" ::"l"(p),
+               "l"(((unsigned long long)e << 32) | __float_as_uint(a)),
+               "l"(((unsigned long long)e << 32) | __float_as_uint(b)) : "memory");
+}
+__device__ __forceinline__ void ld_pair2(const void* p, unsigned long long& a, unsigned long long& b) {
+  asm volatile("ld.volatile.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+
+constexpr int PEER_MAX_COLS = 4096;     // one thread per four columns, at most 1024 threads
+
+__global__ void __launch_bounds__(1024)
+k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, const float* __restrict__ P, PlanView pv,
                     const bf16* __restrict__ G, bf16* __restrict__ Tout, bf16* __restrict__ Nout,
                     int rows, int cols, float eps, int wait_iters, unsigned long long* tl) {
-  constexpr int VB = 3;
   __shared__ float red[32];
   __shared__ unsigned s_epoch;
   tl_begin(tl);
@@ -233,93 +246,87 @@ k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, long long branch_
   tl_waited(tl);
   const int tid = threadIdx.x;
   const int row = blockIdx.x;
+  const int col = 4 * tid;
+  const bool live = col < cols;
   if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned*>(pw.epoch) + 1u;
-  __syncthreads();
-  const unsigned e = s_epoch;
-  if (tid < pw.world && tid != pw.rank) {
-    if (row == 0) {
-      __threadfence_system();
-      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pw.flags[tid] + pw.rank), "r"(e) : "memory");
-    }
-    if (!wait_arrival(pw.flags[pw.rank] + tid, e, wait_iters)) atomicExch(&g_peer_status, 1);
+  // operands that do not depend on the peers: own slots, residual, gain
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float* p0 = P + (size_t)row * cols + (live ? col : 0);
+  const int extra = live ? plan_count(pv, col) - 1 : -1;
+  float4 sl[10];
+#pragma unroll
+  for (int k = 0; k < 10; ++k)
+    sl[k] = (k <= extra && (k == 0 || pv.u != 0)) ? *reinterpret_cast<const float4*>(p0 + (long long)k * pv.slot_stride) : z4;
+  const uint2 xr = live ? *reinterpret_cast<const uint2*>(Xin + (size_t)row * cols + col) : make_uint2(0, 0);
+  const uint2 gn = live ? *reinterpret_cast<const uint2*>(G + col) : make_uint2(0, 0);
+  float4 own = sl[0];
+#pragma unroll
+  for (int k = 1; k < 10; ++k)
+    if (k <= extra) { own.x += sl[k].x; own.y += sl[k].y; own.z += sl[k].z; own.w += sl[k].w; }
+  for (int k = 10; k <= extra; ++k) {
+    const float4 t = *reinterpret_cast<const float4*>(p0 + (long long)k * pv.slot_stride);
+    own.x += t.x; own.y += t.y; own.z += t.z; own.w += t.w;
   }
   __syncthreads();
-  {
-    // All loads of up to four ranks are issued before any is used (a load and its use back
-    // to back would cost one NVLink round trip per load: the pipeline issues in order).
-    float4 acc[VB];
-    uint2 xr[VB], gn[VB];
-    int cnt[VB];
+  const unsigned e = s_epoch;
+  // element offsets in 8-byte pairs: halves alternate with the call counter
+  const size_t half_off = (size_t)(e & 1u) * pw.world * rows * cols;
+  const size_t mine = half_off + ((size_t)pw.rank * rows + row) * cols + col;
+  // 1. push this rank's pairs to every peer
+  if (live) {
 #pragma unroll
-    for (int j = 0; j < VB; ++j) {
-      const int col = 4 * tid + j * 1024;
-      const int cc = col < cols ? col : 0;
-      acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-      xr[j] = *reinterpret_cast<const uint2*>(Xin + (size_t)row * cols + cc);
-      gn[j] = *reinterpret_cast<const uint2*>(G + cc);
-      cnt[j] = plan_count(pv, cc);
-    }
-    for (int r0 = 0; r0 < pw.world; r0 += 4) {
-      float4 v[4][VB][2];
-#pragma unroll
-      for (int rr = 0; rr < 4; ++rr)
-#pragma unroll
-        for (int j = 0; j < VB; ++j) {
-          const int col = 4 * tid + j * 1024;
-          const int cc = col < cols ? col : 0;
-          const bool live = r0 + rr < pw.world;
-          const float* base = pw.partials[live ? r0 + rr : pw.rank] + branch_off + (size_t)row * cols + cc;
-          v[rr][j][0] = live ? ld_peer(base) : make_float4(0.f, 0.f, 0.f, 0.f);
-          v[rr][j][1] = (live && cnt[j] > 1) ? ld_peer(base + pv.slot_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-      for (int rr = 0; rr < 4; ++rr)
-#pragma unroll
-        for (int j = 0; j < VB; ++j) {
-          acc[j].x += v[rr][j][0].x; acc[j].y += v[rr][j][0].y; acc[j].z += v[rr][j][0].z; acc[j].w += v[rr][j][0].w;
-          acc[j].x += v[rr][j][1].x; acc[j].y += v[rr][j][1].y; acc[j].z += v[rr][j][1].z; acc[j].w += v[rr][j][1].w;
-          if (r0 + rr < pw.world && cnt[j] > 2) {      // more than two slots: rare, one at a time
-            const int col = 4 * tid + j * 1024;
-            const int cc = col < cols ? col : 0;
-            const float* base = pw.partials[r0 + rr] + branch_off + (size_t)row * cols + cc;
-            for (int k = 2; k < cnt[j]; ++k) {
-              const float4 t = ld_peer(base + (long long)k * pv.slot_stride);
-              acc[j].x += t.x; acc[j].y += t.y; acc[j].z += t.z; acc[j].w += t.w;
-            }
-          }
-        }
-    }
-    float tot[VB][4];
-    float ss = 0.f;
-#pragma unroll
-    for (int j = 0; j < VB; ++j) {
-      const int col = 4 * tid + j * 1024;
-      if (col < cols) {
-        const float s[4] = {acc[j].x, acc[j].y, acc[j].z, acc[j].w};
-        const float r4[4] = {bf_lo(xr[j].x), bf_hi(xr[j].x), bf_lo(xr[j].y), bf_hi(xr[j].y)};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          tot[j][q] = bf16_round(r4[q] + bf16_round(s[q]));
-          ss += tot[j][q] * tot[j][q];
-        }
+    for (int r = 0; r < Q_MAX_PEERS; ++r)
+      if (r < pw.world && r != pw.rank) {
+        char* dst = reinterpret_cast<char*>(pw.recv[r]) + mine * 8;
+        st_pair2(dst, own.x, own.y, e);
+        st_pair2(dst + 16, own.z, own.w, e);
       }
-    }
-    ss = block_sum(ss, red);
-    const float inv = rsqrtf(ss / (float)cols + eps);
-#pragma unroll
-    for (int j = 0; j < VB; ++j) {
-      const int col = 4 * tid + j * 1024;
-      if (col < cols) {
-        const float g4[4] = {bf_lo(gn[j].x), bf_hi(gn[j].x), bf_lo(gn[j].y), bf_hi(gn[j].y)};
-        uint2 to, no;
-        to.x = pack_bf16(tot[j][0], tot[j][1]);
-        to.y = pack_bf16(tot[j][2], tot[j][3]);
-        no.x = pack_bf16(bf16_round(tot[j][0] * inv) * g4[0], bf16_round(tot[j][1] * inv) * g4[1]);
-        no.y = pack_bf16(bf16_round(tot[j][2] * inv) * g4[2], bf16_round(tot[j][3] * inv) * g4[3]);
-        *reinterpret_cast<uint2*>(Tout + (size_t)row * cols + col) = to;
-        *reinterpret_cast<uint2*>(Nout + (size_t)row * cols + col) = no;
+  }
+  // 2. collect the peers' pairs of this row from the own receive area, in rank order
+  float tot[4] = {0.f, 0.f, 0.f, 0.f};
+  float ss = 0.f;
+  if (live) {
+    float4 acc = z4;
+    bool ok = true;
+    for (int r = 0; r < pw.world; ++r) {
+      float4 t = own;
+      if (r != pw.rank) {
+        const char* src = reinterpret_cast<const char*>(pw.recv[pw.rank]) + (half_off + ((size_t)r * rows + row) * cols + col) * 8;
+        unsigned long long a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+        bool here = false;
+        for (int i = 0; ok && i < wait_iters; ++i) {
+          ld_pair2(src, a0, a1);
+          ld_pair2(src + 16, a2, a3);
+          here = (unsigned)(a0 >> 32) == e && (unsigned)(a1 >> 32) == e && (unsigned)(a2 >> 32) == e &&
+                 (unsigned)(a3 >> 32) == e;
+          if (here) break;
+          if (i > 64) __nanosleep(i > 65536 ? 2000 : (i > 4096 ? 400 : 40));
+        }
+        if (!here) { ok = false; atomicExch(&g_peer_status, 1); }
+        t = make_float4(__uint_as_float((unsigned)a0), __uint_as_float((unsigned)a1), __uint_as_float((unsigned)a2),
+                        __uint_as_float((unsigned)a3));
       }
+      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
     }
+    const float s4[4] = {acc.x, acc.y, acc.z, acc.w};
+    const float r4[4] = {bf_lo(xr.x), bf_hi(xr.x), bf_lo(xr.y), bf_hi(xr.y)};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      tot[q] = bf16_round(r4[q] + bf16_round(s4[q]));
+      ss += tot[q] * tot[q];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)cols + eps);
+  if (live) {
+    const float g4[4] = {bf_lo(gn.x), bf_hi(gn.x), bf_lo(gn.y), bf_hi(gn.y)};
+    uint2 to, no;
+    to.x = pack_bf16(tot[0], tot[1]);
+    to.y = pack_bf16(tot[2], tot[3]);
+    no.x = pack_bf16(bf16_round(tot[0] * inv) * g4[0], bf16_round(tot[1] * inv) * g4[1]);
+    no.y = pack_bf16(bf16_round(tot[2] * inv) * g4[2], bf16_round(tot[3] * inv) * g4[3]);
+    *reinterpret_cast<uint2*>(Tout + (size_t)row * cols + col) = to;
+    *reinterpret_cast<uint2*>(Nout + (size_t)row * cols + col) = no;
   }
   // the last CTA of the call publishes the new call counter
   __syncthreads();
@@ -749,10 +756,10 @@ static int peer_view(const q_peers_t* peers, PeerView* out, const char* who) {
   out->world = peers->world;
   out->epoch = peers->epoch;
   for (int r = 0; r < Q_MAX_PEERS; ++r) {
-    out->partials[r] = r < peers->world ? peers->partials[r] : nullptr;
+    out->recv[r] = r < peers->world ? peers->partials[r] : nullptr;
     out->flags[r] = r < peers->world ? peers->flags[r] : nullptr;
-    Q_CHECK_ARG(r >= peers->world || (out->partials[r] && out->flags[r]), "%s: rank %d unmapped", who, r);
-    Q_CHECK_ARG(((uintptr_t)out->partials[r] & 15) == 0 && ((uintptr_t)out->flags[r] & 15) == 0,
+    Q_CHECK_ARG(r >= peers->world || (out->recv[r] && out->flags[r]), "%s: rank %d unmapped", who, r);
+    Q_CHECK_ARG(((uintptr_t)out->recv[r] & 15) == 0 && ((uintptr_t)out->flags[r] & 15) == 0,
                 "%s: peer buffers must be 16-byte aligned", who);
   }
   return Q_OK;
@@ -763,20 +770,20 @@ extern "C" int q_add_rmsnorm_peers(const void* d_x_in, const q_peers_t* peers, c
                                    void* d_normed_out, int rows, int cols, float eps, void* stream) {
   Q_CHECK_ARG(d_x_in && peers && d_own_branch && d_gain && d_total_out && d_normed_out,
               "q_add_rmsnorm_peers: null pointer");
-  Q_CHECK_ARG(rows >= 1 && rows <= Q_MAX_ROWS && cols >= 4 && cols % 4 == 0 && cols <= 3072,
-              "q_add_rmsnorm_peers: needs 1..%d rows and cols a multiple of 4 up to 3072", Q_MAX_ROWS);
+  Q_CHECK_ARG(rows >= 1 && rows <= Q_MAX_ROWS && cols >= 4 && cols % 4 == 0 && cols <= PEER_MAX_COLS,
+              "q_add_rmsnorm_peers: needs 1..%d rows and cols a multiple of 4 up to %d", Q_MAX_ROWS, PEER_MAX_COLS);
   Q_CHECK_ARG((((uintptr_t)d_x_in | (uintptr_t)d_gain | (uintptr_t)d_total_out | (uintptr_t)d_normed_out) & 7) == 0,
               "q_add_rmsnorm_peers: bf16 operands must be 8-byte aligned");
+  Q_CHECK_ALIGN(d_own_branch, 16, "q_add_rmsnorm_peers");
   int rc = check_plan(plan, rows, cols, "q_add_rmsnorm_peers");
   if (rc) return rc;
   PeerView pw;
   rc = peer_view(peers, &pw, "q_add_rmsnorm_peers");
   if (rc) return rc;
-  const long long off = d_own_branch - peers->partials[peers->rank];
-  Q_CHECK_ARG(off >= 0 && off % 4 == 0, "q_add_rmsnorm_peers: the branch is not inside this rank's peer buffer");
-  Q_CHECK_CUDA(q_launch(k_add_rmsnorm_peers, dim3(rows), dim3(256), 0, S(stream), (const bf16*)d_x_in, pw, off,
-                        plan_view(plan), (const bf16*)d_gain, (bf16*)d_total_out, (bf16*)d_normed_out, rows,
-                        cols, eps, g_peer_wait_iters, q_tl_next(Q_TL_PEER_ADD_NORM)));
+  const int threads = ((cols / 4 + 31) / 32) * 32;
+  Q_CHECK_CUDA(q_launch(k_add_rmsnorm_peers, dim3(rows), dim3(threads), 0, S(stream), (const bf16*)d_x_in, pw,
+                        d_own_branch, plan_view(plan), (const bf16*)d_gain, (bf16*)d_total_out,
+                        (bf16*)d_normed_out, rows, cols, eps, g_peer_wait_iters, q_tl_next(Q_TL_PEER_ADD_NORM)));
   return Q_OK;
 }
 

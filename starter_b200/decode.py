@@ -166,11 +166,11 @@ class DecodeState:
         self.tp_path = "single" if self.tp == 1 else ("peers" if self.peers else "nccl")
 
     def _bind_peers(self) -> None:
-        """Puts the O / down split-K partials of every rank into symmetric memory and hands the
-        peer mappings to the library, so that the two cross-rank sums per layer are read from
-        peer memory inside q_add_rmsnorm_peers instead of going through an all-reduce. All
-        ranks agree on the outcome; if any of them cannot map the others, all keep the
-        all-reduce path."""
+        """Allocates this rank's receive area and flag region in symmetric memory and hands the
+        peer mappings to the library, so that the two cross-rank sums per layer (and the token
+        pick) are exchanged with plain peer stores inside the step's own kernels instead of
+        going through collectives. All ranks agree on the outcome; if any of them cannot map the
+        others, all keep the NCCL path."""
         import torch.distributed as dist
         group = self.group if self.group is not None else dist.group.WORLD
         ok, err = 1, ""
@@ -225,25 +225,21 @@ class DecodeState:
         import torch.distributed as dist
         cfg, dev = self.cfg, self.device
         rank, world = peers.rank, peers.world
-        half = n_floats // 2
-        own = torch.full((n_floats,), (rank + 1) / 16.0, dtype=torch.float32, device=dev)
-        view = self.peer_buffer[:n_floats * 4].view(torch.float32)
-        view.copy_(own)
-        torch.cuda.synchronize(dev)
-        dist.barrier(group=group)
+        own = torch.full((self.rows, cfg.hidden), (rank + 1) / 16.0, dtype=torch.float32, device=dev)
         zeros = torch.zeros((self.rows, cfg.hidden), dtype=torch.bfloat16, device=dev)
         ones = torch.ones(cfg.hidden, dtype=torch.bfloat16, device=dev)
         total, normed = torch.empty_like(zeros), torch.empty_like(zeros)
         s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-        rc = lib.q_add_rmsnorm_peers(_p(zeros), C.byref(peers), C.c_void_p(view.data_ptr() + half * 4),
-                                     None, _p(ones), _p(total), _p(normed), self.rows, cfg.hidden,
-                                     float(cfg.rms_eps), s)
-        torch.cuda.synchronize(dev)
-        unit = sum(r + 1 for r in range(world)) / 16.0
-        good = rc == 0 and bool((total.float() == unit).all()) and self._device_status()[3] == 0
+        good = True
+        for _ in range(2):                       # both halves of the receive area
+            rc = lib.q_add_rmsnorm_peers(_p(zeros), C.byref(peers), _p(own), None, _p(ones), _p(total),
+                                         _p(normed), self.rows, cfg.hidden, float(cfg.rms_eps), s)
+            torch.cuda.synchronize(dev)
+            unit = sum(r + 1 for r in range(world)) / 16.0
+            good = good and rc == 0 and bool((total.float() == unit).all())
+        good = good and self._device_status()[3] == 0
         verdict = torch.tensor([1 if good else 0], dtype=torch.int32, device=dev)
         dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=group)
-        view.zero_()
         torch.cuda.synchronize(dev)
         dist.barrier(group=group)
         return bool(int(verdict.item()))

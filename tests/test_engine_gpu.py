@@ -292,27 +292,29 @@ def test_device_status_is_surfaced_and_cleared(cuda, golden_dir):
     lib, check = _lib.lib, _lib.check
     clear_status()
     rows, cols = 2, 256
-    buf = torch.zeros(rows * cols * 2 + lib.q_peer_flag_bytes() // 4, dtype=torch.float32, device="cuda")
+    recv = 2 * 2 * 2 * rows * cols                   # [2 halves][world][rows][cols] pairs of 2 floats
+    buf = torch.zeros(recv + lib.q_peer_flag_bytes() // 4, dtype=torch.float32, device="cuda")
+    own = torch.ones((rows, cols), dtype=torch.float32, device="cuda")
     counters = torch.zeros(4, dtype=torch.int32, device="cuda")
     peers = _lib.Peers()
     peers.rank, peers.world = 0, 2
     for r in range(2):
         peers.partials[r] = buf.data_ptr()
-        peers.flags[r] = buf.data_ptr() + rows * cols * 2 * 4
+        peers.flags[r] = buf.data_ptr() + recv * 4
     peers.epoch = counters.data_ptr()
     x = torch.zeros((rows, cols), dtype=torch.bfloat16, device="cuda")
     gain = torch.ones(cols, dtype=torch.bfloat16, device="cuda")
     total, normed = torch.empty_like(x), torch.empty_like(x)
     check(lib.q_set_option(b"peer_wait_iters", 2000))
     try:
-        check(lib.q_add_rmsnorm_peers(C.c_void_p(x.data_ptr()), C.byref(peers), C.c_void_p(buf.data_ptr()), None,
+        check(lib.q_add_rmsnorm_peers(C.c_void_p(x.data_ptr()), C.byref(peers), C.c_void_p(own.data_ptr()), None,
                                       C.c_void_p(gain.data_ptr()), C.c_void_p(total.data_ptr()),
                                       C.c_void_p(normed.data_ptr()), rows, cols, 1e-6, None))
         torch.cuda.synchronize()
     finally:
         check(lib.q_set_option(b"peer_wait_iters", 1 << 21))
     assert device_status() == [0, 0, 0, 1]
-    assert counters[0].item() == 1 and counters[1].item() == 0          # the call completed
+    assert counters.tolist() == [1, 0, 0, 0]                            # the call completed, ticket re-armed
     engine = Engine(str(golden_dir / "tiny_qwen3"))
     with pytest.raises(_lib.QDecodeError, match="peer exchange"):
         list(engine.generate([[1, 2, 3]], 4))

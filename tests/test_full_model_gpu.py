@@ -5,7 +5,8 @@ teacher-forced on the engine's own tokens.
 
 Native Hugging Face is itself noisy at this width: its cached-decode logits differ
 from its own full forward by a few hundredths (the measured self-noise is printed
-and bounds the tolerance), so the bar is max(2e-2, 1.5 x self-noise)."""
+and bounds the tolerance), so the bar is max(2e-2, 2 x self-noise): two correct evaluations each sit up to one
+self-noise away from the exact value."""
 import os
 import sys
 from pathlib import Path
@@ -43,7 +44,8 @@ def test_qwen3_4b_logits_and_tokens_vs_native_cpu():
     agree = 0
     while agree < 16 and cached_tokens[agree] == tokens[agree]:
         agree += 1
-    noise = float((cached[:max(agree, 1)] - ref[:max(agree, 1)]).abs().max())
+    from tests.test_full_width_gpu import native_cached_teacher_forced
+    noise = float((native_cached_teacher_forced(native, prompt, tokens) - ref).abs().max())
     diff = (logits.float() - ref).abs().amax(-1)                   # [16, 1]
     gaps = ref.max(-1).values - ref.gather(-1, torch.tensor(tokens)[..., None])[..., 0]
     print(f"max abs logit diff {float(diff.max()):.4f}; native self-noise {noise:.4f}; "
@@ -56,6 +58,6 @@ def test_qwen3_4b_logits_and_tokens_vs_native_cpu():
         "tokens_equal_native_cached": agree, "steps": 16,
         "largest_top1_gap_of_emitted": float(gaps.max()),
         "near_tie_gaps": [float(g) for g in gaps.flatten() if g > 0]})
-    tol = max(2e-2, 1.5 * noise)
+    tol = max(2e-2, 2 * noise)
     assert float(diff.max()) <= tol, (float(diff.max()), tol)
     assert float(gaps.max()) <= tol
