@@ -24,7 +24,6 @@ from __future__ import annotations
 import ctypes as C
 import os
 import sys
-import weakref
 
 import torch
 import torch.nn.functional as F
@@ -36,11 +35,6 @@ from .weights import PackedWeights, rotary_tables
 
 def _p(t):
     return C.c_void_p(0 if t is None else t.data_ptr())
-
-
-def _rms(x, w, eps):
-    f = x.float()
-    return (f * torch.rsqrt(f.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
 
 
 TC_MIN_ROWS = 9     # rows from which the projections run on the tcgen05 kernel
@@ -260,87 +254,120 @@ class DecodeState:
         kv_token = cfg.n_layers * 2 * w.local_kv_heads * HEAD_DIM * 2
         return weights + kv_token * self.batch * visible_keys + kv_token * self.batch
 
-    # ---- prefill: outside the per-step hot path (library GEMMs + SDPA) ----
-    def _allreduce(self, t):
-        if self.tp > 1:
-            torch.distributed.all_reduce(t, group=self.group)
-        return t
+    # ---- prefill: the prompt pass ----
+    PREFILL_ROWS = 2048        # prompt rows processed together (bounds the fp32 partial scratch)
 
-    def _linear_rowpar(self, x, weight):
-        """Row-parallel Linear: fp32 partial per rank, all-reduce, one bf16 rounding."""
-        if self.tp == 1:
-            return F.linear(x, weight)
-        flat = x.reshape(-1, x.shape[-1])
-        part = torch.mm(flat, weight.t(), out_dtype=torch.float32)
-        return self._allreduce(part).to(torch.bfloat16).view(*x.shape[:-1], weight.shape[0])
+    def _prefill_scratch(self, rows: int):
+        """Buffers of the prompt pass for `rows` rows, kept for the next call of the same size."""
+        if getattr(self, "_pf", None) is not None and self._pf["rows"] == rows:
+            return self._pf
+        cfg, w, dev = self.cfg, self.w, self.device
+        nq, nkv, inter = w.local_q_heads, w.local_kv_heads, w.local_inter
+        plans = {"qkv": _lib.plan(rows, (nq + 2 * nkv) * HEAD_DIM, cfg.hidden, tc=True),
+                 "o": _lib.plan(rows, cfg.hidden, nq * HEAD_DIM, tc=True),
+                 "gu": _lib.plan(rows, 2 * inter, cfg.hidden, tc=True),
+                 "down": _lib.plan(rows, cfg.hidden, inter, tc=True)}
+        n_part = max(p.slots * p.M * p.N for p in plans.values())
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        self._pf = None                    # release the previous size first
+        self._pf = {
+            "rows": rows, "plans": plans, "partials": torch.empty(n_part, dtype=torch.float32, device=dev),
+            "x": torch.empty((rows, cfg.hidden), **bf), "normed": torch.empty((rows, cfg.hidden), **bf),
+            "q": torch.empty((rows, nq, HEAD_DIM), **bf), "k": torch.empty((rows, nkv, HEAD_DIM), **bf),
+            "v": torch.empty((rows, nkv, HEAD_DIM), **bf), "att": torch.empty((rows, nq * HEAD_DIM), **bf),
+            "act": torch.empty((rows, inter), **bf), "zero": torch.zeros(1, dtype=torch.int32, device=dev),
+            "reduced": torch.empty((rows, cfg.hidden), dtype=torch.float32, device=dev) if self.tp > 1 else None,
+        }
+        return self._pf
 
     def prefill(self, input_ids: torch.Tensor) -> torch.Tensor:
-        """Runs the whole prompt, fills the KV pages, leaves the first generated
-        token in `tokens` and the prompt length in `position`. Returns the last
-        position's local logits [B, V_local]."""
+        """Runs the whole prompt, fills the KV pages, leaves the first generated token in
+        `tokens` and the prompt length in `position`. Returns the last position's local logits
+        [B, V_local].
+
+        The prompt pass of the reference (engine/prefill.py:26-62) on this library's own
+        kernels: every projection on the tcgen05 kernel over the tiled weights (256 prompt rows
+        per weight pass), embedding + norm, add + norm, SwiGLU and head norm + RoPE + page write
+        (engine/kernels/prefill.py:19-63) as the fused consumers of the decode step, lm_head and
+        argmax likewise. Only the causal attention over the prompt is a library call (PyTorch's
+        scaled_dot_product_attention on the token-major K / V rows the RoPE kernel leaves beside
+        the pages). Sequences are processed PREFILL_ROWS prompt rows at a time. Under tensor
+        parallelism the two row-parallel projections are summed over the ranks in fp32 by an
+        NCCL all-reduce before the single rounding (the prompt pass is outside the per-step
+        path)."""
         cfg, w = self.cfg, self.w
         B, T = input_ids.shape
         if B != self.batch or T != self.shape[1]:
             raise ValueError("prompt shape disagrees with this decode state")
-        nq, nkv = w.local_q_heads, w.local_kv_heads
-        eps = cfg.rms_eps
-        cos, sin = self.cos[:T][None, :, None, :], self.sin[:T][None, :, None, :]
-
-        def rotate(t):
-            half = torch.cat((-t[..., HEAD_DIM // 2:], t[..., :HEAD_DIM // 2]), -1)
-            return t * cos + half * sin
-
-        # Prefill runs on library GEMMs over row-major weights: each tiled matrix is
-        # expanded into a scratch buffer just before use (one layer at a time).
-        embed_rows = w.embed.rows()
-        x = embed_rows[input_ids]                                     # [B, T, H]
-        if w.lm_head.data_ptr() == w.embed.data_ptr() and w.lm_head.shape == w.embed.shape:
-            lm_rows = embed_rows
-        else:
-            del embed_rows
-            lm_rows = None
-        for i, lt in enumerate(w.layers):
-            wqkv, wo, wgu, wdown = lt.wqkv.rows(), lt.wo.rows(), lt.wgu.rows(), lt.wdown.rows()
-            h = _rms(x, lt.ln_in, eps)
-            qkv = F.linear(h, wqkv)
-            q, k, v = qkv.split((nq * HEAD_DIM, nkv * HEAD_DIM, nkv * HEAD_DIM), -1)
-            q = rotate(_rms(q.reshape(B, T, nq, HEAD_DIM), lt.q_gain, eps)).transpose(1, 2)
-            k = rotate(_rms(k.reshape(B, T, nkv, HEAD_DIM), lt.k_gain, eps)).transpose(1, 2)
-            v = v.reshape(B, T, nkv, HEAD_DIM).transpose(1, 2)
-            kc, vc = k.contiguous(), v.contiguous()
-            layout = _lib.KVLayout(self.kpools[i].data_ptr(), self.vpools[i].data_ptr(),
-                                   self.block_table.data_ptr(), self.pages_per_seq, nkv)
-            check(lib.q_kv_scatter(_p(kc), _p(vc), C.byref(layout), B, T, 0,
-                                   C.c_void_p(torch.cuda.current_stream().cuda_stream)))
-            att = F.scaled_dot_product_attention(q, kc, vc, is_causal=True, enable_gqa=True)
-            att = att.transpose(1, 2).reshape(B, T, nq * HEAD_DIM)
-            x = x + self._linear_rowpar(att, wo)
-            h = _rms(x, lt.ln_post, eps)
-            gate, up = F.linear(h, wgu).chunk(2, -1)
-            x = x + self._linear_rowpar(F.silu(gate) * up, wdown)
-            del wqkv, wo, wgu, wdown
-        last = _rms(x[:, -1], w.ln_final, eps)
-        if lm_rows is None:
-            lm_rows = w.lm_head.rows()
-        logits = F.linear(last, lm_rows)                              # [B, V_local]
-        del lm_rows
-        if self.tp == 1:
-            self.tokens.copy_(logits.argmax(-1))
-        else:
-            val, idx = logits.float().max(-1)
-            # torch.max returns the first maximal index on CUDA for 1-D reductions of
-            # distinct values; resolve exact ties explicitly to the lowest index.
-            first = (logits.float() == val[:, None]).int().argmax(-1)
-            vals = [torch.empty_like(val) for _ in range(self.tp)]
-            idxs = [torch.empty_like(first) for _ in range(self.tp)]
-            torch.distributed.all_gather(vals, val, group=self.group)
-            torch.distributed.all_gather(idxs, first + w.vocab_offset, group=self.group)
-            vals, idxs = torch.stack(vals), torch.stack(idxs)
-            best = vals.max(0).values
-            cand = torch.where(vals == best[None], idxs, torch.full_like(idxs, 2 ** 62))
-            self.tokens.copy_(cand.min(0).values)
+        if input_ids.dtype != torch.int64 or not input_ids.is_cuda:
+            raise ValueError("prompt ids must be an int64 CUDA tensor")
+        w.ensure_tc()
+        nq, nkv, inter = w.local_q_heads, w.local_kv_heads, w.local_inter
+        H, eps = cfg.hidden, float(cfg.rms_eps)
+        per = max(1, self.PREFILL_ROWS // T)                 # sequences per pass
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        ids = input_ids.contiguous()
+        logits = torch.empty((B, w.local_vocab), dtype=torch.bfloat16, device=self.device)
+        last = torch.empty((B, H), dtype=torch.bfloat16, device=self.device)
+        for b0 in range(0, B, per):
+            nb = min(per, B - b0)
+            rows = nb * T
+            pf = self._prefill_scratch(rows)
+            pl, part = pf["plans"], pf["partials"]
+            x, normed, act = pf["x"], pf["normed"], pf["act"]
+            table = self.block_table.data_ptr() + b0 * self.pages_per_seq * 4
+            check(lib.q_embed_rmsnorm(_p(ids[b0:b0 + nb]), _p(w.embed), _p(w.layers[0].ln_in), _p(x), _p(normed),
+                                      rows, H, cfg.vocab, eps, stream))
+            for i, lt in enumerate(w.layers):
+                check(lib.q_gemm_tc(_p(normed), _p(lt.wqkv.tc()), _p(part), rows, pl["qkv"].N, H, stream))
+                layout = _lib.KVLayout(self.kpools[i].data_ptr(), self.vpools[i].data_ptr(), table,
+                                       self.pages_per_seq, nkv)
+                check(lib.q_qkv_norm_rope_prefill(_p(part), C.byref(pl["qkv"]), _p(lt.q_gain), _p(lt.k_gain),
+                                                  _p(self.cos), _p(self.sin), _p(pf["zero"]), _p(pf["q"]),
+                                                  _p(pf["k"]), _p(pf["v"]), C.byref(layout), nb, T, nq, eps, stream))
+                q4 = pf["q"].view(nb, T, nq, HEAD_DIM).transpose(1, 2)
+                k4 = pf["k"].view(nb, T, nkv, HEAD_DIM).transpose(1, 2)
+                v4 = pf["v"].view(nb, T, nkv, HEAD_DIM).transpose(1, 2)
+                att = F.scaled_dot_product_attention(q4, k4, v4, is_causal=True, enable_gqa=True)
+                pf["att"].view(nb, T, nq, HEAD_DIM).copy_(att.transpose(1, 2))
+                check(lib.q_gemm_tc(_p(pf["att"]), _p(lt.wo.tc()), _p(part), rows, H, nq * HEAD_DIM, stream))
+                self._prefill_add_norm(pf, pl["o"], lt.ln_post, rows, stream)
+                check(lib.q_gemm_tc(_p(normed), _p(lt.wgu.tc()), _p(part), rows, 2 * inter, H, stream))
+                check(lib.q_swiglu(_p(part), C.byref(pl["gu"]), _p(act), rows, inter, stream))
+                check(lib.q_gemm_tc(_p(act), _p(lt.wdown.tc()), _p(part), rows, H, inter, stream))
+                gain = w.layers[i + 1].ln_in if i + 1 < len(w.layers) else w.ln_final
+                self._prefill_add_norm(pf, pl["down"], gain, rows, stream)
+            last[b0:b0 + nb].copy_(normed.view(nb, T, H)[:, -1])
+        # lm_head on the last position of every sequence, logits rounded once to bf16
+        hp = _lib.plan(B, w.local_vocab, H, tc=True)
+        head_part = torch.empty((hp.slots, B, w.local_vocab), dtype=torch.float32, device=self.device)
+        check(lib.q_gemm_tc(_p(last), _p(w.lm_head.tc()), _p(head_part), B, w.local_vocab, H, stream))
+        val = torch.empty(B, dtype=torch.float32, device=self.device)
+        idx = torch.empty(B, dtype=torch.int32, device=self.device)
+        scratch = torch.zeros(lib.q_argmax_scratch_bytes(B, w.local_vocab), dtype=torch.uint8, device=self.device)
+        check(lib.q_logits_argmax(_p(head_part), C.byref(hp), _p(logits), _p(val), _p(idx),
+                                  _p(self.tokens) if self.tp == 1 else None, None, 0, _p(scratch), B,
+                                  w.local_vocab, w.vocab_offset, stream))
+        if self.tp > 1:
+            gv = torch.empty((self.tp, B), dtype=torch.float32, device=self.device)
+            gi = torch.empty((self.tp, B), dtype=torch.int32, device=self.device)
+            torch.distributed.all_gather_into_tensor(gv, val, group=self.group)
+            torch.distributed.all_gather_into_tensor(gi, idx, group=self.group)
+            check(lib.q_argmax_merge(_p(gv), _p(gi), self.tp, B, _p(self.tokens), None, 0, stream))
         self.position.fill_(T)
         return logits
+
+    def _prefill_add_norm(self, pf, plan, gain, rows: int, stream) -> None:
+        """x, normed <- add + RMSNorm of the projection partials in pf['partials'] (summed over
+        the tensor-parallel ranks first, in fp32)."""
+        H, eps = self.cfg.hidden, float(self.cfg.rms_eps)
+        x, normed, part = pf["x"], pf["normed"], pf["partials"]
+        if self.tp == 1:
+            check(lib.q_add_rmsnorm(_p(x), _p(part), C.byref(plan), _p(gain), _p(x), _p(normed), rows, H, eps, stream))
+            return
+        check(lib.q_reduce_partials(_p(part), C.byref(plan), _p(pf["reduced"]), stream))
+        torch.distributed.all_reduce(pf["reduced"], group=self.group)
+        check(lib.q_add_rmsnorm(_p(x), _p(pf["reduced"]), None, _p(gain), _p(x), _p(normed), rows, H, eps, stream))
 
     # ---- one decode step (the hot path) ----
     def step(self) -> None:
