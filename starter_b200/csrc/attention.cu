@@ -27,6 +27,7 @@ constexpr int TILE_BYTES = 64 * 128 * 2;   // one K or V page tile
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;
 constexpr int CONSUMERS = 4;
 constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr int MAX_CLUSTER = 16;            // most key splits that merge inside one thread-block cluster
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 __device__ int g_status[4];
@@ -418,7 +419,7 @@ k_attn_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml
 // all its tiles before the dependency wait, and the consumer that owns the newest key
 // patches that row into the shared-memory tile (and the owner split writes it to the page
 // for later steps).
-// CL: the S splits of a kv head are one thread-block cluster (S <= 8) and merge through
+// CL: the S splits of a kv head are one thread-block cluster (S <= 16) and merge through
 // distributed shared memory: every CTA parks its (max, sum, O) rows in its own shared
 // memory, the cluster synchronises once, and CTA r of the cluster combines 1/S of the
 // (row, dim) outputs from all S CTAs in split order. No global round trips, no tickets.
@@ -768,9 +769,9 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
       const int v = split * share + i;
       if (v >= total) break;
       const int r = v >> 7, d = v & 127;
-      float ms[8], ls[8], os[8];
+      float ms[MAX_CLUSTER], ls[MAX_CLUSTER], os[MAX_CLUSTER];
 #pragma unroll
-      for (int s = 0; s < 8; ++s) {
+      for (int s = 0; s < MAX_CLUSTER; ++s) {
         ms[s] = -INFINITY; ls[s] = 0.f; os[s] = 0.f;
         if (s < S) {
           uint32_t remote;
@@ -782,11 +783,11 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
       }
       float Mx = -INFINITY;
 #pragma unroll
-      for (int s = 0; s < 8; ++s) Mx = fmaxf(Mx, ls[s] > 0.f ? ms[s] : -INFINITY);
+      for (int s = 0; s < MAX_CLUSTER; ++s) Mx = fmaxf(Mx, ls[s] > 0.f ? ms[s] : -INFINITY);
       if (Mx == -INFINITY) Mx = 0.f;
       float Lsum = 0.f, O = 0.f;
 #pragma unroll
-      for (int s = 0; s < 8; ++s) {
+      for (int s = 0; s < MAX_CLUSTER; ++s) {
         const float wgt = ls[s] > 0.f ? exp2f(ms[s] - Mx) : 0.f;
         Lsum += wgt * ls[s];
         O += wgt * os[s];
@@ -867,7 +868,11 @@ extern "C" int q_attention_splits(int batch, int n_kv_heads, int capacity) {
   if (desired < 1) desired = 1;
   int s = desired < tiles ? desired : tiles;
   // Up to 8 splits merge inside a thread-block cluster (no global round trip); that is
-  // worth more than finer splits while a split still sees at most 4 tiles.
+  // worth more than finer splits while a split still sees at most 4 tiles. (Clusters of up to
+  // 16 are supported by the kernel; 12 splits of at most two tiles each, whose 70 KB CTAs fit
+  // on an SM beside a projection CTA, measured slower at batch 1 / 1 K keys: 10.0 against
+  // 9.1 us per layer - the scheduler packs two such CTAs onto one SM and the O projection
+  // still starts late there.)
   if (s > 8 && tiles <= 32) s = 8;
   if (s > 32) s = 32;
   if (s < 1) s = 1;
@@ -938,8 +943,6 @@ extern "C" int q_attention_decode(const float* d_qkv_partials, const q_gemm_plan
   const int G = n_q_heads / nkv;
   Q_CHECK_ARG(G <= 8, "q_attention_decode: %d query heads per kv head exceed 8", G);
   Q_CHECK_ARG(splits >= 1 && splits <= 32, "q_attention_decode: splits %d outside 1..32", splits);
-  Q_CHECK_ARG(splits <= 8 || (d_scratch_o && d_scratch_ml && d_tickets),
-              "q_attention_decode: split scratch or tickets missing (needed above 8 splits)");
   Q_CHECK_ARG((long long)batch * nkv <= 65535, "q_attention_decode: too many (sequence, kv head) pairs");
   if (plan) {
     Q_CHECK_ARG(plan->M == batch && plan->N == (n_q_heads + 2 * nkv) * 128,
@@ -959,7 +962,34 @@ extern "C" int q_attention_decode(const float* d_qkv_partials, const q_gemm_plan
   // the merge scratch (consumer states, then the CTA's own rows) reuses the ring
   const int scratch_stages = (G * 5 * 130 * 4 + STAGE_BYTES - 1) / STAGE_BYTES;
   if (ring < scratch_stages) ring = scratch_stages;
-  const bool cluster = splits >= 2 && splits <= 8 && !g_attn_no_cluster;
+  bool cluster = splits >= 2 && splits <= MAX_CLUSTER && !g_attn_no_cluster;
+  if (cluster && splits > 8) {
+    // more than 8 CTAs per cluster is an opt-in size; whether such clusters can be placed
+    // at all is asked once per device and split count
+    static int placeable[64][MAX_CLUSTER + 1];          // 0 unknown, 1 yes, -1 no
+    const int dev = q_device_index();
+    if (dev < 0) cluster = false;
+    else {
+      if (placeable[dev][splits] == 0) {
+        int n = 0;
+        cudaError_t e1 = cudaFuncSetAttribute(k_attn_decode<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(splits, batch * nkv);
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = attn_decode_smem(ring);
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = splits; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        cudaError_t e2 = e1 == cudaSuccess ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<true>, &cfg) : e1;
+        if (e2 != cudaSuccess) cudaGetLastError();
+        placeable[dev][splits] = (e2 == cudaSuccess && n >= 1) ? 1 : -1;
+      }
+      cluster = placeable[dev][splits] == 1;
+    }
+  }
+  Q_CHECK_ARG(cluster || splits == 1 || (d_scratch_o && d_scratch_ml && d_tickets),
+              "q_attention_decode: split scratch or tickets missing (needed when the splits cannot merge in a cluster)");
   const float sl2 = scale * 1.4426950408889634f;
   if (cluster) {
     Q_CHECK_CUDA(q_launch_cluster(k_attn_decode<true>, dim3(splits, batch * nkv), dim3(THREADS),

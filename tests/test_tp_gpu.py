@@ -18,7 +18,7 @@ ROOT = Path(__file__).resolve().parents[1]
 
 
 @pytest.mark.parametrize("tp_path", ["peers", "nccl"])
-@pytest.mark.parametrize("world", [2])
+@pytest.mark.parametrize("world", [2, 4])
 def test_tensor_parallel_tokens_match_single_gpu(tmp_path, world, tp_path):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
@@ -26,7 +26,7 @@ def test_tensor_parallel_tokens_match_single_gpu(tmp_path, world, tp_path):
     from starter_b200 import Engine
     torch.manual_seed(11)
     cfg = Qwen3Config(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
-                      num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                      num_attention_heads=8, num_key_value_heads=4, head_dim=128,
                       max_position_embeddings=512, rope_theta=1_000_000.0, tie_word_embeddings=True,
                       sliding_window=None)
     model_dir = tmp_path / "model"
