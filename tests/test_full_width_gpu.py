@@ -12,7 +12,7 @@ therefore set by what the two oracles achieve against each other on the same tok
     same bar against the restatement;
   - the share of logits bit-equal to the restatement >= 0.8 x the share native itself reaches
     against the restatement.
-The numbers are also written to a parity_full_width.json record beside the test logs."""
+The numbers are also written to a parity_full_width.json record (see write_parity_record)."""
 import json
 import os
 import sys
@@ -26,7 +26,9 @@ ROOT = Path(__file__).resolve().parents[1]
 
 
 def write_parity_record(name: str, record: dict) -> None:
-    out = ROOT / "gpurun_out"
+    """Keeps the numbers of a parity run: printed, and written as JSON into the directory the
+    environment variable QDECODE_RECORD_DIR names (default: test_records/ beside the tests)."""
+    out = Path(os.environ.get("QDECODE_RECORD_DIR", ROOT / "test_records"))
     try:
         out.mkdir(exist_ok=True)
         (out / f"parity_{name}.json").write_text(json.dumps(record, indent=1))
