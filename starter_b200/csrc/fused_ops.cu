@@ -244,90 +244,98 @@ k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, const float* __re
   pdl_launch_dependents();
   pdl_wait();                         // this rank's projection has written its partials
   tl_waited(tl);
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31;
   const int row = blockIdx.x;
-  const int col = 4 * tid;
-  const bool live = col < cols;
+  // A warp covers 128 columns; lane l owns columns {2l, 2l+1} and {64+2l, 64+2l+1} of them, so
+  // that each of its two 16-byte pair stores lines up with the other lanes' into 512
+  // contiguous bytes (stores of 16 bytes scattered at a 32-byte stride crossed NVLink as
+  // one small packet each and made the exchange packet-bound at 32 rows).
+  const int cw = (tid >> 5) * 128 + 2 * lane;
+  const int colv[2] = {cw, cw + 64};
+  const bool live[2] = {colv[0] < cols, colv[1] < cols};
   if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned*>(pw.epoch) + 1u;
   // operands that do not depend on the peers: own slots, residual, gain
-  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  const float* p0 = P + (size_t)row * cols + (live ? col : 0);
-  const int extra = live ? plan_count(pv, col) - 1 : -1;
-  float4 sl[10];
+  const float2 z2 = make_float2(0.f, 0.f);
+  float2 own[2];
+  uint32_t xr[2], gn[2];
 #pragma unroll
-  for (int k = 0; k < 10; ++k)
-    sl[k] = (k <= extra && (k == 0 || pv.u != 0)) ? *reinterpret_cast<const float4*>(p0 + (long long)k * pv.slot_stride) : z4;
-  const uint2 xr = live ? *reinterpret_cast<const uint2*>(Xin + (size_t)row * cols + col) : make_uint2(0, 0);
-  const uint2 gn = live ? *reinterpret_cast<const uint2*>(G + col) : make_uint2(0, 0);
-  float4 own = sl[0];
+  for (int h = 0; h < 2; ++h) {
+    const int c = live[h] ? colv[h] : 0;
+    const float* p0 = P + (size_t)row * cols + c;
+    const int extra = live[h] ? plan_count(pv, c) - 1 : -1;
+    float2 sl[10];
 #pragma unroll
-  for (int k = 1; k < 10; ++k)
-    if (k <= extra) { own.x += sl[k].x; own.y += sl[k].y; own.z += sl[k].z; own.w += sl[k].w; }
-  for (int k = 10; k <= extra; ++k) {
-    const float4 t = *reinterpret_cast<const float4*>(p0 + (long long)k * pv.slot_stride);
-    own.x += t.x; own.y += t.y; own.z += t.z; own.w += t.w;
+    for (int k = 0; k < 10; ++k)
+      sl[k] = (k <= extra && (k == 0 || pv.u != 0)) ? *reinterpret_cast<const float2*>(p0 + (long long)k * pv.slot_stride) : z2;
+    xr[h] = live[h] ? *reinterpret_cast<const uint32_t*>(Xin + (size_t)row * cols + c) : 0u;
+    gn[h] = live[h] ? *reinterpret_cast<const uint32_t*>(G + c) : 0u;
+    float2 acc = sl[0];
+#pragma unroll
+    for (int k = 1; k < 10; ++k)
+      if (k <= extra) { acc.x += sl[k].x; acc.y += sl[k].y; }
+    for (int k = 10; k <= extra; ++k) {
+      const float2 t = *reinterpret_cast<const float2*>(p0 + (long long)k * pv.slot_stride);
+      acc.x += t.x; acc.y += t.y;
+    }
+    own[h] = acc;
   }
   __syncthreads();
   const unsigned e = s_epoch;
   // element offsets in 8-byte pairs: halves alternate with the call counter
   const size_t half_off = (size_t)(e & 1u) * pw.world * rows * cols;
-  const size_t mine = half_off + ((size_t)pw.rank * rows + row) * cols + col;
+  const size_t row_off = half_off + ((size_t)pw.rank * rows + row) * cols;
   // 1. push this rank's pairs to every peer
-  if (live) {
 #pragma unroll
-    for (int r = 0; r < Q_MAX_PEERS; ++r)
-      if (r < pw.world && r != pw.rank) {
-        char* dst = reinterpret_cast<char*>(pw.recv[r]) + mine * 8;
-        st_pair2(dst, own.x, own.y, e);
-        st_pair2(dst + 16, own.z, own.w, e);
-      }
-  }
+  for (int r = 0; r < Q_MAX_PEERS; ++r)
+    if (r < pw.world && r != pw.rank) {
+      char* dst = reinterpret_cast<char*>(pw.recv[r]);
+      if (live[0]) st_pair2(dst + (row_off + colv[0]) * 8, own[0].x, own[0].y, e);
+      if (live[1]) st_pair2(dst + (row_off + colv[1]) * 8, own[1].x, own[1].y, e);
+    }
   // 2. collect the peers' pairs of this row from the own receive area, in rank order
-  float tot[4] = {0.f, 0.f, 0.f, 0.f};
+  float tot[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
   float ss = 0.f;
-  if (live) {
-    float4 acc = z4;
+  {
+    float2 acc[2] = {z2, z2};
     bool ok = true;
     for (int r = 0; r < pw.world; ++r) {
-      float4 t = own;
+      float2 t[2] = {own[0], own[1]};
       if (r != pw.rank) {
-        const char* src = reinterpret_cast<const char*>(pw.recv[pw.rank]) + (half_off + ((size_t)r * rows + row) * cols + col) * 8;
+        const char* src = reinterpret_cast<const char*>(pw.recv[pw.rank]) + (half_off + ((size_t)r * rows + row) * cols) * 8;
         unsigned long long a0 = 0, a1 = 0, a2 = 0, a3 = 0;
         bool here = false;
         for (int i = 0; ok && i < wait_iters; ++i) {
-          ld_pair2(src, a0, a1);
-          ld_pair2(src + 16, a2, a3);
-          here = (unsigned)(a0 >> 32) == e && (unsigned)(a1 >> 32) == e && (unsigned)(a2 >> 32) == e &&
-                 (unsigned)(a3 >> 32) == e;
+          if (live[0]) ld_pair2(src + (size_t)colv[0] * 8, a0, a1);
+          if (live[1]) ld_pair2(src + (size_t)colv[1] * 8, a2, a3);
+          here = (!live[0] || ((unsigned)(a0 >> 32) == e && (unsigned)(a1 >> 32) == e)) &&
+                 (!live[1] || ((unsigned)(a2 >> 32) == e && (unsigned)(a3 >> 32) == e));
           if (here) break;
           if (i > 64) __nanosleep(i > 65536 ? 2000 : (i > 4096 ? 400 : 40));
         }
         if (!here) { ok = false; atomicExch(&g_peer_status, 1); }
-        t = make_float4(__uint_as_float((unsigned)a0), __uint_as_float((unsigned)a1), __uint_as_float((unsigned)a2),
-                        __uint_as_float((unsigned)a3));
+        t[0] = make_float2(__uint_as_float((unsigned)a0), __uint_as_float((unsigned)a1));
+        t[1] = make_float2(__uint_as_float((unsigned)a2), __uint_as_float((unsigned)a3));
       }
-      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+      acc[0].x += t[0].x; acc[0].y += t[0].y; acc[1].x += t[1].x; acc[1].y += t[1].y;
     }
-    const float s4[4] = {acc.x, acc.y, acc.z, acc.w};
-    const float r4[4] = {bf_lo(xr.x), bf_hi(xr.x), bf_lo(xr.y), bf_hi(xr.y)};
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      tot[q] = bf16_round(r4[q] + bf16_round(s4[q]));
-      ss += tot[q] * tot[q];
-    }
+    for (int h = 0; h < 2; ++h)
+      if (live[h]) {
+        tot[h][0] = bf16_round(bf_lo(xr[h]) + bf16_round(acc[h].x));
+        tot[h][1] = bf16_round(bf_hi(xr[h]) + bf16_round(acc[h].y));
+        ss += tot[h][0] * tot[h][0] + tot[h][1] * tot[h][1];
+      }
   }
   ss = block_sum(ss, red);
   const float inv = rsqrtf(ss / (float)cols + eps);
-  if (live) {
-    const float g4[4] = {bf_lo(gn.x), bf_hi(gn.x), bf_lo(gn.y), bf_hi(gn.y)};
-    uint2 to, no;
-    to.x = pack_bf16(tot[0], tot[1]);
-    to.y = pack_bf16(tot[2], tot[3]);
-    no.x = pack_bf16(bf16_round(tot[0] * inv) * g4[0], bf16_round(tot[1] * inv) * g4[1]);
-    no.y = pack_bf16(bf16_round(tot[2] * inv) * g4[2], bf16_round(tot[3] * inv) * g4[3]);
-    *reinterpret_cast<uint2*>(Tout + (size_t)row * cols + col) = to;
-    *reinterpret_cast<uint2*>(Nout + (size_t)row * cols + col) = no;
-  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+    if (live[h]) {
+      const uint32_t to = pack_bf16(tot[h][0], tot[h][1]);
+      const uint32_t no = pack_bf16(bf16_round(tot[h][0] * inv) * bf_lo(gn[h]), bf16_round(tot[h][1] * inv) * bf_hi(gn[h]));
+      *reinterpret_cast<uint32_t*>(Tout + (size_t)row * cols + colv[h]) = to;
+      *reinterpret_cast<uint32_t*>(Nout + (size_t)row * cols + colv[h]) = no;
+    }
   // the last CTA of the call publishes the new call counter
   __syncthreads();
   if (tid == 0) {
@@ -784,7 +792,7 @@ extern "C" int q_add_rmsnorm_peers(const void* d_x_in, const q_peers_t* peers, c
   PeerView pw;
   rc = peer_view(peers, &pw, "q_add_rmsnorm_peers");
   if (rc) return rc;
-  const int threads = ((cols / 4 + 31) / 32) * 32;
+  const int threads = ((cols + 127) / 128) * 32;        // one warp per 128 columns
   Q_CHECK_CUDA(q_launch(k_add_rmsnorm_peers, dim3(rows), dim3(threads), 0, S(stream), (const bf16*)d_x_in, pw,
                         d_own_branch, plan_view(plan), (const bf16*)d_gain, (bf16*)d_total_out,
                         (bf16*)d_normed_out, rows, cols, eps, g_peer_wait_iters, q_tl_next(Q_TL_PEER_ADD_NORM)));
