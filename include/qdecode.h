@@ -250,8 +250,8 @@ int q_qkv_norm_rope_cache(const float* d_branch, const q_gemm_plan_t* plan,
 
 /* engine/kernels/prefill.py:19-63 (head norm + RoPE + cache write for all prompt positions):
  * the same kernel over batch * T prompt rows, which additionally leaves the rotated K rows
- * and the V rows token-major in d_k_out / d_v_out [batch*T][n_kv][128] for the prompt pass's
- * causal attention. */
+ * and the V rows token-major in d_k_out / d_v_out [batch*T][n_kv][128] for a caller that
+ * wants them outside the pages (q_attention_prefill reads the pages and does not). */
 int q_qkv_norm_rope_prefill(const float* d_branch, const q_gemm_plan_t* plan,
                             const void* d_q_gain, const void* d_k_gain,
                             const void* d_cos, const void* d_sin, const int32_t* d_pos,
@@ -279,6 +279,16 @@ int q_attention(const void* d_q, const q_kv_layout_t* kv, const int32_t* d_pos,
                 float* d_scratch_o, float* d_scratch_ml, void* d_out,
                 int batch, int T, int n_q_heads, int splits, float scale,
                 void* stream);
+
+/* Causal attention over a whole prompt block of T tokens per sequence (the prompt pass;
+ * engine/prefill.py:45-52 calls the library's scaled-dot-product attention there). d_q is
+ * [batch*T][n_q][128] bf16 (normed, rotated); the keys and values are read from the pages,
+ * which must already hold positions *d_pos .. *d_pos+T-1 of every sequence; row (b,t,head)
+ * sees keys [0, *d_pos + t + 1). No split scratch: one CTA per (sequence, kv head, block of
+ * 128/G tokens). G = n_q_heads / n_kv_heads must be 1, 2, 4 or 8. out is [batch*T][n_q*128]. */
+int q_attention_prefill(const void* d_q, const q_kv_layout_t* kv, const int32_t* d_pos,
+                        void* d_out, int batch, int T, int n_q_heads, float scale,
+                        void* stream);
 
 /* The three kernels above for the single-token decode step in ONE launch:
  * engine/kernels/decode_fused.py:172-210 (head norm + RoPE + K/V write into the page

@@ -123,6 +123,7 @@ SIGNATURES = {
     "q_kv_scatter": (_I, [_P, _P, _KV, _I, _I, _I, _P]),
     "q_attention_splits": (_I, [_I, _I, _I]),
     "q_attention": (_I, [_P, _KV, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P]),
+    "q_attention_prefill": (_I, [_P, _KV, _P, _P, _I, _I, _I, _F, _P]),
     "q_attention_decode": (_I, [_P, _PLAN, _P, _P, _P, _P, _P, _KV, _P, _P, _P, _P, _I, _I, _I, _F, _F, _P]),
     "q_argmax_scratch_bytes": (C.c_int64, [_I, _I]),
     "q_logits_argmax": (_I, [_P, _PLAN, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _P]),

@@ -848,6 +848,218 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
   tl_end(tl);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Causal attention over a whole prompt (the prompt pass; reference: engine/prefill.py:45-52 calls
+// the library's scaled-dot-product attention there). One CTA = one (sequence, kv head, block of
+// 128/G prompt tokens): its 128 query rows (token-major, the G query heads of the kv head side
+// by side) share every K/V page tile. Warps 0..7 each own 16 query rows and all 64 keys of a
+// tile - S = Q K^T, online softmax and P V with mma.m16n8k16, no merge between warps - and warp
+// 8 is the producer that walks the block table. Keys come from the pages the head-norm + RoPE
+// kernel has just filled, tiles past the block's last token are never fetched, and the
+// diagonal tiles are masked per row. Same cast boundaries as the decode kernels.
+constexpr int PF_WARPS = 8;
+constexpr int PF_THREADS = (PF_WARPS + 1) * 32;
+constexpr int PF_NS = 2;
+constexpr size_t PF_SMEM = PF_NS * STAGE_BYTES + 128 * 256 + 2 * PF_NS * 8;
+
+__global__ void __launch_bounds__(PF_THREADS)
+k_attn_prefill(const bf16* __restrict__ Q, const char* __restrict__ kpool, const char* __restrict__ vpool,
+               const int32_t* __restrict__ block_table, int pages_per_seq,
+               const int32_t* __restrict__ pos_ptr, bf16* __restrict__ out, int T, int G, int gshift,
+               int nq, int nkv, float scale_log2) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* stages = smem;                                   // PF_NS * STAGE_BYTES
+  unsigned char* qtile = smem + PF_NS * STAGE_BYTES;              // 128 rows * 256 B
+  uint64_t* bars = reinterpret_cast<uint64_t*>(qtile + 128 * 256);  // full[PF_NS], empty[PF_NS]
+
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.z, kh = blockIdx.y;
+  const int QB = 128 >> gshift;                                   // prompt tokens per CTA
+  const int q0 = blockIdx.x * QB;
+  if (tid == 0) {
+    for (int i = 0; i < PF_NS; ++i) {
+      mbar_init(smem_u32(&bars[i]), 1);
+      mbar_init(smem_u32(&bars[PF_NS + i]), PF_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_wait();                       // q and this pass's K/V rows come from the kernel before
+  const int pos = pos_ptr[0];
+  const int tok_end = min(q0 + QB, T);                            // tokens of this block: [q0, tok_end)
+  const int max_limit = pos + tok_end;                            // keys visible to the last row
+  const int ntiles = (max_limit + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
+
+  if (warp == PF_WARPS) {
+    if (lane == 0) {
+      for (int it = 0; it < ntiles; ++it) {
+        const int s = it % PF_NS;
+        if (it >= PF_NS && !mbar_wait(smem_u32(&bars[PF_NS + s]), ((it / PF_NS) - 1) & 1)) {
+          atomicExch(&g_status[0], 5);
+          break;
+        }
+        const int page = block_table[(size_t)b * pages_per_seq + it];
+        const size_t off = ((size_t)page * nkv + kh) * TILE_BYTES;
+        const uint32_t bar = smem_u32(&bars[s]);
+        mbar_expect_tx(bar, STAGE_BYTES);
+        bulk_g2s(smem_u32(stages + s * STAGE_BYTES), kpool + off, TILE_BYTES, bar);
+        bulk_g2s(smem_u32(stages + s * STAGE_BYTES + TILE_BYTES), vpool + off, TILE_BYTES, bar);
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  // Q block -> shared memory (swizzled rows of 256 B); rows of tokens past the prompt are zero.
+  for (int c = tid; c < 128 * 16; c += PF_WARPS * 32) {
+    const int r = c >> 4, ch = c & 15;
+    const int t = q0 + (r >> gshift), gq = r & (G - 1);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < T) v = *reinterpret_cast<const uint4*>(Q + (((size_t)b * T + t) * nq + kh * G + gq) * 128 + ch * 8);
+    *reinterpret_cast<uint4*>(qtile + r * 256 + ((ch ^ (r & 7)) << 4)) = v;
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(PF_WARPS * 32) : "memory");
+
+  const int g = lane >> 2, t4 = lane & 3;
+  float m_run[2], l_run[2], oacc[16][4];
+  int limit[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    m_run[h] = -INFINITY;
+    l_run[h] = 0.f;
+    const int t = q0 + ((warp * 16 + g + 8 * h) >> gshift);
+    limit[h] = t < T ? pos + t + 1 : 0;                           // a row past the prompt sees nothing
+  }
+#pragma unroll
+  for (int n = 0; n < 16; ++n) oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f;
+  // keys this warp's 16 rows can see: tiles past that are skipped by the warp (still released)
+  const int t_last = min(q0 + ((warp * 16 + 15) >> gshift), T - 1);
+  const int warp_limit = pos + t_last + 1;
+  // the Q fragments of the warp's rows stay in registers for the whole pass
+  uint32_t qa[8][4];
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    const int row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+    const int ch = 2 * ks + (lane >> 4);
+    ldsm_x4(smem_u32(qtile) + row * 256 + ((ch ^ (row & 7)) << 4), qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
+  }
+
+  for (int it = 0; it < ntiles; ++it) {
+    const int s = it % PF_NS;
+    if (!mbar_wait(smem_u32(&bars[s]), (it / PF_NS) & 1)) {
+      atomicExch(&g_status[0], 6);
+      return;
+    }
+    unsigned char* kt = stages + s * STAGE_BYTES;
+    unsigned char* vt = kt + TILE_BYTES;
+    const int key_base = it * Q_PAGE_TOKENS;
+    if (key_base + Q_PAGE_TOKENS > max_limit) {
+      // rows past the newest key may hold stale bits: clear those V rows so that 0 * garbage
+      // cannot produce NaN in P V. Every warp clears all of them itself (the same zeros from
+      // eight warps), so no barrier is needed before it reads the tile.
+      for (int c = lane; c < 64 * 16; c += 32) {
+        const int kr = c >> 4;
+        if (key_base + kr >= max_limit)
+          *reinterpret_cast<uint4*>(vt + kr * 256 + ((c & 15) << 4)) = make_uint4(0, 0, 0, 0);
+      }
+      __syncwarp();
+    }
+    if (key_base < warp_limit) {
+      const uint32_t k_base = smem_u32(kt), v_base = smem_u32(vt);
+      float sacc[8][4];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {                          // 16 keys per ldmatrix
+          uint32_t b0, b1, b2, b3;
+          const int mi = lane >> 3;
+          const int key = kb * 16 + 8 * (mi >> 1) + (lane & 7);
+          const int ch = 2 * ks + (mi & 1);
+          ldsm_x4(k_base + key * 256 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+          mma16816(sacc[2 * kb], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+          mma16816(sacc[2 * kb + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+        }
+      }
+      // online softmax for rows g (h=0) and g+8 (h=1) over the tile's 64 keys
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = key_base + 8 * j + 2 * t4 + e;
+            float v = sacc[j][2 * h + e] * scale_log2;
+            v = key < limit[h] ? v : -INFINITY;
+            sacc[j][2 * h + e] = v;
+            mx = fmaxf(mx, v);
+          }
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[h], mx);
+        const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+        const float resc = exp2f(m_run[h] - m_safe);
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float pv = exp2f(sacc[j][2 * h + e] - m_safe);
+            sacc[j][2 * h + e] = pv;
+            sum += pv;
+          }
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l_run[h] = l_run[h] * resc + sum;
+        m_run[h] = m_new;
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+          oacc[n][2 * h] *= resc;
+          oacc[n][2 * h + 1] *= resc;
+        }
+      }
+#pragma unroll
+      for (int kb = 0; kb < 4; ++kb) {                            // P V, 16 keys per step
+        const uint32_t pa0 = pack_bf16(sacc[2 * kb][0], sacc[2 * kb][1]);
+        const uint32_t pa1 = pack_bf16(sacc[2 * kb][2], sacc[2 * kb][3]);
+        const uint32_t pa2 = pack_bf16(sacc[2 * kb + 1][0], sacc[2 * kb + 1][1]);
+        const uint32_t pa3 = pack_bf16(sacc[2 * kb + 1][2], sacc[2 * kb + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < 8; ++dp) {
+          uint32_t b0, b1, b2, b3;
+          const int mi = lane >> 3;
+          const int key = kb * 16 + 8 * (mi & 1) + (lane & 7);
+          const int ch = 2 * dp + (mi >> 1);
+          ldsm_x4_t(v_base + key * 256 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+          mma16816(oacc[2 * dp], pa0, pa1, pa2, pa3, b0, b1);
+          mma16816(oacc[2 * dp + 1], pa0, pa1, pa2, pa3, b2, b3);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&bars[PF_NS + s]));
+  }
+
+  // one rounding to bf16; the row's 128 dims go to out[(b*T + t)][head][128]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + g + 8 * h;
+    const int t = q0 + (r >> gshift);
+    if (t >= T) continue;
+    const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+    bf16* dst = out + (((size_t)b * T + t) * nq + kh * G + (r & (G - 1))) * 128;
+#pragma unroll
+    for (int n = 0; n < 16; ++n)
+      *reinterpret_cast<uint32_t*>(dst + 8 * n + 2 * t4) = pack_bf16(oacc[n][2 * h] * inv, oacc[n][2 * h + 1] * inv);
+  }
+}
+
 constexpr size_t attn_decode_smem(int ns) { return ns * STAGE_BYTES + 16 * 256 + 2 * ns * 8 + 2 * 128 * 2 + 64; }
 
 template <int RT>
@@ -923,6 +1135,34 @@ extern "C" int q_attention(const void* d_q, const q_kv_layout_t* kv, const int32
     Q_CHECK_CUDA(q_launch(k_attn_merge, dim3((items + 3) / 4), dim3(128), 0, s, d_scratch_o,
                           d_scratch_ml, (bf16*)d_out, batch, T, G, n_q_heads, nkv, splits));
   }
+  return Q_OK;
+}
+
+extern "C" int q_attention_prefill(const void* d_q, const q_kv_layout_t* kv, const int32_t* d_pos,
+                                   void* d_out, int batch, int T, int n_q_heads, float scale,
+                                   void* stream) {
+  Q_CHECK_ARG(d_q && kv && d_pos && d_out, "q_attention_prefill: null pointer");
+  Q_CHECK_ARG(kv->d_kpool && kv->d_vpool && kv->d_block_table && kv->pages_per_seq >= 1 &&
+                  kv->n_kv_heads >= 1,
+              "q_attention_prefill: incomplete KV layout");
+  const int nkv = kv->n_kv_heads;
+  Q_CHECK_ARG(batch >= 1 && batch <= 65535 && nkv <= 65535 && T >= 1 && n_q_heads >= nkv &&
+                  n_q_heads % nkv == 0,
+              "q_attention_prefill: bad batch/T/heads");
+  const int G = n_q_heads / nkv;
+  Q_CHECK_ARG(G <= 8 && (G & (G - 1)) == 0,
+              "q_attention_prefill: %d query heads per kv head (1, 2, 4 or 8 supported)", G);
+  Q_CHECK_ALIGN(d_q, 16, "q_attention_prefill"); Q_CHECK_ALIGN(d_out, 4, "q_attention_prefill");
+  Q_CHECK_ALIGN(kv->d_kpool, 16, "q_attention_prefill"); Q_CHECK_ALIGN(kv->d_vpool, 16, "q_attention_prefill");
+  int gshift = 0;
+  while ((1 << gshift) < G) ++gshift;
+  const int QB = 128 >> gshift;
+  static size_t done[64] = {0};
+  Q_CHECK_CUDA(q_ensure_smem(k_attn_prefill, PF_SMEM, done));
+  Q_CHECK_CUDA(q_launch(k_attn_prefill, dim3((T + QB - 1) / QB, nkv, batch), dim3(PF_THREADS), PF_SMEM,
+                        (cudaStream_t)stream, (const bf16*)d_q, (const char*)kv->d_kpool,
+                        (const char*)kv->d_vpool, kv->d_block_table, kv->pages_per_seq, d_pos,
+                        (bf16*)d_out, T, G, gshift, n_q_heads, nkv, scale * 1.4426950408889634f));
   return Q_OK;
 }
 

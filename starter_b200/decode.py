@@ -26,7 +26,6 @@ import os
 import sys
 
 import torch
-import torch.nn.functional as F
 
 from . import _lib
 from ._lib import HEAD_DIM, PAGE_TOKENS, check, lib
@@ -273,8 +272,7 @@ class DecodeState:
         self._pf = {
             "rows": rows, "plans": plans, "partials": torch.empty(n_part, dtype=torch.float32, device=dev),
             "x": torch.empty((rows, cfg.hidden), **bf), "normed": torch.empty((rows, cfg.hidden), **bf),
-            "q": torch.empty((rows, nq, HEAD_DIM), **bf), "k": torch.empty((rows, nkv, HEAD_DIM), **bf),
-            "v": torch.empty((rows, nkv, HEAD_DIM), **bf), "att": torch.empty((rows, nq * HEAD_DIM), **bf),
+            "q": torch.empty((rows, nq, HEAD_DIM), **bf), "att": torch.empty((rows, nq * HEAD_DIM), **bf),
             "act": torch.empty((rows, inter), **bf), "zero": torch.zeros(1, dtype=torch.int32, device=dev),
             "reduced": torch.empty((rows, cfg.hidden), dtype=torch.float32, device=dev) if self.tp > 1 else None,
         }
@@ -288,10 +286,10 @@ class DecodeState:
         The prompt pass of the reference (engine/prefill.py:26-62) on this library's own
         kernels: every projection on the tcgen05 kernel over the tiled weights (256 prompt rows
         per weight pass), embedding + norm, add + norm, SwiGLU and head norm + RoPE + page write
-        (engine/kernels/prefill.py:19-63) as the fused consumers of the decode step, lm_head and
-        argmax likewise. Only the causal attention over the prompt is a library call (PyTorch's
-        scaled_dot_product_attention on the token-major K / V rows the RoPE kernel leaves beside
-        the pages). Sequences are processed PREFILL_ROWS prompt rows at a time. Under tensor
+        (engine/kernels/prefill.py:19-63) as the fused consumers of the decode step, the causal
+        attention over the prompt as q_attention_prefill reading the pages just written, lm_head
+        and argmax likewise; no library kernel runs. Sequences are processed PREFILL_ROWS prompt
+        rows at a time. Under tensor
         parallelism the two row-parallel projections are summed over the ranks in fp32 by an
         NCCL all-reduce before the single rounding (the prompt pass is outside the per-step
         path)."""
@@ -322,14 +320,11 @@ class DecodeState:
                 check(lib.q_gemm_tc(_p(normed), _p(lt.wqkv.tc()), _p(part), rows, pl["qkv"].N, H, stream))
                 layout = _lib.KVLayout(self.kpools[i].data_ptr(), self.vpools[i].data_ptr(), table,
                                        self.pages_per_seq, nkv)
-                check(lib.q_qkv_norm_rope_prefill(_p(part), C.byref(pl["qkv"]), _p(lt.q_gain), _p(lt.k_gain),
-                                                  _p(self.cos), _p(self.sin), _p(pf["zero"]), _p(pf["q"]),
-                                                  _p(pf["k"]), _p(pf["v"]), C.byref(layout), nb, T, nq, eps, stream))
-                q4 = pf["q"].view(nb, T, nq, HEAD_DIM).transpose(1, 2)
-                k4 = pf["k"].view(nb, T, nkv, HEAD_DIM).transpose(1, 2)
-                v4 = pf["v"].view(nb, T, nkv, HEAD_DIM).transpose(1, 2)
-                att = F.scaled_dot_product_attention(q4, k4, v4, is_causal=True, enable_gqa=True)
-                pf["att"].view(nb, T, nq, HEAD_DIM).copy_(att.transpose(1, 2))
+                check(lib.q_qkv_norm_rope_cache(_p(part), C.byref(pl["qkv"]), _p(lt.q_gain), _p(lt.k_gain),
+                                                _p(self.cos), _p(self.sin), _p(pf["zero"]), _p(pf["q"]),
+                                                C.byref(layout), nb, T, nq, eps, stream))
+                check(lib.q_attention_prefill(_p(pf["q"]), C.byref(layout), _p(pf["zero"]), _p(pf["att"]),
+                                              nb, T, nq, float(HEAD_DIM) ** -0.5, stream))
                 check(lib.q_gemm_tc(_p(pf["att"]), _p(lt.wo.tc()), _p(part), rows, H, nq * HEAD_DIM, stream))
                 self._prefill_add_norm(pf, pl["o"], lt.ln_post, rows, stream)
                 check(lib.q_gemm_tc(_p(normed), _p(lt.wgu.tc()), _p(part), rows, 2 * inter, H, stream))

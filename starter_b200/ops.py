@@ -346,6 +346,26 @@ class SmallQueryAttention:
         return out
 
 
+def prompt_attention(query: torch.Tensor, cache: PagedKV, position: torch.Tensor, tokens_per_seq: int,
+                     scale: float) -> torch.Tensor:
+    """Causal GQA attention of a block of `tokens_per_seq` prompt tokens per sequence over the
+    paged cache, which must already hold their keys and values (the prompt pass; the reference
+    calls the library's scaled-dot-product attention at engine/prefill.py:45-52). query is
+    [batch*T, Hq, 128]; row (b, t, head) attends to keys [0, position + t + 1). Returns
+    [batch*T, Hq*128]."""
+    T = int(tokens_per_seq)
+    if (query.dim() != 3 or query.shape[0] != cache.batch * T or query.shape[2] != HEAD_DIM
+            or query.dtype != torch.bfloat16 or not query.is_cuda or not query.is_contiguous()):
+        raise ValueError("expected contiguous BF16 CUDA Q [batch*T, Hq, 128]")
+    if position.shape != (1,) or position.dtype != torch.int32 or not position.is_cuda:
+        raise ValueError("position must be an int32 CUDA tensor of shape [1]")
+    hq = query.shape[1]
+    out = torch.empty((cache.batch * T, hq * HEAD_DIM), dtype=torch.bfloat16, device=query.device)
+    check(lib.q_attention_prefill(_ptr(query), C.byref(cache.layout), _ptr(position), _ptr(out), cache.batch,
+                                  T, hq, float(scale), _stream()))
+    return out
+
+
 def decode_attention(qkv, q_weight, k_weight, eps, cos, sin, position, cache: PagedKV,
                      attn: SmallQueryAttention, scale) -> torch.Tensor:
     """qkv_norm_rope_cache + SmallQueryAttention.run for one token per sequence in a single

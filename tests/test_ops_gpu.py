@@ -340,6 +340,36 @@ def test_attention_verification_grid(ops, L, T):
         torch.testing.assert_close(out.float(), stepwise.float(), rtol=0.02, atol=5e-3)
 
 
+@pytest.mark.parametrize("B,nq,nkv,T,base", [(1, 32, 8, 1024, 0), (2, 8, 2, 333, 0), (3, 4, 2, 65, 0), (2, 4, 4, 130, 0),
+                                             (1, 8, 1, 64, 0), (2, 8, 2, 1, 0), (2, 8, 2, 100, 77)])
+def test_prompt_attention_vs_fp64(ops, B, nq, nkv, T, base):
+    """Causal attention over a whole prompt block against the fp64 equations, same bars as the
+    decode kernel; unused page rows are NaN. base > 0 is a block appended to an older context."""
+    g = torch.Generator().manual_seed(500 + T)
+    L = base + T
+    q = torch.randn((B, T, nq, 128), generator=g).to(torch.bfloat16)
+    k = torch.randn((B, nkv, L, 128), generator=g).to(torch.bfloat16)
+    v = torch.randn((B, nkv, L, 128), generator=g).to(torch.bfloat16)
+    cache = ops.PagedKV(B, nkv, L + 40, "cuda", poison=float("nan"))
+    cache.scatter(k.cuda(), v.cuda(), 0)
+    position = torch.tensor([base], dtype=torch.int32, device="cuda")
+    out = ops.prompt_attention(q.reshape(B * T, nq, 128).cuda(), cache, position, T, 128 ** -0.5).cpu()
+    limits = (base + torch.arange(T) + 1)[None].repeat(B, 1)
+    ref = O.attention_fp64(q, k, v, limits, 128 ** -0.5).reshape(B * T, nq * 128)
+    assert not torch.isnan(out.float()).any()
+    torch.testing.assert_close(out.float(), ref.float(), rtol=0.02, atol=5e-3)
+    assert ops.device_status()[0] == 0
+
+
+def test_prompt_attention_equals_small_query_kernel(ops):
+    """The prompt kernel and the small-query kernel on the same 8-token block of the same cache."""
+    B, nq, nkv, base, T = 2, 8, 2, 200, 8
+    out, ref, (q, k, v, cache, attn) = _attention_case(ops, B, T, nq, nkv, base, 300, 321)
+    position = torch.tensor([base], dtype=torch.int32, device="cuda")
+    block = ops.prompt_attention(q.reshape(B * T, nq, 128).cuda(), cache, position, T, 128 ** -0.5).cpu()
+    torch.testing.assert_close(block.float(), out.float(), rtol=0.02, atol=5e-3)
+
+
 @pytest.mark.parametrize("cluster", [True, False])
 @pytest.mark.parametrize("B,nq,nkv,pos", [(1, 32, 8, 0), (1, 32, 8, 1100), (3, 8, 2, 63), (2, 8, 2, 64), (4, 4, 2, 700),
                                           (40, 8, 2, 130), (1, 32, 8, 2400)])
