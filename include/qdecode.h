@@ -248,16 +248,6 @@ int q_qkv_norm_rope_cache(const float* d_branch, const q_gemm_plan_t* plan,
                           void* d_q_out, const q_kv_layout_t* kv,
                           int batch, int T, int n_q_heads, float eps, void* stream);
 
-/* engine/kernels/prefill.py:19-63 (head norm + RoPE + cache write for all prompt positions):
- * the same kernel over batch * T prompt rows, which additionally leaves the rotated K rows
- * and the V rows token-major in d_k_out / d_v_out [batch*T][n_kv][128] for a caller that
- * wants them outside the pages (q_attention_prefill reads the pages and does not). */
-int q_qkv_norm_rope_prefill(const float* d_branch, const q_gemm_plan_t* plan,
-                            const void* d_q_gain, const void* d_k_gain,
-                            const void* d_cos, const void* d_sin, const int32_t* d_pos,
-                            void* d_q_out, void* d_k_out, void* d_v_out, const q_kv_layout_t* kv,
-                            int batch, int T, int n_q_heads, float eps, void* stream);
-
 /* Scatters already-rotated K and V rows [batch][n_kv][len][128] (bf16) into the
  * pages at positions start..start+len-1. Host-side helper for prefill
  * (engine/kernels/prefill.py:19-63 writes cache[:, :, :T] the same way). */

@@ -119,7 +119,6 @@ SIGNATURES = {
     "q_swiglu": (_I, [_P, _PLAN, _P, _I, _I, _P]),
     "q_swiglu_interleaved": (_I, [_P, _PLAN, _P, _I, _I, _P]),
     "q_qkv_norm_rope_cache": (_I, [_P, _PLAN, _P, _P, _P, _P, _P, _P, _KV, _I, _I, _I, _F, _P]),
-    "q_qkv_norm_rope_prefill": (_I, [_P, _PLAN, _P, _P, _P, _P, _P, _P, _P, _P, _KV, _I, _I, _I, _F, _P]),
     "q_kv_scatter": (_I, [_P, _P, _KV, _I, _I, _I, _P]),
     "q_attention_splits": (_I, [_I, _I, _I]),
     "q_attention": (_I, [_P, _KV, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P]),

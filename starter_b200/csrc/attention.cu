@@ -492,6 +492,15 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
     }
   }
 
+  // Gains and the rotary row of this position do not depend on the projection: the warp's
+  // first item asks for them before the wait, so only the partials are fetched after it.
+  uint2 graw0 = make_uint2(0, 0), craw0 = make_uint2(0, 0), sraw0 = make_uint2(0, 0);
+  if (warp < G + 1) {
+    graw0 = *reinterpret_cast<const uint2*>((warp < G ? QG : KG) + 4 * lane);
+    craw0 = *reinterpret_cast<const uint2*>(COS + (size_t)pos * 128 + 4 * lane);
+    sraw0 = *reinterpret_cast<const uint2*>(SIN + (size_t)pos * 128 + 4 * lane);
+  }
+
   pdl_wait();          // the QKV partials are complete from here on
   tl_waited(tl);
   if (stamp) g_attn_trace[1] = tl_now();
@@ -518,9 +527,12 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
         sv[k] = (!is_q && (k == 0 || (pv.u != 0 && k <= vextra)))
                     ? *reinterpret_cast<const float4*>(PQ + vsrc + (long long)k * pv.slot_stride) : z4;
       }
-      const uint2 graw = *reinterpret_cast<const uint2*>((is_q ? QG : KG) + 4 * lane);
-      const uint2 craw = *reinterpret_cast<const uint2*>(COS + (size_t)pos * 128 + 4 * lane);
-      const uint2 sraw = *reinterpret_cast<const uint2*>(SIN + (size_t)pos * 128 + 4 * lane);
+      uint2 graw = graw0, craw = craw0, sraw = sraw0;
+      if (h != warp) {
+        graw = *reinterpret_cast<const uint2*>((is_q ? QG : KG) + 4 * lane);
+        craw = *reinterpret_cast<const uint2*>(COS + (size_t)pos * 128 + 4 * lane);
+        sraw = *reinterpret_cast<const uint2*>(SIN + (size_t)pos * 128 + 4 * lane);
+      }
       if (!is_q) {
         float x[4] = {sv[0].x, sv[0].y, sv[0].z, sv[0].w};
 #pragma unroll
@@ -631,12 +643,13 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
       }
       __syncwarp();
       const uint32_t k_base = smem_u32(kt), v_base = smem_u32(vt);
-      float sacc[2][4], sodd[2][4];
+      // the eight k-steps go to four independent accumulator sets (an MMA's result is ~280
+      // cycles away), added at the end
+      float sset[4][2][4];
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
-        sodd[j][0] = sodd[j][1] = sodd[j][2] = sodd[j][3] = 0.f;
-      }
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) sset[q][j][0] = sset[q][j][1] = sset[q][j][2] = sset[q][j][3] = 0.f;
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
@@ -651,18 +664,14 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
           const int ch = 2 * ks + (mi & 1);
           ldsm_x4(k_base + key * 256 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
         }
-        if (ks & 1) {
-          mma16816(sodd[0], a0, a1, a2, a3, b0, b1);
-          mma16816(sodd[1], a0, a1, a2, a3, b2, b3);
-        } else {
-          mma16816(sacc[0], a0, a1, a2, a3, b0, b1);
-          mma16816(sacc[1], a0, a1, a2, a3, b2, b3);
-        }
+        mma16816(sset[ks & 3][0], a0, a1, a2, a3, b0, b1);
+        mma16816(sset[ks & 3][1], a0, a1, a2, a3, b2, b3);
       }
+      float sacc[2][4];
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) sacc[j][e] += sodd[j][e];
+        for (int e = 0; e < 4; ++e) sacc[j][e] = (sset[0][j][e] + sset[1][j][e]) + (sset[2][j][e] + sset[3][j][e]);
       float pr[2][4];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -876,7 +885,7 @@ k_attn_prefill(const bf16* __restrict__ Q, const char* __restrict__ kpool, const
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.z, kh = blockIdx.y;
   const int QB = 128 >> gshift;                                   // prompt tokens per CTA
-  const int q0 = blockIdx.x * QB;
+  const int q0 = (gridDim.x - 1 - blockIdx.x) * QB;              // latest blocks (most key tiles) first
   if (tid == 0) {
     for (int i = 0; i < PF_NS; ++i) {
       mbar_init(smem_u32(&bars[i]), 1);

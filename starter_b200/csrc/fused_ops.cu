@@ -467,8 +467,7 @@ k_qkv_norm_rope_cache(const float* __restrict__ P, PlanView pv, const bf16* __re
                       const bf16* __restrict__ SIN, const int32_t* __restrict__ pos_ptr,
                       bf16* __restrict__ Q, char* __restrict__ kpool, char* __restrict__ vpool,
                       const int32_t* __restrict__ block_table, int pages_per_seq,
-                      int rows, int T, int nq, int nkv, float eps, bf16* __restrict__ Klin,
-                      bf16* __restrict__ Vlin) {
+                      int rows, int T, int nq, int nkv, float eps) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -528,9 +527,6 @@ k_qkv_norm_rope_cache(const float* __restrict__ P, PlanView pv, const bf16* __re
     char* pool = is_v ? vpool : kpool;
     // dims 4l..4l+3 sit in 16-byte chunk l/2 of token row r
     *reinterpret_cast<uint2*>(pool + tile + r * 256 + (((lane >> 1) ^ (r & 7)) << 4) + (lane & 1) * 8) = o;
-    // the prompt pass also wants the rows token-major [rows][n_kv][128] for its attention
-    bf16* lin = is_v ? Vlin : Klin;
-    if (lin) *reinterpret_cast<uint2*>(lin + ((size_t)m * nkv + kh) * 128 + 4 * lane) = o;
   }
 }
 
@@ -849,37 +845,11 @@ extern "C" int q_swiglu_interleaved(const float* d_branch, const q_gemm_plan_t* 
   return q_swiglu_layout(d_branch, plan, d_out, rows, inter, 1, stream);
 }
 
-static int qkv_norm_rope_impl(const float* d_branch, const q_gemm_plan_t* plan,
-                              const void* d_q_gain, const void* d_k_gain, const void* d_cos,
-                              const void* d_sin, const int32_t* d_pos, void* d_q_out, void* d_k_lin, void* d_v_lin,
-                              const q_kv_layout_t* kv, int batch, int T, int n_q_heads,
-                              float eps, void* stream);
-
 extern "C" int q_qkv_norm_rope_cache(const float* d_branch, const q_gemm_plan_t* plan,
                                      const void* d_q_gain, const void* d_k_gain, const void* d_cos,
                                      const void* d_sin, const int32_t* d_pos, void* d_q_out,
                                      const q_kv_layout_t* kv, int batch, int T, int n_q_heads,
                                      float eps, void* stream) {
-  return qkv_norm_rope_impl(d_branch, plan, d_q_gain, d_k_gain, d_cos, d_sin, d_pos, d_q_out, nullptr, nullptr, kv,
-                            batch, T, n_q_heads, eps, stream);
-}
-
-extern "C" int q_qkv_norm_rope_prefill(const float* d_branch, const q_gemm_plan_t* plan,
-                                       const void* d_q_gain, const void* d_k_gain, const void* d_cos,
-                                       const void* d_sin, const int32_t* d_pos, void* d_q_out, void* d_k_out,
-                                       void* d_v_out, const q_kv_layout_t* kv, int batch, int T, int n_q_heads,
-                                       float eps, void* stream) {
-  Q_CHECK_ARG(d_k_out && d_v_out, "q_qkv_norm_rope_prefill: null pointer");
-  Q_CHECK_ALIGN(d_k_out, 8, "q_qkv_norm_rope_prefill"); Q_CHECK_ALIGN(d_v_out, 8, "q_qkv_norm_rope_prefill");
-  return qkv_norm_rope_impl(d_branch, plan, d_q_gain, d_k_gain, d_cos, d_sin, d_pos, d_q_out, d_k_out, d_v_out, kv,
-                            batch, T, n_q_heads, eps, stream);
-}
-
-static int qkv_norm_rope_impl(const float* d_branch, const q_gemm_plan_t* plan,
-                              const void* d_q_gain, const void* d_k_gain, const void* d_cos,
-                              const void* d_sin, const int32_t* d_pos, void* d_q_out, void* d_k_lin, void* d_v_lin,
-                              const q_kv_layout_t* kv, int batch, int T, int n_q_heads,
-                              float eps, void* stream) {
   Q_CHECK_ARG(d_branch && d_q_gain && d_k_gain && d_cos && d_sin && d_pos && d_q_out && kv,
               "q_qkv_norm_rope_cache: null pointer");
   Q_CHECK_ARG(kv->d_kpool && kv->d_vpool && kv->d_block_table && kv->pages_per_seq >= 1 &&
@@ -899,7 +869,7 @@ static int qkv_norm_rope_impl(const float* d_branch, const q_gemm_plan_t* plan,
                         d_branch, plan_view(plan), (const bf16*)d_q_gain, (const bf16*)d_k_gain,
                         (const bf16*)d_cos, (const bf16*)d_sin, d_pos, (bf16*)d_q_out,
                         (char*)kv->d_kpool, (char*)kv->d_vpool, kv->d_block_table, kv->pages_per_seq,
-                        rows, T, n_q_heads, nkv, eps, (bf16*)d_k_lin, (bf16*)d_v_lin));
+                        rows, T, n_q_heads, nkv, eps));
   return Q_OK;
 }
 

@@ -230,6 +230,16 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
   if (lane < 2) tags[warp * 2 + lane] = -1;
   __syncwarp();
 
+  // The norm gains do not depend on the previous kernel: asked for before the wait.
+  uint2 gn[3] = {make_uint2(0, 0), make_uint2(0, 0), make_uint2(0, 0)};
+  if (PRO) {
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      const int col = 4 * tid + j * 1024;
+      gn[j] = *reinterpret_cast<const uint2*>(pro.gain + (col < K ? col : 0));
+    }
+  }
+
   pdl_wait();   // X and the previous readers of P are complete from here on
   tl_waited(tl);
   if (trace) g_gemm_trace[blockIdx.x * 8 + 2] = gtime();
@@ -239,7 +249,7 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
     constexpr int VB = 3;                       // K <= 3072 (checked on the host)
     for (int m = 0; m < M; ++m) {
       float4 s0[VB], s1[VB];
-      uint2 xr[VB], gn[VB];
+      uint2 xr[VB];
 #pragma unroll
       for (int j = 0; j < VB; ++j) {
         const int col = 4 * tid + j * 1024;
@@ -249,7 +259,6 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
                     ? *reinterpret_cast<const float4*>(pro.prev + (size_t)m * K + cc + pro.prev_plan.slot_stride)
                     : make_float4(0.f, 0.f, 0.f, 0.f);
         xr[j] = *reinterpret_cast<const uint2*>(pro.resid_in + (size_t)m * K + cc);
-        gn[j] = *reinterpret_cast<const uint2*>(pro.gain + cc);
       }
       if (m == 0 && lane == 0) {
         // the rest of the ring, behind the prologue's loads in the memory system's queues
