@@ -423,8 +423,8 @@ k_attn_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml
 // distributed shared memory: every CTA parks its (max, sum, O) rows in its own shared
 // memory, the cluster synchronises once, and CTA r of the cluster combines 1/S of the
 // (row, dim) outputs from all S CTAs in split order. No global round trips, no tickets.
-template <bool CL>
-__global__ void __launch_bounds__(THREADS)
+template <bool CL, int DG>
+__global__ void __launch_bounds__((4 * DG + 1) * 32)
 k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict__ QG,
               const bf16* __restrict__ KG, const bf16* __restrict__ COS, const bf16* __restrict__ SIN,
               const int32_t* __restrict__ pos_ptr, char* __restrict__ kpool, char* __restrict__ vpool,
@@ -436,12 +436,18 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
   // two tiles asks for that much shared memory only, so this CTA fits on an SM beside a
   // weight-streaming GEMM CTA (the next projection primes its ring during the attention).
   const int NS = ring_stages;
+  constexpr int DC = 4 * DG;                 // consumer warps: DG groups of four, one tile per group at a time
+  constexpr int DT = (DC + 1) * 32;          // threads; warp DC is the producer
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* stages = smem;                               // NS * STAGE_BYTES
   unsigned char* qtile = smem + NS * STAGE_BYTES;             // 16 rows * 256 B
   uint64_t* bars = reinterpret_cast<uint64_t*>(qtile + 16 * 256);       // full[NS], empty[NS]
   bf16* knew = reinterpret_cast<bf16*>(bars + 2 * NS);        // [128]
   bf16* vnew = knew + 128;                                    // [128]
+  // Cluster merge: every CTA of the cluster stores its part of the rows THIS CTA combines
+  // here ([S][share] sums, then from float G*128+16 on [S][G][2] max / sum of weights), outside the ring, which a
+  // slower CTA is still using when a faster one delivers.
+  float* recv = reinterpret_cast<float*>(vnew + 128);
   __shared__ int s_last;
 
   tl_begin(tl);
@@ -454,7 +460,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
       mbar_init(smem_u32(&bars[i]), 1);
-      mbar_init(smem_u32(&bars[NS + i]), CONSUMERS);
+      mbar_init(smem_u32(&bars[NS + i]), 4);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -465,7 +471,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
   // producer warp fetches this sequence's block-table row together with the position (one
   // memory round trip instead of two before the first KV copy can be issued).
   int my_page = 0;
-  if (warp == CONSUMERS && lane < pages_per_seq) my_page = block_table[(size_t)b * pages_per_seq + lane];
+  if (warp == DC && lane < pages_per_seq) my_page = block_table[(size_t)b * pages_per_seq + lane];
   const int pos = pos_ptr[0];
   const int max_limit = pos + 1;
   const int tiles_used = (max_limit + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
@@ -477,7 +483,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
   const int new_tile = pos / Q_PAGE_TOKENS, new_row = pos % Q_PAGE_TOKENS;
   const bool owns_new = ntiles > 0 && new_tile >= tile0 && new_tile < tile1;
 
-  if (warp == CONSUMERS) {
+  if (warp == DC) {
     for (int it = 0; it < ntiles && it < NS; ++it) {
       const int tile = tile0 + it;
       int page = __shfl_sync(0xffffffffu, my_page, tile & 31);
@@ -510,7 +516,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
   // that with 4 query heads per kv head every warp has one item and one memory round trip.
   {
     const int width = (nq + 2 * nkv) * 128;
-    for (int h = warp; h < G + 1; h += CONSUMERS + 1) {
+    for (int h = warp; h < G + 1; h += DC + 1) {
       const bool is_q = h < G;
       const int head = is_q ? kh * G + h : nq + kh;
       const long long src = (long long)b * width + (long long)head * 128 + 4 * lane;
@@ -580,7 +586,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
         *reinterpret_cast<uint2*>(knew + 4 * lane) = o;
       }
     }
-    for (int i = tid; i < (16 - G) * 16; i += THREADS) {       // query rows G..15 are zero
+    for (int i = tid; i < (16 - G) * 16; i += DT) {       // query rows G..15 are zero
       const int r = G + (i >> 4), ch = i & 15;
       *reinterpret_cast<uint4*>(qtile + r * 256 + ((ch ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
     }
@@ -596,7 +602,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
     *reinterpret_cast<uint4*>(vpool + tile + off) = *reinterpret_cast<const uint4*>(vnew + tid * 8);
   }
 
-  if (warp == CONSUMERS) {
+  if (warp == DC) {
     if (lane == 0) {
       for (int it = NS; it < ntiles; ++it) {
         const int s = it % NS;
@@ -619,7 +625,8 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
 #pragma unroll
     for (int n = 0; n < 16; ++n) oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f;
     const uint32_t q_base = smem_u32(qtile);
-    for (int it = 0; it < ntiles; ++it) {
+    const int grp = warp >> 2, wk = warp & 3;       // tile lane of the warp's group, key quarter of the warp
+    for (int it = grp; it < ntiles; it += DG) {
       const int s = it % NS;
       if (!mbar_wait(smem_u32(&bars[s]), (it / NS) & 1)) {
         atomicExch(&g_status[0], 2);
@@ -628,15 +635,15 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
       unsigned char* kt = stages + s * STAGE_BYTES;
       unsigned char* vt = kt + TILE_BYTES;
       const int key_base = (tile0 + it) * Q_PAGE_TOKENS;
-      const int my_key0 = key_base + warp * 16;
+      const int my_key0 = key_base + wk * 16;
       if (my_key0 + 16 > max_limit) {
         for (int i = lane; i < 16 * 16; i += 32) {
-          const int kr = warp * 16 + (i >> 4);
+          const int kr = wk * 16 + (i >> 4);
           if (key_base + kr >= max_limit)
             *reinterpret_cast<uint4*>(vt + kr * 256 + ((i & 15) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
-      if (tile0 + it == new_tile && (new_row >> 4) == warp && lane < 16) {
+      if (tile0 + it == new_tile && (new_row >> 4) == wk && lane < 16) {
         const int off = new_row * 256 + ((lane ^ (new_row & 7)) << 4);
         *reinterpret_cast<uint4*>(kt + off) = *reinterpret_cast<const uint4*>(knew + lane * 8);
         *reinterpret_cast<uint4*>(vt + off) = *reinterpret_cast<const uint4*>(vnew + lane * 8);
@@ -660,7 +667,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
         }
         {
           const int mi = lane >> 3;
-          const int key = warp * 16 + 8 * (mi >> 1) + (lane & 7);
+          const int key = wk * 16 + 8 * (mi >> 1) + (lane & 7);
           const int ch = 2 * ks + (mi & 1);
           ldsm_x4(k_base + key * 256 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
         }
@@ -713,7 +720,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
       for (int dp = 0; dp < 8; ++dp) {
         uint32_t b0, b1, b2, b3;
         const int mi = lane >> 3;
-        const int key = warp * 16 + 8 * (mi & 1) + (lane & 7);
+        const int key = wk * 16 + 8 * (mi & 1) + (lane & 7);
         const int ch = 2 * dp + (mi >> 1);
         ldsm_x4_t(v_base + key * 256 + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
         mma16816(oacc[2 * dp], pa0, pa1, pa2, pa3, b0, b1);
@@ -723,10 +730,10 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
       if (lane == 0) mbar_arrive(smem_u32(&bars[NS + s]));
     }
     if (stamp) g_attn_trace[3] = tl_now();
-    // merge the four consumer states through shared memory (only the G real query rows)
-    consumer_sync();
-    float* mo = reinterpret_cast<float*>(stages);            // [4][G][128]: fits one stage for G <= 15
-    float* mml = mo + CONSUMERS * G * 128;                   // [4][G][2]
+    // merge the consumer warps' states through shared memory (only the G real query rows)
+    asm volatile("bar.sync 1, %0;" ::"n"(DC * 32) : "memory");
+    float* mo = reinterpret_cast<float*>(stages);            // [DC][G][128]
+    float* mml = mo + DC * G * 128;                          // [DC][G][2]
     if (g < G) {
       float* dst = mo + ((size_t)warp * G + g) * 128;
 #pragma unroll
@@ -737,16 +744,16 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
         mml[((size_t)warp * G + g) * 2 + 1] = l_run[0];
       }
     }
-    consumer_sync();
-    const int d = tid;
-    for (int r = 0; r < G; ++r) {
-      float mw[CONSUMERS], Mx = -INFINITY;
+    asm volatile("bar.sync 1, %0;" ::"n"(DC * 32) : "memory");
+    const int d = tid & 127;
+    for (int r = tid >> 7; r < G; r += DG) {
+      float mw[DC], Mx = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < CONSUMERS; ++w) { mw[w] = mml[((size_t)w * G + r) * 2]; Mx = fmaxf(Mx, mw[w]); }
+      for (int w = 0; w < DC; ++w) { mw[w] = mml[((size_t)w * G + r) * 2]; Mx = fmaxf(Mx, mw[w]); }
       const float Ms = Mx == -INFINITY ? 0.f : Mx;
       float Lsum = 0.f, O = 0.f;
 #pragma unroll
-      for (int w = 0; w < CONSUMERS; ++w) {
+      for (int w = 0; w < DC; ++w) {
         const float wt = exp2f(mw[w] - Ms);
         Lsum += wt * mml[((size_t)w * G + r) * 2 + 1];
         O += wt * mo[((size_t)w * G + r) * 128 + d];
@@ -754,9 +761,18 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
       if (S == 1) {
         out[((size_t)b * nq + kh * G + r) * 128 + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
       } else if (CL) {
-        float* fo = mml + CONSUMERS * G * 2;                   // [G][128] then [G][2]
-        fo[r * 128 + d] = O;
-        if (d == 0) { fo[G * 128 + r * 2] = Mx; fo[G * 128 + r * 2 + 1] = Lsum; }
+        // deliver to the CTA that combines this (row, dim): slot `split` of its receive area
+        const int total = G * 128, share = (total + S - 1) / S;
+        const int v = r * 128 + d, owner = v / share;
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(recv)), "r"(owner));
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)(split * share + (v - owner * share)) * 4u), "f"(O) : "memory");
+        if (d < S) {
+          // the row's max and sum of weights go to every CTA of the cluster (thread d -> CTA d)
+          const uint32_t ml_off = (uint32_t)((total + 16) + (split * G + r) * 2) * 4u;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(recv)), "r"(d));
+          asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(remote + ml_off), "f"(Mx), "f"(Lsum) : "memory");
+        }
       } else {
         const size_t row = ((size_t)bh * S + split) * G + r;
         part_o[row * 128 + d] = O;
@@ -771,42 +787,31 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (stamp) g_attn_trace[5] = tl_now();
-    const uint32_t fo_local = smem_u32(stages) + (uint32_t)(CONSUMERS * G * 130) * 4u;
+    // Everything this CTA combines is in its own receive area now: no remote reads, so no
+    // second barrier before it may leave.
     const int total = G * 128;
     const int share = (total + S - 1) / S;
-    for (int i = tid; i < share; i += THREADS) {
+    const float* rml = recv + (total + 16);
+    for (int i = tid; i < share; i += DT) {
       const int v = split * share + i;
       if (v >= total) break;
       const int r = v >> 7, d = v & 127;
-      float ms[MAX_CLUSTER], ls[MAX_CLUSTER], os[MAX_CLUSTER];
-#pragma unroll
-      for (int s = 0; s < MAX_CLUSTER; ++s) {
-        ms[s] = -INFINITY; ls[s] = 0.f; os[s] = 0.f;
-        if (s < S) {
-          uint32_t remote;
-          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(fo_local), "r"(s));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ms[s]) : "r"(remote + (uint32_t)(total + r * 2) * 4u));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ls[s]) : "r"(remote + (uint32_t)(total + r * 2 + 1) * 4u));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(os[s]) : "r"(remote + (uint32_t)(r * 128 + d) * 4u));
-        }
-      }
       float Mx = -INFINITY;
-#pragma unroll
-      for (int s = 0; s < MAX_CLUSTER; ++s) Mx = fmaxf(Mx, ls[s] > 0.f ? ms[s] : -INFINITY);
+      for (int s = 0; s < S; ++s) {
+        const float2 ml = *reinterpret_cast<const float2*>(rml + (s * G + r) * 2);
+        Mx = fmaxf(Mx, ml.y > 0.f ? ml.x : -INFINITY);
+      }
       if (Mx == -INFINITY) Mx = 0.f;
       float Lsum = 0.f, O = 0.f;
-#pragma unroll
-      for (int s = 0; s < MAX_CLUSTER; ++s) {
-        const float wgt = ls[s] > 0.f ? exp2f(ms[s] - Mx) : 0.f;
-        Lsum += wgt * ls[s];
-        O += wgt * os[s];
+      for (int s = 0; s < S; ++s) {
+        const float2 ml = *reinterpret_cast<const float2*>(rml + (s * G + r) * 2);
+        const float wgt = ml.y > 0.f ? exp2f(ml.x - Mx) : 0.f;
+        Lsum += wgt * ml.y;
+        O += wgt * recv[s * share + i];
       }
       const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
       out[((size_t)b * nq + kh * G + r) * 128 + d] = __float2bfloat16_rn(O * inv);
     }
-    // nobody leaves while a peer may still read its shared memory
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (stamp) g_attn_trace[6] = tl_now();
     tl_end(tl);
     return;
@@ -823,7 +828,7 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
   }
   __syncthreads();
   if (!s_last) { tl_end(tl); return; }
-  for (int r = warp; r < G; r += CONSUMERS + 1) {
+  for (int r = warp; r < G; r += DC + 1) {
     const size_t base = ((size_t)bh * S) * G + r;
     float m = -INFINITY, l = 0.f;
     if (lane < S) {
@@ -1069,7 +1074,7 @@ k_attn_prefill(const bf16* __restrict__ Q, const char* __restrict__ kpool, const
   }
 }
 
-constexpr size_t attn_decode_smem(int ns) { return ns * STAGE_BYTES + 16 * 256 + 2 * ns * 8 + 2 * 128 * 2 + 64; }
+constexpr size_t attn_decode_smem(int ns) { return ns * STAGE_BYTES + 16 * 256 + 2 * ns * 8 + 2 * 128 * 2 + 64 + (8 * 128 + 16 + MAX_CLUSTER * 8 * 2) * 4; }
 
 template <int RT>
 constexpr size_t attn_smem() { return NS * STAGE_BYTES + RT * 16 * 256 + 2 * NS * 8; }
@@ -1202,15 +1207,27 @@ extern "C" int q_attention_decode(const float* d_qkv_partials, const q_gemm_plan
   Q_CHECK_ALIGN(d_sin, 8, "q_attention_decode"); Q_CHECK_ALIGN(kv->d_kpool, 16, "q_attention_decode");
   Q_CHECK_ALIGN(kv->d_vpool, 16, "q_attention_decode"); Q_CHECK_ALIGN(d_scratch_o, 16, "q_attention_decode");
   Q_CHECK_ALIGN(d_scratch_ml, 8, "q_attention_decode"); Q_CHECK_ALIGN(d_out, 8, "q_attention_decode");
-  static size_t done_plain[64] = {0}, done_cluster[64] = {0};
-  Q_CHECK_CUDA(q_ensure_smem(k_attn_decode<false>, attn_decode_smem(NS), done_plain));
-  Q_CHECK_CUDA(q_ensure_smem(k_attn_decode<true>, attn_decode_smem(NS), done_cluster));
   // most tiles one split can be handed: ceil(tiles / splits) over the page capacity
   int ring = (kv->pages_per_seq + splits - 1) / splits;
   ring = ring < 1 ? 1 : (ring > NS ? NS : ring);
+  // Three warp groups (one tile each at a time) when every CTA of the launch gets an SM of its
+  // own; otherwise one group, so that two CTAs still fit on an SM. A ring stage must always be
+  // consumed by the same group (its mbarrier parity is tracked per group), so the three groups
+  // need the three-stage ring.
+  int sms = q_sm_count();
+  if (sms <= 0) sms = 148;
+  const bool wide = splits > 1 && (long long)splits * batch * nkv <= sms && ring == 3 && NS == 3;
+  const int dc = wide ? 12 : 4;
+  const dim3 block((dc + 1) * 32);
+  static size_t done[4][64] = {{0}};
+  Q_CHECK_CUDA(q_ensure_smem(k_attn_decode<false, 1>, attn_decode_smem(NS), done[0]));
+  Q_CHECK_CUDA(q_ensure_smem(k_attn_decode<true, 1>, attn_decode_smem(NS), done[1]));
+  Q_CHECK_CUDA(q_ensure_smem(k_attn_decode<false, 3>, attn_decode_smem(NS), done[2]));
+  Q_CHECK_CUDA(q_ensure_smem(k_attn_decode<true, 3>, attn_decode_smem(NS), done[3]));
   // the merge scratch (consumer states, then the CTA's own rows) reuses the ring
-  const int scratch_stages = (G * 5 * 130 * 4 + STAGE_BYTES - 1) / STAGE_BYTES;
+  const int scratch_stages = (G * (dc + 1) * 130 * 4 + STAGE_BYTES - 1) / STAGE_BYTES;
   if (ring < scratch_stages) ring = scratch_stages;
+  Q_CHECK_ARG(ring <= NS, "q_attention_decode: merge scratch does not fit the ring");
   bool cluster = splits >= 2 && splits <= MAX_CLUSTER && !g_attn_no_cluster;
   if (cluster && splits > 8) {
     // more than 8 CTAs per cluster is an opt-in size; whether such clusters can be placed
@@ -1221,16 +1238,18 @@ extern "C" int q_attention_decode(const float* d_qkv_partials, const q_gemm_plan
     else {
       if (placeable[dev][splits] == 0) {
         int n = 0;
-        cudaError_t e1 = cudaFuncSetAttribute(k_attn_decode<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cudaError_t e1 = cudaFuncSetAttribute(k_attn_decode<true, 1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e1 == cudaSuccess)
+          e1 = cudaFuncSetAttribute(k_attn_decode<true, 3>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(splits, batch * nkv);
-        cfg.blockDim = dim3(THREADS);
-        cfg.dynamicSmemBytes = attn_decode_smem(ring);
+        cfg.blockDim = dim3(13 * 32);
+        cfg.dynamicSmemBytes = attn_decode_smem(NS);
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
         at[0].val.clusterDim.x = splits; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
-        cudaError_t e2 = e1 == cudaSuccess ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<true>, &cfg) : e1;
+        cudaError_t e2 = e1 == cudaSuccess ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<true, 3>, &cfg) : e1;
         if (e2 != cudaSuccess) cudaGetLastError();
         placeable[dev][splits] = (e2 == cudaSuccess && n >= 1) ? 1 : -1;
       }
@@ -1240,22 +1259,22 @@ extern "C" int q_attention_decode(const float* d_qkv_partials, const q_gemm_plan
   Q_CHECK_ARG(cluster || splits == 1 || (d_scratch_o && d_scratch_ml && d_tickets),
               "q_attention_decode: split scratch or tickets missing (needed when the splits cannot merge in a cluster)");
   const float sl2 = scale * 1.4426950408889634f;
+#define Q_ATTN_DECODE_ARGS                                                                              \
+  d_qkv_partials, plan_view(plan), (const bf16*)d_q_gain, (const bf16*)d_k_gain, (const bf16*)d_cos,   \
+      (const bf16*)d_sin, d_pos, (char*)kv->d_kpool, (char*)kv->d_vpool, kv->d_block_table,             \
+      kv->pages_per_seq, d_scratch_o, d_scratch_ml, d_tickets, (bf16*)d_out, batch, G, n_q_heads, nkv,  \
+      splits, sl2, eps, ring, q_tl_next(Q_TL_ATTENTION)
+  const dim3 grid(splits, batch * nkv);
+  const size_t smem = attn_decode_smem(ring);
+  cudaStream_t st = (cudaStream_t)stream;
   if (cluster) {
-    Q_CHECK_CUDA(q_launch_cluster(k_attn_decode<true>, dim3(splits, batch * nkv), dim3(THREADS),
-                                  attn_decode_smem(ring), (cudaStream_t)stream, (unsigned)splits,
-                                  d_qkv_partials, plan_view(plan), (const bf16*)d_q_gain,
-                                  (const bf16*)d_k_gain, (const bf16*)d_cos, (const bf16*)d_sin, d_pos,
-                                  (char*)kv->d_kpool, (char*)kv->d_vpool, kv->d_block_table,
-                                  kv->pages_per_seq, d_scratch_o, d_scratch_ml, d_tickets, (bf16*)d_out,
-                                  batch, G, n_q_heads, nkv, splits, sl2, eps, ring, q_tl_next(Q_TL_ATTENTION)));
+    if (wide) Q_CHECK_CUDA(q_launch_cluster(k_attn_decode<true, 3>, grid, block, smem, st, (unsigned)splits, Q_ATTN_DECODE_ARGS));
+    else Q_CHECK_CUDA(q_launch_cluster(k_attn_decode<true, 1>, grid, block, smem, st, (unsigned)splits, Q_ATTN_DECODE_ARGS));
   } else {
-    Q_CHECK_CUDA(q_launch(k_attn_decode<false>, dim3(splits, batch * nkv), dim3(THREADS),
-                          attn_decode_smem(ring), (cudaStream_t)stream, d_qkv_partials, plan_view(plan),
-                          (const bf16*)d_q_gain, (const bf16*)d_k_gain, (const bf16*)d_cos,
-                          (const bf16*)d_sin, d_pos, (char*)kv->d_kpool, (char*)kv->d_vpool,
-                          kv->d_block_table, kv->pages_per_seq, d_scratch_o, d_scratch_ml, d_tickets,
-                          (bf16*)d_out, batch, G, n_q_heads, nkv, splits, sl2, eps, ring, q_tl_next(Q_TL_ATTENTION)));
+    if (wide) Q_CHECK_CUDA(q_launch(k_attn_decode<false, 3>, grid, block, smem, st, Q_ATTN_DECODE_ARGS));
+    else Q_CHECK_CUDA(q_launch(k_attn_decode<false, 1>, grid, block, smem, st, Q_ATTN_DECODE_ARGS));
   }
+#undef Q_ATTN_DECODE_ARGS
   return Q_OK;
 }
 

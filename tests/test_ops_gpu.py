@@ -376,8 +376,11 @@ def test_prompt_attention_equals_small_query_kernel(ops):
 def test_fused_decode_attention_equals_the_three_kernels(ops, B, nq, nkv, pos, cluster):
     """One launch (norm + RoPE + K/V write + attention + merge) against the separate
     kernels on the same inputs: bit-identical pages; the attended rows agree to bf16
-    rounding (the fused kernel adds the QK^T k-steps in two interleaved chains) and both
-    sit within rtol=0.02, atol=5e-3 of each other like every attention check here.
+    rounding and sit within rtol=0.02, atol=5e-3 of each other like every attention check
+    here. Most elements are bit-equal, not all: the probabilities are rounded to bf16 relative
+    to the running maximum of the softmax state they belong to, and the fused kernel keeps one
+    state per (tile, key quarter) when its CTAs have an SM each, the three-kernel path one per
+    (split, key quarter).
     `cluster`: up to 8 splits merge through distributed shared memory (default) or, like
     more than 8 splits always do, through global memory and a ticket."""
     from starter_b200 import _lib
@@ -412,7 +415,7 @@ def _fused_decode_attention_case(ops, B, nq, nkv, pos):
     for _ in range(2):                                  # twice: the tickets must reset themselves
         got = ops.decode_attention(part, qg, kg, 1e-6, cos, sin, position, caches[1], attn, 128 ** -0.5)
         torch.testing.assert_close(got.float(), ref.float(), rtol=0.02, atol=5e-3)
-        assert bit_equal_fraction(got, ref) > 0.9
+        assert bit_equal_fraction(got, ref) > 0.6
     ka, va = caches[0].gather(pos + 1)
     kb, vb = caches[1].gather(pos + 1)
     assert torch.equal(ka.view(torch.int16), kb.view(torch.int16))
