@@ -165,7 +165,10 @@ int q_reduce_partials(const float* d_partials, const q_gemm_plan_t* plan,
  * image with 128-byte swizzle that tcgen05.mma reads (rows past N and k past K zero).
  * q_gemm_tc writes the same kind of partial slots as q_gemm_splitk, with a "group" of 128
  * weight rows: plan.group_rows = 128, chunks_per_group = k tiles, units_per_worker = tiles
- * per CTA. Rows are processed in chunks of up to 256 (one weight pass per chunk); X is
+ * per CTA. More than 256 rows run as row chunks of 256 inside the same launch, tiles in
+ * (row chunk, weight block, k tile) order (one weight pass per chunk); the plan's groups
+ * are then the (row chunk, weight block) pairs, groups = ceil(M/256) * ceil(N/128), and the
+ * slot count of element (m, n) is that of group (m / 256) * ceil(N/128) + n / 128. X is
  * row-major [M][K], 16-byte aligned; d_w_tc 1024-byte aligned. */
 int64_t q_packed_weight_bytes_tc(int N, int K);
 int q_pack_weight_tc(const void* d_rowmajor, void* d_tiled, int N, int K, void* stream);

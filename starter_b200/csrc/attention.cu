@@ -867,16 +867,16 @@ k_attn_decode(const float* __restrict__ PQ, PlanView pv, const bf16* __restrict_
 // the library's scaled-dot-product attention there). One CTA = one (sequence, kv head, block of
 // 128/G prompt tokens): its 128 query rows (token-major, the G query heads of the kv head side
 // by side) share every K/V page tile. Warps 0..7 each own 16 query rows and all 64 keys of a
-// tile - S = Q K^T, online softmax and P V with mma.m16n8k16, no merge between warps - and warp
-// 8 is the producer that walks the block table. Keys come from the pages the head-norm + RoPE
+// tile - S = Q K^T, online softmax and P V with mma.m16n8k16, no merge between warps; one lane
+// walks the block table and keeps the two-stage ring full. Keys come from the pages the head-norm + RoPE
 // kernel has just filled, tiles past the block's last token are never fetched, and the
 // diagonal tiles are masked per row. Same cast boundaries as the decode kernels.
 constexpr int PF_WARPS = 8;
-constexpr int PF_THREADS = (PF_WARPS + 1) * 32;
+constexpr int PF_THREADS = PF_WARPS * 32;
 constexpr int PF_NS = 2;
 constexpr size_t PF_SMEM = PF_NS * STAGE_BYTES + 128 * 256 + 2 * PF_NS * 8;
 
-__global__ void __launch_bounds__(PF_THREADS)
+__global__ void __launch_bounds__(PF_THREADS, 2)
 k_attn_prefill(const bf16* __restrict__ Q, const char* __restrict__ kpool, const char* __restrict__ vpool,
                const int32_t* __restrict__ block_table, int pages_per_seq,
                const int32_t* __restrict__ pos_ptr, bf16* __restrict__ out, int T, int G, int gshift,
@@ -906,24 +906,20 @@ k_attn_prefill(const bf16* __restrict__ Q, const char* __restrict__ kpool, const
   const int max_limit = pos + tok_end;                            // keys visible to the last row
   const int ntiles = (max_limit + Q_PAGE_TOKENS - 1) / Q_PAGE_TOKENS;
 
-  if (warp == PF_WARPS) {
-    if (lane == 0) {
-      for (int it = 0; it < ntiles; ++it) {
-        const int s = it % PF_NS;
-        if (it >= PF_NS && !mbar_wait(smem_u32(&bars[PF_NS + s]), ((it / PF_NS) - 1) & 1)) {
-          atomicExch(&g_status[0], 5);
-          break;
-        }
-        const int page = block_table[(size_t)b * pages_per_seq + it];
-        const size_t off = ((size_t)page * nkv + kh) * TILE_BYTES;
-        const uint32_t bar = smem_u32(&bars[s]);
-        mbar_expect_tx(bar, STAGE_BYTES);
-        bulk_g2s(smem_u32(stages + s * STAGE_BYTES), kpool + off, TILE_BYTES, bar);
-        bulk_g2s(smem_u32(stages + s * STAGE_BYTES + TILE_BYTES), vpool + off, TILE_BYTES, bar);
-      }
-    }
-    return;
-  }
+  // Lane 0 of warp 0 is also the producer: it asks for the first tiles here and for tile
+  // it + PF_NS when every warp has let go of tile it (no ninth warp: 256 threads leave each
+  // thread 128 registers with two CTAs on an SM).
+  auto fetch_tile = [&](int it) {
+    const int s = it % PF_NS;
+    const int page = block_table[(size_t)b * pages_per_seq + it];
+    const size_t off = ((size_t)page * nkv + kh) * TILE_BYTES;
+    const uint32_t bar = smem_u32(&bars[s]);
+    mbar_expect_tx(bar, STAGE_BYTES);
+    bulk_g2s(smem_u32(stages + s * STAGE_BYTES), kpool + off, TILE_BYTES, bar);
+    bulk_g2s(smem_u32(stages + s * STAGE_BYTES + TILE_BYTES), vpool + off, TILE_BYTES, bar);
+  };
+  if (tid == 0)
+    for (int it = 0; it < ntiles && it < PF_NS; ++it) fetch_tile(it);
 
   // ---------------- consumers ----------------
   // Q block -> shared memory (swizzled rows of 256 B); rows of tokens past the prompt are zero.
@@ -951,14 +947,7 @@ k_attn_prefill(const bf16* __restrict__ Q, const char* __restrict__ kpool, const
   // keys this warp's 16 rows can see: tiles past that are skipped by the warp (still released)
   const int t_last = min(q0 + ((warp * 16 + 15) >> gshift), T - 1);
   const int warp_limit = pos + t_last + 1;
-  // the Q fragments of the warp's rows stay in registers for the whole pass
-  uint32_t qa[8][4];
-#pragma unroll
-  for (int ks = 0; ks < 8; ++ks) {
-    const int row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
-    const int ch = 2 * ks + (lane >> 4);
-    ldsm_x4(smem_u32(qtile) + row * 256 + ((ch ^ (row & 7)) << 4), qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
-  }
+  const uint32_t q_base = smem_u32(qtile);
 
   for (int it = 0; it < ntiles; ++it) {
     const int s = it % PF_NS;
@@ -987,6 +976,14 @@ k_attn_prefill(const bf16* __restrict__ Q, const char* __restrict__ kpool, const
       for (int j = 0; j < 8; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
+        // Q fragment of this k-step (re-read per tile: keeping all eight in registers costs
+        // the second CTA per SM)
+        uint32_t qa[8][4];
+        {
+          const int row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+          const int ch = 2 * ks + (lane >> 4);
+          ldsm_x4(q_base + row * 256 + ((ch ^ (row & 7)) << 4), qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
+        }
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) {                          // 16 keys per ldmatrix
           uint32_t b0, b1, b2, b3;
@@ -1058,6 +1055,13 @@ k_attn_prefill(const bf16* __restrict__ Q, const char* __restrict__ kpool, const
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_u32(&bars[PF_NS + s]));
+    if (tid == 0 && it + PF_NS < ntiles) {
+      // a wait that runs out leaves the tile unrequested: the consumers' own bounded wait
+      // for it then ends the CTA
+      if (mbar_wait(smem_u32(&bars[PF_NS + s]), (it / PF_NS) & 1)) fetch_tile(it + PF_NS);
+      else atomicExch(&g_status[0], 5);
+    }
+    __syncwarp();
   }
 
   // one rounding to bf16; the row's 128 dims go to out[(b*T + t)][head][128]

@@ -150,6 +150,7 @@ struct PlanView {
   int u;       // units per worker
   int C;       // chunks per group
   int gshift;  // log2(weight rows per group): 4 (stream-K units) or 7 (tcgen05 tiles)
+  int nblk;    // tcgen05 plan of more than 256 rows: weight blocks per row chunk of 256 (else 0)
   long long slot_stride;  // M*N floats
 };
 
@@ -159,9 +160,10 @@ static inline PlanView plan_view(const q_gemm_plan_t* p) {
     v.u = p->units_per_worker;
     v.C = p->chunks_per_group;
     v.gshift = p->group_rows == 128 ? 7 : 4;
+    v.nblk = (p->group_rows == 128 && p->M > 256) ? (p->N + 127) / 128 : 0;
     v.slot_stride = (long long)p->M * p->N;
   } else {
-    v.u = 0; v.C = 0; v.gshift = 4; v.slot_stride = 0;
+    v.u = 0; v.C = 0; v.gshift = 4; v.nblk = 0; v.slot_stride = 0;
   }
   return v;
 }
@@ -210,10 +212,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&p);
 }
 
-// Number of split-K slots that hold a partial for column n.
-__device__ __forceinline__ int plan_count(const PlanView& pv, int n) {
+// Number of split-K slots that hold a partial for column n (of row `row`: plans of more than
+// 256 rows count their groups per row chunk).
+__device__ __forceinline__ int plan_count(const PlanView& pv, int n, int row = 0) {
   if (pv.u == 0) return 1;
-  const unsigned g = (unsigned)n >> pv.gshift, C = (unsigned)pv.C, u = (unsigned)pv.u;
+  const unsigned g = ((unsigned)n >> pv.gshift) + (unsigned)(row >> 8) * (unsigned)pv.nblk;
+  const unsigned C = (unsigned)pv.C, u = (unsigned)pv.u;
   const unsigned first = (g * C) / u;
   const unsigned last = ((g + 1) * C - 1) / u;
   return (int)(last - first + 1);
@@ -223,11 +227,11 @@ __device__ __forceinline__ int plan_count(const PlanView& pv, int n) {
 // partial buffer has at least two slots, so slot 1 is loaded unconditionally
 // (in parallel with slot 0) and only used when it holds data.
 __device__ __forceinline__ float plan_sum(const float* __restrict__ P, const PlanView& pv,
-                                          long long idx, int n) {
+                                          long long idx, int n, int row = 0) {
   float s = P[idx];
   if (pv.u != 0) {
     const float s1 = P[idx + pv.slot_stride];
-    const int cnt = plan_count(pv, n);
+    const int cnt = plan_count(pv, n, row);
     if (cnt > 1) s += s1;
     for (int k = 2; k < cnt; ++k) s += P[idx + k * pv.slot_stride];
   }

@@ -92,8 +92,8 @@ k_embed_rmsnorm(const int64_t* __restrict__ tokens, const bf16* __restrict__ E,
 // L2, so the kernel is one memory round trip + one block reduction).
 constexpr int ADD_VB = 10;     // 256 threads * 4 columns * 10 = 10240 columns
 
-__device__ __forceinline__ int plan_extra(const PlanView& pv, int n) {   // slots beyond the first
-  return plan_count(pv, n) - 1;
+__device__ __forceinline__ int plan_extra(const PlanView& pv, int n, int row) {   // slots beyond the first
+  return plan_count(pv, n, row) - 1;
 }
 
 // THREADS = 256, or 1024 for rows of up to 4096 columns (VB = 1): a row is then spread over
@@ -132,7 +132,7 @@ k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanVie
     for (int j = 0; j < VB; ++j) {
       const int col = 4 * threadIdx.x + j * 1024;
       const int cc = col < cols ? col : 0;
-      const int extra = plan_extra(pv, cc);
+      const int extra = plan_extra(pv, cc, (int)row);
 #pragma unroll
       for (int k = 0; k < EX; ++k)
         sx[j][k] = (k + 2 <= extra) ? *reinterpret_cast<const float4*>(p0 + cc + (long long)(k + 2) * pv.slot_stride)
@@ -145,7 +145,7 @@ k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanVie
   for (int j = 0; j < VB; ++j) {
     const int col = 4 * threadIdx.x + j * 1024;
     if (col < cols) {
-      const int extra = plan_extra(pv, col);        // the 4 columns share one group
+      const int extra = plan_extra(pv, col, (int)row);        // the 4 columns share one group
       float s[4] = {s0[j].x, s0[j].y, s0[j].z, s0[j].w};
       if (extra > 0) { s[0] += s1[j].x; s[1] += s1[j].y; s[2] += s1[j].z; s[3] += s1[j].w; }
       if (EX > 0 && two) {
@@ -432,7 +432,7 @@ k_swiglu(const float* __restrict__ P, PlanView pv, bf16* __restrict__ O, int row
   const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
   const float4 g1 = two ? *reinterpret_cast<const float4*>(base + gc + pv.slot_stride) : z;
   const float4 u1 = two ? *reinterpret_cast<const float4*>(base + uc + pv.slot_stride) : z;
-  const int eg = plan_count(pv, gc) - 1, eu = plan_count(pv, uc) - 1;
+  const int eg = plan_count(pv, gc, m) - 1, eu = plan_count(pv, uc, m) - 1;
   float gs[4] = {g0.x, g0.y, g0.z, g0.w}, us[4] = {u0.x, u0.y, u0.z, u0.w};
   if (eg > 0) { gs[0] += g1.x; gs[1] += g1.y; gs[2] += g1.z; gs[3] += g1.w; }
   if (eu > 0) { us[0] += u1.x; us[1] += u1.y; us[2] += u1.z; us[3] += u1.w; }
@@ -486,7 +486,7 @@ k_qkv_norm_rope_cache(const float* __restrict__ P, PlanView pv, const bf16* __re
   const uint2 graw = is_v ? make_uint2(0, 0) : *reinterpret_cast<const uint2*>((is_q ? QG : KG) + 4 * lane);
   const uint2 craw = *reinterpret_cast<const uint2*>(COS + (size_t)pos * 128 + 4 * lane);
   const uint2 sraw = *reinterpret_cast<const uint2*>(SIN + (size_t)pos * 128 + 4 * lane);
-  const int extra = plan_count(pv, head * 128 + 4 * lane) - 1;
+  const int extra = plan_count(pv, head * 128 + 4 * lane, m) - 1;
   float x[4] = {s0.x, s0.y, s0.z, s0.w};
   if (extra > 0) { x[0] += s1.x; x[1] += s1.y; x[2] += s1.z; x[3] += s1.w; }
   for (int k = 2; k <= extra; ++k) {
@@ -589,7 +589,7 @@ k_logits_argmax(const float* __restrict__ P, PlanView pv, bf16* __restrict__ log
       const float4 a = *reinterpret_cast<const float4*>(p0 + c);
       const float4 b = two ? *reinterpret_cast<const float4*>(p0 + c + pv.slot_stride)
                            : make_float4(0.f, 0.f, 0.f, 0.f);
-      const int extra = plan_count(pv, c) - 1;
+      const int extra = plan_count(pv, c, row) - 1;
       float s[4] = {a.x, a.y, a.z, a.w};
       if (extra > 0) { s[0] += b.x; s[1] += b.y; s[2] += b.z; s[3] += b.w; }
       for (int k = 2; k <= extra; ++k) {
@@ -612,7 +612,7 @@ k_logits_argmax(const float* __restrict__ P, PlanView pv, bf16* __restrict__ log
   } else {
     for (int c = c0 + threadIdx.x; c < c0 + ARG_COLS && c < vocab; c += 256) {
       long long i = (long long)row * vocab + c;
-      bf16 r = __float2bfloat16_rn(plan_sum(P, pv, i, c));
+      bf16 r = __float2bfloat16_rn(plan_sum(P, pv, i, c, row));
       if (logits) logits[i] = r;
       float v = __bfloat162float(r);
       if (v != v) v = -INFINITY;  // NaN never wins

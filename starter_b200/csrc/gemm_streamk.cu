@@ -504,7 +504,7 @@ __global__ void k_reduce_partials(const float* __restrict__ P, float* __restrict
     const float4 a = *reinterpret_cast<const float4*>(P + i);
     const float4 b = pv.u != 0 ? *reinterpret_cast<const float4*>(P + i + pv.slot_stride)
                                : make_float4(0.f, 0.f, 0.f, 0.f);
-    const int extra = plan_count(pv, n) - 1;
+    const int extra = plan_count(pv, n, (int)(i / N)) - 1;
     float4 s = a;
     if (extra > 0) { s.x += b.x; s.y += b.y; s.z += b.z; s.w += b.w; }
     // slots 2..9 are requested together (the tcgen05 plan splits long-K projections ~10 ways)
@@ -526,7 +526,7 @@ __global__ void k_reduce_partials(const float* __restrict__ P, float* __restrict
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const int n = (int)(i % N);
-  out[i] = plan_sum(P, pv, i, n);
+  out[i] = plan_sum(P, pv, i, n, (int)(i / N));
 }
 
 // Row-major [N][K] <-> tiled units. One thread per 16-byte piece of the tiled side.

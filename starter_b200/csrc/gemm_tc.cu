@@ -156,10 +156,11 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
 }
 
 struct TcShape {
-  int M;          // activation rows of this launch (<= m_pad)
+  int M;          // activation rows of this launch (more than m_pad: row chunks of m_pad rows)
   int N;          // weight rows
   int KT;         // k tiles (K rounded up to 64, / 64)
-  int total;      // tiles = row blocks * KT
+  int nblk;       // 128-row weight blocks
+  int total;      // tiles = row chunks * nblk * KT, in (row chunk, weight block, k tile) order
   int U;          // tiles per CTA
   int m_pad;      // MMA N: 16, 32, 64, 128 or 256
   int stages;     // ring depth
@@ -227,17 +228,19 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restr
     if (lane == 0) {
       const uint64_t policy = stream_policy();
       const int first = min(sh.stages, n_tiles);
+      const int per_chunk = sh.nblk * sh.KT;               // tiles of one pass over the weight
       for (int i = 0; i < first; ++i) {
         mbar_expect_tx(bar_full + 8 * i, stage_bytes);
-        bulk_g2s(base + i * stage_bytes, W + (size_t)(t0 + i) * W_TILE_BYTES, W_TILE_BYTES, bar_full + 8 * i,
-                 policy);
+        bulk_g2s(base + i * stage_bytes, W + (size_t)((t0 + i) % per_chunk) * W_TILE_BYTES, W_TILE_BYTES,
+                 bar_full + 8 * i, policy);
       }
       pdl_wait();                       // the activations are complete from here on
       tl_waited(tl);
       if (trace) tr[2] = gtime();
       for (int i = 0; i < first; ++i) {
         const int kt = (t0 + i) % sh.KT;
-        tma_load_2d(base + i * stage_bytes + W_TILE_BYTES, &xmap, kt * TILE_K, sh.row0, bar_full + 8 * i);
+        const int xrow = sh.row0 + ((t0 + i) / per_chunk) * sh.m_pad;
+        tma_load_2d(base + i * stage_bytes + W_TILE_BYTES, &xmap, kt * TILE_K, xrow, bar_full + 8 * i);
       }
       // Refill loop. One thread issues everything, so its instruction count per tile is what
       // bounds the copy rate: stage index, barrier parity and k tile are carried along instead
@@ -248,8 +251,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restr
         int st = 0;                                        // stage of tile `first`
         uint32_t parity = 0;                               // phase of empty[st] to wait for
         int kt = (t0 + first) % sh.KT;
+        int in_chunk = (t0 + first) % per_chunk;           // tile index inside the weight pass
+        int xrow = sh.row0 + ((t0 + first) / per_chunk) * sh.m_pad;
         uint32_t dst = base, full = bar_full, empty = bar_empty;
-        const unsigned char* src = W + (size_t)(t0 + first) * W_TILE_BYTES;
+        const unsigned char* src = W + (size_t)in_chunk * W_TILE_BYTES;
         for (int i = first; i < n_tiles; ++i) {
           if (!mbar_wait(empty, parity, abort_flag)) {
             atomicExch(&g_tc_status[0], 1);
@@ -259,10 +264,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restr
           }
           mbar_expect_tx(full, stage_bytes);
           bulk_g2s(dst, src, W_TILE_BYTES, full, policy);
-          tma_load_2d(dst + W_TILE_BYTES, &xmap, kt * TILE_K, sh.row0, full);
+          tma_load_2d(dst + W_TILE_BYTES, &xmap, kt * TILE_K, xrow, full);
           issued_tiles = i + 1;
           src += W_TILE_BYTES;
           if (++kt == sh.KT) kt = 0;
+          if (++in_chunk == per_chunk) { in_chunk = 0; src = W; xrow += sh.m_pad; }   // next row chunk
           if (++st == sh.stages) {
             st = 0; parity ^= 1u; dst = base; full = bar_full; empty = bar_empty;
           } else {
@@ -360,16 +366,18 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const unsigned char* __restr
       tc_fence_after();
       const int first_cta = (int)(((long long)block * sh.KT) / sh.U);
       float* out = P + (long long)((int)blockIdx.x - first_cta) * sh.slot_stride;
-      const int n = block * TILE_ROWS + q * 32 + lane;
+      const int chunk = block / sh.nblk, wblock = block - chunk * sh.nblk;
+      const int m0 = chunk * sh.m_pad;                      // first row of this segment's row chunk
+      const int n = wblock * TILE_ROWS + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * acc_cols);
       for (int c0 = 0; c0 < sh.m_pad; c0 += 16) {
-        if (c0 >= sh.M) break;          // warp-uniform
+        if (m0 + c0 >= sh.M) break;     // warp-uniform
         float v[16];
         tc_ld16(taddr + c0, v);
         if (n < sh.N) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int m = c0 + j;
+            const int m = m0 + c0 + j;
             if (m < sh.M) out[(size_t)(sh.row0 + m) * sh.N + n] = v[j];
           }
         }
@@ -497,9 +505,12 @@ extern "C" int q_gemm_tc_plan(int M, int N, int K, q_gemm_plan_t* plan) {
   int sms = q_sm_count();
   if (sms <= 0) sms = 148;
   const int KT = (K + TILE_K - 1) / TILE_K;
-  const int blocks = (N + TILE_ROWS - 1) / TILE_ROWS;
-  const long long total = (long long)blocks * KT;
-  Q_CHECK_ARG(total < (1ll << 30), "q_gemm_tc_plan: weight too large");
+  // More than 256 rows: row chunks of 256, one launch over (row chunk, weight block, k tile);
+  // a "group" of the plan is then one (row chunk, weight block) pair.
+  const int row_chunks = (M + 255) / 256;
+  const long long blocks = (long long)((N + TILE_ROWS - 1) / TILE_ROWS) * row_chunks;
+  const long long total = blocks * KT;
+  Q_CHECK_ARG(total < (1ll << 30), "q_gemm_tc_plan: too many tiles");
   long long u = (total + sms - 1) / sms;
   if (u < 1) u = 1;
   const long long workers = (total + u - 1) / u;
@@ -508,7 +519,7 @@ extern "C" int q_gemm_tc_plan(int M, int N, int K, q_gemm_plan_t* plan) {
   if (slots < 2) slots = 2;
   plan->M = M; plan->N = N; plan->K = K;
   plan->chunks_per_group = KT;
-  plan->groups = blocks;
+  plan->groups = (int)blocks;
   plan->units_per_worker = (int)u;
   plan->workers = (int)workers;
   plan->slots = (int)slots;
@@ -518,8 +529,9 @@ extern "C" int q_gemm_tc_plan(int M, int N, int K, q_gemm_plan_t* plan) {
   return Q_OK;
 }
 
-// Launches the projection for rows [0, plan->M) of X (leading dimension K) in chunks of at
-// most 256 rows; every chunk streams the weight once.
+// Launches the projection for rows [0, plan->M) of X (leading dimension K): one launch; above
+// 256 rows every CTA walks (row chunk, weight block, k tile) in that order, so the weight is
+// streamed once per 256 rows (from L2 after the first pass where it fits).
 int q_gemm_tc_launch(const void* d_x, const void* d_w_tc, float* d_partials, const q_gemm_plan_t* plan,
                      void* stream) {
   const q_gemm_plan_t& p = *plan;
@@ -527,29 +539,28 @@ int q_gemm_tc_launch(const void* d_x, const void* d_w_tc, float* d_partials, con
   encode_tiled_fn enc = encoder();
   if (!enc) { q_set_error("q_gemm_tc: the driver has no cuTensorMapEncodeTiled"); return Q_ERR_CUDA; }
   static size_t smem_done[64] = {0};
-  for (int row0 = 0; row0 < p.M; row0 += 256) {
-    const int rows = p.M - row0 < 256 ? p.M - row0 : 256;
-    const int m_pad = pad_rows(rows);
-    const int stages = stages_for(m_pad);
-    CUtensorMap map;
-    const cuuint64_t gdim[2] = {(cuuint64_t)p.K, (cuuint64_t)p.M};
-    const cuuint64_t gstride[1] = {(cuuint64_t)p.K * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)m_pad};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(d_x), gdim, gstride, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { q_set_error("q_gemm_tc: cuTensorMapEncodeTiled failed (%d)", (int)r); return Q_ERR_CUDA; }
-    TcShape sh;
-    sh.M = rows; sh.N = p.N; sh.KT = p.chunks_per_group; sh.total = p.groups * p.chunks_per_group;
-    sh.U = p.units_per_worker; sh.m_pad = m_pad; sh.stages = stages; sh.row0 = row0;
-    sh.slot_stride = (long long)p.M * p.N; sh.out_rows = p.M;
-    const size_t smem = tc_smem(m_pad, stages);
-    Q_CHECK_CUDA(q_ensure_smem(k_gemm_tc, smem, smem_done));
-    Q_CHECK_CUDA(q_launch(k_gemm_tc, dim3(p.grid), dim3(TC_THREADS), smem, (cudaStream_t)stream, map,
-                          (const unsigned char*)d_w_tc, d_partials, sh, g_gemm_debug_flags,
-                          q_tl_next(Q_TL_GEMM_TC)));
-  }
+  const int m_pad = pad_rows(p.M);
+  const int stages = stages_for(m_pad);
+  const int nblk = (p.N + TILE_ROWS - 1) / TILE_ROWS;
+  Q_CHECK_ARG(p.groups == nblk * ((p.M + 255) / 256), "q_gemm_tc: the plan does not match its own shape");
+  CUtensorMap map;
+  const cuuint64_t gdim[2] = {(cuuint64_t)p.K, (cuuint64_t)p.M};
+  const cuuint64_t gstride[1] = {(cuuint64_t)p.K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)m_pad};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(d_x), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { q_set_error("q_gemm_tc: cuTensorMapEncodeTiled failed (%d)", (int)r); return Q_ERR_CUDA; }
+  TcShape sh;
+  sh.M = p.M; sh.N = p.N; sh.KT = p.chunks_per_group; sh.nblk = nblk; sh.total = p.groups * p.chunks_per_group;
+  sh.U = p.units_per_worker; sh.m_pad = m_pad; sh.stages = stages; sh.row0 = 0;
+  sh.slot_stride = (long long)p.M * p.N; sh.out_rows = p.M;
+  const size_t smem = tc_smem(m_pad, stages);
+  Q_CHECK_CUDA(q_ensure_smem(k_gemm_tc, smem, smem_done));
+  Q_CHECK_CUDA(q_launch(k_gemm_tc, dim3(p.grid), dim3(TC_THREADS), smem, (cudaStream_t)stream, map,
+                        (const unsigned char*)d_w_tc, d_partials, sh, g_gemm_debug_flags,
+                        q_tl_next(Q_TL_GEMM_TC)));
   return Q_OK;
 }
 

@@ -8,11 +8,14 @@ def sum_slots(partials):
     p = partials.plan
     data = partials.data.detach().cpu()
     Cg, u = p.chunks_per_group, p.units_per_worker
-    g = torch.arange(p.N) // p.group_rows
+    g = (torch.arange(p.N) // p.group_rows)[None, :].repeat(p.M, 1)
+    if p.group_rows == 128 and p.M > 256:
+        # the tcgen05 plan of more than 256 rows counts its groups per row chunk of 256
+        g = g + (torch.arange(p.M) // 256)[:, None] * ((p.N + 127) // 128)
     cnt = ((g + 1) * Cg - 1) // u - (g * Cg) // u + 1
     total = torch.zeros((p.M, p.N), dtype=torch.float32)
     for k in range(p.slots):
-        total += torch.where((k < cnt)[None, :], data[k], torch.zeros(()))
+        total += torch.where(k < cnt, data[k], torch.zeros(()))
     return total
 
 

@@ -186,14 +186,15 @@ def test_misaligned_pointers_are_argument_errors():
 
 
 @pytest.mark.parametrize("M,N,K", [(32, 19456, 2560), (64, 2560, 9728), (9, 6144, 2560), (16, 151936, 2560),
-                                   (12, 127, 128), (300, 48, 96), (1, 16, 32)])
+                                   (12, 127, 128), (300, 48, 96), (1, 16, 32), (2048, 2560, 9728)])
 def test_tc_plan_covers_every_tile_once(M, N, K):
-    """The tcgen05 kernel's stream-K split: every (128-row block, 64-k tile) belongs to exactly
-    one CTA, and the slot a CTA writes for a block is below `slots`."""
+    """The tcgen05 kernel's stream-K split: every (row chunk of 256, 128-row block, 64-k tile)
+    belongs to exactly one CTA, and the slot a CTA writes for a block is below `slots`."""
     from starter_b200 import _lib
     p = _lib.plan(M, N, K, tc=True)
     KT, u = p.chunks_per_group, p.units_per_worker
-    assert p.group_rows == 128 and p.groups == (N + 127) // 128 and KT == (K + 63) // 64
+    blocks, row_chunks = (N + 127) // 128, (M + 255) // 256
+    assert p.group_rows == 128 and p.groups == blocks * row_chunks and KT == (K + 63) // 64
     total = p.groups * KT
     assert p.workers == (total + u - 1) // u == p.grid
     covered, max_slot = 0, 0
@@ -205,4 +206,4 @@ def test_tc_plan_covers_every_tile_once(M, N, K):
             assert first <= w <= last
             max_slot = max(max_slot, last - first + 1)
     assert covered == total and max_slot <= p.slots
-    assert _lib.lib.q_packed_weight_bytes_tc(N, K) == total * 16384
+    assert _lib.lib.q_packed_weight_bytes_tc(N, K) == blocks * KT * 16384

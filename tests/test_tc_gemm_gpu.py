@@ -81,8 +81,8 @@ def test_tc_gemm_matches_fp32_product(ops, name, M):
 @pytest.mark.parametrize("M,N,K", [(1, 16, 32), (3, 127, 128), (5, 40, 64), (64, 256, 512), (33, 48, 96),
                                    (100, 300, 160), (256, 384, 256), (300, 130, 2560), (700, 512, 128)])
 def test_tc_gemm_ragged_tiny_and_many_rows(ops, M, N, K):
-    """Ragged N and K (zero-padded tiles), one row, and more rows than one launch takes
-    (chunks of 256 rows)."""
+    """Ragged N and K (zero-padded tiles), one row, and more than 256 rows (row chunks of 256
+    inside one launch)."""
     w, x = randw(N, K, 5), randx(M, K, 6)
     part = ops.linear_partials_tc(x.cuda(), w.cuda())
     torch.testing.assert_close(sum_slots(part), O.linear_fp32(x, w), rtol=2e-3, atol=2e-3)
@@ -114,6 +114,31 @@ def test_consumers_read_tc_partials(ops, M):
     ref = O.swiglu(sum_slots(pg))
     torch.testing.assert_close(got.float(), ref.float(), rtol=8e-3, atol=1e-6)
     assert bit_equal_fraction(got, ref) > 0.99
+
+
+@pytest.mark.parametrize("M", [257, 600])
+def test_consumers_read_many_row_partials(ops, M):
+    """More than 256 rows (the prompt pass): one launch over row chunks of 256, the slot count
+    of an element depends on its row chunk too. add+norm, SwiGLU and the per-element slot sum
+    read such partials."""
+    w, x = randw(H, 1024, 41), randx(M, 1024, 42)
+    res = randx(M, H, 43)
+    gain = (1 + 0.1 * torch.randn(H, generator=torch.Generator().manual_seed(44))).to(torch.bfloat16)
+    part = ops.linear_partials_tc(x.cuda(), w.cuda())
+    torch.testing.assert_close(sum_slots(part), O.linear_fp32(x, w), rtol=2e-3, atol=2e-3)
+    assert torch.equal(part.sum().cpu(), sum_slots(part))
+    total, normed = ops.add_rms_norm(res.cuda(), part, gain.cuda(), 1e-6)
+    et, en = O.add_rms_norm(res, sum_slots(part), gain, 1e-6)
+    assert torch.equal(total.cpu().view(torch.int16), et.view(torch.int16))
+    assert bit_equal_fraction(normed.cpu(), en) > 0.99
+
+    wgu, xg = randw(2 * 1216, 512, 45), randx(M, 512, 46) * 3
+    pg = ops.linear_partials_tc(xg.cuda(), wgu.cuda())
+    got = ops.silu_mul(pg).cpu()
+    ref = O.swiglu(sum_slots(pg))
+    torch.testing.assert_close(got.float(), ref.float(), rtol=8e-3, atol=1e-6)
+    assert bit_equal_fraction(got, ref) > 0.99
+    assert ops.device_status() == [0, 0, 0, 0]
 
 
 def test_tc_gemm_rejects_bad_operands(ops):
