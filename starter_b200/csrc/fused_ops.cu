@@ -430,9 +430,13 @@ k_swiglu(const float* __restrict__ P, PlanView pv, bf16* __restrict__ O, int row
   const float4 g0 = *reinterpret_cast<const float4*>(base + gc);
   const float4 u0 = *reinterpret_cast<const float4*>(base + uc);
   const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-  const float4 g1 = two ? *reinterpret_cast<const float4*>(base + gc + pv.slot_stride) : z;
-  const float4 u1 = two ? *reinterpret_cast<const float4*>(base + uc + pv.slot_stride) : z;
   const int eg = plan_count(pv, gc, m) - 1, eu = plan_count(pv, uc, m) - 1;
+  // Up to 256 rows the second slot is asked for without looking (one round trip, the lines
+  // are in L2); the partials of a prompt pass are hundreds of MB, there only slots that hold
+  // a partial are read.
+  const bool many = pv.nblk != 0;
+  const float4 g1 = two && (!many || eg > 0) ? *reinterpret_cast<const float4*>(base + gc + pv.slot_stride) : z;
+  const float4 u1 = two && (!many || eu > 0) ? *reinterpret_cast<const float4*>(base + uc + pv.slot_stride) : z;
   float gs[4] = {g0.x, g0.y, g0.z, g0.w}, us[4] = {u0.x, u0.y, u0.z, u0.w};
   if (eg > 0) { gs[0] += g1.x; gs[1] += g1.y; gs[2] += g1.z; gs[3] += g1.w; }
   if (eu > 0) { us[0] += u1.x; us[1] += u1.y; us[2] += u1.z; us[3] += u1.w; }
@@ -481,12 +485,13 @@ k_qkv_norm_rope_cache(const float* __restrict__ P, PlanView pv, const bf16* __re
   const bool is_q = head < nq, is_v = head >= nq + nkv;
   const long long src = (long long)m * width + (long long)head * 128 + 4 * lane;
   const float4 s0 = *reinterpret_cast<const float4*>(P + src);
-  const float4 s1 = pv.u != 0 ? *reinterpret_cast<const float4*>(P + src + pv.slot_stride)
-                              : make_float4(0.f, 0.f, 0.f, 0.f);
+  const int extra = plan_count(pv, head * 128 + 4 * lane, m) - 1;
+  const float4 s1 = pv.u != 0 && (pv.nblk == 0 || extra > 0)
+                        ? *reinterpret_cast<const float4*>(P + src + pv.slot_stride)
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
   const uint2 graw = is_v ? make_uint2(0, 0) : *reinterpret_cast<const uint2*>((is_q ? QG : KG) + 4 * lane);
   const uint2 craw = *reinterpret_cast<const uint2*>(COS + (size_t)pos * 128 + 4 * lane);
   const uint2 sraw = *reinterpret_cast<const uint2*>(SIN + (size_t)pos * 128 + 4 * lane);
-  const int extra = plan_count(pv, head * 128 + 4 * lane, m) - 1;
   float x[4] = {s0.x, s0.y, s0.z, s0.w};
   if (extra > 0) { x[0] += s1.x; x[1] += s1.y; x[2] += s1.z; x[3] += s1.w; }
   for (int k = 2; k <= extra; ++k) {
