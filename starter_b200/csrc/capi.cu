@@ -43,6 +43,7 @@ int g_gemm_debug_flags = 0;
 int g_gemm_trace_launch = -1;    // measurement aid: the one GEMM launch that records its CTA trace
 int g_gemm_launches = 0;
 int g_attn_no_cluster = 0;        // 1 = decode attention merges its splits through global memory
+static int g_peer_in_gemm = 1;   // 1 = tensor parallel at 1-8 rows exchanges inside the projections
 static int g_norm_in_gemm = 1;   // 1 = residual add + RMSNorm as the prologue of the next projection
 static int g_tc_min_rows = 9;    // fewest rows that take the tcgen05 projections (when their tiling is bound)
 int g_peer_wait_iters = 1 << 21; // polling limit of the waits for a tensor-parallel peer
@@ -101,6 +102,10 @@ extern "C" int q_set_option(const char* name, int value) {
   if (strcmp(name, "gemm_prefetch_kb") == 0) {
     Q_CHECK_ARG(value >= 0 && value <= 8192, "q_set_option: gemm_prefetch_kb outside 0..8192");
     g_gemm_prefetch_kb = value;
+    return Q_OK;
+  }
+  if (strcmp(name, "peer_in_gemm") == 0) {
+    g_peer_in_gemm = value != 0;
     return Q_OK;
   }
   if (strcmp(name, "norm_in_gemm") == 0) {
@@ -366,7 +371,14 @@ static bool norm_in_gemm(const q_engine* e) {
          e->cfg.hidden <= 3072 && g_norm_in_gemm;
 }
 
-// attention .. O projection, from the QKV partials in st.partials.
+// Tensor parallel, up to 8 rows: the cross-rank sums are exchanged inside the projections.
+static bool peer_exchange_in_gemm(const q_engine* e) {
+  return e->cfg.tp_size > 1 && e->has_peers && !e->tc && e->T == 1 && e->rows <= 8 && e->cfg.hidden % 4 == 0 &&
+         e->cfg.hidden <= 3072 && e->p_o.slots <= 2 && e->p_down.slots <= 2 && g_peer_in_gemm;
+}
+
+// attention .. O projection, from the QKV partials in st.partials. o_partials == nullptr: the O
+// projection pushes its partials to the tensor-parallel peers instead (1-8 rows).
 static int attn_after_qkv(q_engine* e, int layer, float* o_partials, void* stream) {
   const q_config_t& c = e->cfg;
   const q_state_t& s = e->st;
@@ -383,6 +395,7 @@ static int attn_after_qkv(q_engine* e, int layer, float* o_partials, void* strea
     TRY(q_attention(s.q, &kv, s.pos, s.attn_o, s.attn_ml, s.attended, s.batch, e->T, c.n_q_heads,
                     s.attn_splits, c.attn_scale, stream));
   }
+  if (!o_partials) return q_gemm_push_planned(s.attended, w.wo, &e->p_o, &e->peers, stream);
   return project(e, s.attended, w.wo, w.wo_tc, o_partials, e->p_o, stream);
 }
 
@@ -501,11 +514,12 @@ extern "C" int q_step_merge(q_engine* e, const float* d_val, const int32_t* d_id
   return q_argmax_merge_tap(d_val, d_idx, e->cfg.tp_size, e->rows, s.tokens, s.pos, 1, status_tap(e), stream);
 }
 
-// Receive area of the cross-rank sums: [2 halves][world][rows][hidden] pairs {fp32 sum, call
-// counter} of 8 bytes per rank, counted in floats.
+// Receive area of the cross-rank sums: [2 halves][world][2 slots][rows][hidden] pairs {fp32
+// partial, call counter} of 8 bytes per rank, counted in floats (the one-kernel exchange above
+// 8 rows uses half of it: [2 halves][world][rows][hidden]).
 extern "C" int64_t q_engine_peer_floats(const q_engine* e, int rows) {
   if (!e || rows < 1 || rows > Q_MAX_ROWS) return -1;
-  return 2ll * 2ll * e->cfg.tp_size * rows * e->cfg.hidden;
+  return 2ll * 2ll * 2ll * e->cfg.tp_size * rows * e->cfg.hidden;
 }
 
 extern "C" int q_bind_peers(q_engine* e, const q_peers_t* peers) {
@@ -538,6 +552,26 @@ extern "C" int q_decode_step_peers(q_engine* e, void* stream) {
   const q_config_t& c = e->cfg;
   const q_state_t& s = e->st;
   TRY(q_step_begin(e, stream));
+  if (peer_exchange_in_gemm(e)) {
+    // 1-8 rows: five launches per layer as on one GPU. The O and down projections push their
+    // partials to every rank, the projection after them adds all ranks' in its add+norm
+    // prologue; the residual alternates between st.x and st.normed as in run_layers.
+    const int rows = e->rows;
+    TRY(q_gemm_launch_planned(s.normed, e->layers[0].wqkv, s.partials, &e->p_qkv, stream));
+    for (int l = 0; l < c.n_layers; ++l) {
+      TRY(attn_after_qkv(e, l, nullptr, stream));
+      TRY(q_gemm_swiglu_addnorm_peers(s.x, &e->peers, &e->p_o, e->layers[l].ln_post, s.normed, e->layers[l].wgu,
+                                      s.act, rows, c.inter, c.hidden, c.rms_eps, stream));
+      TRY(q_gemm_push_planned(s.act, e->layers[l].wdown, &e->p_down, &e->peers, stream));
+      const bool last = l + 1 == c.n_layers;
+      TRY(q_gemm_splitk_addnorm_peers(s.normed, &e->peers, &e->p_down, next_gain(e, l), s.x,
+                                      last ? s.lm_head : e->layers[l + 1].wqkv, s.partials, rows,
+                                      last ? c.vocab : e->p_qkv.N, c.hidden, c.rms_eps, stream));
+    }
+    TRY(head_argmax(e, false, stream));
+    return q_argmax_merge_peers_tap(s.arg_val, s.arg_idx, &e->peers, e->rows, s.tokens, s.pos, 1, status_tap(e),
+                                    stream);
+  }
   for (int l = 0; l < c.n_layers; ++l) {
     TRY(attn_block(e, l, s.partials, stream));
     TRY(q_add_rmsnorm_peers(s.x, &e->peers, s.partials, &e->p_o, e->layers[l].ln_post, s.x, s.normed, e->rows,

@@ -132,6 +132,18 @@ int q_gemm_launch_planned(const void* d_x, const void* d_w_tiled, float* d_parti
 int q_gemm_tc_launch(const void* d_x, const void* d_w_tc, float* d_partials, const q_gemm_plan_t* plan,
                      void* stream);
 
+// Tensor parallel over peer memory at 1-8 rows, the exchange inside the projections: the
+// projection before an add+norm pushes its partials to every rank's receive area, the
+// projection after it polls them in its prologue (gemm_streamk.cu, PEER).
+int q_gemm_push_planned(const void* d_x, const void* d_w_tiled, const q_gemm_plan_t* plan, const q_peers_t* peers,
+                        void* stream);
+int q_gemm_splitk_addnorm_peers(const void* d_resid_in, const q_peers_t* peers, const q_gemm_plan_t* prev_plan,
+                                const void* d_gain, void* d_resid_out, const void* d_w_tiled, float* d_partials,
+                                int M, int N, int K, float eps, void* stream);
+int q_gemm_swiglu_addnorm_peers(const void* d_resid_in, const q_peers_t* peers, const q_gemm_plan_t* prev_plan,
+                                const void* d_gain, void* d_resid_out, const void* d_w_tiled, void* d_act, int M,
+                                int inter, int K, float eps, void* stream);
+
 // q_swiglu on partials whose columns are in q_gemm_swiglu's interleaved gate/up order
 // (interleaved = 1) or in [gate | up] order (0).
 int q_swiglu_layout(const float* d_branch, const q_gemm_plan_t* plan, void* d_out, int rows, int inter,
@@ -143,6 +155,16 @@ int q_swiglu_layout(const float* d_branch, const q_gemm_plan_t* plan, void* d_ou
 enum q_tl_kind { Q_TL_GEMM = 1, Q_TL_GEMM_TC = 2, Q_TL_ATTENTION = 3, Q_TL_ADD_NORM = 4, Q_TL_SWIGLU = 5,
                  Q_TL_EMBED = 6, Q_TL_ARGMAX = 7, Q_TL_PEER_ADD_NORM = 8 };
 unsigned long long* q_tl_next(int kind);
+
+// This rank's view of the tensor-parallel peers (q_peers_t with the pointers checked).
+struct PeerView {
+  int rank, world;
+  float* recv[Q_MAX_PEERS];      // rank r's receive area [2 halves][world][rows][cols] pairs of 8 bytes
+  uint32_t* flags[Q_MAX_PEERS];
+  uint32_t* epoch;     // [0] call counter of the add+norm exchange, [1] its ticket, [2] counter of the token exchange
+};
+
+int q_peer_view(const q_peers_t* peers, PeerView* out, const char* who);
 
 // Split-K plan passed by value to consumer kernels. u == 0 means "one plain
 // fp32 [rows][cols] buffer".
@@ -170,6 +192,23 @@ static inline PlanView plan_view(const q_gemm_plan_t* p) {
 
 // ---- device side ---------------------------------------------------------------
 #ifdef __CUDACC__
+
+// {value, call counter} pairs of the peer exchange: an 8-byte store is single-copy atomic, so a
+// pair that carries this call's counter HAS arrived with its value.
+__device__ __forceinline__ void st_pair2(void* p, float a, float b, unsigned e) {
+  // two {value, counter} pairs, each element an 8-byte single-copy-atomic store
+  asm volatile("st.volatile.global.v2.b64 [%0], {%1, %2};" ::"l"(p),
+               "l"(((unsigned long long)e << 32) | __float_as_uint(a)),
+               "l"(((unsigned long long)e << 32) | __float_as_uint(b)) : "memory");
+}
+__device__ __forceinline__ void ld_pair2(const void* p, unsigned long long& a, unsigned long long& b) {
+  asm volatile("ld.volatile.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+
+__device__ __forceinline__ void st_pair1(void* p, float a, unsigned e) {
+  asm volatile("st.volatile.global.b64 [%0], %1;" ::"l"(p), "l"(((unsigned long long)e << 32) | __float_as_uint(a))
+               : "memory");
+}
 
 __device__ __forceinline__ unsigned long long tl_now() {
   unsigned long long t;

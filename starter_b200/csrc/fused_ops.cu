@@ -200,13 +200,6 @@ k_add_rmsnorm(const bf16* __restrict__ Xin, const float* __restrict__ P, PlanVie
 // arrived, i.e. after every peer finished this call. A stale pair can never look fresh: it
 // carries an older counter. The call counter is bumped by the last CTA to finish (a
 // ticket), so every CTA of a call reads the same value. All ranks make the same calls.
-struct PeerView {
-  int rank, world;
-  float* recv[Q_MAX_PEERS];      // rank r's receive area [2 halves][world][rows][cols] pairs of 8 bytes
-  uint32_t* flags[Q_MAX_PEERS];
-  uint32_t* epoch;     // [0] call counter of the add+norm exchange, [1] its ticket, [2] counter of the token exchange
-};
-
 __device__ int g_peer_status;      // 1 = a wait for a peer ran out
 
 // Bounded wait for `word` to reach `e` (wrap-around safe). The limit is in polling
@@ -220,16 +213,6 @@ __device__ __forceinline__ bool wait_arrival(const uint32_t* word, unsigned e, i
     if (i > 64) __nanosleep(i > 65536 ? 2000 : (i > 4096 ? 400 : 40));
   }
   return false;
-}
-
-__device__ __forceinline__ void st_pair2(void* p, float a, float b, unsigned e) {
-  // two {value, counter} pairs, each element an 8-byte single-copy-atomic store
-  asm volatile("st.volatile.global.v2.b64 [%0], {%1, %2};" ::"l"(p),
-               "l"(((unsigned long long)e << 32) | __float_as_uint(a)),
-               "l"(((unsigned long long)e << 32) | __float_as_uint(b)) : "memory");
-}
-__device__ __forceinline__ void ld_pair2(const void* p, unsigned long long& a, unsigned long long& b) {
-  asm volatile("ld.volatile.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
 
 constexpr int PEER_MAX_COLS = 4096;     // one thread per four columns, at most 1024 threads
@@ -298,25 +281,46 @@ k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, const float* __re
   {
     float2 acc[2] = {z2, z2};
     bool ok = true;
-    for (int r = 0; r < pw.world; ++r) {
-      float2 t[2] = {own[0], own[1]};
-      if (r != pw.rank) {
-        const char* src = reinterpret_cast<const char*>(pw.recv[pw.rank]) + (half_off + ((size_t)r * rows + row) * cols) * 8;
-        unsigned long long a0 = 0, a1 = 0, a2 = 0, a3 = 0;
-        bool here = false;
-        for (int i = 0; ok && i < wait_iters; ++i) {
-          if (live[0]) ld_pair2(src + (size_t)colv[0] * 8, a0, a1);
-          if (live[1]) ld_pair2(src + (size_t)colv[1] * 8, a2, a3);
-          here = (!live[0] || ((unsigned)(a0 >> 32) == e && (unsigned)(a1 >> 32) == e)) &&
-                 (!live[1] || ((unsigned)(a2 >> 32) == e && (unsigned)(a3 >> 32) == e));
-          if (here) break;
-          if (i > 64) __nanosleep(i > 65536 ? 2000 : (i > 4096 ? 400 : 40));
+    // Four peers at a time: their loads are in flight together (one round trip per poll, not
+    // one per peer), and the sums are still added in rank order.
+    for (int r0 = 0; r0 < pw.world; r0 += 4) {
+      unsigned long long a[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) a[j][0] = a[j][1] = a[j][2] = a[j][3] = 0;
+      bool here = false;
+      for (int i = 0; ok && i < wait_iters; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = r0 + j;
+          if (r < pw.world && r != pw.rank) {
+            const char* src = reinterpret_cast<const char*>(pw.recv[pw.rank]) + (half_off + ((size_t)r * rows + row) * cols) * 8;
+            if (live[0]) ld_pair2(src + (size_t)colv[0] * 8, a[j][0], a[j][1]);
+            if (live[1]) ld_pair2(src + (size_t)colv[1] * 8, a[j][2], a[j][3]);
+          }
         }
-        if (!here) { ok = false; atomicExch(&g_peer_status, 1); }
-        t[0] = make_float2(__uint_as_float((unsigned)a0), __uint_as_float((unsigned)a1));
-        t[1] = make_float2(__uint_as_float((unsigned)a2), __uint_as_float((unsigned)a3));
+        here = true;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = r0 + j;
+          if (r < pw.world && r != pw.rank)
+            here = here && (!live[0] || ((unsigned)(a[j][0] >> 32) == e && (unsigned)(a[j][1] >> 32) == e)) &&
+                   (!live[1] || ((unsigned)(a[j][2] >> 32) == e && (unsigned)(a[j][3] >> 32) == e));
+        }
+        if (here) break;
+        if (i > 64) __nanosleep(i > 65536 ? 2000 : (i > 4096 ? 400 : 40));
       }
-      acc[0].x += t[0].x; acc[0].y += t[0].y; acc[1].x += t[1].x; acc[1].y += t[1].y;
+      if (!here) { ok = false; atomicExch(&g_peer_status, 1); }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = r0 + j;
+        if (r >= pw.world) break;
+        float2 t[2] = {own[0], own[1]};
+        if (r != pw.rank) {
+          t[0] = make_float2(__uint_as_float((unsigned)a[j][0]), __uint_as_float((unsigned)a[j][1]));
+          t[1] = make_float2(__uint_as_float((unsigned)a[j][2]), __uint_as_float((unsigned)a[j][3]));
+        }
+        acc[0].x += t[0].x; acc[0].y += t[0].y; acc[1].x += t[1].x; acc[1].y += t[1].y;
+      }
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h)
@@ -761,7 +765,7 @@ extern "C" int q_add_rmsnorm(const void* d_x_in, const float* d_branch, const q_
 }
 
 
-static int peer_view(const q_peers_t* peers, PeerView* out, const char* who) {
+int q_peer_view(const q_peers_t* peers, PeerView* out, const char* who) {
   Q_CHECK_ARG(peers->world >= 2 && peers->world <= Q_MAX_PEERS && peers->rank >= 0 &&
                   peers->rank < peers->world && peers->epoch,
               "%s: bad rank/world or no counter words", who);
@@ -791,7 +795,7 @@ extern "C" int q_add_rmsnorm_peers(const void* d_x_in, const q_peers_t* peers, c
   int rc = check_plan(plan, rows, cols, "q_add_rmsnorm_peers");
   if (rc) return rc;
   PeerView pw;
-  rc = peer_view(peers, &pw, "q_add_rmsnorm_peers");
+  rc = q_peer_view(peers, &pw, "q_add_rmsnorm_peers");
   if (rc) return rc;
   const int threads = ((cols + 127) / 128) * 32;        // one warp per 128 columns
   Q_CHECK_CUDA(q_launch(k_add_rmsnorm_peers, dim3(rows), dim3(threads), 0, S(stream), (const bf16*)d_x_in, pw,
@@ -810,7 +814,7 @@ int q_argmax_merge_peers_tap(const float* d_val, const int32_t* d_idx, const q_p
   Q_CHECK_ARG(d_val && d_idx && peers && d_tokens && rows >= 1 && rows <= Q_MAX_ROWS,
               "q_argmax_merge_peers: bad argument");
   PeerView pw;
-  int rc = peer_view(peers, &pw, "q_argmax_merge_peers");
+  int rc = q_peer_view(peers, &pw, "q_argmax_merge_peers");
   if (rc) return rc;
   Q_CHECK_CUDA(q_launch(k_argmax_merge_peers, dim3(1), dim3(64), 0, S(stream), d_val, d_idx, pw, rows, d_tokens,
                         d_pos, pos_inc, g_peer_wait_iters, tap));

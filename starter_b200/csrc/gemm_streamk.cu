@@ -44,6 +44,7 @@ extern int g_gemm_prefetch_kb;   // set through q_set_option
 extern int g_gemm_debug_flags;   // set through q_set_option: 4 = record the per-CTA trace
 extern int g_gemm_trace_launch;  // >= 0: only that GEMM launch (counted from when it was set) records
 extern int g_gemm_launches;
+extern int g_peer_wait_iters;     // q_set_option "peer_wait_iters"
 
 namespace {
 
@@ -151,6 +152,15 @@ __device__ __forceinline__ bf16 swiglu_bf16(float gate, float up) {
   return __float2bfloat16_rn(bf16_round(gt / (1.0f + expf(-gt))) * u);
 }
 
+// One partial of output element (m, n), slot `slot`, to every rank's receive area (PEER == 1).
+__device__ __forceinline__ void peer_push(const PeerView& pw, unsigned e, int slot, int M, int N, int m, int n,
+                                          float v) {
+  const size_t idx = ((((size_t)(e & 1u) * pw.world + pw.rank) * 2 + slot) * M + m) * N + n;
+#pragma unroll
+  for (int r = 0; r < Q_MAX_PEERS; ++r)
+    if (r < pw.world) st_pair1(reinterpret_cast<char*>(pw.recv[r]) + idx * 8, v, e);
+}
+
 // Optional prologue: instead of reading a ready activation matrix, every CTA builds it
 // from the previous projection's partials: resid_out = bf16(resid_in + bf16(sum of
 // slots)); X = RMSNorm(resid_out) * gain (engine/kernels/decode_fused.py:19-44). All CTAs
@@ -174,11 +184,21 @@ struct NormPrologue {
 // epilogue writes silu(gate) * up as bf16 [M][N/2] into P instead of fp32 partials
 // (engine/kernels/skinny_gemm.py:49-72): one MMA tile holds a gate row in c0/c1 and its up
 // row in c2/c3 of the same thread, so no exchange is needed.
-template <int NT, bool PRO, bool ACT, int SU>
+//
+// PEER (tensor parallel over peer memory, 1-8 rows): 1 = the epilogue does not write partial
+// slots but stores every partial, paired with the call counter, into the receive area of
+// EVERY rank (its own too): [half][rank][2 slots][M][N] pairs of 8 bytes; 2 = the add+norm
+// prologue does not read local slots but polls (bounded) the own receive area for all ranks'
+// pairs of the previous projection and adds them in (rank, slot) order, and the last CTA
+// through the prologue publishes the new call counter. The two are the halves of one
+// exchange: the projection before pushes, the projection after polls, no kernel in between.
+// Halves alternate with the counter, as in k_add_rmsnorm_peers.
+template <int NT, bool PRO, bool ACT, int SU, int PEER = 0>
 __global__ void __launch_bounds__(THREADS, (WARPS * STAGES * SU * 1024 <= 100 * 1024 ? 2 : 1))
 k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
                float* __restrict__ P, int M, int N, int K, int C, int total, int U,
-               int prefetch_bytes, int dbg, NormPrologue pro, unsigned long long* tl) {
+               int prefetch_bytes, int dbg, NormPrologue pro, PeerView pw, int peer_wait,
+               unsigned long long* tl) {
   extern __shared__ __align__(1024) unsigned char smem[];
   float* red = reinterpret_cast<float*>(smem + WARPS * STAGES * SU * 1024);            // [WARPS][2][NT*128]
   int* tags = reinterpret_cast<int*>(red + WARPS * 2 * NT * 128);      // [WARPS][2] group or -1
@@ -244,9 +264,14 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
   tl_waited(tl);
   if (trace) g_gemm_trace[blockIdx.x * 8 + 2] = gtime();
 
+  // call counter of the peer exchange this launch takes part in (same in every CTA: the counter
+  // word moves only when all CTAs of a polling launch are through their prologue)
+  unsigned pe = 0;
+  if (PEER != 0) pe = *reinterpret_cast<volatile unsigned*>(pw.epoch) + 1u;
   if (PRO) {
     // add + norm: thread t owns columns 4t..4t+3 (+1024 j); all loads first
     constexpr int VB = 3;                       // K <= 3072 (checked on the host)
+    bool ok = true;                             // PEER == 2: no wait for a peer has run out yet
     for (int m = 0; m < M; ++m) {
       float4 s0[VB], s1[VB];
       uint2 xr[VB];
@@ -254,10 +279,12 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
       for (int j = 0; j < VB; ++j) {
         const int col = 4 * tid + j * 1024;
         const int cc = col < K ? col : 0;
-        s0[j] = *reinterpret_cast<const float4*>(pro.prev + (size_t)m * K + cc);
-        s1[j] = pro.prev_plan.u != 0
-                    ? *reinterpret_cast<const float4*>(pro.prev + (size_t)m * K + cc + pro.prev_plan.slot_stride)
-                    : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (PEER != 2) {
+          s0[j] = *reinterpret_cast<const float4*>(pro.prev + (size_t)m * K + cc);
+          s1[j] = pro.prev_plan.u != 0
+                      ? *reinterpret_cast<const float4*>(pro.prev + (size_t)m * K + cc + pro.prev_plan.slot_stride)
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
         xr[j] = *reinterpret_cast<const uint2*>(pro.resid_in + (size_t)m * K + cc);
       }
       if (m == 0 && lane == 0) {
@@ -269,6 +296,66 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
                    bar0 + 8 * s, policy);
         }
       }
+      // PEER == 2: every rank's pairs of this thread's columns - slot 0 and, where the previous
+      // plan has one for the group, slot 1 - two ranks' worth of loads in flight per poll, the
+      // sums added in (rank, slot) order.
+      float peer_acc[VB][4];
+      if (PEER == 2) {
+#pragma unroll
+        for (int j = 0; j < VB; ++j) peer_acc[j][0] = peer_acc[j][1] = peer_acc[j][2] = peer_acc[j][3] = 0.f;
+        int extra_j[VB];
+#pragma unroll
+        for (int j = 0; j < VB; ++j) {
+          const int col = 4 * tid + j * 1024;
+          extra_j[j] = col < K ? plan_count(pro.prev_plan, col) - 1 : -1;     // -1: no column
+        }
+        const size_t half = (size_t)(pe & 1u) * pw.world;
+        const char* mine = reinterpret_cast<const char*>(pw.recv[pw.rank]);
+        for (int r0 = 0; r0 < pw.world; r0 += 2) {
+          unsigned long long a[2][VB][2][2];
+          bool here = false;
+          for (int i = 0; ok && i < peer_wait; ++i) {
+            here = true;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              if (r0 + q >= pw.world) break;
+#pragma unroll
+              for (int j = 0; j < VB; ++j) {
+#pragma unroll
+                for (int sl = 0; sl < 2; ++sl) {
+                  a[q][j][sl][0] = a[q][j][sl][1] = 0;
+                  if (sl > extra_j[j]) continue;
+                  const size_t idx = (((half + (r0 + q)) * 2 + sl) * M + m) * K + (4 * tid + j * 1024);
+                  unsigned long long b0, b1, b2, b3;
+                  ld_pair2(mine + idx * 8, b0, b1);
+                  ld_pair2(mine + idx * 8 + 16, b2, b3);
+                  here = here && (unsigned)(b0 >> 32) == pe && (unsigned)(b1 >> 32) == pe &&
+                         (unsigned)(b2 >> 32) == pe && (unsigned)(b3 >> 32) == pe;
+                  a[q][j][sl][0] = (b0 & 0xffffffffull) | (b1 << 32);
+                  a[q][j][sl][1] = (b2 & 0xffffffffull) | (b3 << 32);
+                }
+              }
+            }
+            if (here) break;
+            if (i > 64) __nanosleep(i > 65536 ? 2000 : (i > 4096 ? 400 : 40));
+          }
+          if (!here) { ok = false; atomicExch(&g_gemm_status[0], 4); }
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            if (r0 + q >= pw.world) break;
+#pragma unroll
+            for (int j = 0; j < VB; ++j)
+#pragma unroll
+              for (int sl = 0; sl < 2; ++sl) {
+                if (sl > extra_j[j]) continue;
+                peer_acc[j][0] += __uint_as_float((unsigned)a[q][j][sl][0]);
+                peer_acc[j][1] += __uint_as_float((unsigned)(a[q][j][sl][0] >> 32));
+                peer_acc[j][2] += __uint_as_float((unsigned)a[q][j][sl][1]);
+                peer_acc[j][3] += __uint_as_float((unsigned)(a[q][j][sl][1] >> 32));
+              }
+          }
+        }
+      }
       float tot[VB][4];
       float ss = 0.f;
 #pragma unroll
@@ -276,12 +363,17 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
         const int col = 4 * tid + j * 1024;
         if (col < K) {
           const int extra = plan_count(pro.prev_plan, col) - 1;
-          float s[4] = {s0[j].x, s0[j].y, s0[j].z, s0[j].w};
-          if (extra > 0) { s[0] += s1[j].x; s[1] += s1[j].y; s[2] += s1[j].z; s[3] += s1[j].w; }
-          for (int k = 2; k <= extra; ++k) {
-            const float4 sk = *reinterpret_cast<const float4*>(pro.prev + (size_t)m * K + col +
-                                                               (long long)k * pro.prev_plan.slot_stride);
-            s[0] += sk.x; s[1] += sk.y; s[2] += sk.z; s[3] += sk.w;
+          float s[4] = {0.f, 0.f, 0.f, 0.f};
+          if (PEER == 2) {
+            s[0] = peer_acc[j][0]; s[1] = peer_acc[j][1]; s[2] = peer_acc[j][2]; s[3] = peer_acc[j][3];
+          } else {
+            s[0] = s0[j].x; s[1] = s0[j].y; s[2] = s0[j].z; s[3] = s0[j].w;
+            if (extra > 0) { s[0] += s1[j].x; s[1] += s1[j].y; s[2] += s1[j].z; s[3] += s1[j].w; }
+            for (int k = 2; k <= extra; ++k) {
+              const float4 sk = *reinterpret_cast<const float4*>(pro.prev + (size_t)m * K + col +
+                                                                 (long long)k * pro.prev_plan.slot_stride);
+              s[0] += sk.x; s[1] += sk.y; s[2] += sk.z; s[3] += sk.w;
+            }
           }
           const float r[4] = {bf_lo(xr[j].x), bf_hi(xr[j].x), bf_lo(xr[j].y), bf_hi(xr[j].y)};
 #pragma unroll
@@ -310,6 +402,15 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
       }
     }
     __syncthreads();
+    if (PEER == 2 && tid == 0) {
+      // every CTA has read the counter word before it takes a ticket: the last one moves it on
+      const unsigned ticket = atomicAdd(pw.epoch + 1, 1u);
+      if (ticket == gridDim.x - 1) {
+        pw.epoch[1] = 0;
+        __threadfence();
+        *reinterpret_cast<volatile unsigned*>(pw.epoch) = pe;
+      }
+    }
   }
   if (trace) g_gemm_trace[blockIdx.x * 8 + 3] = gtime();
 
@@ -409,6 +510,17 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
               }
               continue;
             }
+            if (PEER == 1) {
+              if (m0 < M) {
+                if (n0 < N) peer_push(pw, pe, 0, M, N, m0, n0, tot[nt][0]);
+                if (n0 + 8 < N) peer_push(pw, pe, 0, M, N, m0, n0 + 8, tot[nt][2]);
+              }
+              if (m0 + 1 < M) {
+                if (n0 < N) peer_push(pw, pe, 0, M, N, m0 + 1, n0, tot[nt][1]);
+                if (n0 + 8 < N) peer_push(pw, pe, 0, M, N, m0 + 1, n0 + 8, tot[nt][3]);
+              }
+              continue;
+            }
             if (m0 < M) {
               if (n0 < N) P[(size_t)m0 * N + n0] = tot[nt][0];
               if (n0 + 8 < N) P[(size_t)m0 * N + n0 + 8] = tot[nt][2];
@@ -474,6 +586,18 @@ k_gemm_streamk(const bf16* __restrict__ X, const unsigned char* __restrict__ Wt,
         if (col < half) {
           if (m0 < M) A[(size_t)m0 * half + col] = swiglu_bf16(sum.x, sum.z);
           if (m0 + 1 < M) A[(size_t)(m0 + 1) * half + col] = swiglu_bf16(sum.y, sum.w);
+        }
+        continue;
+      }
+      if (PEER == 1) {
+        const int slot = (int)blockIdx.x - (int)first;
+        if (m0 < M) {
+          if (n0 < N) peer_push(pw, pe, slot, M, N, m0, n0, sum.x);
+          if (n0 + 8 < N) peer_push(pw, pe, slot, M, N, m0, n0 + 8, sum.z);
+        }
+        if (m0 + 1 < M) {
+          if (n0 < N) peer_push(pw, pe, slot, M, N, m0 + 1, n0, sum.y);
+          if (n0 + 8 < N) peer_push(pw, pe, slot, M, N, m0 + 1, n0 + 8, sum.w);
         }
         continue;
       }
@@ -569,7 +693,21 @@ cudaError_t launch_gemm(const q_gemm_plan_t& p, const bf16* X, const unsigned ch
   return q_launch(k_gemm_streamk<NT, false, ACT, SU>, dim3(grid), dim3(p.block), (size_t)gemm_smem<NT, SU>(), s, X,
                   W, P, p.M, p.N, p.K, p.chunks_per_group, p.groups * p.chunks_per_group,
                   p.units_per_worker, g_gemm_prefetch_kb * 1024 / WARPS, debug_flags_of_this_launch(), none,
-                  q_tl_next(Q_TL_GEMM));
+                  PeerView{}, 0, q_tl_next(Q_TL_GEMM));
+}
+
+// The same launch with the peer-push epilogue (1-8 rows, no SwiGLU): partials go to every
+// rank's receive area instead of P.
+cudaError_t launch_gemm_push(const q_gemm_plan_t& p, const bf16* X, const unsigned char* W, const PeerView& pw,
+                             cudaStream_t s) {
+  static size_t done[64] = {0};
+  auto kern = k_gemm_streamk<1, false, false, STAGE_UNITS, 1>;
+  cudaError_t e0 = q_ensure_smem(kern, (size_t)gemm_smem<1, STAGE_UNITS>(), done);
+  if (e0 != cudaSuccess) return e0;
+  NormPrologue none = {};
+  return q_launch(kern, dim3(p.grid), dim3(p.block), (size_t)gemm_smem<1, STAGE_UNITS>(), s, X, W, (float*)nullptr,
+                  p.M, p.N, p.K, p.chunks_per_group, p.groups * p.chunks_per_group, p.units_per_worker, 0,
+                  debug_flags_of_this_launch(), none, pw, 0, q_tl_next(Q_TL_GEMM));
 }
 
 template <bool ACT>
@@ -582,7 +720,23 @@ cudaError_t launch_gemm_norm(const q_gemm_plan_t& p, const unsigned char* W, flo
   const int grid = ACT ? (p.groups < p.grid ? p.groups : p.grid) : p.grid;
   return q_launch(k_gemm_streamk<1, true, ACT, STAGE_UNITS>, dim3(grid), dim3(p.block), smem, s, (const bf16*)nullptr, W,
                   P, p.M, p.N, p.K, p.chunks_per_group, p.groups * p.chunks_per_group,
-                  p.units_per_worker, 0, debug_flags_of_this_launch(), pro, q_tl_next(Q_TL_GEMM));
+                  p.units_per_worker, 0, debug_flags_of_this_launch(), pro, PeerView{}, 0, q_tl_next(Q_TL_GEMM));
+}
+
+// ... and with the prologue that polls the receive area for all ranks' partials of the previous
+// projection (pro.prev is unused, pro.prev_plan says which slots exist).
+template <bool ACT>
+cudaError_t launch_gemm_norm_poll(const q_gemm_plan_t& p, const unsigned char* W, float* P,
+                                  const NormPrologue& pro, const PeerView& pw, cudaStream_t s) {
+  const size_t smem = (size_t)gemm_smem<1>() + (size_t)p.M * (p.K + 32) * 2 + 32 * 4;
+  static size_t done[64] = {0};
+  auto kern = k_gemm_streamk<1, true, ACT, STAGE_UNITS, 2>;
+  cudaError_t e0 = q_ensure_smem(kern, smem, done);
+  if (e0 != cudaSuccess) return e0;
+  const int grid = ACT ? (p.groups < p.grid ? p.groups : p.grid) : p.grid;
+  return q_launch(kern, dim3(grid), dim3(p.block), smem, s, (const bf16*)nullptr, W, P, p.M, p.N, p.K,
+                  p.chunks_per_group, p.groups * p.chunks_per_group, p.units_per_worker, 0,
+                  debug_flags_of_this_launch(), pro, pw, g_peer_wait_iters, q_tl_next(Q_TL_GEMM));
 }
 
 }  // namespace
@@ -831,6 +985,80 @@ extern "C" int q_gemm_swiglu_addnorm(const void* d_resid_in, const float* d_prev
   pro.eps = eps;
   Q_CHECK_CUDA(launch_gemm_norm<true>(p, (const unsigned char*)d_w_tiled, reinterpret_cast<float*>(d_act), pro,
                                       (cudaStream_t)stream));
+  return Q_OK;
+}
+
+// ---- tensor parallel over peer memory, 1-8 rows: the exchange inside the projections ----
+// (internal: the engine's peer step calls these; see the PEER template parameter)
+
+// X[M,K] @ W^T, every partial pushed to every rank's receive area.
+int q_gemm_push_planned(const void* d_x, const void* d_w_tiled, const q_gemm_plan_t* plan, const q_peers_t* peers,
+                        void* stream) {
+  Q_CHECK_ARG(d_x && d_w_tiled && plan && peers, "q_gemm_push_planned: null pointer");
+  Q_CHECK_ARG(plan->M >= 1 && plan->M <= 8 && plan->slots <= 2 && plan->group_rows == 16,
+              "q_gemm_push_planned: needs a stream-K plan of 1..8 rows with at most two slots");
+  Q_CHECK_ALIGN(d_x, 16, "q_gemm_push_planned"); Q_CHECK_ALIGN(d_w_tiled, 16, "q_gemm_push_planned");
+  PeerView pw;
+  int rc = q_peer_view(peers, &pw, "q_gemm_push_planned");
+  if (rc) return rc;
+  Q_CHECK_CUDA(launch_gemm_push(*plan, (const bf16*)d_x, (const unsigned char*)d_w_tiled, pw, (cudaStream_t)stream));
+  return Q_OK;
+}
+
+static int addnorm_peers_common(const void* d_resid_in, const q_peers_t* peers, const q_gemm_plan_t* prev_plan,
+                                const void* d_gain, void* d_resid_out, const void* d_w_tiled, void* d_out, int M,
+                                int K, float eps, NormPrologue* pro, PeerView* pw, const char* who) {
+  Q_CHECK_ARG(d_resid_in && peers && prev_plan && d_gain && d_resid_out && d_w_tiled && d_out, "%s: null pointer", who);
+  Q_CHECK_ARG(d_resid_in != d_resid_out, "%s: the residual cannot be updated in place", who);
+  Q_CHECK_ALIGN(d_resid_in, 8, who); Q_CHECK_ALIGN(d_gain, 8, who); Q_CHECK_ALIGN(d_resid_out, 8, who);
+  Q_CHECK_ALIGN(d_w_tiled, 16, who); Q_CHECK_ALIGN(d_out, 4, who);
+  Q_CHECK_ARG(M >= 1 && M <= 8 && K % 4 == 0 && K <= 3072, "%s: needs 1..8 rows and K a multiple of 4 up to 3072", who);
+  Q_CHECK_ARG(prev_plan->M == M && prev_plan->N == K && prev_plan->slots <= 2 && prev_plan->group_rows == 16,
+              "%s: the pushing projection's plan must be a stream-K plan [%d,%d] with at most two slots", who, M, K);
+  int rc = q_peer_view(peers, pw, who);
+  if (rc) return rc;
+  pro->prev = nullptr;
+  pro->prev_plan = plan_view(prev_plan);
+  pro->resid_in = (const bf16*)d_resid_in;
+  pro->resid_out = (bf16*)d_resid_out;
+  pro->gain = (const bf16*)d_gain;
+  pro->eps = eps;
+  return Q_OK;
+}
+
+// q_gemm_splitk_addnorm with the previous projection's partials of ALL ranks taken from the
+// receive area (pushed by q_gemm_push_planned on every rank).
+int q_gemm_splitk_addnorm_peers(const void* d_resid_in, const q_peers_t* peers, const q_gemm_plan_t* prev_plan,
+                                const void* d_gain, void* d_resid_out, const void* d_w_tiled, float* d_partials,
+                                int M, int N, int K, float eps, void* stream) {
+  NormPrologue pro;
+  PeerView pw;
+  int rc = addnorm_peers_common(d_resid_in, peers, prev_plan, d_gain, d_resid_out, d_w_tiled, d_partials, M, K, eps,
+                                &pro, &pw, "q_gemm_splitk_addnorm_peers");
+  if (rc) return rc;
+  q_gemm_plan_t p;
+  rc = q_gemm_plan(M, N, K, &p);
+  if (rc) return rc;
+  Q_CHECK_CUDA(launch_gemm_norm_poll<false>(p, (const unsigned char*)d_w_tiled, d_partials, pro, pw, (cudaStream_t)stream));
+  return Q_OK;
+}
+
+// q_gemm_swiglu_addnorm likewise.
+int q_gemm_swiglu_addnorm_peers(const void* d_resid_in, const q_peers_t* peers, const q_gemm_plan_t* prev_plan,
+                                const void* d_gain, void* d_resid_out, const void* d_w_tiled, void* d_act, int M,
+                                int inter, int K, float eps, void* stream) {
+  NormPrologue pro;
+  PeerView pw;
+  int rc = addnorm_peers_common(d_resid_in, peers, prev_plan, d_gain, d_resid_out, d_w_tiled, d_act, M, K, eps, &pro,
+                                &pw, "q_gemm_swiglu_addnorm_peers");
+  if (rc) return rc;
+  rc = swiglu_shape_ok(M, inter, K, "q_gemm_swiglu_addnorm_peers");
+  if (rc) return rc;
+  q_gemm_plan_t p;
+  rc = q_gemm_plan(M, 2 * inter, K, &p);
+  if (rc) return rc;
+  Q_CHECK_CUDA(launch_gemm_norm_poll<true>(p, (const unsigned char*)d_w_tiled, reinterpret_cast<float*>(d_act), pro, pw,
+                                           (cudaStream_t)stream));
   return Q_OK;
 }
 
