@@ -54,6 +54,11 @@ int q_set_pdl(int enabled);
  *       ticket like it does above 8 splits, instead of inside a thread-block cluster (default 0).
  *   "peer_wait_iters": polling iterations (about 1 us each once the wait has backed off) after which
  *       q_add_rmsnorm_peers / q_argmax_merge_peers give up on a peer and set status word 3 (default 2^21).
+ *   "peer_in_gemm": largest tensor-parallel world (default 2, 0 = never) for which
+ *       q_decode_step_peers at 1-8 rows exchanges inside the projections: the O and down
+ *       projections store their partials into every rank's receive area from their epilogue and
+ *       the next projection's add+norm prologue polls them, instead of q_add_rmsnorm_peers as
+ *       a kernel of its own (the step then has the five launches per layer of one GPU).
  *   "tc_min_rows": fewest rows for which q_decode_step uses the tcgen05 projections when the
  *       engine has the 128 x 64 tiling of its weights bound (default 9).
  *   "gemm_debug_flags": measurement aid, 4 = per-CTA time stamps for q_debug_gemm_trace, 8 = a
@@ -392,7 +397,8 @@ typedef struct q_state_t {
 
 /* Tensor parallel over peer memory (no reference counterpart: the reference is single-GPU).
  * Every rank owns a receive area the other ranks can write (CUDA IPC / symmetric memory;
- * q_engine_peer_floats() floats: [2 halves][world][rows][hidden] pairs {fp32 sum, call
+ * q_engine_peer_floats() floats: room for [2 halves][world][2 slots][rows][hidden] pairs of
+ * the in-projection exchange, of which q_add_rmsnorm_peers uses [2 halves][world][rows][hidden] pairs {fp32 sum, call
  * counter}, 8 bytes each, the halves used by alternate calls) and a flag region (q_peer_flag_bytes() bytes) of arrival words and the
  * token-exchange pairs. partials[r] / flags[r] are rank r's receive area and flag region as
  * mapped into THIS process (entry `rank` is this rank's own); both are zeroed once before
@@ -445,7 +451,8 @@ void q_destroy(q_engine* e);
 /* Tensor parallel over peer memory: floats of the peer-readable partial buffer for `rows`,
  * and the binding (after q_bind_state). With peers bound, q_decode_step_peers runs the whole
  * sharded step - embed .. lm_head shard .. local argmax .. q_argmax_merge_peers - with
- * q_add_rmsnorm_peers in place of the two all-reduces per layer. No collective library call
+ * q_add_rmsnorm_peers in place of the two all-reduces per layer (or, see option
+ * "peer_in_gemm", the same exchange inside the projections). No collective library call
  * is left in the step. q_bind_peers(e, NULL) unbinds; q_bind_state unbinds too. */
 int64_t q_engine_peer_floats(const q_engine* e, int rows);
 int q_bind_peers(q_engine* e, const q_peers_t* peers);

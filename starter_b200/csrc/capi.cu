@@ -43,7 +43,10 @@ int g_gemm_debug_flags = 0;
 int g_gemm_trace_launch = -1;    // measurement aid: the one GEMM launch that records its CTA trace
 int g_gemm_launches = 0;
 int g_attn_no_cluster = 0;        // 1 = decode attention merges its splits through global memory
-static int g_peer_in_gemm = 1;   // 1 = tensor parallel at 1-8 rows exchanges inside the projections
+// Largest tensor-parallel world whose 1-8 row step exchanges inside the projections (0 = never).
+// Every CTA of the polling projection reads all ranks' pairs, so the cost grows with the world:
+// measured at batch 1 it wins at 2 ranks (1.73 against 1.79 ms) and loses at 4 (1.71 against 1.61).
+static int g_peer_in_gemm = 2;
 static int g_norm_in_gemm = 1;   // 1 = residual add + RMSNorm as the prologue of the next projection
 static int g_tc_min_rows = 9;    // fewest rows that take the tcgen05 projections (when their tiling is bound)
 int g_peer_wait_iters = 1 << 21; // polling limit of the waits for a tensor-parallel peer
@@ -105,7 +108,8 @@ extern "C" int q_set_option(const char* name, int value) {
     return Q_OK;
   }
   if (strcmp(name, "peer_in_gemm") == 0) {
-    g_peer_in_gemm = value != 0;
+    Q_CHECK_ARG(value >= 0 && value <= Q_MAX_PEERS, "q_set_option: peer_in_gemm outside 0..%d", Q_MAX_PEERS);
+    g_peer_in_gemm = value;
     return Q_OK;
   }
   if (strcmp(name, "norm_in_gemm") == 0) {
@@ -374,7 +378,7 @@ static bool norm_in_gemm(const q_engine* e) {
 // Tensor parallel, up to 8 rows: the cross-rank sums are exchanged inside the projections.
 static bool peer_exchange_in_gemm(const q_engine* e) {
   return e->cfg.tp_size > 1 && e->has_peers && !e->tc && e->T == 1 && e->rows <= 8 && e->cfg.hidden % 4 == 0 &&
-         e->cfg.hidden <= 3072 && e->p_o.slots <= 2 && e->p_down.slots <= 2 && g_peer_in_gemm;
+         e->cfg.hidden <= 3072 && e->p_o.slots <= 2 && e->p_down.slots <= 2 && e->cfg.tp_size <= g_peer_in_gemm;
 }
 
 // attention .. O projection, from the QKV partials in st.partials. o_partials == nullptr: the O
