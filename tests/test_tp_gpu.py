@@ -1,6 +1,6 @@
-"""Tensor-parallel engine on 2 GPUs against the single-GPU engine and native Hugging Face:
-with the cross-rank sums read from peer memory inside the add+norm kernel (default), and with
-NCCL all-reduces inside the captured graph."""
+"""Tensor-parallel engine on 2 and 4 GPUs against the single-GPU engine and native Hugging Face:
+with the cross-rank sums exchanged through peer memory (inside the projections, or in the
+add+norm kernel), and with NCCL all-reduces inside the captured graph."""
 import json
 import os
 import subprocess
@@ -17,9 +17,14 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
 
-@pytest.mark.parametrize("tp_path", ["peers", "nccl"])
+@pytest.mark.parametrize("tp_path", ["peers", "peers-kernel", "nccl"])
 @pytest.mark.parametrize("world", [2, 4])
 def test_tensor_parallel_tokens_match_single_gpu(tmp_path, world, tp_path):
+    """"peers": at 1-8 rows the exchange runs inside the projections (forced for every world
+    size here; by default only up to two ranks); "peers-kernel": q_add_rmsnorm_peers as a kernel
+    of its own at every row count; above 8 rows both are the same path."""
+    in_gemm = {"peers": "8", "peers-kernel": "0", "nccl": "0"}[tp_path]
+    tp_path = "peers" if tp_path == "peers-kernel" else tp_path
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from transformers import Qwen3Config, Qwen3ForCausalLM
@@ -41,7 +46,7 @@ def test_tensor_parallel_tokens_match_single_gpu(tmp_path, world, tp_path):
     port = 29600 + os.getpid() % 1000
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), str(ROOT / "tests" / "tp_worker.py"),
-           str(model_dir), str(out_path), json.dumps(cases), tp_path]
+           str(model_dir), str(out_path), json.dumps(cases), tp_path, in_gemm]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
     report = json.loads(out_path.read_text())

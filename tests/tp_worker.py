@@ -23,6 +23,8 @@ def main():
     from starter_b200 import Engine, _lib
     if os.environ.get("TP_NO_PDL"):
         _lib.check(_lib.lib.q_set_pdl(0))
+    if len(sys.argv) > 5:          # largest world that exchanges inside the projections at 1-8 rows
+        _lib.check(_lib.lib.q_set_option(b"peer_in_gemm", int(sys.argv[5])))
     engine = Engine(model_dir, device=f"cuda:{local}", group=dist.group.WORLD, tp_path=tp_path)
     if os.environ.get("TP_NO_GRAPH"):
         from starter_b200.decode import DecodeState
