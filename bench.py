@@ -347,6 +347,16 @@ def time_in_step(state, reps: int = 8):
         counts = {}
         for i in range(n):
             counts[kinds[i]] = counts.get(kinds[i], 0) + 1
+        # the same shares by launch position inside a layer (a layer starts at its attention
+        # launch), mean over the inner layers of the last replay
+        att = [i for i in range(n) if kinds[i] == 3]
+        layer = []
+        if len(att) >= 6:
+            period = att[1] - att[0]
+            inner = att[2:-2]
+            for j in range(period):
+                vals = [(int(buf[4 * (a + j) + 2]) - int(buf[4 * (a + j - 1) + 2])) / 1e3 for a in inner]
+                layer.append([KIND_NAMES.get(kinds[att[2] + j], str(kinds[att[2] + j])), round(sum(vals) / len(vals), 2)])
     finally:
         check(lib.q_set_option(b"timeline", 0))
         state.tokens.copy_(saved[0])
@@ -354,7 +364,7 @@ def time_in_step(state, reps: int = 8):
     med = lambda v: sorted(v)[len(v) // 2]
     return {"us": {KIND_NAMES.get(k, str(k)): med(v) for k, v in shares.items()},
             "launches": {KIND_NAMES.get(k, str(k)): c for k, c in counts.items()},
-            "step_span_us": med(span)}
+            "layer_us": layer, "step_span_us": med(span)}
 
 
 def kernels_per_step(state) -> int:
@@ -516,12 +526,13 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             ms3, keys3, clocks3 = measure_decode(st3, K3, W, world, dev, local_rank)
             bytes3 = st3.step_bytes(int(round(keys3)))
             digest = tokens_digest([first_tokens, st3.tokens.cpu().tolist()])
+            in3 = time_in_step(st3) or {}
             c3 = {"workload": f"c3: batch {b3}, prompt {p3}", "steps": K3, "ms_per_step": ms3 / K3,
                   "value": b3 * K3 / (ms3 * 1e-3), "unit": "tok/s", "tp_path": st3.tp_path,
                   "projections": "tcgen05" if st3.uses_tc else "mma.sync",
                   "bytes_per_step_per_gpu": bytes3, "step_gbs_per_gpu": bytes3 / (ms3 / K3 * 1e-3) / 1e9,
                   "gpu_launches": kernels_per_step(st3) * K3, "prefill_ms": prefill_ms,
-                  "in_step_us": (time_in_step(st3) or {}).get("us"),
+                  "in_step_us": in3.get("us"), "in_step_layer_us": in3.get("layer_us"),
                   "tokens_sha16": digest, "clocks": clocks3, "device_status": status_over_ranks()}
             st3.graph = None
             del st3
@@ -587,6 +598,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         "roofline": roofline,
         "gemm_kernel": gemm_info,
         "in_step_us": in_step["us"] if in_step else None,
+        "in_step_layer_us": in_step["layer_us"] if in_step else None,
         "e2e": e2e,
         "tp_path": tp_path,
         "gpu_launches": launches * K,
