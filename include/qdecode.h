@@ -433,6 +433,29 @@ int q_add_rmsnorm_peers(const void* d_x_in, const q_peers_t* peers, const float*
                         const q_gemm_plan_t* plan, const void* d_gain, void* d_total_out,
                         void* d_normed_out, int rows, int cols, float eps, void* stream);
 
+/* The same exchange INSIDE the projections, for 1..8 rows (no reference counterpart). The
+ * projection BEFORE an add+norm (O, down) runs as q_gemm_push: instead of writing partial
+ * slots it stores every partial, paired with the call counter, into the receive area of every
+ * rank - [half][rank][2 slots][M][N] pairs of 8 bytes, its own rank's too. The projection
+ * AFTER the add+norm runs as q_gemm_splitk_addnorm_peers / q_gemm_swiglu_addnorm_peers:
+ * q_gemm_splitk_addnorm / q_gemm_swiglu_addnorm whose prologue polls (bounded by option
+ * "peer_wait_iters") the own receive area for all ranks' partials of the pushing projection
+ * (prev_plan = that projection's plan: which slots exist), adds them in (rank, slot) order
+ * and moves the call counter on. A wait that runs out sets q_device_status word 1 to 4. All
+ * ranks make the same sequence of calls; the counter words are shared with
+ * q_add_rmsnorm_peers (peers->epoch). plan / prev_plan: a q_gemm_plan of 1..8 rows with at
+ * most two slots; K of the polling projection a multiple of 4 up to 3072. */
+int q_gemm_push(const void* d_x, const void* d_w_tiled, const q_gemm_plan_t* plan,
+                const q_peers_t* peers, void* stream);
+int q_gemm_splitk_addnorm_peers(const void* d_resid_in, const q_peers_t* peers,
+                                const q_gemm_plan_t* prev_plan, const void* d_gain,
+                                void* d_resid_out, const void* d_w_tiled, float* d_partials,
+                                int M, int N, int K, float eps, void* stream);
+int q_gemm_swiglu_addnorm_peers(const void* d_resid_in, const q_peers_t* peers,
+                                const q_gemm_plan_t* prev_plan, const void* d_gain,
+                                void* d_resid_out, const void* d_w_tiled, void* d_act,
+                                int M, int inter, int K, float eps, void* stream);
+
 /* engine/decode.py:106-107 (argmax, position += 1) over vocabulary shards held by different
  * ranks, without a collective library call: every rank stores its per-row (value, index) pair
  * (d_val / d_idx, as q_logits_argmax leaves them) into every rank's exchange area with plain

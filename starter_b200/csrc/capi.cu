@@ -399,7 +399,7 @@ static int attn_after_qkv(q_engine* e, int layer, float* o_partials, void* strea
     TRY(q_attention(s.q, &kv, s.pos, s.attn_o, s.attn_ml, s.attended, s.batch, e->T, c.n_q_heads,
                     s.attn_splits, c.attn_scale, stream));
   }
-  if (!o_partials) return q_gemm_push_planned(s.attended, w.wo, &e->p_o, &e->peers, stream);
+  if (!o_partials) return q_gemm_push(s.attended, w.wo, &e->p_o, &e->peers, stream);
   return project(e, s.attended, w.wo, w.wo_tc, o_partials, e->p_o, stream);
 }
 
@@ -566,7 +566,7 @@ extern "C" int q_decode_step_peers(q_engine* e, void* stream) {
       TRY(attn_after_qkv(e, l, nullptr, stream));
       TRY(q_gemm_swiglu_addnorm_peers(s.x, &e->peers, &e->p_o, e->layers[l].ln_post, s.normed, e->layers[l].wgu,
                                       s.act, rows, c.inter, c.hidden, c.rms_eps, stream));
-      TRY(q_gemm_push_planned(s.act, e->layers[l].wdown, &e->p_down, &e->peers, stream));
+      TRY(q_gemm_push(s.act, e->layers[l].wdown, &e->p_down, &e->peers, stream));
       const bool last = l + 1 == c.n_layers;
       TRY(q_gemm_splitk_addnorm_peers(s.normed, &e->peers, &e->p_down, next_gain(e, l), s.x,
                                       last ? s.lm_head : e->layers[l + 1].wqkv, s.partials, rows,

@@ -132,18 +132,6 @@ int q_gemm_launch_planned(const void* d_x, const void* d_w_tiled, float* d_parti
 int q_gemm_tc_launch(const void* d_x, const void* d_w_tc, float* d_partials, const q_gemm_plan_t* plan,
                      void* stream);
 
-// Tensor parallel over peer memory at 1-8 rows, the exchange inside the projections: the
-// projection before an add+norm pushes its partials to every rank's receive area, the
-// projection after it polls them in its prologue (gemm_streamk.cu, PEER).
-int q_gemm_push_planned(const void* d_x, const void* d_w_tiled, const q_gemm_plan_t* plan, const q_peers_t* peers,
-                        void* stream);
-int q_gemm_splitk_addnorm_peers(const void* d_resid_in, const q_peers_t* peers, const q_gemm_plan_t* prev_plan,
-                                const void* d_gain, void* d_resid_out, const void* d_w_tiled, float* d_partials,
-                                int M, int N, int K, float eps, void* stream);
-int q_gemm_swiglu_addnorm_peers(const void* d_resid_in, const q_peers_t* peers, const q_gemm_plan_t* prev_plan,
-                                const void* d_gain, void* d_resid_out, const void* d_w_tiled, void* d_act, int M,
-                                int inter, int K, float eps, void* stream);
-
 // q_swiglu on partials whose columns are in q_gemm_swiglu's interleaved gate/up order
 // (interleaved = 1) or in [gate | up] order (0).
 int q_swiglu_layout(const float* d_branch, const q_gemm_plan_t* plan, void* d_out, int rows, int inter,

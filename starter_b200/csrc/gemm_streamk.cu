@@ -989,17 +989,17 @@ extern "C" int q_gemm_swiglu_addnorm(const void* d_resid_in, const float* d_prev
 }
 
 // ---- tensor parallel over peer memory, 1-8 rows: the exchange inside the projections ----
-// (internal: the engine's peer step calls these; see the PEER template parameter)
+// (see the PEER template parameter)
 
 // X[M,K] @ W^T, every partial pushed to every rank's receive area.
-int q_gemm_push_planned(const void* d_x, const void* d_w_tiled, const q_gemm_plan_t* plan, const q_peers_t* peers,
-                        void* stream) {
-  Q_CHECK_ARG(d_x && d_w_tiled && plan && peers, "q_gemm_push_planned: null pointer");
+extern "C" int q_gemm_push(const void* d_x, const void* d_w_tiled, const q_gemm_plan_t* plan, const q_peers_t* peers,
+                           void* stream) {
+  Q_CHECK_ARG(d_x && d_w_tiled && plan && peers, "q_gemm_push: null pointer");
   Q_CHECK_ARG(plan->M >= 1 && plan->M <= 8 && plan->slots <= 2 && plan->group_rows == 16,
-              "q_gemm_push_planned: needs a stream-K plan of 1..8 rows with at most two slots");
-  Q_CHECK_ALIGN(d_x, 16, "q_gemm_push_planned"); Q_CHECK_ALIGN(d_w_tiled, 16, "q_gemm_push_planned");
+              "q_gemm_push: needs a stream-K plan of 1..8 rows with at most two slots");
+  Q_CHECK_ALIGN(d_x, 16, "q_gemm_push"); Q_CHECK_ALIGN(d_w_tiled, 16, "q_gemm_push");
   PeerView pw;
-  int rc = q_peer_view(peers, &pw, "q_gemm_push_planned");
+  int rc = q_peer_view(peers, &pw, "q_gemm_push");
   if (rc) return rc;
   Q_CHECK_CUDA(launch_gemm_push(*plan, (const bf16*)d_x, (const unsigned char*)d_w_tiled, pw, (cudaStream_t)stream));
   return Q_OK;
@@ -1027,10 +1027,10 @@ static int addnorm_peers_common(const void* d_resid_in, const q_peers_t* peers, 
 }
 
 // q_gemm_splitk_addnorm with the previous projection's partials of ALL ranks taken from the
-// receive area (pushed by q_gemm_push_planned on every rank).
-int q_gemm_splitk_addnorm_peers(const void* d_resid_in, const q_peers_t* peers, const q_gemm_plan_t* prev_plan,
-                                const void* d_gain, void* d_resid_out, const void* d_w_tiled, float* d_partials,
-                                int M, int N, int K, float eps, void* stream) {
+// receive area (pushed by q_gemm_push on every rank).
+extern "C" int q_gemm_splitk_addnorm_peers(const void* d_resid_in, const q_peers_t* peers, const q_gemm_plan_t* prev_plan,
+                                           const void* d_gain, void* d_resid_out, const void* d_w_tiled, float* d_partials,
+                                           int M, int N, int K, float eps, void* stream) {
   NormPrologue pro;
   PeerView pw;
   int rc = addnorm_peers_common(d_resid_in, peers, prev_plan, d_gain, d_resid_out, d_w_tiled, d_partials, M, K, eps,
@@ -1044,9 +1044,9 @@ int q_gemm_splitk_addnorm_peers(const void* d_resid_in, const q_peers_t* peers, 
 }
 
 // q_gemm_swiglu_addnorm likewise.
-int q_gemm_swiglu_addnorm_peers(const void* d_resid_in, const q_peers_t* peers, const q_gemm_plan_t* prev_plan,
-                                const void* d_gain, void* d_resid_out, const void* d_w_tiled, void* d_act, int M,
-                                int inter, int K, float eps, void* stream) {
+extern "C" int q_gemm_swiglu_addnorm_peers(const void* d_resid_in, const q_peers_t* peers, const q_gemm_plan_t* prev_plan,
+                                           const void* d_gain, void* d_resid_out, const void* d_w_tiled, void* d_act, int M,
+                                           int inter, int K, float eps, void* stream) {
   NormPrologue pro;
   PeerView pw;
   int rc = addnorm_peers_common(d_resid_in, peers, prev_plan, d_gain, d_resid_out, d_w_tiled, d_act, M, K, eps, &pro,

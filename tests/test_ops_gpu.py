@@ -210,6 +210,117 @@ def test_swiglu_on_interleaved_partials(ops, M, inter, K):
     assert bit_equal_fraction(out.cpu(), ref) > 0.99
 
 
+def _emulated_peers(rows, cols, world=2):
+    """Two tensor-parallel "ranks" on ONE GPU: both ranks' receive areas are the same buffer
+    (every push lands in it once per destination), the counter words are shared, and the
+    launches of the ranks run one after the other on one stream - nothing ever waits for a
+    launch that has not finished."""
+    import ctypes as C
+    from starter_b200 import _lib
+    pairs = 2 * world * 2 * rows * cols                       # [2 halves][world][2 slots][rows][cols]
+    buf = torch.zeros(2 * pairs + _lib.lib.q_peer_flag_bytes() // 4, dtype=torch.float32, device="cuda")
+    counters = torch.zeros(4, dtype=torch.int32, device="cuda")
+    views = []
+    for rank in range(world):
+        peers = _lib.Peers()
+        peers.rank, peers.world = rank, world
+        for r in range(world):
+            peers.partials[r] = buf.data_ptr()
+            peers.flags[r] = buf.data_ptr() + 2 * pairs * 4
+        peers.epoch = counters.data_ptr()
+        views.append(peers)
+    return views, counters, buf
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+def test_peer_exchange_inside_the_projections(ops, M):
+    """q_gemm_push on two emulated ranks (a row-parallel projection split over K), then the
+    polling add+norm prologue of the next projection on one of them: residual and projection
+    against the same computation on the unsplit operands. Twice (both halves of the receive
+    area), then the SwiGLU form."""
+    import ctypes as C
+    from starter_b200 import _lib
+    from starter_b200.weights import TiledWeight
+    lib, check = _lib.lib, _lib.check
+    P = lambda t: C.c_void_p(t.data_ptr())
+    Kp, N1 = 1024, 384
+    w0, x = randw(H, 2 * Kp, 161), randx(M, 2 * Kp, 162)
+    res = randx(M, H, 163).cuda()
+    gain = (1 + 0.1 * torch.randn(H, generator=torch.Generator().manual_seed(164))).to(torch.bfloat16).cuda()
+    w1 = randw(N1, H, 165).cuda()
+    wgu = randw(2 * 1216, H, 166).cuda()
+    shards = [(x[:, r * Kp:(r + 1) * Kp].contiguous().cuda(), TiledWeight.pack(w0[:, r * Kp:(r + 1) * Kp].contiguous().cuda()))
+              for r in range(2)]
+    views, counters, _ = _emulated_peers(M, H)
+    plan0 = _lib.plan(M, H, Kp)
+    # the unsplit route: partials of the whole projection, add+norm as the next one's prologue
+    whole = ops.linear_partials(x.cuda(), w0.cuda())
+    want_total, want = ops.add_rms_norm_linear(res, whole, gain, 1e-6, w1)
+    w1t = TiledWeight.pack(w1)
+    p1 = _lib.plan(M, N1, H)
+    for call in (1, 2):
+        for r in range(2):
+            check(lib.q_gemm_push(P(shards[r][0]), P(shards[r][1].data), C.byref(plan0), C.byref(views[r]), None))
+        total = torch.empty_like(res)
+        data = torch.empty((p1.slots, M, N1), dtype=torch.float32, device="cuda")
+        check(lib.q_gemm_splitk_addnorm_peers(P(res), C.byref(views[0]), C.byref(plan0), P(gain), P(total),
+                                              P(w1t.data), P(data), M, N1, H, 1e-6, None))
+        torch.cuda.synchronize()
+        assert counters.tolist() == [call, 0, 0, 0]
+        # same products, another fp32 order: the rounded residual agrees except at rounding ties
+        assert bit_equal_fraction(total, want_total) > 0.995
+        got = ops.Partials(data, p1).sum()
+        torch.testing.assert_close(got, want.sum(), rtol=2e-2, atol=2e-2)
+    et, en = O.add_rms_norm(res.cpu(), O.linear_fp32(x, w0), gain.cpu(), 1e-6)
+    assert bit_equal_fraction(total.cpu(), et) > 0.995
+    torch.testing.assert_close(got.cpu(), O.linear_fp32(en, w1.cpu()), rtol=2e-2, atol=2e-2)
+    # SwiGLU form
+    for r in range(2):
+        check(lib.q_gemm_push(P(shards[r][0]), P(shards[r][1].data), C.byref(plan0), C.byref(views[r]), None))
+    wt = TiledWeight.pack(wgu, interleave8=True)
+    total2 = torch.empty_like(res)
+    act = torch.empty((M, 1216), dtype=torch.bfloat16, device="cuda")
+    check(lib.q_gemm_swiglu_addnorm_peers(P(res), C.byref(views[1]), C.byref(plan0), P(gain), P(total2), P(wt.data),
+                                          P(act), M, 1216, H, 1e-6, None))
+    torch.cuda.synchronize()
+    assert torch.equal(total2, total) and counters.tolist() == [3, 0, 0, 0]
+    _, want_act = ops.add_rms_norm_linear_silu_mul(res, whole, gain, 1e-6, wgu)
+    torch.testing.assert_close(act.float(), want_act.float(), rtol=4e-2, atol=2e-3)
+    assert ops.device_status() == [0, 0, 0, 0]
+
+
+def test_peer_exchange_inside_the_projections_times_out(ops):
+    """Only one of two ranks pushes: the polling prologue gives up after the wait limit, sets
+    status word 1 to 4 and finishes (nothing hangs); q_clear_status re-arms."""
+    import ctypes as C
+    from starter_b200 import _lib
+    from starter_b200.weights import TiledWeight
+    lib, check = _lib.lib, _lib.check
+    P = lambda t: C.c_void_p(t.data_ptr())
+    M, Kp, N1 = 2, 256, 128
+    x, w0 = randx(M, Kp, 171).cuda(), TiledWeight.pack(randw(H, Kp, 172).cuda())
+    res = randx(M, H, 173).cuda()
+    gain = torch.ones(H, dtype=torch.bfloat16, device="cuda")
+    w1 = TiledWeight.pack(randw(N1, H, 174).cuda())
+    views, counters, _ = _emulated_peers(M, H)
+    plan0, p1 = _lib.plan(M, H, Kp), _lib.plan(M, N1, H)
+    ops.clear_status()
+    check(lib.q_gemm_push(P(x), P(w0.data), C.byref(plan0), C.byref(views[0]), None))       # rank 1 never pushes
+    total = torch.empty_like(res)
+    data = torch.empty((p1.slots, M, N1), dtype=torch.float32, device="cuda")
+    check(lib.q_set_option(b"peer_wait_iters", 2000))
+    try:
+        check(lib.q_gemm_splitk_addnorm_peers(P(res), C.byref(views[0]), C.byref(plan0), P(gain), P(total), P(w1.data),
+                                              P(data), M, N1, H, 1e-6, None))
+        torch.cuda.synchronize()
+    finally:
+        check(lib.q_set_option(b"peer_wait_iters", 1 << 21))
+    assert ops.device_status() == [0, 4, 0, 0]
+    assert counters.tolist() == [1, 0, 0, 0]                   # the call completed all the same
+    ops.clear_status()
+    assert ops.device_status() == [0, 0, 0, 0]
+
+
 def test_rms_norm_plain(ops):
     x = randx(7, H, 41)
     gain = (1 + 0.1 * torch.randn(H, generator=torch.Generator().manual_seed(42))).to(torch.bfloat16)
