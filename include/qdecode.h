@@ -59,9 +59,6 @@ int q_set_pdl(int enabled);
  *       projections store their partials into every rank's receive area from their epilogue and
  *       the next projection's add+norm prologue polls them, instead of q_add_rmsnorm_peers as
  *       a kernel of its own (the step then has the five launches per layer of one GPU).
- *   "peer_push": 1 (default) = where that does not apply, q_decode_step_peers at 1-8 rows still
- *       lets the O and down projections push (q_gemm_push) and runs q_add_rmsnorm_pushed; 0 =
- *       q_add_rmsnorm_peers reads the local slots and pushes itself, as above 8 rows.
  *   "tc_min_rows": fewest rows for which q_decode_step uses the tcgen05 projections when the
  *       engine has the 128 x 64 tiling of its weights bound (default 9).
  *   "gemm_debug_flags": measurement aid, 4 = per-CTA time stamps for q_debug_gemm_trace, 8 = a
@@ -450,12 +447,6 @@ int q_add_rmsnorm_peers(const void* d_x_in, const q_peers_t* peers, const float*
  * most two slots; K of the polling projection a multiple of 4 up to 3072. */
 int q_gemm_push(const void* d_x, const void* d_w_tiled, const q_gemm_plan_t* plan,
                 const q_peers_t* peers, void* stream);
-/* q_add_rmsnorm_peers for partials that q_gemm_push has already delivered: one CTA per row
- * polls all ranks' slots and adds + normalises; nothing is read locally or pushed (the form
- * q_decode_step_peers uses at 1..8 rows above the "peer_in_gemm" world size). */
-int q_add_rmsnorm_pushed(const void* d_x_in, const q_peers_t* peers, const q_gemm_plan_t* prev_plan,
-                         const void* d_gain, void* d_total_out, void* d_normed_out, int rows,
-                         int cols, float eps, void* stream);
 int q_gemm_splitk_addnorm_peers(const void* d_resid_in, const q_peers_t* peers,
                                 const q_gemm_plan_t* prev_plan, const void* d_gain,
                                 void* d_resid_out, const void* d_w_tiled, float* d_partials,

@@ -109,7 +109,6 @@ SIGNATURES = {
     "q_clear_status": (_I, []),
     "q_add_rmsnorm_peers": (_I, [_P, C.POINTER(Peers), _P, _PLAN, _P, _P, _P, _I, _I, _F, _P]),
     "q_gemm_push": (_I, [_P, _P, _PLAN, C.POINTER(Peers), _P]),
-    "q_add_rmsnorm_pushed": (_I, [_P, C.POINTER(Peers), _PLAN, _P, _P, _P, _I, _I, _F, _P]),
     "q_gemm_splitk_addnorm_peers": (_I, [_P, C.POINTER(Peers), _PLAN, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
     "q_gemm_swiglu_addnorm_peers": (_I, [_P, C.POINTER(Peers), _PLAN, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
     "q_engine_peer_floats": (C.c_int64, [_P, _I]),

@@ -47,7 +47,6 @@ int g_attn_no_cluster = 0;        // 1 = decode attention merges its splits thro
 // Every CTA of the polling projection reads all ranks' pairs, so the cost grows with the world:
 // measured at batch 1 it wins at 2 ranks (1.73 against 1.79 ms) and loses at 4 (1.71 against 1.61).
 static int g_peer_in_gemm = 2;
-static int g_peer_push = 1;      // 1 = at 1-8 rows the O / down projections push their partials themselves
 static int g_norm_in_gemm = 1;   // 1 = residual add + RMSNorm as the prologue of the next projection
 static int g_tc_min_rows = 9;    // fewest rows that take the tcgen05 projections (when their tiling is bound)
 int g_peer_wait_iters = 1 << 21; // polling limit of the waits for a tensor-parallel peer
@@ -106,10 +105,6 @@ extern "C" int q_set_option(const char* name, int value) {
   if (strcmp(name, "gemm_prefetch_kb") == 0) {
     Q_CHECK_ARG(value >= 0 && value <= 8192, "q_set_option: gemm_prefetch_kb outside 0..8192");
     g_gemm_prefetch_kb = value;
-    return Q_OK;
-  }
-  if (strcmp(name, "peer_push") == 0) {
-    g_peer_push = value != 0;
     return Q_OK;
   }
   if (strcmp(name, "peer_in_gemm") == 0) {
@@ -386,12 +381,6 @@ static bool peer_exchange_in_gemm(const q_engine* e) {
          e->cfg.hidden <= 3072 && e->p_o.slots <= 2 && e->p_down.slots <= 2 && e->cfg.tp_size <= g_peer_in_gemm;
 }
 
-// ... above that world size the projections still push, and q_add_rmsnorm_pushed polls.
-static bool peer_push_from_gemm(const q_engine* e) {
-  return e->cfg.tp_size > 1 && e->has_peers && !e->tc && e->T == 1 && e->rows <= 8 && e->cfg.hidden % 4 == 0 &&
-         e->cfg.hidden <= 4096 && e->p_o.slots <= 2 && e->p_down.slots <= 2 && g_peer_push;
-}
-
 // attention .. O projection, from the QKV partials in st.partials. o_partials == nullptr: the O
 // projection pushes its partials to the tensor-parallel peers instead (1-8 rows).
 static int attn_after_qkv(q_engine* e, int layer, float* o_partials, void* stream) {
@@ -584,24 +573,6 @@ extern "C" int q_decode_step_peers(q_engine* e, void* stream) {
                                       last ? c.vocab : e->p_qkv.N, c.hidden, c.rms_eps, stream));
     }
     TRY(head_argmax(e, false, stream));
-    return q_argmax_merge_peers_tap(s.arg_val, s.arg_idx, &e->peers, e->rows, s.tokens, s.pos, 1, status_tap(e),
-                                    stream);
-  }
-  if (peer_push_from_gemm(e)) {
-    // 1-8 rows, more ranks than the in-projection exchange is used for: the O and down
-    // projections still push from their epilogue (148 CTAs storing as they finish, instead of one
-    // CTA per row after reading the slots back), the add+norm kernel only polls
-    for (int l = 0; l < c.n_layers; ++l) {
-      TRY(project(e, s.normed, e->layers[l].wqkv, nullptr, s.partials, e->p_qkv, stream));
-      TRY(attn_after_qkv(e, l, nullptr, stream));
-      TRY(q_add_rmsnorm_pushed(s.x, &e->peers, &e->p_o, e->layers[l].ln_post, s.x, s.normed, e->rows, c.hidden,
-                               c.rms_eps, stream));
-      TRY(q_gemm_swiglu(s.normed, e->layers[l].wgu, s.act, e->rows, c.inter, c.hidden, stream));
-      TRY(q_gemm_push(s.act, e->layers[l].wdown, &e->p_down, &e->peers, stream));
-      TRY(q_add_rmsnorm_pushed(s.x, &e->peers, &e->p_down, next_gain(e, l), s.x, s.normed, e->rows, c.hidden,
-                               c.rms_eps, stream));
-    }
-    TRY(head(e, false, stream));
     return q_argmax_merge_peers_tap(s.arg_val, s.arg_idx, &e->peers, e->rows, s.tokens, s.pos, 1, status_tap(e),
                                     stream);
   }

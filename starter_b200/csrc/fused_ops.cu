@@ -217,11 +217,6 @@ __device__ __forceinline__ bool wait_arrival(const uint32_t* word, unsigned e, i
 
 constexpr int PEER_MAX_COLS = 4096;     // one thread per four columns, at most 1024 threads
 
-// PUSHED: the projection before has already stored every rank's partial SLOTS into the receive
-// areas from its epilogue (q_gemm_push: [half][rank][2 slots][rows][cols] pairs), so this kernel
-// neither reads local slots nor pushes: it polls for all ranks' slots (its own rank's too) and
-// adds them in (rank, slot) order.
-template <bool PUSHED>
 __global__ void __launch_bounds__(1024)
 k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, const float* __restrict__ P, PlanView pv,
                     const bf16* __restrict__ G, bf16* __restrict__ Tout, bf16* __restrict__ Nout,
@@ -246,20 +241,17 @@ k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, const float* __re
   const float2 z2 = make_float2(0.f, 0.f);
   float2 own[2];
   uint32_t xr[2], gn[2];
-  int extra_h[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int c = live[h] ? colv[h] : 0;
     const float* p0 = P + (size_t)row * cols + c;
     const int extra = live[h] ? plan_count(pv, c) - 1 : -1;
-    xr[h] = live[h] ? *reinterpret_cast<const uint32_t*>(Xin + (size_t)row * cols + c) : 0u;
-    gn[h] = live[h] ? *reinterpret_cast<const uint32_t*>(G + c) : 0u;
-    extra_h[h] = extra;
-    if (PUSHED) { own[h] = z2; continue; }
     float2 sl[10];
 #pragma unroll
     for (int k = 0; k < 10; ++k)
       sl[k] = (k <= extra && (k == 0 || pv.u != 0)) ? *reinterpret_cast<const float2*>(p0 + (long long)k * pv.slot_stride) : z2;
+    xr[h] = live[h] ? *reinterpret_cast<const uint32_t*>(Xin + (size_t)row * cols + c) : 0u;
+    gn[h] = live[h] ? *reinterpret_cast<const uint32_t*>(G + c) : 0u;
     float2 acc = sl[0];
 #pragma unroll
     for (int k = 1; k < 10; ++k)
@@ -278,7 +270,7 @@ k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, const float* __re
   // 1. push this rank's pairs to every peer
 #pragma unroll
   for (int r = 0; r < Q_MAX_PEERS; ++r)
-    if (!PUSHED && r < pw.world && r != pw.rank) {
+    if (r < pw.world && r != pw.rank) {
       char* dst = reinterpret_cast<char*>(pw.recv[r]);
       if (live[0]) st_pair2(dst + (row_off + colv[0]) * 8, own[0].x, own[0].y, e);
       if (live[1]) st_pair2(dst + (row_off + colv[1]) * 8, own[1].x, own[1].y, e);
@@ -289,57 +281,9 @@ k_add_rmsnorm_peers(const bf16* __restrict__ Xin, PeerView pw, const float* __re
   {
     float2 acc[2] = {z2, z2};
     bool ok = true;
-    if (PUSHED) {
-      // all ranks' slots of this row, two ranks (x two slots) in flight per poll
-      const size_t half2 = (size_t)(e & 1u) * pw.world;
-      const char* mine = reinterpret_cast<const char*>(pw.recv[pw.rank]);
-      for (int r0 = 0; r0 < pw.world; r0 += 2) {
-        unsigned long long a[2][2][4];
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-          for (int sl = 0; sl < 2; ++sl) a[j][sl][0] = a[j][sl][1] = a[j][sl][2] = a[j][sl][3] = 0;
-        bool here = false;
-        for (int i = 0; ok && i < wait_iters; ++i) {
-          here = true;
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            if (r0 + j >= pw.world) break;
-#pragma unroll
-            for (int sl = 0; sl < 2; ++sl) {
-              const char* src = mine + ((((half2 + (r0 + j)) * 2 + sl) * rows + row) * cols) * 8;
-              if (live[0] && sl <= extra_h[0]) {
-                ld_pair2(src + (size_t)colv[0] * 8, a[j][sl][0], a[j][sl][1]);
-                here = here && (unsigned)(a[j][sl][0] >> 32) == e && (unsigned)(a[j][sl][1] >> 32) == e;
-              }
-              if (live[1] && sl <= extra_h[1]) {
-                ld_pair2(src + (size_t)colv[1] * 8, a[j][sl][2], a[j][sl][3]);
-                here = here && (unsigned)(a[j][sl][2] >> 32) == e && (unsigned)(a[j][sl][3] >> 32) == e;
-              }
-            }
-          }
-          if (here) break;
-          if (i > 64) __nanosleep(i > 65536 ? 2000 : (i > 4096 ? 400 : 40));
-        }
-        if (!here) { ok = false; atomicExch(&g_peer_status, 1); }
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          if (r0 + j >= pw.world) break;
-#pragma unroll
-          for (int sl = 0; sl < 2; ++sl) {
-            if (live[0] && sl <= extra_h[0]) {
-              acc[0].x += __uint_as_float((unsigned)a[j][sl][0]); acc[0].y += __uint_as_float((unsigned)a[j][sl][1]);
-            }
-            if (live[1] && sl <= extra_h[1]) {
-              acc[1].x += __uint_as_float((unsigned)a[j][sl][2]); acc[1].y += __uint_as_float((unsigned)a[j][sl][3]);
-            }
-          }
-        }
-      }
-    }
     // Four peers at a time: their loads are in flight together (one round trip per poll, not
     // one per peer), and the sums are still added in rank order.
-    for (int r0 = 0; !PUSHED && r0 < pw.world; r0 += 4) {
+    for (int r0 = 0; r0 < pw.world; r0 += 4) {
       unsigned long long a[4][4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) a[j][0] = a[j][1] = a[j][2] = a[j][3] = 0;
@@ -854,30 +798,8 @@ extern "C" int q_add_rmsnorm_peers(const void* d_x_in, const q_peers_t* peers, c
   rc = q_peer_view(peers, &pw, "q_add_rmsnorm_peers");
   if (rc) return rc;
   const int threads = ((cols + 127) / 128) * 32;        // one warp per 128 columns
-  Q_CHECK_CUDA(q_launch(k_add_rmsnorm_peers<false>, dim3(rows), dim3(threads), 0, S(stream), (const bf16*)d_x_in, pw,
+  Q_CHECK_CUDA(q_launch(k_add_rmsnorm_peers, dim3(rows), dim3(threads), 0, S(stream), (const bf16*)d_x_in, pw,
                         d_own_branch, plan_view(plan), (const bf16*)d_gain, (bf16*)d_total_out,
-                        (bf16*)d_normed_out, rows, cols, eps, g_peer_wait_iters, q_tl_next(Q_TL_PEER_ADD_NORM)));
-  return Q_OK;
-}
-
-extern "C" int q_add_rmsnorm_pushed(const void* d_x_in, const q_peers_t* peers, const q_gemm_plan_t* prev_plan,
-                                    const void* d_gain, void* d_total_out, void* d_normed_out, int rows, int cols,
-                                    float eps, void* stream) {
-  Q_CHECK_ARG(d_x_in && peers && prev_plan && d_gain && d_total_out && d_normed_out,
-              "q_add_rmsnorm_pushed: null pointer");
-  Q_CHECK_ARG(rows >= 1 && rows <= 8 && cols >= 4 && cols % 4 == 0 && cols <= PEER_MAX_COLS,
-              "q_add_rmsnorm_pushed: needs 1..8 rows and cols a multiple of 4 up to %d", PEER_MAX_COLS);
-  Q_CHECK_ARG(prev_plan->M == rows && prev_plan->N == cols && prev_plan->slots <= 2 && prev_plan->group_rows == 16,
-              "q_add_rmsnorm_pushed: the pushing projection's plan must be a stream-K plan [%d,%d] with at most two slots",
-              rows, cols);
-  Q_CHECK_ARG((((uintptr_t)d_x_in | (uintptr_t)d_gain | (uintptr_t)d_total_out | (uintptr_t)d_normed_out) & 7) == 0,
-              "q_add_rmsnorm_pushed: bf16 operands must be 8-byte aligned");
-  PeerView pw;
-  int rc = q_peer_view(peers, &pw, "q_add_rmsnorm_pushed");
-  if (rc) return rc;
-  const int threads = ((cols + 127) / 128) * 32;        // one warp per 128 columns
-  Q_CHECK_CUDA(q_launch(k_add_rmsnorm_peers<true>, dim3(rows), dim3(threads), 0, S(stream), (const bf16*)d_x_in, pw,
-                        (const float*)nullptr, plan_view(prev_plan), (const bf16*)d_gain, (bf16*)d_total_out,
                         (bf16*)d_normed_out, rows, cols, eps, g_peer_wait_iters, q_tl_next(Q_TL_PEER_ADD_NORM)));
   return Q_OK;
 }

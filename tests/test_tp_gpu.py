@@ -17,16 +17,14 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
 
-@pytest.mark.parametrize("tp_path", ["peers", "peers-pushed", "peers-kernel", "nccl"])
+@pytest.mark.parametrize("tp_path", ["peers", "peers-kernel", "nccl"])
 @pytest.mark.parametrize("world", [2, 4])
 def test_tensor_parallel_tokens_match_single_gpu(tmp_path, world, tp_path):
-    """The three forms of the peer-memory exchange at 1-8 rows. "peers": inside the projections
-    (forced for every world size here; by default only up to two ranks); "peers-pushed": the
-    projections push, q_add_rmsnorm_pushed polls (the default above two ranks); "peers-kernel":
-    q_add_rmsnorm_peers reads the local slots and pushes itself. Above 8 rows all three are
-    the last one."""
-    in_gemm = {"peers": "8,1", "peers-pushed": "0,1", "peers-kernel": "0,0", "nccl": "0,0"}[tp_path]
-    tp_path = "nccl" if tp_path == "nccl" else "peers"
+    """"peers": at 1-8 rows the exchange runs inside the projections (forced for every world
+    size here; by default only up to two ranks); "peers-kernel": q_add_rmsnorm_peers as a kernel
+    of its own at every row count; above 8 rows both are the same path."""
+    in_gemm = {"peers": "8", "peers-kernel": "0", "nccl": "0"}[tp_path]
+    tp_path = "peers" if tp_path == "peers-kernel" else tp_path
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from transformers import Qwen3Config, Qwen3ForCausalLM

@@ -23,10 +23,8 @@ def main():
     from starter_b200 import Engine, _lib
     if os.environ.get("TP_NO_PDL"):
         _lib.check(_lib.lib.q_set_pdl(0))
-    if len(sys.argv) > 5:          # "in_gemm,push": which form the exchange takes at 1-8 rows
-        in_gemm, push = (int(v) for v in sys.argv[5].split(","))
-        _lib.check(_lib.lib.q_set_option(b"peer_in_gemm", in_gemm))
-        _lib.check(_lib.lib.q_set_option(b"peer_push", push))
+    if len(sys.argv) > 5:          # largest world that exchanges inside the projections at 1-8 rows
+        _lib.check(_lib.lib.q_set_option(b"peer_in_gemm", int(sys.argv[5])))
     engine = Engine(model_dir, device=f"cuda:{local}", group=dist.group.WORLD, tp_path=tp_path)
     if os.environ.get("TP_NO_GRAPH"):
         from starter_b200.decode import DecodeState
