@@ -101,6 +101,28 @@ def test_live_random_models(cuda, tmp_path, nq, nkv, hidden, inter, vocab, layer
         assert_parity(native, prompt, tokens, logits)
 
 
+def test_long_prompts_through_the_prompt_pass(cuda, tmp_path):
+    """Prompts longer than one row chunk of the tcgen05 projection (256), longer than the
+    prompt-pass row budget (2048: one sequence per pass then) and several sequences per pass,
+    with 8 query heads per kv head: the own causal attention and the many-row partial plans
+    against native Hugging Face."""
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    from starter_b200 import Engine
+    torch.manual_seed(77)
+    cfg = Qwen3Config(vocab_size=300, hidden_size=256, intermediate_size=384, num_hidden_layers=2,
+                      num_attention_heads=8, num_key_value_heads=1, head_dim=128, max_position_embeddings=4096,
+                      rope_theta=1_000_000.0, tie_word_embeddings=True, sliding_window=None)
+    model = Qwen3ForCausalLM(cfg).eval().to(torch.bfloat16)
+    model.save_pretrained(tmp_path, safe_serialization=True)
+    native = O.native_model(str(tmp_path))
+    engine = Engine(str(tmp_path), keep_logits=True)
+    gen = torch.Generator().manual_seed(6)
+    for batch, length, count in ((1, 2300, 3), (3, 700, 3), (2, 257, 4)):
+        prompt = torch.randint(0, 300, (batch, length), generator=gen).tolist()
+        tokens, logits = stepwise_logits(engine, prompt, count)
+        assert_parity(native, prompt, tokens, logits)
+
+
 def test_generate_contract_and_graph_replay(cuda, golden_dir):
     """N yields of B ids, none for N<=0, state reused across calls, stable
     addresses, graph replay equals eager stepping (reference tests/test_decode.py:94-118,
